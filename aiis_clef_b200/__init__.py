@@ -1,0 +1,7 @@
+"""B200 (sm_100a) implementation of aiis-clef's fused per-layer elementwise hot path.
+
+The product is the C-ABI shared library built from csrc/ (see include/clef_fused.h); this package
+holds its build step and a ctypes binding whose `Device` class mirrors the reference launchers.
+"""
+from .lib import (CLEF_BF16, CLEF_F32, ClefError, Device, load, nvfp4_m_tile_for, nvfp4_sizes,  # noqa: F401
+                  set_kernel_choice, sf_atom_for_tile_m)

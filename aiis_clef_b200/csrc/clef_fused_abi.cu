@@ -1,0 +1,610 @@
+// C-ABI of the fused elementwise kernels: argument checks, kernel selection, grid sizing, launch.
+// Declarations and the reference interface each entry point replaces: include/clef_fused.h.
+//
+// Nothing here allocates, synchronises or copies; every launch is asynchronous on the caller's
+// stream and its grid depends only on the shape arguments, so the calls can be captured in a CUDA
+// graph and replayed while only buffer CONTENTS change (the reference's geometry-keyed replay).
+
+#include "../../include/clef_fused.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "kernels_generic.cuh"
+#include "kernels_hot.cuh"
+
+namespace {
+
+thread_local char g_error[512] = "";
+std::atomic<int> g_kernel_choice{0};
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    int cc_major = 0;
+};
+
+// Per-device facts, looked up once per device (no allocation; attribute queries only).
+int device_info(DeviceInfo& out) {
+    static std::atomic<int> cached_sms[64];
+    static std::atomic<int> cached_cc[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        return fail(CLEF_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    }
+    if (dev < 0 || dev >= 64) {
+        return fail(CLEF_ERR_CUDA, "device ordinal %d out of range", dev);
+    }
+    int sms = cached_sms[dev].load(std::memory_order_relaxed);
+    int cc = cached_cc[dev].load(std::memory_order_relaxed);
+    if (sms == 0) {
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess) {
+            e = cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev);
+        }
+        if (e != cudaSuccess) {
+            return fail(CLEF_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+        }
+        cached_sms[dev].store(sms, std::memory_order_relaxed);
+        cached_cc[dev].store(cc, std::memory_order_relaxed);
+    }
+    if (cc != 10) {
+        return fail(CLEF_ERR_CUDA, "this library holds sm_100a code only; device %d is compute capability %d.x", dev,
+                    cc);
+    }
+    out.sms = sms;
+    out.cc_major = cc;
+    return CLEF_OK;
+}
+
+// Resident CTAs per SM of a kernel (cached per kernel instantiation by the caller's static).
+template <typename K>
+int ctas_per_sm(K kernel, size_t dyn_smem, std::atomic<int>& cache) {
+    int n = cache.load(std::memory_order_relaxed);
+    if (n > 0) {
+        return n;
+    }
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, clef::kCtaThreads, dyn_smem) != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        n = 1;
+    }
+    cache.store(n, std::memory_order_relaxed);
+    return n;
+}
+
+inline unsigned clamp_grid(size_t wanted, size_t cap) {
+    size_t g = wanted < cap ? wanted : cap;
+    return (unsigned)(g < 1 ? 1 : g);
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return fail(CLEF_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    }
+    return CLEF_OK;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int check_dtype(int dtype, const char* what) {
+    if (dtype != CLEF_BF16 && dtype != CLEF_F32) {
+        return fail(CLEF_ERR_INVALID, "%s: dtype %d is neither CLEF_BF16 nor CLEF_F32", what, dtype);
+    }
+    return CLEF_OK;
+}
+
+int check_scale_layout(const char* what, int rows, int cols, int blk_mn, int chunk) {
+    if (rows < 0 || cols <= 0) {
+        return fail(CLEF_ERR_INVALID, "%s: rows %d / cols %d", what, rows, cols);
+    }
+    if (cols % 64 != 0) {
+        return fail(CLEF_ERR_INVALID,
+                    "%s: cols %d is not a multiple of 64 (four 16-value blocks fill one scale group)", what, cols);
+    }
+    if (blk_mn <= 0 || chunk != blk_mn * 4) {
+        return fail(CLEF_ERR_INVALID, "%s: scale atom blk_mn %d / chunk %d (chunk must be blk_mn * 4)", what, blk_mn,
+                    chunk);
+    }
+    return CLEF_OK;
+}
+
+inline bool use_hot() { return g_kernel_choice.load(std::memory_order_relaxed) == 0; }
+
+inline cudaStream_t as_stream(clef_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+template <typename T>
+using Storage = typename T::storage;
+
+}  // namespace
+
+using namespace clef;
+
+extern "C" {
+
+const char* clef_last_error(void) { return g_error; }
+
+int clef_version(void) { return 100; }
+
+void clef_set_kernel_choice(int choice) { g_kernel_choice.store(choice == 1 ? 1 : 0, std::memory_order_relaxed); }
+
+int clef_sf_atom_for_tile_m(int tile_m, int* blk_mn, int* chunk) {
+    if (tile_m <= 0) {
+        return fail(CLEF_ERR_INVALID, "clef_sf_atom_for_tile_m: tile_m %d", tile_m);
+    }
+    int atom = 0;
+    if (tile_m < 128) {
+        atom = 128;
+    } else {
+        const int candidates[4] = {128, 96, 64, 32};
+        for (int c : candidates) {
+            if (tile_m % c == 0) {
+                atom = c;
+                break;
+            }
+        }
+    }
+    if (atom == 0) {
+        return fail(CLEF_ERR_INVALID, "clef_sf_atom_for_tile_m: tile_m %d is not a multiple of 32", tile_m);
+    }
+    if (blk_mn) *blk_mn = atom;
+    if (chunk) *chunk = atom * 4;
+    return CLEF_OK;
+}
+
+int clef_nvfp4_sizes(int rows, int cols, int blk_mn, int* rows_padded, size_t* packed_bytes, size_t* scale_bytes) {
+    if (rows < 0 || cols <= 0 || cols % 16 != 0 || blk_mn <= 0) {
+        return fail(CLEF_ERR_INVALID, "clef_nvfp4_sizes: rows %d cols %d blk_mn %d", rows, cols, blk_mn);
+    }
+    const long long padded = ((long long)rows + blk_mn - 1) / blk_mn * blk_mn;
+    if (padded > 0x7fffffffLL) {
+        return fail(CLEF_ERR_TOO_LARGE, "clef_nvfp4_sizes: %lld padded rows", padded);
+    }
+    if (rows_padded) *rows_padded = (int)padded;
+    if (packed_bytes) *packed_bytes = (size_t)padded * (size_t)(cols / 2);
+    if (scale_bytes) *scale_bytes = (size_t)padded * (size_t)(cols / 16);
+    return CLEF_OK;
+}
+
+int clef_embed_gather(clef_stream_t stream, const void* table, const int32_t* ids, void* out, int tokens, int hidden,
+                      int dtype) {
+    if (int r = check_dtype(dtype, "clef_embed_gather")) return r;
+    if (!table || !ids || !out) return fail(CLEF_ERR_INVALID, "clef_embed_gather: null pointer");
+    if (tokens < 0 || hidden <= 0) return fail(CLEF_ERR_INVALID, "clef_embed_gather: tokens %d hidden %d", tokens, hidden);
+    const size_t row_bytes = (size_t)hidden * (dtype == CLEF_BF16 ? 2 : 4);
+    if (row_bytes % 16 != 0 || !aligned(table, 16) || !aligned(out, 16)) {
+        return fail(CLEF_ERR_INVALID, "clef_embed_gather: rows of %zu bytes / pointers must be 16-byte aligned", row_bytes);
+    }
+    if (tokens == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    const bool hot_ok = use_hot() && aligned(table, 32) && aligned(out, 32);
+    if (hot_ok && (row_bytes == 4096 || row_bytes == 8192 || row_bytes == 2048 || row_bytes == 1024)) {
+        const size_t groups = ((size_t)tokens + 7) / 8;
+#define CLEF_EMBED_HOT(CH)                                                                                       \
+    {                                                                                                            \
+        static std::atomic<int> occ{0};                                                                          \
+        const int per_sm = ctas_per_sm(embed_gather_hot_kernel<CH>, 0, occ);                                     \
+        embed_gather_hot_kernel<CH><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0,              \
+                                      as_stream(stream)>>>((const uint8_t*)table, ids, (uint8_t*)out, tokens);   \
+    }
+        switch (row_bytes / 1024) {
+            case 1: CLEF_EMBED_HOT(1) break;
+            case 2: CLEF_EMBED_HOT(2) break;
+            case 4: CLEF_EMBED_HOT(4) break;
+            default: CLEF_EMBED_HOT(8) break;
+        }
+#undef CLEF_EMBED_HOT
+        return check_launch("clef_embed_gather");
+    }
+    static std::atomic<int> occ{0};
+    const int per_sm = ctas_per_sm(embed_gather_generic_kernel, 0, occ);
+    const size_t vecs = (size_t)tokens * (row_bytes / 16);
+    embed_gather_generic_kernel<<<clamp_grid((vecs + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm),
+                                  kCtaThreads, 0, as_stream(stream)>>>((const uint8_t*)table, ids, (uint8_t*)out,
+                                                                       tokens, row_bytes);
+    return check_launch("clef_embed_gather");
+}
+
+// ---- rms_norm family -----------------------------------------------------------------------------
+
+}  // extern "C"
+
+template <typename T, bool QUANT>
+static int launch_rms_norm_generic(cudaStream_t stream, const DeviceInfo& dev, const void* x, const float* weight,
+                                   void* out, uint8_t* packed, uint8_t* scales, int rows, int rows_total, int cols,
+                                   float eps, float global_scale, int blk_mn, int chunk) {
+    static std::atomic<int> occ{0};
+    auto kernel = rms_norm_generic_kernel<T, QUANT>;
+    const int per_sm = ctas_per_sm(kernel, 0, occ);
+    const int rpb = kCtaThreads / ref_threads_per_row(cols);
+    const size_t groups = ((size_t)rows_total + rpb - 1) / rpb;
+    kernel<<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0, stream>>>(
+        (const Storage<T>*)x, weight, (Storage<T>*)out, packed, scales, rows, rows_total, cols, eps, global_scale,
+        blk_mn, chunk);
+    return CLEF_OK;
+}
+
+extern "C" {
+
+int clef_rms_norm(clef_stream_t stream, const void* x, const float* weight, void* out, int rows, int cols, float eps,
+                  int dtype) {
+    if (int r = check_dtype(dtype, "clef_rms_norm")) return r;
+    if (!x || !out) return fail(CLEF_ERR_INVALID, "clef_rms_norm: null pointer");
+    if (rows < 0 || cols <= 0 || cols % 4 != 0) {
+        return fail(CLEF_ERR_INVALID, "clef_rms_norm: rows %d, cols %d (cols must be a positive multiple of 4)", rows, cols);
+    }
+    if (!aligned(x, 16) || !aligned(out, 16) || (weight && !aligned(weight, 16))) {
+        return fail(CLEF_ERR_INVALID, "clef_rms_norm: pointers must be 16-byte aligned");
+    }
+    if (rows == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16) {
+        launch_rms_norm_generic<Bf16, false>(as_stream(stream), dev, x, weight, out, nullptr, nullptr, rows, rows, cols,
+                                             eps, 0.0f, 1, 4);
+    } else {
+        launch_rms_norm_generic<F32, false>(as_stream(stream), dev, x, weight, out, nullptr, nullptr, rows, rows, cols,
+                                            eps, 0.0f, 1, 4);
+    }
+    return check_launch("clef_rms_norm");
+}
+
+int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const float* weight, uint8_t* packed,
+                                 uint8_t* scales, int rows, int cols, float eps, float global_scale, int blk_mn,
+                                 int chunk, int dtype) {
+    const char* what = "clef_rms_norm_quantise_nvfp4";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!x || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
+    if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(packed, 8)) {
+        return fail(CLEF_ERR_INVALID, "%s: x and weight must be 16-byte aligned, packed 8-byte aligned", what);
+    }
+    int rows_total = 0;
+    if (int r = clef_nvfp4_sizes(rows, cols, blk_mn, &rows_total, nullptr, nullptr)) return r;
+    if (rows_total == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    cudaStream_t s = as_stream(stream);
+    if (dtype == CLEF_BF16 && use_hot() && (cols == 2048 || cols == 4096) && aligned(x, 32)) {
+        const size_t groups = ((size_t)rows_total + 7) / 8;
+        const size_t smem = (size_t)cols * sizeof(float);
+        if (cols == 2048) {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<4>, smem, occ);
+            rms_norm_quant_hot_kernel<4><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem, s>>>(
+                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk);
+        } else {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<8>, smem, occ);
+            rms_norm_quant_hot_kernel<8><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem, s>>>(
+                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk);
+        }
+        return check_launch(what);
+    }
+    if (dtype == CLEF_BF16) {
+        launch_rms_norm_generic<Bf16, true>(s, dev, x, weight, nullptr, packed, scales, rows, rows_total, cols, eps,
+                                            global_scale, blk_mn, chunk);
+    } else {
+        launch_rms_norm_generic<F32, true>(s, dev, x, weight, nullptr, packed, scales, rows, rows_total, cols, eps,
+                                           global_scale, blk_mn, chunk);
+    }
+    return check_launch(what);
+}
+
+// ---- gated rms_norm family -------------------------------------------------------------------------
+
+}  // extern "C"
+
+template <typename T, bool QUANT>
+static void launch_gated_generic(cudaStream_t stream, const DeviceInfo& dev, const void* x, const void* gate,
+                                 const float* weight, void* out, uint8_t* packed, uint8_t* scales, int rows_live,
+                                 int rows_total, int cols, float eps, float global_scale, int blk_mn, int chunk,
+                                 int vh) {
+    static std::atomic<int> occ{0};
+    auto kernel = rms_norm_gated_generic_kernel<T, QUANT>;
+    const int per_sm = ctas_per_sm(kernel, 0, occ);
+    const int rpb = kCtaThreads / ref_threads_per_row(cols);
+    const size_t groups = ((size_t)rows_total + rpb - 1) / rpb;
+    kernel<<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0, stream>>>(
+        (const Storage<T>*)x, (const Storage<T>*)gate, weight, (Storage<T>*)out, packed, scales, rows_live,
+        rows_total, cols, eps, global_scale, blk_mn, chunk, vh);
+}
+
+extern "C" {
+
+int clef_rms_norm_gated(clef_stream_t stream, const void* x, const void* gate, const float* weight, void* out,
+                        int rows, int cols, float eps, int dtype) {
+    const char* what = "clef_rms_norm_gated";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!x || !out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (rows < 0 || cols <= 0 || cols % 4 != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: rows %d, cols %d (cols must be a positive multiple of 4)", what, rows, cols);
+    }
+    if (!aligned(x, 16) || !aligned(out, 16) || (gate && !aligned(gate, 16)) || (weight && !aligned(weight, 16))) {
+        return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
+    }
+    if (rows == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16) {
+        launch_gated_generic<Bf16, false>(as_stream(stream), dev, x, gate, weight, out, nullptr, nullptr, rows, rows,
+                                          cols, eps, 0.0f, 1, 4, 1);
+    } else {
+        launch_gated_generic<F32, false>(as_stream(stream), dev, x, gate, weight, out, nullptr, nullptr, rows, rows,
+                                         cols, eps, 0.0f, 1, 4, 1);
+    }
+    return check_launch(what);
+}
+
+int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, const void* gate, const float* weight,
+                                       uint8_t* packed, uint8_t* scales, int rows, int cols, float eps,
+                                       float global_scale, int blk_mn, int chunk, int vh, int rows_live, int dtype) {
+    const char* what = "clef_rms_norm_gated_quantise_nvfp4";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!x || !gate || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (vh <= 0 || cols <= 0 || cols % 16 != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: vh %d, cols %d (cols must be a multiple of 16)", what, vh, cols);
+    }
+    if ((long long)vh * cols > 0x7fffffffLL) return fail(CLEF_ERR_TOO_LARGE, "%s: vh*cols overflows", what);
+    if (rows < 0 || rows % vh != 0 || rows_live < 0 || rows_live > rows) {
+        return fail(CLEF_ERR_INVALID, "%s: rows %d must be a multiple of vh %d and rows_live %d <= rows", what, rows, vh,
+                    rows_live);
+    }
+    if (int r = check_scale_layout(what, rows / vh, vh * cols, blk_mn, chunk)) return r;
+    if ((rows / vh) % blk_mn != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: rows/vh = %d tokens is not a multiple of blk_mn %d (rows counts padding)", what,
+                    rows / vh, blk_mn);
+    }
+    if (!aligned(x, 16) || !aligned(gate, 16) || !aligned(weight, 16) || !aligned(packed, 8)) {
+        return fail(CLEF_ERR_INVALID, "%s: x, gate and weight must be 16-byte aligned, packed 8-byte aligned", what);
+    }
+    if (rows == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    cudaStream_t s = as_stream(stream);
+    if (dtype == CLEF_BF16 && use_hot() && cols == 128 && aligned(x, 32) && aligned(gate, 32)) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(gated_norm_quant_hot_kernel, 0, occ);
+        const size_t groups = ((size_t)rows + 31) / 32;   // 32 head rows per CTA step
+        gated_norm_quant_hot_kernel<<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
+            (const uint16_t*)x, (const uint16_t*)gate, weight, packed, scales, rows_live, rows, eps, global_scale,
+            blk_mn, chunk, vh);
+        return check_launch(what);
+    }
+    if (dtype == CLEF_BF16) {
+        launch_gated_generic<Bf16, true>(s, dev, x, gate, weight, nullptr, packed, scales, rows_live, rows, cols, eps,
+                                         global_scale, blk_mn, chunk, vh);
+    } else {
+        launch_gated_generic<F32, true>(s, dev, x, gate, weight, nullptr, packed, scales, rows_live, rows, cols, eps,
+                                        global_scale, blk_mn, chunk, vh);
+    }
+    return check_launch(what);
+}
+
+// ---- swiglu / quantise -------------------------------------------------------------------------------
+
+int clef_swiglu(clef_stream_t stream, const void* gate, const void* up, void* out, size_t total, int dtype) {
+    const char* what = "clef_swiglu";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!gate || !up || !out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (!aligned(gate, 16) || !aligned(up, 16) || !aligned(out, 16)) {
+        return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
+    }
+    if (total == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    const size_t quads = (total + 3) / 4;
+    if (dtype == CLEF_BF16) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(swiglu_generic_kernel<Bf16>, 0, occ);
+        swiglu_generic_kernel<Bf16><<<clamp_grid((quads + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm),
+                                      kCtaThreads, 0, as_stream(stream)>>>((const uint16_t*)gate, (const uint16_t*)up,
+                                                                           (uint16_t*)out, total);
+    } else {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(swiglu_generic_kernel<F32>, 0, occ);
+        swiglu_generic_kernel<F32><<<clamp_grid((quads + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm),
+                                     kCtaThreads, 0, as_stream(stream)>>>((const float*)gate, (const float*)up,
+                                                                          (float*)out, total);
+    }
+    return check_launch(what);
+}
+
+}  // extern "C"
+
+template <typename T, bool SWIGLU>
+static void launch_quantise_generic(cudaStream_t stream, const DeviceInfo& dev, const void* a, const void* b,
+                                    uint8_t* packed, uint8_t* scales, int rows, int rows_total, int cols,
+                                    float global_scale, int blk_mn, int chunk) {
+    static std::atomic<int> occ{0};
+    auto kernel = quantise_generic_kernel<T, SWIGLU>;
+    const int per_sm = ctas_per_sm(kernel, 0, occ);
+    const size_t blocks = (size_t)rows_total * (cols / 16);
+    kernel<<<clamp_grid((blocks + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), kCtaThreads, 0, stream>>>(
+        (const Storage<T>*)a, (const Storage<T>*)b, packed, scales, rows, rows_total, cols, global_scale, blk_mn, chunk);
+}
+
+extern "C" {
+
+int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                        float global_scale, int blk_mn, int chunk, int dtype) {
+    const char* what = "clef_quantise_nvfp4";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!x || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
+    if (!aligned(x, 16) || !aligned(packed, 8)) {
+        return fail(CLEF_ERR_INVALID, "%s: x must be 16-byte aligned, packed 8-byte aligned", what);
+    }
+    int rows_total = 0;
+    if (int r = clef_nvfp4_sizes(rows, cols, blk_mn, &rows_total, nullptr, nullptr)) return r;
+    if (rows_total == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16) {
+        launch_quantise_generic<Bf16, false>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
+                                             global_scale, blk_mn, chunk);
+    } else {
+        launch_quantise_generic<F32, false>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
+                                            global_scale, blk_mn, chunk);
+    }
+    return check_launch(what);
+}
+
+int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const void* up, uint8_t* packed,
+                               uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                               int dtype) {
+    const char* what = "clef_swiglu_quantise_nvfp4";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!gate || !up || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
+    if (!aligned(gate, 16) || !aligned(up, 16) || !aligned(packed, 8)) {
+        return fail(CLEF_ERR_INVALID, "%s: gate and up must be 16-byte aligned, packed 8-byte aligned", what);
+    }
+    int rows_total = 0;
+    if (int r = clef_nvfp4_sizes(rows, cols, blk_mn, &rows_total, nullptr, nullptr)) return r;
+    if (rows_total == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    cudaStream_t s = as_stream(stream);
+    const size_t total_blocks = (size_t)rows_total * (cols / 16);
+    if (dtype == CLEF_BF16 && use_hot() && aligned(gate, 32) && aligned(up, 32)) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(swiglu_quant_hot_kernel<2>, 0, occ);
+        const size_t ctas = (total_blocks + 2 * kCtaThreads - 1) / (2 * kCtaThreads);
+        swiglu_quant_hot_kernel<2><<<clamp_grid(ctas, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
+            (const uint16_t*)gate, (const uint16_t*)up, packed, scales, rows, rows_total, cols, global_scale, blk_mn,
+            chunk);
+        return check_launch(what);
+    }
+    if (dtype == CLEF_BF16) {
+        launch_quantise_generic<Bf16, true>(s, dev, gate, up, packed, scales, rows, rows_total, cols, global_scale,
+                                            blk_mn, chunk);
+    } else {
+        launch_quantise_generic<F32, true>(s, dev, gate, up, packed, scales, rows, rows_total, cols, global_scale,
+                                           blk_mn, chunk);
+    }
+    return check_launch(what);
+}
+
+// ---- rope ----------------------------------------------------------------------------------------------
+
+static int check_rope_shape(const char* what, int rows, int heads, int head_dim, int rotary_dim) {
+    if (rows < 0 || heads <= 0 || head_dim <= 0 || rotary_dim < 0) {
+        return fail(CLEF_ERR_INVALID, "%s: rows %d heads %d head_dim %d rotary_dim %d", what, rows, heads, head_dim,
+                    rotary_dim);
+    }
+    if (head_dim % 4 != 0 || rotary_dim % 8 != 0 || rotary_dim > head_dim) {
+        return fail(CLEF_ERR_INVALID,
+                    "%s: head_dim %d must be a multiple of 4 and rotary_dim %d a multiple of 8 not above it", what,
+                    head_dim, rotary_dim);
+    }
+    return CLEF_OK;
+}
+
+int clef_rope(clef_stream_t stream, void* out, const void* x, const float* cos_table, const float* sin_table,
+              int rows, int heads, int head_dim, int rotary_dim, const int32_t* seq_start, const int32_t* pos_base,
+              const int32_t* pos_map, int dtype) {
+    const char* what = "clef_rope";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!out || !x || !cos_table || !sin_table) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (int r = check_rope_shape(what, rows, heads, head_dim, rotary_dim)) return r;
+    if (out == x) return fail(CLEF_ERR_INVALID, "%s: out must not alias x", what);
+    if (!aligned(x, 16) || !aligned(out, 16) || !aligned(cos_table, 16) || !aligned(sin_table, 16)) {
+        return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
+    }
+    if (rows == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    cudaStream_t s = as_stream(stream);
+    if (dtype == CLEF_BF16 && use_hot() && head_dim % 32 == 0 && rotary_dim % 32 == 0 && aligned(x, 32) &&
+        aligned(out, 32)) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(rope_hot_kernel, 0, occ);
+        const size_t items = (size_t)rows * heads * (head_dim / 32);
+        rope_hot_kernel<<<clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), kCtaThreads, 0,
+                          s>>>((uint16_t*)out, (const uint16_t*)x, cos_table, sin_table, rows, heads, head_dim,
+                               rotary_dim, seq_start, pos_base, pos_map);
+        return check_launch(what);
+    }
+    const size_t items = (size_t)rows * heads * ((rotary_dim / 8) + (head_dim - rotary_dim) / 4);
+    if (dtype == CLEF_BF16) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(rope_generic_kernel<Bf16>, 0, occ);
+        rope_generic_kernel<Bf16><<<clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm),
+                                    kCtaThreads, 0, s>>>((uint16_t*)out, (const uint16_t*)x, cos_table, sin_table, rows,
+                                                         heads, head_dim, rotary_dim, seq_start, pos_base, pos_map);
+    } else {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(rope_generic_kernel<F32>, 0, occ);
+        rope_generic_kernel<F32><<<clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm),
+                                   kCtaThreads, 0, s>>>((float*)out, (const float*)x, cos_table, sin_table, rows, heads,
+                                                        head_dim, rotary_dim, seq_start, pos_base, pos_map);
+    }
+    return check_launch(what);
+}
+
+int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, const float* cos_table,
+                      const float* sin_table, void* out, void* gate_out, int rows, int heads, int head_dim,
+                      int rotary_dim, float eps, const int32_t* seq_start, const int32_t* pos_base,
+                      const int32_t* pos_map, int dtype) {
+    const char* what = "clef_qk_norm_rope";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!x || !weight || !cos_table || !sin_table || !out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (int r = check_rope_shape(what, rows, heads, head_dim, rotary_dim)) return r;
+    if (head_dim > 1024) return fail(CLEF_ERR_TOO_LARGE, "%s: head_dim %d above 1024", what, head_dim);
+    if (!aligned(x, 16) || !aligned(out, 16) || !aligned(weight, 16) || (gate_out && !aligned(gate_out, 16))) {
+        return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
+    }
+    if (rows == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    const size_t smem = (size_t)8 * head_dim * sizeof(float);
+    const size_t groups = ((size_t)rows + 7) / 8;
+    if (dtype == CLEF_BF16) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(qk_norm_rope_generic_kernel<Bf16>, smem, occ);
+        qk_norm_rope_generic_kernel<Bf16><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem,
+                                            as_stream(stream)>>>((const uint16_t*)x, weight, cos_table, sin_table,
+                                                                 (uint16_t*)out, (uint16_t*)gate_out, rows, heads,
+                                                                 head_dim, rotary_dim, eps, seq_start, pos_base, pos_map);
+    } else {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(qk_norm_rope_generic_kernel<F32>, smem, occ);
+        qk_norm_rope_generic_kernel<F32><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem,
+                                           as_stream(stream)>>>((const float*)x, weight, cos_table, sin_table,
+                                                                (float*)out, (float*)gate_out, rows, heads, head_dim,
+                                                                rotary_dim, eps, seq_start, pos_base, pos_map);
+    }
+    return check_launch(what);
+}
+
+int clef_rope_tables(clef_stream_t stream, const int32_t* positions, float* cos_out, float* sin_out, int rows,
+                     int rotary_dim, float theta) {
+    const char* what = "clef_rope_tables";
+    if (!positions || !cos_out || !sin_out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (rows < 0 || rotary_dim <= 0 || rotary_dim % 2 != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: rows %d rotary_dim %d", what, rows, rotary_dim);
+    }
+    if (rows == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    static std::atomic<int> occ{0};
+    const int per_sm = ctas_per_sm(rope_tables_kernel, 0, occ);
+    const size_t total = (size_t)rows * rotary_dim;
+    rope_tables_kernel<<<clamp_grid((total + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), kCtaThreads, 0,
+                         as_stream(stream)>>>(positions, cos_out, sin_out, rows, rotary_dim, theta);
+    return check_launch(what);
+}
+
+}  // extern "C"

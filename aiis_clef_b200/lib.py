@@ -1,0 +1,282 @@
+"""ctypes binding of libclef_fused.so (the C-ABI declared in include/clef_fused.h).
+
+`Device` mirrors, name for name, the launchers of the reference's `impl Device`
+(aiis-clef src/cuda/mod.rs:2133-2400, 2718-3074): each `*_dev` method takes device buffers
+(torch CUDA tensors stand in for the reference's `Buffer`), allocates the outputs the reference
+launcher allocates, issues one asynchronous launch on the current torch stream and returns the
+outputs; a shape the entry point declines returns None (the reference's `Ok(None)`).
+
+There is no fallback: if the shared library is missing or a call fails, an exception is raised.
+torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+CLEF_BF16 = 0
+CLEF_F32 = 1
+
+CLEF_OK = 0
+CLEF_DECLINED = 1
+
+_PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = _PKG_DIR / "libclef_fused.so"
+
+# (name, restype, argtypes) of every symbol include/clef_fused.h declares.
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+_SZ = ctypes.c_size_t
+SYMBOLS = {
+    "clef_last_error": (ctypes.c_char_p, []),
+    "clef_version": (_I, []),
+    "clef_sf_atom_for_tile_m": (_I, [_I, ctypes.POINTER(_I), ctypes.POINTER(_I)]),
+    "clef_nvfp4_sizes": (_I, [_I, _I, _I, ctypes.POINTER(_I), ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
+    "clef_embed_gather": (_I, [_P, _P, _P, _P, _I, _I, _I]),
+    "clef_rms_norm": (_I, [_P, _P, _P, _P, _I, _I, _F, _I]),
+    "clef_rms_norm_gated": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I]),
+    "clef_swiglu": (_I, [_P, _P, _P, _P, _SZ, _I]),
+    "clef_rope": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _I]),
+    "clef_qk_norm_rope": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P, _P, _I]),
+    "clef_rope_tables": (_I, [_P, _P, _P, _P, _I, _I, _F]),
+    "clef_quantise_nvfp4": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
+    "clef_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
+    "clef_rms_norm_gated_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I, _I, _I]),
+    "clef_swiglu_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
+    "clef_set_kernel_choice": (None, [_I]),
+}
+
+
+class ClefError(RuntimeError):
+    """A C-ABI call returned a negative status, or the library could not be loaded."""
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libclef_fused.so (built in-tree by aiis_clef_b200.build) and type its symbols."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ClefError(
+            f"{LIB_PATH} is missing: build it with `python -m aiis_clef_b200.build` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(os.fspath(LIB_PATH))
+    for name, (restype, argtypes) in SYMBOLS.items():
+        fn = getattr(lib, name)   # AttributeError if the header and the library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().clef_last_error().decode()
+
+
+def _check(status: int, what: str):
+    if status < 0:
+        raise ClefError(f"{what} failed ({status}): {last_error()}")
+    return status
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return CLEF_BF16
+    if t.dtype == torch.float32:
+        return CLEF_F32
+    raise ClefError(f"activations must be bfloat16 or float32, got {t.dtype}")
+
+
+def _dev_tensor(t: torch.Tensor, what: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ClefError(f"{what} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise ClefError(f"{what} must be contiguous")
+    return t
+
+
+def sf_atom_for_tile_m(tile_m: int) -> tuple[int, int]:
+    """(blk_mn, chunk) for a GEMM M-tile (aiis-clef src/swizzle.rs:16-30)."""
+    blk, chunk = _I(0), _I(0)
+    _check(load().clef_sf_atom_for_tile_m(tile_m, ctypes.byref(blk), ctypes.byref(chunk)), "clef_sf_atom_for_tile_m")
+    return blk.value, chunk.value
+
+
+def nvfp4_sizes(rows: int, cols: int, blk_mn: int) -> tuple[int, int, int]:
+    """(rows_padded, packed_bytes, scale_bytes) (aiis-clef src/cuda/mod.rs:2183-2187)."""
+    rp, pb, sb = _I(0), _SZ(0), _SZ(0)
+    _check(load().clef_nvfp4_sizes(rows, cols, blk_mn, ctypes.byref(rp), ctypes.byref(pb), ctypes.byref(sb)),
+           "clef_nvfp4_sizes")
+    return rp.value, pb.value, sb.value
+
+
+def nvfp4_m_tile_for(m: int) -> int:
+    """GEMM M-tile the reference picks for m rows (src/cuda/mod.rs:1164-1181 without env overrides)."""
+    return 128
+
+
+def set_kernel_choice(choice: int) -> None:
+    """0: tuned kernel when the shape has one (default); 1: always the shape-general kernel."""
+    load().clef_set_kernel_choice(int(choice))
+
+
+class Device:
+    """Mirror of the hot-path launchers of the reference's `Device` (src/cuda/mod.rs).
+
+    Outputs are allocated here with torch (uninitialised: the kernels write every byte, padding
+    included); all launches go to the current torch stream of `device`.
+    """
+
+    def __init__(self, device: int | str | torch.device = 0):
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        self.lib = load()
+        if not torch.cuda.is_available():
+            raise ClefError("no CUDA device: the fused kernels run on a B200 only")
+
+    # -- helpers ------------------------------------------------------------------------------
+    def _empty(self, shape, dtype):
+        return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def _quant_outputs(self, rows: int, cols: int, tile_m: int):
+        blk_mn, chunk = sf_atom_for_tile_m(tile_m)
+        rows_padded, packed_bytes, scale_bytes = nvfp4_sizes(rows, cols, blk_mn)
+        packed = self._empty((rows_padded, cols // 2), torch.uint8)
+        scales = self._empty((scale_bytes,), torch.uint8)
+        return blk_mn, chunk, rows_padded, packed, scales
+
+    # -- src/cuda/mod.rs:2908-2928 ------------------------------------------------------------
+    def embed_gather_dev(self, table, ids, tokens: int, hidden: int):
+        _dev_tensor(table, "table"), _dev_tensor(ids, "ids")
+        out = self._empty((tokens, hidden), table.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_embed_gather(_stream(), _ptr(table), _ptr(ids), _ptr(out), tokens, hidden,
+                                              _dtype_code(table)), "clef_embed_gather")
+        return out
+
+    # -- src/cuda/mod.rs:2718-2739 ------------------------------------------------------------
+    def rms_norm_dev(self, x, weight, rows: int, cols: int, eps: float):
+        _dev_tensor(x, "x")
+        out = self._empty((rows, cols), x.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rms_norm(_stream(), _ptr(x), _ptr(weight), _ptr(out), rows, cols, eps,
+                                          _dtype_code(x)), "clef_rms_norm")
+        return out
+
+    # -- src/cuda/mod.rs:2741-2763 ------------------------------------------------------------
+    def rms_norm_gated_dev(self, x, gate, weight, rows: int, cols: int, eps: float):
+        _dev_tensor(x, "x")
+        out = self._empty((rows, cols), x.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rms_norm_gated(_stream(), _ptr(x), _ptr(gate), _ptr(weight), _ptr(out), rows, cols,
+                                                eps, _dtype_code(x)), "clef_rms_norm_gated")
+        return out
+
+    # -- src/cuda/mod.rs:2765-2782 ------------------------------------------------------------
+    def swiglu_dev(self, gate, up, total: int):
+        _dev_tensor(gate, "gate"), _dev_tensor(up, "up")
+        out = self._empty((total,), gate.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_swiglu(_stream(), _ptr(gate), _ptr(up), _ptr(out), total, _dtype_code(gate)),
+                   "clef_swiglu")
+        return out
+
+    # -- src/cuda/mod.rs:2983-3005 ------------------------------------------------------------
+    def rope_tables_dev(self, positions, rows: int, rotary_dim: int, theta: float):
+        _dev_tensor(positions, "positions")
+        cos = self._empty((rows, rotary_dim), torch.float32)
+        sin = self._empty((rows, rotary_dim), torch.float32)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rope_tables(_stream(), _ptr(positions), _ptr(cos), _ptr(sin), rows, rotary_dim,
+                                             theta), "clef_rope_tables")
+        return cos, sin
+
+    # -- src/cuda/mod.rs:3045-3074 ------------------------------------------------------------
+    def rope_apply_dev(self, x, cos, sin, rows: int, heads: int, head_dim: int, rotary_dim: int,
+                       seq_start=None, pos_base=None, pos_map=None):
+        _dev_tensor(x, "x")
+        out = self._empty((rows, heads, head_dim), x.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rope(_stream(), _ptr(out), _ptr(x), _ptr(cos), _ptr(sin), rows, heads, head_dim,
+                                      rotary_dim, _ptr(seq_start), _ptr(pos_base), _ptr(pos_map), _dtype_code(x)),
+                   "clef_rope")
+        return out
+
+    # -- src/cuda/mod.rs:3008-3043 ------------------------------------------------------------
+    def qk_norm_rope_dev(self, x, weight, cos, sin, rows: int, heads: int, head_dim: int, rotary_dim: int,
+                         eps: float, seq_start=None, pos_base=None, pos_map=None, with_gate: bool = False):
+        _dev_tensor(x, "x")
+        out = self._empty((rows, head_dim), x.dtype)
+        gate = self._empty((rows, head_dim), x.dtype) if with_gate else None
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_qk_norm_rope(_stream(), _ptr(x), _ptr(weight), _ptr(cos), _ptr(sin), _ptr(out),
+                                              _ptr(gate), rows, heads, head_dim, rotary_dim, eps, _ptr(seq_start),
+                                              _ptr(pos_base), _ptr(pos_map), _dtype_code(x)), "clef_qk_norm_rope")
+        return out, gate
+
+    # -- src/cuda/mod.rs:2169-2207 ------------------------------------------------------------
+    def quantise_nvfp4_dev(self, x, rows: int, cols: int, global_scale: float, tile_m: int):
+        _dev_tensor(x, "x")
+        blk_mn, chunk, _, packed, scales = self._quant_outputs(rows, cols, tile_m)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_quantise_nvfp4(_stream(), _ptr(x), _ptr(packed), _ptr(scales), rows, cols,
+                                                global_scale, blk_mn, chunk, _dtype_code(x)), "clef_quantise_nvfp4")
+        return packed, scales
+
+    # -- src/cuda/mod.rs:2133-2167 ------------------------------------------------------------
+    def rms_norm_quantise_nvfp4_dev(self, x, weight, rows: int, cols: int, eps: float, global_scale: float,
+                                    tile_m: int):
+        _dev_tensor(x, "x")
+        if cols % 64 != 0:
+            return None   # declined: the caller runs rms_norm_dev + quantise_nvfp4_dev
+        blk_mn, chunk, _, packed, scales = self._quant_outputs(rows, cols, tile_m)
+        with torch.cuda.device(self.device):
+            st = _check(self.lib.clef_rms_norm_quantise_nvfp4(_stream(), _ptr(x), _ptr(weight), _ptr(packed),
+                                                              _ptr(scales), rows, cols, eps, global_scale, blk_mn,
+                                                              chunk, _dtype_code(x)), "clef_rms_norm_quantise_nvfp4")
+        return None if st == CLEF_DECLINED else (packed, scales)
+
+    # -- src/cuda/mod.rs:2269-2302 ------------------------------------------------------------
+    def rms_norm_gated_quantise_nvfp4_dev(self, x, gate, weight, rows: int, cols: int, vh: int, eps: float,
+                                          global_scale: float, tile_m: int):
+        """`rows` counts live head rows (tokens * vh), as in the reference launcher."""
+        _dev_tensor(x, "x"), _dev_tensor(gate, "gate")
+        flat_cols = vh * cols
+        tokens = rows // vh
+        blk_mn, chunk, tokens_padded, _, scales = self._quant_outputs(tokens, flat_cols, tile_m)
+        rows_padded = tokens_padded * vh
+        packed = self._empty((rows_padded, cols // 2), torch.uint8)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rms_norm_gated_quantise_nvfp4(_stream(), _ptr(x), _ptr(gate), _ptr(weight),
+                                                               _ptr(packed), _ptr(scales), rows_padded, cols, eps,
+                                                               global_scale, blk_mn, chunk, vh, rows,
+                                                               _dtype_code(x)),
+                   "clef_rms_norm_gated_quantise_nvfp4")
+        return packed, scales
+
+    # -- src/cuda/mod.rs:2359-2400 ------------------------------------------------------------
+    def swiglu_quantise_nvfp4_dev(self, gate, up, rows: int, cols: int, global_scale: float, tile_m: int):
+        _dev_tensor(gate, "gate"), _dev_tensor(up, "up")
+        if cols % 64 != 0:
+            return None
+        blk_mn, chunk, _, packed, scales = self._quant_outputs(rows, cols, tile_m)
+        with torch.cuda.device(self.device):
+            st = _check(self.lib.clef_swiglu_quantise_nvfp4(_stream(), _ptr(gate), _ptr(up), _ptr(packed),
+                                                            _ptr(scales), rows, cols, global_scale, blk_mn, chunk,
+                                                            _dtype_code(gate)), "clef_swiglu_quantise_nvfp4")
+        return None if st == CLEF_DECLINED else (packed, scales)

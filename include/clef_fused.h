@@ -1,0 +1,148 @@
+/* clef_fused.h -- C ABI of the B200 (sm_100a) fused per-layer elementwise kernels.
+ *
+ * Drop-in boundary: each entry point replaces one launcher of aiis-clef's CUDA launch layer
+ * (`impl Device` in src/cuda/mod.rs) together with the kernel it launches (kernels/elementwise.cu,
+ * kernels/quantise.cu). The argument order after `stream` is the reference KERNEL's positional
+ * parameter list, so a binding only has to pass what it already passes to `launch_builder().arg(..)`.
+ *
+ * Contract of every launch function:
+ *   - asynchronous on `stream` (a CUstream / cudaStream_t); no allocation, no synchronisation, no
+ *     host<->device copy, so it may be called while the stream is being captured into a CUDA graph;
+ *     grid sizes depend only on the shape arguments, never on buffer contents;
+ *   - the caller owns every buffer; inputs are never written; outputs are fully written, including
+ *     the padding rows of NVFP4 outputs (zero codes, zero scales), so no memset is needed first;
+ *   - optional per-token maps are passed as NULL when absent (the reference passes a raw 0);
+ *   - returns CLEF_OK, CLEF_DECLINED (shape not served by this entry point: the reference's
+ *     `Ok(None)`, caller runs its unfused chain) or a negative error; nothing is launched unless
+ *     the return value is CLEF_OK; clef_last_error() gives a message for the calling thread.
+ *
+ * Activations are bf16 (CLEF_BF16) or f32 (CLEF_F32, the reference engine's residual-stream type);
+ * norm weights and RoPE tables are f32 in both cases, ids and maps are int32.
+ *
+ * NVFP4 output of a [rows x cols] matrix (kernels/quantise.cu:22-52, kernels/nvfp4_quant.h):
+ *   packed: rows_padded * cols/2 bytes, E2M1 codes, low nibble = even column;
+ *   scales: rows_padded * cols/16 bytes, E4M3, at
+ *           ((row / blk_mn) * (cols/64) + block/4) * chunk + (row % blk_mn) * 4 + block % 4;
+ *   rows_padded = rows rounded up to blk_mn; (blk_mn, chunk) come from clef_sf_atom_for_tile_m.
+ *   global_scale is the checkpoint's per-projection input_global_scale, passed by value.
+ */
+#ifndef CLEF_FUSED_H
+#define CLEF_FUSED_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* clef_stream_t; /* CUstream / cudaStream_t; NULL is the legacy default stream */
+
+enum clef_dtype { CLEF_BF16 = 0, CLEF_F32 = 1 };
+
+enum clef_status {
+    CLEF_OK = 0,
+    CLEF_DECLINED = 1,          /* shape outside this entry point: fall back to the unfused chain */
+    CLEF_ERR_INVALID = -1,      /* null pointer, bad size, bad alignment, bad dtype */
+    CLEF_ERR_CUDA = -2,         /* a CUDA runtime call failed (launch error, no sm_100 device...) */
+    CLEF_ERR_TOO_LARGE = -3     /* a size beyond a stated maximum */
+};
+
+/* Message describing the last non-OK status returned on this thread ("" if none). */
+const char* clef_last_error(void);
+
+/* Library version as major*10000 + minor*100 + patch. */
+int clef_version(void);
+
+/* src/swizzle.rs:16-30 (blk_mn_for_tile_m, sf_chunk_stride_for_tile_m): the row atom and the tile
+ * stride of the scale layout for a GEMM M-tile. tile_m < 128 -> (128, 512); 128 -> (128, 512);
+ * 192 -> (96, 384). */
+int clef_sf_atom_for_tile_m(int tile_m, int* blk_mn, int* chunk);
+
+/* Output sizes of an NVFP4 quantisation (src/cuda/mod.rs:2183-2187): rows_padded, packed bytes,
+ * scale bytes. Any out pointer may be NULL. */
+int clef_nvfp4_sizes(int rows, int cols, int blk_mn, int* rows_padded, size_t* packed_bytes, size_t* scale_bytes);
+
+/* embed_gather_kernel (kernels/elementwise.cu:396-407), Device::embed_gather_dev
+ * (src/cuda/mod.rs:2908-2928): out[t, :] = table[ids[t], :]. ids must be valid row numbers. */
+int clef_embed_gather(clef_stream_t stream, const void* table, const int32_t* ids, void* out, int tokens, int hidden,
+                      int dtype);
+
+/* rms_norm_kernel (kernels/elementwise.cu:4-68), Device::rms_norm_dev (src/cuda/mod.rs:2718-2739):
+ * out = x * rsqrt(mean(x^2) + eps) * (1 + weight); weight may be NULL (no scaling). cols % 4 == 0. */
+int clef_rms_norm(clef_stream_t stream, const void* x, const float* weight, void* out, int rows, int cols, float eps,
+                  int dtype);
+
+/* rms_norm_gated_kernel (kernels/elementwise.cu:144-223), Device::rms_norm_gated_dev
+ * (src/cuda/mod.rs:2741-2763): out = x * rsqrt(mean(x^2) + eps) * weight * silu(gate); plain weight
+ * (no +1); weight and gate may each be NULL (weight skipped; gate = 0). cols % 4 == 0. */
+int clef_rms_norm_gated(clef_stream_t stream, const void* x, const void* gate, const float* weight, void* out,
+                        int rows, int cols, float eps, int dtype);
+
+/* swiglu_kernel (kernels/elementwise.cu:225-241), Device::swiglu_dev (src/cuda/mod.rs:2765-2782):
+ * out[i] = silu(gate[i]) * up[i], i < total. */
+int clef_swiglu(clef_stream_t stream, const void* gate, const void* up, void* out, size_t total, int dtype);
+
+/* rope_kernel (kernels/elementwise.cu:276-315), Device::rope_apply_dev (src/cuda/mod.rs:3045-3074):
+ * x, out [rows, heads, head_dim]; the first rotary_dim dims of each head are rotated in pairs
+ * (j, j + rotary_dim/2) by cos/sin[pos * rotary_dim + j]; the rest are copied.
+ * pos = pos_map ? pos_map[row] : (seq_start ? row - seq_start[row] : row) + (pos_base ? *pos_base : 0).
+ * The engine passes its per-token `rope_pos` / `cpos` map as pos_map. out must not alias x. */
+int clef_rope(clef_stream_t stream, void* out, const void* x, const float* cos_table, const float* sin_table,
+              int rows, int heads, int head_dim, int rotary_dim, const int32_t* seq_start, const int32_t* pos_base,
+              const int32_t* pos_map, int dtype);
+
+/* qk_norm_rope_kernel (kernels/elementwise.cu:70-142), Device::qk_norm_rope_dev
+ * (src/cuda/mod.rs:3008-3043): per-head RMSNorm with (1 + weight), then RoPE as above.
+ * rows counts head rows (tokens * heads). With gate_out != NULL the input rows are [q | gate]
+ * (2 * head_dim wide) and the gate half is copied to gate_out. The reference serves head_dim 256
+ * only; this entry point serves any head_dim % 4 == 0 with the arithmetic of the unfused chain
+ * (rms_norm_kernel per head row, then rope_kernel). */
+int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, const float* cos_table,
+                      const float* sin_table, void* out, void* gate_out, int rows, int heads, int head_dim,
+                      int rotary_dim, float eps, const int32_t* seq_start, const int32_t* pos_base,
+                      const int32_t* pos_map, int dtype);
+
+/* rope_tables_kernel (kernels/elementwise.cu:446-462), Device::rope_tables_dev
+ * (src/cuda/mod.rs:2983-3005): cos/sin [rows, rotary_dim] f32 of positions[row] / theta^(2i/rotary_dim). */
+int clef_rope_tables(clef_stream_t stream, const int32_t* positions, float* cos_out, float* sin_out, int rows,
+                     int rotary_dim, float theta);
+
+/* quantise_nvfp4_kernel (kernels/quantise.cu:6-53), Device::quantise_nvfp4_dev
+ * (src/cuda/mod.rs:2169-2207). cols % 64 == 0. */
+int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                        float global_scale, int blk_mn, int chunk, int dtype);
+
+/* rms_norm_quantise_nvfp4_kernel (kernels/quantise.cu:193-271), Device::rms_norm_quantise_nvfp4_dev
+ * (src/cuda/mod.rs:2133-2167): clef_rms_norm followed by clef_quantise_nvfp4 without the f32 round
+ * trip, byte-identical to that chain. The reference declines cols != 4096; this serves cols % 64 == 0. */
+int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const float* weight, uint8_t* packed,
+                                 uint8_t* scales, int rows, int cols, float eps, float global_scale, int blk_mn,
+                                 int chunk, int dtype);
+
+/* rms_norm_gated_quantise_nvfp4_kernel (kernels/quantise.cu:57-121),
+ * Device::rms_norm_gated_quantise_nvfp4_dev (src/cuda/mod.rs:2269-2302). As in the reference kernel,
+ * `rows` counts head rows INCLUDING padding (tokens_padded * vh, tokens_padded a multiple of
+ * blk_mn), `rows_live` the head rows that hold data; `cols` is the head width; a token's vh head
+ * rows form one quantised row of width vh * cols. packed: rows * cols/2 bytes; scales:
+ * (rows / vh) * (vh * cols / 16) bytes. (vh * cols) % 64 == 0, cols % 16 == 0. */
+int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, const void* gate, const float* weight,
+                                       uint8_t* packed, uint8_t* scales, int rows, int cols, float eps,
+                                       float global_scale, int blk_mn, int chunk, int vh, int rows_live, int dtype);
+
+/* swiglu_quantise_nvfp4_kernel (kernels/quantise.cu:523-591), Device::swiglu_quantise_nvfp4_dev
+ * (src/cuda/mod.rs:2359-2400): clef_swiglu followed by clef_quantise_nvfp4, byte-identical to that
+ * chain. gate and up are two dense [rows, cols] matrices. cols % 64 == 0. */
+int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const void* up, uint8_t* packed,
+                               uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                               int dtype);
+
+/* Kernel selection for tests and measurements: 0 = automatic (tuned kernel when the shape has one),
+ * 1 = always the shape-general kernel. Process-wide; not part of the reference interface. */
+void clef_set_kernel_choice(int choice);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CLEF_FUSED_H */

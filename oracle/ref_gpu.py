@@ -1,0 +1,267 @@
+"""Launch the REFERENCE's own CUDA kernels (oracle/_ref/*.cubin) on torch tensors.
+
+TEST INFRASTRUCTURE. The cubins are compiled by oracle/Makefile from the reference's unmodified
+kernels/elementwise.cu and kernels/quantise.cu for sm_100a; this module only loads them with the
+CUDA driver API (cuda-python) and launches them with the grid/block shapes the reference's
+launch layer uses (aiis-clef src/cuda/mod.rs, cited per function). The reference kernels take
+f32 activations; bf16 test inputs are widened exactly before the call.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_DIR = Path(__file__).resolve().parent / "_ref"
+_modules: dict[str, object] = {}
+_functions: dict[tuple[str, str], object] = {}
+
+
+def available() -> bool:
+    return all((_DIR / f"{n}.cubin").exists() for n in ("elementwise", "quantise", "ref_probe"))
+
+
+def _cu():
+    from cuda.bindings import driver as cu
+
+    return cu
+
+
+def _check(res):
+    err = res[0]
+    if int(err) != 0:
+        raise RuntimeError(f"CUDA driver error {err}")
+    return res[1] if len(res) == 2 else res[1:]
+
+
+def function(module: str, name: str):
+    key = (module, name)
+    if key not in _functions:
+        cu = _cu()
+        torch.cuda.init()
+        torch.zeros(1, device="cuda")   # makes torch's primary context current on this thread
+        if module not in _modules:
+            data = (_DIR / f"{module}.cubin").read_bytes()
+            _modules[module] = _check(cu.cuModuleLoadData(data))
+        _functions[key] = _check(cu.cuModuleGetFunction(_modules[module], name.encode()))
+    return _functions[key]
+
+
+def launch(module: str, name: str, grid, block, args, smem: int = 0):
+    cu = _cu()
+    vals, types = [], []
+    for a in args:
+        if a is None:
+            vals.append(0)
+            types.append(ctypes.c_void_p)
+        elif isinstance(a, torch.Tensor):
+            vals.append(a.data_ptr())
+            types.append(ctypes.c_void_p)
+        elif isinstance(a, tuple):
+            vals.append(a[0])
+            types.append(a[1])
+        elif isinstance(a, bool):
+            raise TypeError("pass ints, not bools")
+        elif isinstance(a, int):
+            vals.append(a)
+            types.append(ctypes.c_int)
+        elif isinstance(a, float):
+            vals.append(a)
+            types.append(ctypes.c_float)
+        else:
+            raise TypeError(type(a))
+    gx, gy, gz = (list(grid) + [1, 1])[:3]
+    bx, by, bz = (list(block) + [1, 1])[:3]
+    stream = torch.cuda.current_stream().cuda_stream
+    res = cu.cuLaunchKernel(function(module, name), gx, gy, gz, bx, by, bz, smem, stream,
+                            (tuple(vals), tuple(types)), 0)
+    if int(res[0]) != 0:
+        raise RuntimeError(f"cuLaunchKernel({name}) -> {res[0]}")
+
+
+def _row_blocks(rows: int, cols: int) -> int:
+    # src/cuda/mod.rs:5435-5439
+    tpr = min(256, max(32, -(-cols // 256) * 32))
+    rpb = 256 // tpr
+    return -(-rows // rpb)
+
+
+def _round_up(v, n):
+    return -(-v // n) * n
+
+
+# ---- elementwise.cu ------------------------------------------------------------------------------
+def rms_norm(x, weight, rows, cols, eps):
+    """src/cuda/mod.rs:2718-2739."""
+    out = torch.empty(rows * cols, dtype=torch.float32, device=x.device)
+    launch("elementwise", "rms_norm_kernel", (_row_blocks(rows, cols),), (256,), [x, weight, out, rows, cols, float(eps)])
+    return out.view(rows, cols)
+
+
+def rms_norm_gated(x, gate, weight, rows, cols, eps):
+    """src/cuda/mod.rs:2741-2763."""
+    out = torch.empty(rows * cols, dtype=torch.float32, device=x.device)
+    launch("elementwise", "rms_norm_gated_kernel", (_row_blocks(rows, cols),), (256,),
+           [x, gate, weight, out, rows, cols, float(eps)])
+    return out.view(rows, cols)
+
+
+def swiglu(gate, up, total):
+    """src/cuda/mod.rs:2765-2782."""
+    out = torch.empty(total, dtype=torch.float32, device=gate.device)
+    launch("elementwise", "swiglu_kernel", ((total + 1023) // 1024,), (256,), [gate, up, out, total])
+    return out
+
+
+def embed_gather(table, ids, tokens, hidden):
+    """src/cuda/mod.rs:2908-2928."""
+    out = torch.empty(tokens * hidden, dtype=torch.float32, device=table.device)
+    launch("elementwise", "embed_gather_kernel", ((tokens * hidden + 255) // 256,), (256,),
+           [table, ids, out, tokens, hidden])
+    return out.view(tokens, hidden)
+
+
+def rope_tables(positions, rows, rotary_dim, theta):
+    """src/cuda/mod.rs:2983-3005."""
+    cos = torch.empty(rows * rotary_dim, dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    launch("elementwise", "rope_tables_kernel", ((rows * rotary_dim + 255) // 256,), (256,),
+           [positions, cos, sin, rows, rotary_dim, float(theta)])
+    return cos.view(rows, rotary_dim), sin.view(rows, rotary_dim)
+
+
+def rope(x, cos, sin, rows, heads, head_dim, rotary_dim, seq_start=None, pos_base=None, pos_map=None):
+    """src/cuda/mod.rs:3045-3074."""
+    out = torch.empty(rows * heads * head_dim, dtype=torch.float32, device=x.device)
+    total = rows * heads * (head_dim // 2)
+    launch("elementwise", "rope_kernel", ((total + 255) // 256,), (256,),
+           [out, x, cos, sin, rows, heads, head_dim, rotary_dim, seq_start, pos_base, pos_map])
+    return out.view(rows, heads, head_dim)
+
+
+def qk_norm_rope(x, weight, cos, sin, rows, heads, head_dim, rotary_dim, eps, seq_start=None, pos_base=None,
+                 pos_map=None, with_gate=False):
+    """src/cuda/mod.rs:3008-3043 (head_dim 256 only)."""
+    assert head_dim == 256
+    out = torch.empty(rows * head_dim, dtype=torch.float32, device=x.device)
+    gate = torch.empty(rows * head_dim, dtype=torch.float32, device=x.device) if with_gate else None
+    launch("elementwise", "qk_norm_rope_kernel", ((rows + 7) // 8,), (256,),
+           [x, weight, cos, sin, out, gate, rows, heads, head_dim, rotary_dim, float(eps), seq_start, pos_base,
+            pos_map])
+    return out.view(rows, head_dim), (gate.view(rows, head_dim) if with_gate else None)
+
+
+# ---- quantise.cu -----------------------------------------------------------------------------------
+def _zeroed_outputs(rows_padded, cols, device, slack_rows=0):
+    # The reference allocates both outputs zeroed (src/cuda/mod.rs:2186-2187). `slack_rows` covers
+    # the rows its folded (grid.y, grid.z) launch touches beyond rows_padded above 65535 rows.
+    packed = torch.zeros((rows_padded + slack_rows) * (cols // 2), dtype=torch.uint8, device=device)
+    scales = torch.zeros((rows_padded + slack_rows) * (cols // 16), dtype=torch.uint8, device=device)
+    return packed, scales
+
+
+def quantise_nvfp4(x, rows, cols, global_scale, blk_mn=128, chunk=512):
+    """src/cuda/mod.rs:2169-2207."""
+    rows_padded = _round_up(rows, blk_mn)
+    gy, gz = min(rows_padded, 65535), -(-rows_padded // 65535)
+    slack = _round_up(gy * gz, blk_mn) - rows_padded
+    packed, scales = _zeroed_outputs(rows_padded, cols, x.device, slack)
+    blocks = cols // 16
+    launch("quantise", "quantise_nvfp4_kernel", ((blocks + 63) // 64, gy, gz), (64,),
+           [x, packed, scales, rows, cols, float(global_scale), blk_mn, chunk])
+    return packed[: rows_padded * (cols // 2)], scales[: rows_padded * (cols // 16)]
+
+
+def rms_norm_quantise_nvfp4(x, weight, rows, cols, eps, global_scale, blk_mn=128, chunk=512):
+    """src/cuda/mod.rs:2133-2167 (cols 4096 only)."""
+    assert cols == 4096
+    rows_padded = _round_up(rows, blk_mn)
+    packed, scales = _zeroed_outputs(rows_padded, cols, x.device)
+    launch("quantise", "rms_norm_quantise_nvfp4_kernel", (rows_padded,), (256,),
+           [x, weight, packed, scales, rows, cols, float(eps), float(global_scale), blk_mn, chunk])
+    return packed, scales
+
+
+def rms_norm_gated_quantise_nvfp4(x, gate, weight, rows, cols, vh, eps, global_scale, blk_mn=128, chunk=512):
+    """src/cuda/mod.rs:2269-2302 (cols 128 only); `rows` = live head rows."""
+    assert cols == 128
+    tokens = rows // vh
+    tokens_padded = _round_up(tokens, blk_mn)
+    rows_padded = tokens_padded * vh
+    packed = torch.zeros(rows_padded * (cols // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.zeros(tokens_padded * (vh * cols // 16), dtype=torch.uint8, device=x.device)
+    launch("quantise", "rms_norm_gated_quantise_nvfp4_kernel", ((rows_padded + 7) // 8,), (256,),
+           [x, gate, weight, packed, scales, rows_padded, cols, float(eps), float(global_scale), blk_mn, chunk, vh,
+            rows])
+    return packed, scales
+
+
+def swiglu_quantise_nvfp4(gate, up, rows, cols, global_scale, blk_mn=128, chunk=512):
+    """src/cuda/mod.rs:2359-2400."""
+    assert cols <= 768 * 16
+    rows_padded = _round_up(rows, blk_mn)
+    gy, gz = min(rows_padded, 65535), -(-rows_padded // 65535)
+    slack = _round_up(gy * gz, blk_mn) - rows_padded
+    packed, scales = _zeroed_outputs(rows_padded, cols, gate.device, slack)
+    per_row = cols // 16
+    threads = max(32, min(768, per_row))
+    launch("quantise", "swiglu_quantise_nvfp4_kernel", (-(-per_row // threads), gy, gz), (threads,),
+           [gate, up, packed, scales, rows, cols, float(global_scale), blk_mn, chunk])
+    return packed[: rows_padded * (cols // 2)], scales[: rows_padded * (cols // 16)]
+
+
+# ---- ref_probe.cubin -----------------------------------------------------------------------------------
+def _result_buffer(n):
+    # struct ProbeResult { u64 checked; u64 mismatches; u32 first_bad[16]; } = 80 bytes
+    return torch.zeros(n * 80, dtype=torch.uint8, device="cuda")
+
+
+def _read_results(buf, n):
+    import numpy as np
+
+    raw = buf.cpu().numpy()
+    out = []
+    for i in range(n):
+        rec = raw[i * 80:(i + 1) * 80]
+        checked, mism = np.frombuffer(rec[:16].tobytes(), np.uint64)
+        bad = np.frombuffer(rec[16:].tobytes(), np.uint32)[: min(int(mism), 16)]
+        out.append({"checked": int(checked), "mismatches": int(mism), "first_bad": [int(b) for b in bad]})
+    return out
+
+
+def probe_e2m1(base: int, count: int):
+    buf = _result_buffer(3)
+    launch("ref_probe", "probe_e2m1", (148 * 8,), (256,),
+           [(base, ctypes.c_ulonglong), (count, ctypes.c_ulonglong), buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 3)
+
+
+def probe_e4m3(base: int, count: int):
+    buf = _result_buffer(1)
+    launch("ref_probe", "probe_e4m3", (148 * 8,), (256,),
+           [(base, ctypes.c_ulonglong), (count, ctypes.c_ulonglong), buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 1)
+
+
+def probe_e4m3_decode(global_scale: float):
+    buf = _result_buffer(2)
+    launch("ref_probe", "probe_e4m3_decode", (1,), (256,), [float(global_scale), buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 2)
+
+
+def probe_blocks(values, global_scale: float):
+    """values: CUDA f32 tensor of n_blocks*16. Returns (results, want_scale, want_packed, got_scale, got_packed)."""
+    n = values.numel() // 16
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    wp = torch.empty(n * 8, dtype=torch.uint8, device="cuda")
+    gs = torch.empty_like(ws)
+    gp = torch.empty_like(wp)
+    buf = _result_buffer(2)
+    launch("ref_probe", "probe_blocks", (min(148 * 8, (n + 255) // 256),), (256,),
+           [values, (n, ctypes.c_ulonglong), float(global_scale), ws, wp, gs, gp, buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 2), ws, wp, gs, gp

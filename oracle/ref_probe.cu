@@ -1,0 +1,158 @@
+// ref_probe.cu -- TEST INFRASTRUCTURE, not product code.
+//
+// Device-side comparison of this repo's NVFP4 codec (aiis_clef_b200/csrc/nvfp4_codec.cuh) with the
+// reference's own encoder header, which is included from the reference tree where it lies
+// (-I<reference>/kernels, see Makefile): to_e2m1, to_e4m3, from_e4m3 of kernels/nvfp4_quant.h.
+// Built only into oracle/_ref/ref_probe.cubin and launched only by the GPU tests.
+//
+// Every kernel walks f32 bit patterns, evaluates both sides and counts disagreements; up to 16
+// disagreeing patterns are kept for the test's failure message.
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "nvfp4_quant.h"    // the reference's header (to_e2m1 / to_e4m3 / from_e4m3)
+#include "nvfp4_codec.cuh"  // this repo's codec (namespace clef)
+
+struct ProbeResult {
+    unsigned long long checked;
+    unsigned long long mismatches;
+    uint32_t first_bad[16];
+};
+
+__device__ void report(ProbeResult* r, uint32_t pattern) {
+    const unsigned long long slot = atomicAdd(&r->mismatches, 1ull);
+    if (slot < 16) {
+        r->first_bad[slot] = pattern;
+    }
+}
+
+__device__ __forceinline__ uint32_t mix(uint32_t x) {
+    x ^= x >> 16;
+    x *= 0x7feb352du;
+    x ^= x >> 15;
+    x *= 0x846ca68bu;
+    x ^= x >> 16;
+    return x;
+}
+
+// All 2^32 patterns starting at `base` for `count` patterns (count may be 2^32 = 0 wrapped: pass as u64).
+// result[0]: fast pair converter, low nibble, on its domain (|p| < 2^24)
+// result[1]: fast pair converter, high nibble, same domain
+// result[2]: literal single-value encoder e2m1_exact on every pattern
+extern "C" __global__ void probe_e2m1(unsigned long long base, unsigned long long count, ProbeResult* result) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    unsigned long long checked_fast = 0, checked_all = 0;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const uint32_t bits = (uint32_t)(base + i);
+        const float p = __uint_as_float(bits);
+        const uint32_t want = to_e2m1(p);
+        ++checked_all;
+        if (clef::e2m1_exact(p) != want) {
+            report(&result[2], bits);
+        }
+        const float a = fabsf(p);
+        if (a < clef::kE2m1FastLimit) {   // false for NaN
+            ++checked_fast;
+            // A partner value that is always inside the fast path's domain (|q| < 2).
+            const uint32_t qbits = mix(bits) & 0xBFFFFFFFu;
+            const float q = __uint_as_float(qbits);
+            const uint32_t want_q = to_e2m1(q);
+            const uint32_t lo_first = clef::e2m1x2_fast(p, q);
+            const uint32_t hi_first = clef::e2m1x2_fast(q, p);
+            if (lo_first != (want | (want_q << 4))) {
+                report(&result[0], bits);
+            }
+            if (hi_first != (want_q | (want << 4))) {
+                report(&result[1], bits);
+            }
+        }
+    }
+    atomicAdd(&result[0].checked, checked_fast);
+    atomicAdd(&result[1].checked, checked_fast);
+    atomicAdd(&result[2].checked, checked_all);
+}
+
+// result[0]: scale encoder on every pattern. +inf goes through the literal branch of the rare path
+// (clef::quantise16_rare handles it the same way), everything else through e4m3_encode_finite.
+extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long long count, ProbeResult* result) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    unsigned long long checked = 0;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const uint32_t bits = (uint32_t)(base + i);
+        const float v = __uint_as_float(bits);
+        const uint32_t want = to_e4m3(v);
+        const uint32_t got = (bits == 0x7F800000u) ? ((6u << 3) | 7u) : clef::e4m3_encode_finite(v);
+        ++checked;
+        if (got != want) {
+            report(&result[0], bits);
+        }
+    }
+    atomicAdd(&result[0].checked, checked);
+}
+
+// result[0]: decoder on all 256 bytes (bit-exact f32); result[1]: inv_scale for `global_scale`.
+extern "C" __global__ void probe_e4m3_decode(float global_scale, ProbeResult* result) {
+    const uint32_t b = threadIdx.x;
+    if (b < 256) {
+        const float want = from_e4m3((uint8_t)b);
+        const float got = clef::e4m3_decode(b);
+        atomicAdd(&result[0].checked, 1ull);
+        if (__float_as_uint(want) != __float_as_uint(got)) {
+            report(&result[0], b);
+        }
+        const float want_inv = (want > 0.0f) ? global_scale / want : 0.0f;
+        atomicAdd(&result[1].checked, 1ull);
+        if (__float_as_uint(want_inv) != __float_as_uint(clef::inv_scale_of(b, global_scale))) {
+            report(&result[1], b);
+        }
+    }
+}
+
+// Whole 16-value blocks: the reference recipe of kernels/quantise.cu:22-52 spelled with the
+// reference's encoder functions, against clef::quantise16. `values` holds n_blocks * 16 floats.
+// result[0]: scale byte, result[1]: packed codes (counted per block). first_bad holds block indices.
+extern "C" __global__ void probe_blocks(const float* values, unsigned long long n_blocks, float global_scale,
+                                        uint8_t* want_scale, uint8_t* want_packed, uint8_t* got_scale,
+                                        uint8_t* got_packed, ProbeResult* result) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += stride) {
+        const float* src = values + b * 16;
+        float amax = 0.0f;
+        for (int i = 0; i < 16; ++i) {
+            amax = fmaxf(amax, fabsf(src[i]));
+        }
+        const float block_scale = amax / 6.0f;
+        const uint8_t stored = to_e4m3(block_scale * global_scale);
+        const float stored_f = from_e4m3(stored);
+        const float inv_scale = (stored_f > 0.0f) ? global_scale / stored_f : 0.0f;
+        uint8_t want[8];
+        for (int pair = 0; pair < 8; ++pair) {
+            const uint8_t lo = to_e2m1(src[pair * 2] * inv_scale);
+            const uint8_t hi = to_e2m1(src[pair * 2 + 1] * inv_scale);
+            want[pair] = (uint8_t)(lo | (hi << 4));
+        }
+        float v[16];
+        for (int i = 0; i < 16; ++i) {
+            v[i] = src[i];
+        }
+        uint32_t got_stored, lo, hi;
+        clef::quantise16(v, global_scale, nullptr, got_stored, lo, hi);
+        const unsigned long long got_bits = (unsigned long long)lo | ((unsigned long long)hi << 32);
+        unsigned long long want_bits = 0;
+        for (int pair = 0; pair < 8; ++pair) {
+            want_bits |= (unsigned long long)want[pair] << (8 * pair);
+            want_packed[b * 8 + pair] = want[pair];
+            got_packed[b * 8 + pair] = (uint8_t)(got_bits >> (8 * pair));
+        }
+        want_scale[b] = stored;
+        got_scale[b] = (uint8_t)got_stored;
+        atomicAdd(&result[0].checked, 1ull);
+        atomicAdd(&result[1].checked, 1ull);
+        if (got_stored != stored) {
+            report(&result[0], (uint32_t)b);
+        }
+        if (got_bits != want_bits) {
+            report(&result[1], (uint32_t)b);
+        }
+    }
+}

@@ -1,0 +1,91 @@
+"""Device-side comparison of the NVFP4 codec with the reference's encoder header
+(kernels/nvfp4_quant.h compiled into oracle/_ref/ref_probe.cubin): every f32 bit pattern."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import binding as orc
+from oracle import ref_gpu
+from gpu_util import unswizzle
+
+pytestmark = pytest.mark.gpu
+
+
+def _fmt(res):
+    return ", ".join(f"{r['mismatches']}/{r['checked']} bad (first {[hex(b) for b in r['first_bad'][:6]]})" for r in res)
+
+
+def test_e2m1_all_patterns():
+    """Hardware-converter path on its domain (both nibbles) and the literal encoder everywhere."""
+    res = ref_gpu.probe_e2m1(0, 1 << 32)
+    assert res[2]["checked"] == 1 << 32
+    assert res[0]["checked"] == res[1]["checked"] and res[0]["checked"] > (1 << 31)
+    assert all(r["mismatches"] == 0 for r in res), _fmt(res)
+
+
+def test_e4m3_encoder_all_patterns():
+    res = ref_gpu.probe_e4m3(0, 1 << 32)
+    assert res[0]["checked"] == 1 << 32
+    assert res[0]["mismatches"] == 0, _fmt(res)
+
+
+@pytest.mark.parametrize("global_scale", [1.0, 64.0, 215.0, 1.0 / 12.5, 2688.0, 1e-3])
+def test_e4m3_decoder_and_inverse_scale(global_scale):
+    res = ref_gpu.probe_e4m3_decode(global_scale)
+    assert res[0]["checked"] == 256 and res[1]["checked"] == 256
+    assert all(r["mismatches"] == 0 for r in res), _fmt(res)
+
+
+def _adversarial_blocks(rng):
+    """Blocks that hit exact ties, sign corner cases, denormals, huge and non-finite values."""
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], np.float32)
+    blocks = []
+    for amax in [6.0, 3.0, 1.0, 448.0, 0.001, 12.0]:
+        base = np.zeros(16, np.float32)
+        base[0] = amax                                    # scale maps amax to 6
+        vals = ties * np.float32(amax / 6.0)
+        for shift in (0, 1, -1):
+            b = base.copy()
+            v = vals.view(np.uint32).astype(np.int64) + shift
+            b[1:8] = v.astype(np.uint32).view(np.float32)
+            b[8:15] = -b[1:8]
+            b[15] = -0.0
+            blocks.append(b)
+    blocks.append(np.zeros(16, np.float32))
+    blocks.append(np.full(16, -0.0, np.float32))
+    blocks.append(np.full(16, 1e-45, np.float32))                      # denormals only
+    blocks.append(np.array([1e-40, -1e-40, 3e-39, 1.0] + [0] * 12, np.float32))
+    blocks.append(np.array([np.nan, 1.0, -2.0, 3.0] + [0.5] * 12, np.float32))
+    blocks.append(np.array([np.inf, 1.0, -2.0, 3.0] + [0.5] * 12, np.float32))
+    blocks.append(np.array([-np.inf, np.nan, -2.0, 3.0] + [0.5] * 12, np.float32))
+    blocks.append(np.array([3e38, -3e38, 1e30, 1e20] + [1.0] * 12, np.float32))
+    blocks.append(np.array([1e12, -5e11, 1e9, 7e7] + [1.0] * 12, np.float32))
+    blocks.append(np.full(16, np.nan, np.float32))
+    rnd = rng.standard_normal((4096, 16)).astype(np.float32) * np.float32(10.0) ** rng.integers(-6, 6, (4096, 1)).astype(np.float32)
+    out = np.concatenate([np.stack(blocks), rnd])
+    return out[: out.shape[0] // 4 * 4]
+
+
+@pytest.mark.parametrize("global_scale", [1.0, 64.0, 215.0, 1.0 / 12.5, 2688.0, 1e-6, 1e6, 0.0, -3.0, 3e38])
+def test_block_quantiser_on_adversarial_blocks(global_scale):
+    rng = np.random.default_rng(11)
+    blocks = _adversarial_blocks(rng)
+    vals = torch.from_numpy(blocks).cuda()
+    res, ws, wp, gs, gp = ref_gpu.probe_blocks(vals, global_scale)
+    assert res[0]["checked"] == blocks.shape[0]
+    assert all(r["mismatches"] == 0 for r in res), f"global {global_scale}: " + _fmt(res)
+    # the CPU oracle agrees with the reference header on the same blocks, non-finite ones included
+    rows = blocks.shape[0] // 4
+    want_p, want_s = orc.quantise_nvfp4(blocks.reshape(rows, 64), rows, 64, global_scale)
+    rows_padded = (rows + 127) // 128 * 128
+    cpu_scales = unswizzle(want_s, rows_padded, 4)[:rows].reshape(-1)
+    assert np.array_equal(ws.cpu().numpy(), cpu_scales), "CPU oracle scale bytes differ from the reference header's"
+    assert np.array_equal(wp.cpu().numpy(), want_p[: rows * 32]), "CPU oracle codes differ from the reference header's"
+
+
+def test_block_quantiser_on_random_blocks_large():
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((1 << 20, 16)).astype(np.float32)
+    x[:, 3] *= 20.0
+    res, *_ = ref_gpu.probe_blocks(torch.from_numpy(x).cuda(), 448.0 * 6.0 / 100.0)
+    assert all(r["mismatches"] == 0 for r in res), _fmt(res)
