@@ -143,19 +143,29 @@ __device__ __forceinline__ float pair_sq(float a, float b) {
 }
 __device__ __forceinline__ float quad_sq(float4 v) { return __fadd_rn(pair_sq(v.x, v.y), pair_sq(v.z, v.w)); }
 
-// RoPE pair, lo*c - hi*s and hi*c + lo*s (kernels/elementwise.cu:308-309), same idea.
-#ifndef CLEF_ROPE_FMA
-#define CLEF_ROPE_FMA 1
+// RoPE pair, lo*c - hi*s and hi*c + lo*s (kernels/elementwise.cu:308-309), same idea; the two
+// expressions are contracted independently by the reference build:
+//   CLEF_ROPE_FMA_LO 1: fma(lo, c, -(hi*s))   2: fma(-hi, s, lo*c)   0: no FMA
+//   CLEF_ROPE_FMA_HI 1: fma(hi, c, lo*s)      2: fma(lo, s, hi*c)    0: no FMA
+#ifndef CLEF_ROPE_FMA_LO
+#define CLEF_ROPE_FMA_LO 1
+#endif
+#ifndef CLEF_ROPE_FMA_HI
+#define CLEF_ROPE_FMA_HI 2
 #endif
 __device__ __forceinline__ void rope_pair(float lo, float hi, float c, float s, float& out_lo, float& out_hi) {
-#if CLEF_ROPE_FMA == 1
+#if CLEF_ROPE_FMA_LO == 1
     out_lo = __fmaf_rn(lo, c, -__fmul_rn(hi, s));
-    out_hi = __fmaf_rn(hi, c, __fmul_rn(lo, s));
-#elif CLEF_ROPE_FMA == 2
+#elif CLEF_ROPE_FMA_LO == 2
     out_lo = __fmaf_rn(-hi, s, __fmul_rn(lo, c));
-    out_hi = __fmaf_rn(lo, s, __fmul_rn(hi, c));
 #else
     out_lo = __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s));
+#endif
+#if CLEF_ROPE_FMA_HI == 1
+    out_hi = __fmaf_rn(hi, c, __fmul_rn(lo, s));
+#elif CLEF_ROPE_FMA_HI == 2
+    out_hi = __fmaf_rn(lo, s, __fmul_rn(hi, c));
+#else
     out_hi = __fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, s));
 #endif
 }

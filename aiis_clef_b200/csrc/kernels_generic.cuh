@@ -45,7 +45,8 @@ __device__ __forceinline__ float team_sum_squares(const typename T::storage* xro
     for (int off = 4; off > 0; off >>= 1) {
         t = __fadd_rn(t, __shfl_xor_sync(kFullMask, t, off));
     }
-    __syncthreads();   // s_part is reused by the next row group
+    t = __shfl_sync(kFullMask, t, 0);   // lanes >= 8 summed zeros among themselves
+    __syncthreads();                    // s_part is reused by the next row group
     return t;
 }
 

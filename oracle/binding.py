@@ -18,7 +18,7 @@ LIB_PATH = _DIR / "libclef_oracle.so"
 # FMA contraction of the reference build, fixed by comparison with the reference cubin on the GPU
 # (see clef_oracle.cpp: fma_mode / rope_fma).
 SUMSQ_FMA = 1
-ROPE_FMA = 1
+ROPE_FMA = 1 + 3 * 2   # lo_mode + 3 * hi_mode (rope_head in clef_oracle.cpp): fma(lo,c,-(hi*s)) and fma(lo,s,hi*c)
 
 _lib = None
 _vp = ctypes.c_void_p

@@ -277,23 +277,30 @@ inline void rms_norm_gated_row(const float* x, const float* g, const float* w, i
 }
 
 // kernels/elementwise.cu:276-315 rope_kernel, one (row, head): pairs (j, j+half), j < half;
-// dims >= rotary_dim are copied. rope_fma: 0 = none, 1 = fma on the first product
-// (fma(lo,c,-(hi*s)), fma(hi,c,lo*s)), 2 = fma on the second product (fma(-hi,s,lo*c), fma(lo,s,hi*c)).
+// dims >= rotary_dim are copied. rope_fma = lo_mode + 3 * hi_mode picks the contraction of each
+// expression independently:
+//   lo_mode (lo*c - hi*s): 0 none, 1 fma(lo,c,-(hi*s)), 2 fma(-hi,s,lo*c)
+//   hi_mode (hi*c + lo*s): 0 none, 1 fma(hi,c,lo*s),    2 fma(lo,s,hi*c)
 inline void rope_head(const float* x, float* out, const float* cos_row, const float* sin_row,
                       int head_dim, int rotary_dim, int rope_fma) {
     const int half = rotary_dim / 2;
+    const int lo_mode = rope_fma % 3, hi_mode = rope_fma / 3;
     for (int j = 0; j < half; ++j) {
         const float c = cos_row[j], s = sin_row[j];
         const float lo = x[j], hi = x[j + half];
         float a, b;
-        if (rope_fma == 1) {
+        if (lo_mode == 1) {
             a = std::fma(lo, c, -(hi * s));
-            b = std::fma(hi, c, lo * s);
-        } else if (rope_fma == 2) {
+        } else if (lo_mode == 2) {
             a = std::fma(-hi, s, lo * c);
-            b = std::fma(lo, s, hi * c);
         } else {
             a = lo * c - hi * s;
+        }
+        if (hi_mode == 1) {
+            b = std::fma(hi, c, lo * s);
+        } else if (hi_mode == 2) {
+            b = std::fma(lo, s, hi * c);
+        } else {
             b = hi * c + lo * s;
         }
         out[j] = a;

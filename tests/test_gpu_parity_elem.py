@@ -95,7 +95,8 @@ def test_rms_norm_reference_recipe():
     x = (((i * 37 % 101).astype(np.float32) - 50.0) / 11.0).reshape(rows, cols)
     w = ((np.arange(cols) % 7).astype(np.float32) - 3.0) / 8.0
     out = out_buffer(rows * cols, F32)
-    assert call("clef_rms_norm", stream(), ptr(torch.from_numpy(x).cuda()), ptr(torch.from_numpy(w).cuda()), out.ptr, rows, cols, 1e-6, F32) == 0
+    dx, dw = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    assert call("clef_rms_norm", stream(), ptr(dx), ptr(dw), out.ptr, rows, cols, 1e-6, F32) == 0
     torch.cuda.synchronize()
     want = np.stack([orc.model_rms_norm(x[r], w, 1e-6) for r in range(rows)])
     assert np.abs(out.as_f32().reshape(rows, cols) - want).max() < 1e-4
@@ -255,14 +256,18 @@ def test_qk_norm_rope(tokens, heads, head_dim, rot, with_gate):
 
 
 def test_rope_contraction_matches_the_reference_build():
-    """Which FMA contraction the reference build applies to lo*c - hi*s / hi*c + lo*s."""
+    """Which FMA contraction the reference build applies to lo*c - hi*s and to hi*c + lo*s (each
+    expression on its own): the modes the CPU oracle uses must reproduce rope_kernel's f32 output."""
     rows, heads, head_dim, rot = 512, 4, 128, 64
+    half = rot // 2
     rng = np.random.default_rng(3)
     x = rng.standard_normal((rows, heads, head_dim)).astype(np.float32)
     cos, sin = clef.Device(0).rope_tables_dev(torch.arange(rows, dtype=torch.int32, device="cuda"), rows, rot, 1e7)
     ref = ref_gpu.rope(torch.from_numpy(x).cuda(), cos, sin, rows, heads, head_dim, rot).cpu().numpy()
     diffs = {}
     for mode in (0, 1, 2):
-        f32, _ = orc.rope(x, cos.cpu().numpy(), sin.cpu().numpy(), rows, heads, head_dim, rot, rope_fma=mode)
-        diffs[mode] = int((f32.view(np.uint32) != ref.view(np.uint32)).sum())
-    assert diffs[orc.ROPE_FMA] == 0, f"f32 words differing per contraction mode: {diffs}"
+        f32, _ = orc.rope(x, cos.cpu().numpy(), sin.cpu().numpy(), rows, heads, head_dim, rot, rope_fma=mode + 3 * mode)
+        bad = f32.view(np.uint32) != ref.view(np.uint32)
+        diffs[mode] = (int(bad[:, :, :half].sum()), int(bad[:, :, half:rot].sum()))
+    lo_mode, hi_mode = orc.ROPE_FMA % 3, orc.ROPE_FMA // 3
+    assert diffs[lo_mode][0] == 0 and diffs[hi_mode][1] == 0, f"(lo, hi) f32 words differing per contraction mode: {diffs}"

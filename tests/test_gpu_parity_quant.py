@@ -130,7 +130,8 @@ def test_rms_norm_quantise_96_row_atom():
     w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
     blk_mn, chunk = clef.sf_atom_for_tile_m(192)
     assert (blk_mn, chunk) == (96, 384)
-    got_p, got_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(dev_bf16(x)), ptr(torch.from_numpy(w).cuda())],
+    dx, dw = dev_bf16(x), torch.from_numpy(w).cuda()   # keep the inputs alive across the call
+    got_p, got_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(dx), ptr(dw)],
                              [rows, cols, 1e-6, 64.0, blk_mn, chunk, BF16], blk_mn=96)
     want_p, want_s = orc.rms_norm_quantise_nvfp4(x, w, rows, cols, 1e-6, 64.0, blk_mn, chunk)
     assert_bytes_equal(got_p, want_p, "packed (96-row atom)")
