@@ -3,5 +3,6 @@
 The product is the C-ABI shared library built from csrc/ (see include/clef_fused.h); this package
 holds its build step and a ctypes binding whose `Device` class mirrors the reference launchers.
 """
-from .lib import (CLEF_BF16, CLEF_F32, ClefError, Device, load, nvfp4_m_tile_for, nvfp4_sizes,  # noqa: F401
+from .lib import (CLEF_BF16, CLEF_F32, ClefError, Device, HostDevice, load, load_host, nvfp4_m_tile_for,  # noqa: F401
+                  nvfp4_sizes, pass_geometries, pass_maps, rungs_decompose, shard_rows,
                   set_kernel_choice, sf_atom_for_tile_m)

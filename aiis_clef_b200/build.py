@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libclef_fused.so"
-SOURCES = ["clef_fused_abi.cu"]
+SOURCES = ["clef_fused_abi.cu", "clef_host.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -29,7 +29,7 @@ def find_nvcc() -> str:
 def needs_build() -> bool:
     if not OUT.exists():
         return True
-    newest = max(p.stat().st_mtime for p in list(CSRC.glob("*")) + [PKG.parent / "include" / "clef_fused.h"])
+    newest = max(p.stat().st_mtime for p in list(CSRC.glob("*")) + list((PKG.parent / "include").glob("*.h")))
     return newest > OUT.stat().st_mtime
 
 

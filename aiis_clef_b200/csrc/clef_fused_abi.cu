@@ -12,14 +12,15 @@
 #include <cstdio>
 #include <cstring>
 
+#include "internal.hpp"
 #include "kernels_generic.cuh"
 #include "kernels_hot.cuh"
 
 namespace {
-
 thread_local char g_error[512] = "";
-std::atomic<int> g_kernel_choice{0};
+}
 
+namespace clef {
 int fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -27,6 +28,12 @@ int fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+}  // namespace clef
+
+namespace {
+
+using clef::fail;
+std::atomic<int> g_kernel_choice{0};
 
 struct DeviceInfo {
     int sms = 0;

@@ -280,3 +280,200 @@ class Device:
                                                             _ptr(scales), rows, cols, global_scale, blk_mn, chunk,
                                                             _dtype_code(gate)), "clef_swiglu_quantise_nvfp4")
         return None if st == CLEF_DECLINED else (packed, scales)
+
+
+# =================================================================================================
+# Host-side companions (include/clef_host.h): device handle + host-slice launchers, per-token maps.
+# =================================================================================================
+import numpy as _np  # noqa: E402
+
+
+class _ChunkSpec(ctypes.Structure):
+    _fields_ = [("ids", ctypes.POINTER(ctypes.c_uint32)), ("ids_len", _SZ), ("pos", _SZ), ("slot", _SZ), ("rows", _SZ)]
+
+
+class _PassMaps(ctypes.Structure):
+    _fields_ = [("ids", _P), ("seq_start", _P), ("seq_end", _P), ("cpos", _P), ("cbase", _P), ("slot_map", _P),
+                ("rope_pos", _P), ("chunk_start", _P), ("state_slot", _P), ("hist_save", _P), ("rows_real", _P),
+                ("offs", _P), ("cache_len", ctypes.c_int32), ("total", _SZ)]
+
+
+HOST_SYMBOLS = {
+    "clef_device_open": (_I, [_I, ctypes.POINTER(_P)]),
+    "clef_device_close": (_I, [_P]),
+    "clef_device_ordinal": (_I, [_P]),
+    "clef_device_stream": (_P, [_P]),
+    "clef_device_synchronize": (_I, [_P]),
+    "clef_device_alloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
+    "clef_device_free": (_I, [_P, _P]),
+    "clef_device_upload": (_I, [_P, _P, _P, _SZ]),
+    "clef_device_download": (_I, [_P, _P, _P, _SZ]),
+    "clef_host_alloc_pinned": (_I, [_SZ, ctypes.POINTER(_P)]),
+    "clef_host_free_pinned": (_I, [_P]),
+    "clef_host_embed_gather": (_I, [_P, _P, _P, _P, _I, _I, _I]),
+    "clef_host_quantise_nvfp4": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _I]),
+    "clef_host_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I]),
+    "clef_host_swiglu_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I]),
+    "clef_host_rms_norm_gated_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _I, _I]),
+    "clef_host_rope": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I]),
+    "clef_pass_maps_build": (_I, [ctypes.POINTER(_ChunkSpec), _SZ, _SZ, _I, _SZ, _SZ, ctypes.POINTER(_PassMaps)]),
+    "clef_pass_geometries": (_I, [_SZ, _SZ, ctypes.POINTER(_SZ), _SZ]),
+    "clef_rungs_decompose": (_I, [_SZ, _SZ, _SZ, ctypes.POINTER(_SZ), ctypes.POINTER(_SZ), _SZ]),
+    "clef_shard_rows": (_I, [_I, _I, _I, _I, ctypes.POINTER(_I), ctypes.POINTER(_I)]),
+}
+
+_host_typed = False
+
+
+def load_host() -> ctypes.CDLL:
+    """The same shared library with the symbols of include/clef_host.h typed."""
+    global _host_typed
+    lib = load()
+    if not _host_typed:
+        for name, (restype, argtypes) in HOST_SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _host_typed = True
+    return lib
+
+
+def pass_geometries(slots: int = 1, max_chunk: int = 8192) -> list[int]:
+    """Row totals a pass may have (aiis-clef src/gpu.rs:779-795)."""
+    lib = load_host()
+    buf = (_SZ * 4096)()
+    n = lib.clef_pass_geometries(slots, max_chunk, buf, 4096)
+    return [int(buf[i]) for i in range(n)]
+
+
+def rungs_decompose(tokens: int, slots: int = 1, max_chunk: int = 8192) -> list[tuple[int, int]]:
+    """Rungs::decompose (src/gpu.rs:762-775): (base, rows) chunks, largest rung first."""
+    lib = load_host()
+    cap = tokens // 64 + 2
+    bases, rows = (_SZ * cap)(), (_SZ * cap)()
+    n = lib.clef_rungs_decompose(tokens, slots, max_chunk, bases, rows, cap)
+    return [(int(bases[i]), int(rows[i])) for i in range(n)]
+
+
+def shard_rows(rows: int, blk_mn: int, n_shards: int, shard: int) -> tuple[int, int]:
+    """(first_row, n_rows) of a shard: contiguous, aligned to the scale atom."""
+    first, n = _I(0), _I(0)
+    _check(load_host().clef_shard_rows(rows, blk_mn, n_shards, shard, ctypes.byref(first), ctypes.byref(n)),
+           "clef_shard_rows")
+    return first.value, n.value
+
+
+def pass_maps(chunks, capacity: int, check_geometry: bool = False, slots: int = 1, max_chunk: int = 8192) -> dict:
+    """Per-token maps of one pass (src/gpu.rs:948-1013).
+
+    chunks: iterable of (ids: uint32 array, pos, slot, rows). Returns a dict of numpy arrays
+    (ids, seq_start, seq_end, cpos, cbase, slot_map, rope_pos per row; chunk_start, state_slot per
+    64-row granule; hist_save [n, 2]; rows_real, offs per chunk) plus cache_len and total.
+    """
+    lib = load_host()
+    chunks = list(chunks)
+    n = len(chunks)
+    specs = (_ChunkSpec * max(n, 1))()
+    keep = []
+    total = 0
+    for i, (ids, pos, slot, rows) in enumerate(chunks):
+        arr = _np.ascontiguousarray(ids, dtype=_np.uint32)
+        keep.append(arr)
+        specs[i] = _ChunkSpec(arr.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), arr.size, pos, slot, rows)
+        total += int(rows)
+    gran = max(total // 64, 1)
+    out = {
+        "ids": _np.zeros(total, _np.uint32), "seq_start": _np.zeros(total, _np.int32),
+        "seq_end": _np.zeros(total, _np.int32), "cpos": _np.zeros(total, _np.int32),
+        "cbase": _np.zeros(total, _np.int32), "slot_map": _np.zeros(total, _np.int32),
+        "rope_pos": _np.zeros(total, _np.int32), "chunk_start": _np.zeros(gran, _np.int32),
+        "state_slot": _np.zeros(gran, _np.int32), "hist_save": _np.zeros((max(n, 1), 2), _np.uint32),
+        "rows_real": _np.zeros(max(n, 1), _np.uint64), "offs": _np.zeros(max(n, 1), _np.uint64),
+    }
+    m = _PassMaps(*[out[k].ctypes.data_as(_P) for k in ("ids", "seq_start", "seq_end", "cpos", "cbase", "slot_map",
+                                                        "rope_pos", "chunk_start", "state_slot", "hist_save",
+                                                        "rows_real", "offs")], 0, 0)
+    _check(lib.clef_pass_maps_build(specs, n, capacity, int(check_geometry), slots, max_chunk, ctypes.byref(m)),
+           "clef_pass_maps_build")
+    out["chunk_start"] = out["chunk_start"][: total // 64]
+    out["state_slot"] = out["state_slot"][: total // 64]
+    out["hist_save"] = out["hist_save"][:n]
+    out["rows_real"] = out["rows_real"][:n].astype(_np.int64)
+    out["offs"] = out["offs"][:n].astype(_np.int64)
+    out["cache_len"] = int(m.cache_len)
+    out["total"] = int(m.total)
+    return out
+
+
+class HostDevice:
+    """Device handle with the host-slice launchers (include/clef_host.h): numpy arrays or pinned torch
+    CPU tensors in, the same out. Mirrors the reference's host-slice wrappers
+    (aiis-clef src/cuda/mod.rs:853-1075), which upload, launch and download in one call."""
+
+    def __init__(self, ordinal: int = 0):
+        self.lib = load_host()
+        handle = _P()
+        _check(self.lib.clef_device_open(ordinal, ctypes.byref(handle)), "clef_device_open")
+        self.handle = handle
+        self.ordinal = ordinal
+
+    def close(self):
+        if self.handle:
+            self.lib.clef_device_close(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _hp(a):
+        if a is None:
+            return None
+        if isinstance(a, torch.Tensor):
+            assert not a.is_cuda and a.is_contiguous()
+            return ctypes.c_void_p(a.data_ptr())
+        assert a.flags["C_CONTIGUOUS"]
+        return ctypes.c_void_p(a.ctypes.data)
+
+    @staticmethod
+    def _code(a):
+        dt = a.dtype
+        if dt in (torch.bfloat16, _np.uint16):
+            return CLEF_BF16
+        if dt in (torch.float32, _np.float32):
+            return CLEF_F32
+        raise ClefError(f"activations must be bf16 (uint16 bits / torch.bfloat16) or float32, got {dt}")
+
+    def embed_gather(self, table_dev: torch.Tensor, ids, out, tokens: int, hidden: int):
+        _check(self.lib.clef_host_embed_gather(self.handle, _ptr(table_dev), self._hp(ids), self._hp(out), tokens,
+                                               hidden, _dtype_code(table_dev)), "clef_host_embed_gather")
+
+    def quantise_nvfp4(self, x, packed, scales, rows, cols, global_scale, tile_m=128):
+        _check(self.lib.clef_host_quantise_nvfp4(self.handle, self._hp(x), self._hp(packed), self._hp(scales), rows,
+                                                 cols, global_scale, tile_m, self._code(x)), "clef_host_quantise_nvfp4")
+
+    def rms_norm_quantise_nvfp4(self, x, weight, packed, scales, rows, cols, eps, global_scale, tile_m=128):
+        _check(self.lib.clef_host_rms_norm_quantise_nvfp4(self.handle, self._hp(x), self._hp(weight), self._hp(packed),
+                                                          self._hp(scales), rows, cols, eps, global_scale, tile_m,
+                                                          self._code(x)), "clef_host_rms_norm_quantise_nvfp4")
+
+    def swiglu_quantise_nvfp4(self, gate, up, packed, scales, rows, cols, global_scale, tile_m=128):
+        _check(self.lib.clef_host_swiglu_quantise_nvfp4(self.handle, self._hp(gate), self._hp(up), self._hp(packed),
+                                                        self._hp(scales), rows, cols, global_scale, tile_m,
+                                                        self._code(gate)), "clef_host_swiglu_quantise_nvfp4")
+
+    def rms_norm_gated_quantise_nvfp4(self, x, gate, weight, packed, scales, rows, cols, vh, eps, global_scale,
+                                      tile_m=128):
+        _check(self.lib.clef_host_rms_norm_gated_quantise_nvfp4(self.handle, self._hp(x), self._hp(gate),
+                                                                self._hp(weight), self._hp(packed), self._hp(scales),
+                                                                rows, cols, vh, eps, global_scale, tile_m,
+                                                                self._code(x)),
+               "clef_host_rms_norm_gated_quantise_nvfp4")
+
+    def rope(self, out, x, cos, sin, table_rows, rows, heads, head_dim, rotary_dim, pos_map=None):
+        _check(self.lib.clef_host_rope(self.handle, self._hp(out), self._hp(x), self._hp(cos), self._hp(sin),
+                                       table_rows, rows, heads, head_dim, rotary_dim, self._hp(pos_map),
+                                       self._code(x)), "clef_host_rope")

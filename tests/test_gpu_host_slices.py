@@ -1,0 +1,105 @@
+"""The host-slice launchers (include/clef_host.h): host buffers in, host buffers out, row tiles
+streamed through two CUDA streams. Results must equal the CPU oracle's (exact kernels) or the
+device-resident C-ABI path's (kernels with approximate intrinsics), byte for byte."""
+import numpy as np
+import pytest
+import torch
+
+import aiis_clef_b200 as clef
+from oracle import binding as orc
+from gpu_util import dev_bf16
+from util import assert_bytes_equal, normal_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def host_dev():
+    d = clef.HostDevice(0)
+    yield d
+    d.close()
+
+
+def pinned(a: np.ndarray) -> torch.Tensor:
+    t = torch.from_numpy(a)
+    return t.pin_memory()
+
+
+@pytest.mark.parametrize("rows", [1, 778, 8192, 20000])
+def test_host_rms_norm_quantise(host_dev, rows):
+    cols = 2048
+    rng = np.random.default_rng(rows)
+    x = normal_bf16(rng, (rows, cols), outlier_channels=8)
+    w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
+    rp, pb, sb = clef.nvfp4_sizes(rows, cols, 128)
+    packed, scales = pinned(np.full(pb, 0xA5, np.uint8)), pinned(np.full(sb, 0xA5, np.uint8))
+    xin = orc.bits_to_torch_bf16(x).pin_memory()
+    host_dev.rms_norm_quantise_nvfp4(xin, w, packed, scales, rows, cols, 1e-6, 64.0)
+    want_p, want_s = orc.rms_norm_quantise_nvfp4(x, w, rows, cols, 1e-6, 64.0)
+    assert_bytes_equal(packed.numpy(), want_p, "host rms_norm+quant packed")
+    assert_bytes_equal(scales.numpy(), want_s, "host rms_norm+quant scales")
+
+
+@pytest.mark.parametrize("rows", [7, 8192])
+def test_host_swiglu_quantise_and_quantise(host_dev, rows):
+    cols = 6144
+    rng = np.random.default_rng(rows + 1)
+    gate, up = normal_bf16(rng, (rows, cols)), normal_bf16(rng, (rows, cols))
+    rp, pb, sb = clef.nvfp4_sizes(rows, cols, 128)
+    packed, scales = np.full(pb, 0xA5, np.uint8), np.full(sb, 0xA5, np.uint8)   # pageable host memory also works
+    host_dev.swiglu_quantise_nvfp4(gate, up, packed, scales, rows, cols, 64.0)
+    ref_p, ref_s = clef.Device(0).swiglu_quantise_nvfp4_dev(dev_bf16(gate), dev_bf16(up), rows, cols, 64.0, 128)
+    torch.cuda.synchronize()
+    assert_bytes_equal(packed, ref_p.cpu().numpy().reshape(-1), "host swiglu+quant packed")
+    assert_bytes_equal(scales, ref_s.cpu().numpy(), "host swiglu+quant scales")
+    p2, s2 = np.full(pb, 0xA5, np.uint8), np.full(sb, 0xA5, np.uint8)
+    host_dev.quantise_nvfp4(gate, p2, s2, rows, cols, 64.0)
+    want_p, want_s = orc.quantise_nvfp4(gate, rows, cols, 64.0)
+    assert_bytes_equal(p2, want_p, "host quantise packed")
+    assert_bytes_equal(s2, want_s, "host quantise scales")
+
+
+@pytest.mark.parametrize("tokens", [5, 1300])
+def test_host_gated(host_dev, tokens):
+    vh, cols = 16, 128
+    rows = tokens * vh
+    rng = np.random.default_rng(tokens)
+    x, g = normal_bf16(rng, (rows, cols)), normal_bf16(rng, (rows, cols))
+    w = (1 + rng.standard_normal(cols) * 0.1).astype(np.float32)
+    tp, pb, sb = clef.nvfp4_sizes(tokens, vh * cols, 128)
+    packed, scales = np.full(pb, 0xA5, np.uint8), np.full(sb, 0xA5, np.uint8)
+    host_dev.rms_norm_gated_quantise_nvfp4(x, g, w, packed, scales, rows, cols, vh, 1e-6, 64.0)
+    ref_p, ref_s = clef.Device(0).rms_norm_gated_quantise_nvfp4_dev(dev_bf16(x), dev_bf16(g), torch.from_numpy(w).cuda(),
+                                                                     rows, cols, vh, 1e-6, 64.0, 128)
+    torch.cuda.synchronize()
+    assert_bytes_equal(packed, ref_p.cpu().numpy().reshape(-1), "host gated packed")
+    assert_bytes_equal(scales, ref_s.cpu().numpy(), "host gated scales")
+
+
+def test_host_rope_and_embed(host_dev):
+    rows, heads, hd, rot = 3000, 16, 128, 64
+    rng = np.random.default_rng(9)
+    x = normal_bf16(rng, (rows, heads, hd))
+    table_rows = 4096
+    cos, sin = orc.rope_tables(np.arange(table_rows, dtype=np.int32), rot, 1e7)
+    pos = rng.integers(0, table_rows, rows).astype(np.int32)
+    out = np.zeros_like(x)
+    host_dev.rope(out, x, cos, sin, table_rows, rows, heads, hd, rot, pos)
+    d = clef.Device(0)
+    want = d.rope_apply_dev(dev_bf16(x), torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda(), rows, heads, hd, rot,
+                            pos_map=torch.from_numpy(pos).cuda())
+    torch.cuda.synchronize()
+    assert_bytes_equal(out, orc.bf16_bits(want.cpu()), "host rope")
+    out2 = np.zeros_like(x)
+    host_dev.rope(out2, x, cos, sin, table_rows, rows, heads, hd, rot, None)          # position = row index
+    _, want2 = orc.rope(x, cos, sin, rows, heads, hd, rot)
+    from util import bf16_ulp_distance
+    assert bf16_ulp_distance(out2.reshape(-1), want2.reshape(-1)).max() <= 2
+    with pytest.raises(clef.ClefError, match="outside"):
+        host_dev.rope(out, x, cos, sin, table_rows, rows, heads, hd, rot, pos + 5000)
+    vocab, hidden, tokens = 5000, 2048, 9000
+    table = normal_bf16(rng, (vocab, hidden), scale=0.02)
+    ids = rng.integers(0, vocab, tokens).astype(np.int32)
+    got = np.zeros((tokens, hidden), np.uint16)
+    host_dev.embed_gather(dev_bf16(table), ids, got, tokens, hidden)
+    assert_bytes_equal(got, table[ids], "host embed gather")
