@@ -286,16 +286,17 @@ int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const floa
     if (dtype == CLEF_BF16 && use_hot() && (cols == 2048 || cols == 4096) && aligned(x, 32)) {
         const size_t groups = ((size_t)rows_total + 7) / 8;
         const size_t smem = (size_t)cols * sizeof(float);
+        const FastDiv atom_div = make_fast_div((uint32_t)blk_mn);
         if (cols == 2048) {
             static std::atomic<int> occ{0};
             const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<4>, smem, occ);
             rms_norm_quant_hot_kernel<4><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem, s>>>(
-                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk);
+                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk, atom_div);
         } else {
             static std::atomic<int> occ{0};
             const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<8>, smem, occ);
             rms_norm_quant_hot_kernel<8><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem, s>>>(
-                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk);
+                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk, atom_div);
         }
         return check_launch(what);
     }
@@ -386,7 +387,7 @@ int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, cons
         const size_t groups = ((size_t)rows + 31) / 32;   // 32 head rows per CTA step
         gated_norm_quant_hot_kernel<<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
             (const uint16_t*)x, (const uint16_t*)gate, weight, packed, scales, rows_live, rows, eps, global_scale,
-            blk_mn, chunk, vh);
+            blk_mn, chunk, vh, make_fast_div((uint32_t)vh), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {
@@ -485,13 +486,17 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
     const size_t total_blocks = (size_t)rows_total * (cols / 16);
-    if (dtype == CLEF_BF16 && use_hot() && aligned(gate, 32) && aligned(up, 32)) {
+    if (dtype == CLEF_BF16 && use_hot() && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(gate, 32) &&
+        aligned(up, 32)) {
+        constexpr int kUnits = 2;
         static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(swiglu_quant_hot_kernel<2>, 0, occ);
-        const size_t ctas = (total_blocks + 2 * kCtaThreads - 1) / (2 * kCtaThreads);
-        swiglu_quant_hot_kernel<2><<<clamp_grid(ctas, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
-            (const uint16_t*)gate, (const uint16_t*)up, packed, scales, rows, rows_total, cols, global_scale, blk_mn,
-            chunk);
+        const int per_sm = ctas_per_sm(swiglu_quant_hot_kernel<kUnits>, 0, occ);
+        const uint32_t segs = (uint32_t)(cols / 512);
+        const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;
+        const size_t ctas = ((size_t)total_units + kUnits * 8 - 1) / (kUnits * 8);
+        swiglu_quant_hot_kernel<kUnits><<<clamp_grid(ctas, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
+            (const uint16_t*)gate, (const uint16_t*)up, packed, scales, live_units, total_units, cols, global_scale,
+            blk_mn, chunk, make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {
@@ -534,14 +539,15 @@ int clef_rope(clef_stream_t stream, void* out, const void* x, const float* cos_t
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
-    if (dtype == CLEF_BF16 && use_hot() && head_dim % 32 == 0 && rotary_dim % 32 == 0 && aligned(x, 32) &&
-        aligned(out, 32)) {
+    const size_t hot_items = (size_t)rows * heads * (head_dim / 32);
+    if (dtype == CLEF_BF16 && use_hot() && head_dim % 32 == 0 && rotary_dim % 32 == 0 && hot_items < 0x7fffffffull &&
+        aligned(x, 32) && aligned(out, 32)) {
         static std::atomic<int> occ{0};
         const int per_sm = ctas_per_sm(rope_hot_kernel, 0, occ);
-        const size_t items = (size_t)rows * heads * (head_dim / 32);
-        rope_hot_kernel<<<clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), kCtaThreads, 0,
-                          s>>>((uint16_t*)out, (const uint16_t*)x, cos_table, sin_table, rows, heads, head_dim,
-                               rotary_dim, seq_start, pos_base, pos_map);
+        rope_hot_kernel<<<clamp_grid((hot_items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), kCtaThreads,
+                          0, s>>>((uint16_t*)out, (const uint16_t*)x, cos_table, sin_table, (uint32_t)hot_items, heads,
+                                  head_dim, rotary_dim, seq_start, pos_base, pos_map,
+                                  make_fast_div((uint32_t)(head_dim / 32)), make_fast_div((uint32_t)heads));
         return check_launch(what);
     }
     const size_t items = (size_t)rows * heads * ((rotary_dim / 8) + (head_dim - rotary_dim) / 4);

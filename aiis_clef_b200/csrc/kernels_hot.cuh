@@ -1,23 +1,123 @@
 // Tuned sm_100a kernels for bf16 activations at the shapes the fused layer runs at.
 //
 // Common shape of every kernel here: persistent CTAs (grid = SM count x resident CTAs), each lane
-// moves 32 contiguous bytes per access (256-bit ld/st, a warp covers 1 KiB), so one lane owns
-// one whole 16-value NVFP4 block; row reductions are warp shuffles arranged to reproduce the
-// reference's summation tree; nothing is staged through global scratch memory.
+// moves 32 contiguous bytes per access (256-bit ld/st, a warp covers 1 KiB), so one lane owns one
+// whole 16-value NVFP4 block; arithmetic runs on packed fp32 pairs (f32x2.cuh) because these
+// kernels are bound by instruction issue before they are bound by HBM; row reductions are warp
+// shuffles arranged to reproduce the reference's summation tree; no global scratch memory.
+//
+// Register layout of one 16-value block ("quad pairs"): for quad q (elements 4q..4q+3 = x,y,z,w)
+// pair 2q holds (x, z) and pair 2q+1 holds (y, w). That is the layout in which the reference's
+// (x*x + y*y) + (z*z + w*w) becomes one packed multiply and one packed FMA, and the quantiser
+// accepts it directly.
 #pragma once
 
 #include "common.cuh"
+#include "f32x2.cuh"
 #include "nvfp4_codec.cuh"
 
 namespace clef {
 
-// Unpack a 32-byte chunk of 16 bf16 values to f32.
-__device__ __forceinline__ void unpack16(const U8x32& d, float* v) {
+// n / d for n < 2^31 by multiply-high (d fixed per launch, prepared on the host).
+struct FastDiv {
+    uint32_t d, mul, shr;
+};
+inline FastDiv make_fast_div(uint32_t d) {
+    FastDiv f{d, 0u, 0u};
+    if (d > 1) {
+        uint32_t lg = 0;
+        while ((1ull << lg) < d) ++lg;
+        const uint32_t p = 31 + lg;
+        f.mul = (uint32_t)(((1ull << p) + d - 1) / d);
+        f.shr = p - 32;
+    }
+    return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+    return f.d == 1 ? n : (__umulhi(n, f.mul) >> f.shr);
+}
+
+// 32 bytes = 16 bf16 values -> 8 packed pairs in the quad-pair layout.
+__device__ __forceinline__ void unpack16_quadpairs(const U8x32& d, f32x2* v) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint32_t w0 = d.w[2 * q], w1 = d.w[2 * q + 1];
+        v[2 * q] = f2_pack(bf16_lo(w0), bf16_lo(w1));       // (x, z)
+        v[2 * q + 1] = f2_pack(bf16_hi(w0), bf16_hi(w1));   // (y, w)
+    }
+}
+
+// Sum of squares of the 4 quads of a block, reference association and contraction:
+// quad = fma(x,x,y*y) + fma(z,z,w*w).
+__device__ __forceinline__ void quad_squares(const f32x2* v, float* quad) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const f32x2 t = f2_mul(v[2 * q + 1], v[2 * q + 1]);       // (y*y, w*w)
+        const f32x2 s = f2_fma(v[2 * q], v[2 * q], t);            // (fma(x,x,y*y), fma(z,z,w*w))
+        float a, b;
+        f2_unpack(s, a, b);
+        quad[q] = __fadd_rn(a, b);
+    }
+}
+
+// Quad-pair layout -> natural order (rare path only).
+__device__ __forceinline__ void quadpairs_to_natural(const f32x2* v, float* a, bool negate) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float x, z, y, w;
+        f2_unpack(v[2 * q], x, z);
+        f2_unpack(v[2 * q + 1], y, w);
+        a[4 * q] = negate ? -x : x;
+        a[4 * q + 1] = negate ? -y : y;
+        a[4 * q + 2] = negate ? -z : z;
+        a[4 * q + 3] = negate ? -w : w;
+    }
+}
+
+// Block quantiser on the quad-pair layout. NEG: the pairs hold the NEGATED values (the SwiGLU fast
+// path produces -v); magnitudes are unaffected and the sign is restored by scaling with -inv_scale.
+template <bool NEG>
+__device__ __forceinline__ void quantise16_qp(const f32x2* v, float global_scale, const float* inv_table,
+                                              uint32_t& stored_out, uint32_t& lo_out, uint32_t& hi_out) {
+    float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        v[2 * i] = bf16_lo(d.w[i]);
-        v[2 * i + 1] = bf16_hi(d.w[i]);
+        float a, b;
+        f2_unpack(v[i], a, b);
+        amax = max3_abs_nan(amax, a, b);
     }
+    const float sv = __fmul_rn(div_six_fast(amax), global_scale);
+    const uint32_t stored = e4m3_encode_finite(sv);
+    const float inv = inv_table[stored];
+    const float pmax = __fmul_rn(amax, inv);
+    const bool tiny = (amax < kDivSixExactFrom) && (amax > 0.0f);
+    if (!(fabsf(sv) <= 3.0e38f) || !(pmax < kE2m1FastLimit) || tiny) {
+        float a[16];
+        quadpairs_to_natural(v, a, NEG);
+        quantise16_rare(a, global_scale, stored_out, lo_out, hi_out);
+        return;
+    }
+    constexpr float kNudge = -4.33488326e-08f;   // see e2m1x2_fast
+    const f32x2 inv2 = f2_splat(NEG ? -inv : inv);
+    const f32x2 nudge2 = f2_splat(kNudge);
+    uint32_t bytes[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const f32x2 pa = f2_mul(v[2 * q], inv2);
+        const f32x2 pb = f2_mul(v[2 * q + 1], inv2);
+        float x, z, y, w;
+        f2_unpack(f2_fma(pa, nudge2, pa), x, z);
+        f2_unpack(f2_fma(pb, nudge2, pb), y, w);
+        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
+            : "=r"(bytes[2 * q])
+            : "f"(y), "f"(x));
+        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
+            : "=r"(bytes[2 * q + 1])
+            : "f"(w), "f"(z));
+    }
+    stored_out = stored;
+    lo_out = bytes[0] | (bytes[1] << 8) | (bytes[2] << 16) | (bytes[3] << 24);
+    hi_out = bytes[4] | (bytes[5] << 8) | (bytes[6] << 16) | (bytes[7] << 24);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -29,62 +129,57 @@ __device__ __forceinline__ void unpack16(const U8x32& d, float* v) {
 // Here lane L holds chunks c = L + 32 j (j < NB), i.e. quads 4c + k (k < 4), so
 //   sub            = k + 4 L + 128 (j & 1)        reference lane = k + 4 (L & 7)
 //   reference warp = (L >> 3) + 4 (j & 1)
-// and the same tree is: in-lane over j (stride 2, ascending), shuffles over L bits 2,1,0, in-lane
-// over k (k^2 then k^1), in-lane over j & 1, shuffles over L bit 4 then L bit 3.
+// The 8 per-lane partial sums P[j & 1][k] go through the same tree as a reduce-scatter: each of the
+// three levels over L bits 2,1,0 halves the values a lane keeps (every tree node is computed once,
+// not in every lane), then butterflies over k (k^2, k^1), j & 1, L bit 4, L bit 3. 12 shuffles.
 // ---------------------------------------------------------------------------------------------
-template <int NB>
-__device__ __forceinline__ float row_sum_squares_256(const U8x32* d) {
-    float p[2][4];
+__device__ __forceinline__ float row_tree_256(const float (&p)[2][4], int lane) {
+    const bool l2 = lane & 4, l1 = lane & 2, l0 = lane & 1;
+    float s[4];
 #pragma unroll
-    for (int j0 = 0; j0 < 2; ++j0) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            float acc = 0.0f;
-#pragma unroll
-            for (int j = j0; j < NB; j += 2) {
-                const uint32_t a = d[j].w[2 * k], b = d[j].w[2 * k + 1];
-                acc = __fadd_rn(acc, quad_sq(make_float4(bf16_lo(a), bf16_hi(a), bf16_lo(b), bf16_hi(b))));
-            }
-            p[j0][k] = acc;
-        }
+    for (int k = 0; k < 4; ++k) {   // level L bit 2: keep j0 == l2
+        const float send = l2 ? p[0][k] : p[1][k];
+        const float keep = l2 ? p[1][k] : p[0][k];
+        s[k] = __fadd_rn(keep, __shfl_xor_sync(kFullMask, send, 4));
     }
+    float t[2];
 #pragma unroll
-    for (int off = 4; off > 0; off >>= 1) {
-#pragma unroll
-        for (int j0 = 0; j0 < 2; ++j0) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                p[j0][k] = __fadd_rn(p[j0][k], __shfl_xor_sync(kFullMask, p[j0][k], off));
-            }
-        }
+    for (int m = 0; m < 2; ++m) {   // level L bit 1: keep k bit 1 == l1
+        const float send = l1 ? s[m] : s[2 + m];
+        const float keep = l1 ? s[2 + m] : s[m];
+        t[m] = __fadd_rn(keep, __shfl_xor_sync(kFullMask, send, 2));
     }
-    float w[2];
-#pragma unroll
-    for (int j0 = 0; j0 < 2; ++j0) {
-        w[j0] = __fadd_rn(__fadd_rn(p[j0][0], p[j0][2]), __fadd_rn(p[j0][1], p[j0][3]));
-    }
-    float t = __fadd_rn(w[0], w[1]);
-    t = __fadd_rn(t, __shfl_xor_sync(kFullMask, t, 16));
-    t = __fadd_rn(t, __shfl_xor_sync(kFullMask, t, 8));
-    return t;
+    // level L bit 0: keep k bit 0 == l0
+    float u = __fadd_rn(l0 ? t[1] : t[0], __shfl_xor_sync(kFullMask, l0 ? t[0] : t[1], 1));
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 2));    // k ^ 2
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 1));    // k ^ 1   -> reference warp sum
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 4));    // reference warps w, w + 4
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 16));   // w, w + 2
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 8));    // w, w + 1
+    return u;
 }
 
+#ifndef CLEF_RMS_MIN_CTAS
+#define CLEF_RMS_MIN_CTAS 3
+#endif
 template <int NB>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? CLEF_RMS_MIN_CTAS : 2))
 rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight,
                           uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows, int rows_total,
-                          float eps, float global_scale, int blk_mn, int chunk) {
+                          float eps, float global_scale, int blk_mn, int chunk, FastDiv atom_div) {
     constexpr int COLS = NB * 512;
     constexpr int BLOCKS = COLS / 16;
     __shared__ float s_inv[kInvScaleTableSize];
-    extern __shared__ float4 s_w[];   // (1 + w), transposed so lane L reads s_w[(4 j + q) * 32 + L]
+    // (1 + w) in the quad-pair layout, transposed so lane L reads s_w[(4 j + q) * 32 + L] = the pairs
+    // (1+w_x, 1+w_z), (1+w_y, 1+w_w) of quad q of chunk L + 32 j.
+    extern __shared__ float4 s_w[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
 
     int row = blockIdx.x * 8 + warp;
     U8x32 d[NB];
-    const bool first_live = row < rows;
-    if (first_live) {
+    bool loaded = row < rows;
+    if (loaded) {
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
             d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
@@ -94,18 +189,21 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
     for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
         const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
         const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
-        s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.y, 1.0f + w.z, 1.0f + w.w);
+        s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
     }
     __syncthreads();
 
-    bool loaded = first_live;
     for (; row < rows_total; row += gridDim.x * 8) {
         uint8_t* prow = packed + (size_t)row * (COLS / 2);
+        const uint32_t m_rest = fast_div((uint32_t)row, atom_div);
+        const uint32_t m_atom = (uint32_t)row - m_rest * (uint32_t)blk_mn;
+        uint8_t* srow = scales + (size_t)m_rest * (BLOCKS / 4) * (size_t)chunk + (size_t)m_atom * 4;
         if (row >= rows) {
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
                 const int b = lane + 32 * j;
-                store_block(prow, scales, (size_t)b * 8, scale_offset(row, b, BLOCKS, blk_mn, chunk), 0u, 0u, 0u);
+                *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(0u, 0u);
+                srow[(size_t)(b >> 2) * chunk + (b & 3)] = 0;
             }
             continue;
         }
@@ -116,88 +214,154 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
             }
         }
         loaded = false;
-        const float inv = inv_rms(row_sum_squares_256<NB>(d), COLS, eps);
+        // partial sums P[j & 1][k]: in-lane over j (stride 2, ascending), as the reference thread does
+        float p[2][4];
+#pragma unroll
+        for (int j0 = 0; j0 < 2; ++j0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) p[j0][k] = 0.0f;
+        }
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            float v[16];
-            unpack16(d[j], v);
+            f32x2 v[8];
+            float quad[4];
+            unpack16_quadpairs(d[j], v);
+            quad_squares(v, quad);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                p[j & 1][k] = __fadd_rn(p[j & 1][k], quad[k]);
+            }
+        }
+        const float inv = inv_rms(row_tree_256(p, lane), COLS, eps);
+        const f32x2 inv2 = f2_splat(inv);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            f32x2 v[8];
+            unpack16_quadpairs(d[j], v);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float4 w = s_w[(4 * j + q) * 32 + lane];
-                v[4 * q + 0] = v[4 * q + 0] * inv * w.x;
-                v[4 * q + 1] = v[4 * q + 1] * inv * w.y;
-                v[4 * q + 2] = v[4 * q + 2] * inv * w.z;
-                v[4 * q + 3] = v[4 * q + 3] * inv * w.w;
+                v[2 * q] = f2_mul(f2_mul(v[2 * q], inv2), make_float2(w.x, w.y));
+                v[2 * q + 1] = f2_mul(f2_mul(v[2 * q + 1], inv2), make_float2(w.z, w.w));
             }
             uint32_t stored, lo, hi;
-            quantise16(v, global_scale, s_inv, stored, lo, hi);
+            quantise16_qp<false>(v, global_scale, s_inv, stored, lo, hi);
             const int b = lane + 32 * j;
-            store_block(prow, scales, (size_t)b * 8, scale_offset(row, b, BLOCKS, blk_mn, chunk), stored, lo, hi);
+            *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(lo, hi);
+            srow[(size_t)(b >> 2) * chunk + (b & 3)] = (uint8_t)stored;
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// SwiGLU + NVFP4 quantiser (kernels/quantise.cu:523-591): silu(gate) * up, one lane per block,
-// UNROLL blocks in flight per lane. Rows in [rows, rows_total) are zero-filled.
+// SwiGLU + NVFP4 quantiser (kernels/quantise.cu:523-591) for cols % 512 == 0.
+// A warp handles "units" of 32 consecutive blocks (1 KiB of gate, 1 KiB of up); unit u covers
+// elements [512 u, 512 u + 512) of the dense [rows, cols] matrices, so only the scale address needs
+// the row. UNITS units are in flight per warp.
+//
+// silu(g) = g / (1 + __expf(-g)) with the IEEE division replaced, for bf16 g with |g| <= 44, by
+//   r = rcp.approx(-d), q0 = g * r, rem = fma(d, q0, g), q = fma(rem, r, q0)   (q = -g/d)
+// which equals div.rn.f32(g, d) negated for every such g (all 65536 bf16 patterns are compared on
+// the device by the tests; -0.0 gives +0.0, which the quantiser cannot tell apart). Blocks holding a
+// larger |g|, an infinity or a NaN take the literal expression.
 // ---------------------------------------------------------------------------------------------
-template <int UNROLL>
-__global__ void __launch_bounds__(kCtaThreads)
-swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up,
-                        uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows, int rows_total,
-                        int cols, float global_scale, int blk_mn, int chunk) {
-    __shared__ float s_inv[kInvScaleTableSize];
-    const int blocks = cols >> 4;
-    const size_t live_blocks = (size_t)rows * blocks;
-    const size_t total_blocks = (size_t)rows_total * blocks;
-    const size_t stride = (size_t)gridDim.x * kCtaThreads;
-    size_t idx0 = (size_t)blockIdx.x * kCtaThreads + threadIdx.x;
+constexpr float kSiluFastMaxAbs = 44.0f;
 
-    U8x32 g[UNROLL], u[UNROLL];
+// (g0, g1) -> (-silu(g0), -silu(g1)), fast form; see above for the domain.
+__device__ __forceinline__ f32x2 neg_silu_fast_x2(f32x2 g2) {
+    float g0, g1;
+    f2_unpack(g2, g0, g1);
+    const f32x2 d2 = f2_add(f2_splat(1.0f), f2_pack(__expf(-g0), __expf(-g1)));
+    float d0, d1, r0, r1;
+    f2_unpack(d2, d0, d1);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(-d0));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(-d1));
+    const f32x2 r2 = f2_pack(r0, r1);
+    const f32x2 q0 = f2_mul(g2, r2);            // -(g * rcp(d))
+    const f32x2 rem = f2_fma(d2, q0, g2);       // g - d * (g * rcp(d)), exact
+    return f2_fma(rem, r2, q0);                 // -(q0' + rem * rcp(d))
+}
+
+template <int UNITS>
+__global__ void __launch_bounds__(kCtaThreads, 3)
+swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up,
+                        uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t live_units,
+                        uint32_t total_units, int cols, float global_scale, int blk_mn, int chunk, FastDiv seg_div,
+                        FastDiv atom_div) {
+    __shared__ float s_inv[kInvScaleTableSize];
+    const int lane = threadIdx.x & 31;
+    const uint32_t warps = gridDim.x * (kCtaThreads / 32);
+    uint32_t unit0 = blockIdx.x * (kCtaThreads / 32) + (threadIdx.x >> 5);
+    const int k1_count = cols >> 6;
+
+    U8x32 g[UNITS], u[UNITS];
 #pragma unroll
-    for (int k = 0; k < UNROLL; ++k) {
-        const size_t idx = idx0 + k * stride;
-        if (idx < live_blocks) {
-            g[k] = ldg_stream_v8(gate + idx * 16);
-            u[k] = ldg_stream_v8(up + idx * 16);
+    for (int k = 0; k < UNITS; ++k) {
+        const uint32_t unit = unit0 + k * warps;
+        if (unit < live_units) {
+            g[k] = ldg_stream_v8(gate + (size_t)unit * 512 + lane * 16);
+            u[k] = ldg_stream_v8(up + (size_t)unit * 512 + lane * 16);
         }
     }
     fill_inv_scale_table(s_inv, global_scale);
     __syncthreads();
 
     bool loaded = true;
-    for (; idx0 < total_blocks; idx0 += UNROLL * stride) {
+    for (; unit0 < total_units; unit0 += UNITS * warps) {
         if (!loaded) {
 #pragma unroll
-            for (int k = 0; k < UNROLL; ++k) {
-                const size_t idx = idx0 + k * stride;
-                if (idx < live_blocks) {
-                    g[k] = ldg_stream_v8(gate + idx * 16);
-                    u[k] = ldg_stream_v8(up + idx * 16);
+            for (int k = 0; k < UNITS; ++k) {
+                const uint32_t unit = unit0 + k * warps;
+                if (unit < live_units) {
+                    g[k] = ldg_stream_v8(gate + (size_t)unit * 512 + lane * 16);
+                    u[k] = ldg_stream_v8(up + (size_t)unit * 512 + lane * 16);
                 }
             }
         }
         loaded = false;
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-            const size_t idx = idx0 + k * stride;
-            if (idx >= total_blocks) {
+        for (int k = 0; k < UNITS; ++k) {
+            const uint32_t unit = unit0 + k * warps;
+            if (unit >= total_units) {
                 break;
             }
-            const int row = (int)(idx / blocks);
-            const int blk = (int)(idx - (size_t)row * blocks);
+            const uint32_t row = fast_div(unit, seg_div);
+            const uint32_t block = (unit - row * seg_div.d) * 32 + lane;
+            const uint32_t m_rest = fast_div(row, atom_div);
+            const uint32_t m_atom = row - m_rest * (uint32_t)blk_mn;
+            uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
+            uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)unit * 256 + lane * 8);
             uint32_t stored = 0, lo = 0, hi = 0;
-            if (idx < live_blocks) {
-                float v[16], w[16];
-                unpack16(g[k], v);
-                unpack16(u[k], w);
+            if (unit < live_units) {
+                f32x2 gv[8], uv[8];
+                unpack16_quadpairs(g[k], gv);
+                unpack16_quadpairs(u[k], uv);
+                float gmax = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    v[i] = silu_ieee_div(v[i]) * w[i];
+                for (int i = 0; i < 8; ++i) {
+                    float a, b;
+                    f2_unpack(gv[i], a, b);
+                    gmax = max3_abs_nan(gmax, a, b);
                 }
-                quantise16(v, global_scale, s_inv, stored, lo, hi);
+                if (gmax <= kSiluFastMaxAbs) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        gv[i] = f2_mul(neg_silu_fast_x2(gv[i]), uv[i]);   // -(silu(g) * u)
+                    }
+                    quantise16_qp<true>(gv, global_scale, s_inv, stored, lo, hi);
+                } else {
+                    float a[16], b[16];
+                    quadpairs_to_natural(gv, a, false);
+                    quadpairs_to_natural(uv, b, false);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        a[i] = silu_ieee_div(a[i]) * b[i];
+                    }
+                    quantise16(a, global_scale, s_inv, stored, lo, hi);
+                }
             }
-            store_block(packed, scales, idx * 8, scale_offset(row, blk, blocks, blk_mn, chunk), stored, lo, hi);
+            *pdst = make_uint2(lo, hi);
+            *sdst = (uint8_t)stored;
         }
     }
 }
@@ -206,86 +370,96 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
 // Gated RMSNorm + NVFP4 quantiser for 128-wide heads (kernels/quantise.cu:57-121).
 // Eight lanes own one head row (8 chunks of 16), a warp handles 4 head rows per step.
 // Reference association: lane l of a warp holds quad l; tree 16,8,4,2,1 over l. Here lane m (of 8)
-// holds quads 4m + k, so the tree is: shuffles over m bits 2,1,0, then in-lane k^2, k^1.
+// holds quads 4m + k: reduce-scatter over m bits 2,1 (keeping k bit 1, then k bit 0), butterfly over
+// m bit 0, then over k bit 1 (now lane bit 2) and k bit 0 (lane bit 1). 6 shuffles.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kCtaThreads)
+__device__ __forceinline__ float head_tree_32(const float* quad, int lane) {
+    const bool m2 = lane & 4, m1 = lane & 2;
+    float s[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {   // level m bit 2: keep k bit 1 == m2
+        const float send = m2 ? quad[i] : quad[2 + i];
+        const float keep = m2 ? quad[2 + i] : quad[i];
+        s[i] = __fadd_rn(keep, __shfl_xor_sync(kFullMask, send, 4));
+    }
+    // level m bit 1: keep k bit 0 == m1
+    float u = __fadd_rn(m1 ? s[1] : s[0], __shfl_xor_sync(kFullMask, m1 ? s[0] : s[1], 2));
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 1));   // level m bit 0
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 4));   // k ^ 2
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 2));   // k ^ 1
+    return u;
+}
+
+__global__ void __launch_bounds__(kCtaThreads, 3)
 gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
                             const float* __restrict__ weight, uint8_t* __restrict__ packed,
                             uint8_t* __restrict__ scales, int rows_live, int rows_total, float eps,
-                            float global_scale, int blk_mn, int chunk, int vh) {
+                            float global_scale, int blk_mn, int chunk, int vh, FastDiv vh_div, FastDiv atom_div) {
     constexpr int COLS = 128;
     __shared__ float s_inv[kInvScaleTableSize];
     const int lane = threadIdx.x & 31;
     const int m = lane & 7;
-    const int blocks = vh * (COLS / 16);
+    const int k1_count = (vh * (COLS / 16)) >> 2;
 
     // Head row handled by this lane group in step s: (global group index) + s * (groups in grid).
-    const size_t groups_in_grid = (size_t)gridDim.x * (kCtaThreads / 8);
-    size_t hrow = (size_t)blockIdx.x * (kCtaThreads / 8) + (threadIdx.x >> 3);
+    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 8);
+    uint32_t hrow = blockIdx.x * (kCtaThreads / 8) + (threadIdx.x >> 3);
 
     U8x32 dx, dg;
-    if (hrow < (size_t)rows_live) {
-        dx = ldg_stream_v8(x + hrow * COLS + m * 16);
-        dg = ldg_stream_v8(gate + hrow * COLS + m * 16);
+    if (hrow < (uint32_t)rows_live) {
+        dx = ldg_stream_v8(x + (size_t)hrow * COLS + m * 16);
+        dg = ldg_stream_v8(gate + (size_t)hrow * COLS + m * 16);
     }
-    float w[16];
+    f32x2 w[8];   // plain weight in the quad-pair layout
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const float4 t = *reinterpret_cast<const float4*>(weight + m * 16 + 4 * q);
-        w[4 * q] = t.x;
-        w[4 * q + 1] = t.y;
-        w[4 * q + 2] = t.z;
-        w[4 * q + 3] = t.w;
+        w[2 * q] = f2_pack(t.x, t.z);
+        w[2 * q + 1] = f2_pack(t.y, t.w);
     }
     fill_inv_scale_table(s_inv, global_scale);
     __syncthreads();
 
     bool loaded = true;
     // Every lane of a warp runs the same number of steps (the shuffles need the full warp).
-    const size_t warp_first = hrow - (size_t)((lane >> 3));
-    for (size_t base = warp_first; base < (size_t)rows_total; base += groups_in_grid, hrow += groups_in_grid) {
-        const bool in_range = hrow < (size_t)rows_total;
-        const bool live = hrow < (size_t)rows_live;
+    for (uint32_t base = hrow - (uint32_t)(lane >> 3); base < (uint32_t)rows_total; base += groups_in_grid, hrow += groups_in_grid) {
+        const bool in_range = hrow < (uint32_t)rows_total;
+        const bool live = hrow < (uint32_t)rows_live;
         if (!loaded && live) {
-            dx = ldg_stream_v8(x + hrow * COLS + m * 16);
-            dg = ldg_stream_v8(gate + hrow * COLS + m * 16);
+            dx = ldg_stream_v8(x + (size_t)hrow * COLS + m * 16);
+            dg = ldg_stream_v8(gate + (size_t)hrow * COLS + m * 16);
         }
         loaded = false;
-        float v[16];
-        float p[4] = {0.f, 0.f, 0.f, 0.f};
+        f32x2 v[8];
+        float quad[4] = {0.f, 0.f, 0.f, 0.f};
         if (live) {
-            unpack16(dx, v);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                p[k] = __fadd_rn(0.0f, quad_sq(make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3])));
-            }
+            unpack16_quadpairs(dx, v);
+            quad_squares(v, quad);
         }
-#pragma unroll
-        for (int off = 4; off > 0; off >>= 1) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                p[k] = __fadd_rn(p[k], __shfl_xor_sync(kFullMask, p[k], off));
-            }
-        }
+        const float total = head_tree_32(quad, lane);
         if (!in_range) {
             continue;
         }
-        const int token = (int)(hrow / vh);
-        const int head = (int)(hrow - (size_t)token * vh);
+        const uint32_t token = fast_div(hrow, vh_div);
+        const uint32_t block = (hrow - token * (uint32_t)vh) * (COLS / 16) + m;
+        const uint32_t m_rest = fast_div(token, atom_div);
+        const uint32_t m_atom = token - m_rest * (uint32_t)blk_mn;
         uint32_t stored = 0, lo = 0, hi = 0;
         if (live) {
-            const float total = __fadd_rn(__fadd_rn(p[0], p[2]), __fadd_rn(p[1], p[3]));
-            const float inv = inv_rms(total, COLS, eps);
-            float g[16];
-            unpack16(dg, g);
+            const f32x2 inv2 = f2_splat(inv_rms(total, COLS, eps));
+            f32x2 gv[8];
+            unpack16_quadpairs(dg, gv);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                v[i] = v[i] * inv * w[i] * silu_fast_div(g[i]);
+            for (int i = 0; i < 8; ++i) {
+                float g0, g1;
+                f2_unpack(gv[i], g0, g1);
+                const f32x2 s = f2_pack(silu_fast_div(g0), silu_fast_div(g1));
+                v[i] = f2_mul(f2_mul(f2_mul(v[i], inv2), w[i]), s);   // ((x * inv) * w) * silu(g)
             }
-            quantise16(v, global_scale, s_inv, stored, lo, hi);
+            quantise16_qp<false>(v, global_scale, s_inv, stored, lo, hi);
         }
-        store_block(packed, scales, hrow * (COLS / 2) + (size_t)m * 8,
-                    scale_offset(token, head * (COLS / 16) + m, blocks, blk_mn, chunk), stored, lo, hi);
+        *reinterpret_cast<uint2*>(packed + (size_t)hrow * (COLS / 2) + m * 8) = make_uint2(lo, hi);
+        scales[((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3)] = (uint8_t)stored;
     }
 }
 
@@ -298,39 +472,35 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kCtaThreads)
 rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, const float* __restrict__ cos_t,
-                const float* __restrict__ sin_t, int rows, int heads, int head_dim, int rotary_dim,
+                const float* __restrict__ sin_t, uint32_t total_items, int heads, int head_dim, int rotary_dim,
                 const int* __restrict__ seq_start, const int* __restrict__ pos_base,
-                const int* __restrict__ pos_map) {
-    const int rot_items = rotary_dim >> 5;
-    const int items = head_dim >> 5;
-    const size_t total = (size_t)rows * heads * items;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        const size_t head_row = idx / items;
-        const int item = (int)(idx - head_row * items);
-        const uint16_t* xr = x + head_row * head_dim;
-        uint16_t* orow = out + head_row * head_dim;
+                const int* __restrict__ pos_map, FastDiv items_div, FastDiv heads_div) {
+    const uint32_t rot_items = rotary_dim >> 5;
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_items; idx += stride) {
+        const uint32_t head_row = fast_div(idx, items_div);
+        const uint32_t item = idx - head_row * items_div.d;
+        const uint16_t* xr = x + (size_t)head_row * head_dim;
+        uint16_t* orow = out + (size_t)head_row * head_dim;
         if (item < rot_items) {
-            const int row = (int)(head_row / heads);
+            const int row = (int)fast_div(head_row, heads_div);
             const int pos = rope_position(row, seq_start, pos_base, pos_map);
             const int half = rotary_dim >> 1;
             const U8x32 dlo = ldg_stream_v8(xr + item * 16);
             const U8x32 dhi = ldg_stream_v8(xr + half + item * 16);
             const float* cp = cos_t + (size_t)pos * rotary_dim + item * 16;
             const float* sp = sin_t + (size_t)pos * rotary_dim + item * 16;
-            float lo[16], hi[16];
-            unpack16(dlo, lo);
-            unpack16(dhi, hi);
             U8x32 olo, ohi;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float4 c = __ldg(reinterpret_cast<const float4*>(cp) + q);
                 const float4 s = __ldg(reinterpret_cast<const float4*>(sp) + q);
+                const uint32_t l0 = dlo.w[2 * q], l1 = dlo.w[2 * q + 1], h0 = dhi.w[2 * q], h1 = dhi.w[2 * q + 1];
                 float a0, b0, a1, b1, a2, b2, a3, b3;
-                rope_pair(lo[4 * q], hi[4 * q], c.x, s.x, a0, b0);
-                rope_pair(lo[4 * q + 1], hi[4 * q + 1], c.y, s.y, a1, b1);
-                rope_pair(lo[4 * q + 2], hi[4 * q + 2], c.z, s.z, a2, b2);
-                rope_pair(lo[4 * q + 3], hi[4 * q + 3], c.w, s.w, a3, b3);
+                rope_pair(bf16_lo(l0), bf16_lo(h0), c.x, s.x, a0, b0);
+                rope_pair(bf16_hi(l0), bf16_hi(h0), c.y, s.y, a1, b1);
+                rope_pair(bf16_lo(l1), bf16_lo(h1), c.z, s.z, a2, b2);
+                rope_pair(bf16_hi(l1), bf16_hi(h1), c.w, s.w, a3, b3);
                 olo.w[2 * q] = pack_bf16x2(a0, a1);
                 olo.w[2 * q + 1] = pack_bf16x2(a2, a3);
                 ohi.w[2 * q] = pack_bf16x2(b0, b1);
@@ -339,7 +509,7 @@ rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, cons
             stg_v8(orow + item * 16, olo);
             stg_v8(orow + half + item * 16, ohi);
         } else {
-            const int c0 = rotary_dim + (item - rot_items) * 32;
+            const int c0 = rotary_dim + (int)(item - rot_items) * 32;
             const U8x32 a = ldg_stream_v8(xr + c0);
             const U8x32 b = ldg_stream_v8(xr + c0 + 16);
             stg_v8(orow + c0, a);

@@ -14,6 +14,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#include "f32x2.cuh"
+
 namespace clef {
 
 // --------------------------------------------------------------------------------------------
@@ -193,6 +195,60 @@ __device__ __forceinline__ void quantise16(const float* v, float global_scale, c
     stored_out = stored;
     lo_out = e2m1x8_fast(p);
     hi_out = e2m1x8_fast(p + 8);
+}
+
+// amax / 6 without the IEEE-division sequence: q0 = x * RN(1/6), one exact-remainder correction.
+// Checked against div.rn.f32 for every non-negative finite f32: equal for x = 0 and for every
+// x >= 2^-100; smaller non-zero x go to the literal path.
+constexpr float kDivSixExactFrom = 7.888609052e-31f;   // 2^-100
+__device__ __forceinline__ float div_six_fast(float x) {
+    constexpr float kSixth = 0.16666667163372040f;
+    const float q0 = __fmul_rn(x, kSixth);
+    const float rem = __fmaf_rn(-6.0f, q0, x);
+    return __fmaf_rn(rem, kSixth, q0);
+}
+
+// Same block quantiser on 8 packed pairs (f32x2.cuh): 3-input NaN-propagating max, the short
+// division by six, packed multiply and nudge. Falls back to quantise16_rare exactly when the
+// scalar version would, and additionally for 0 < amax < 2^-100.
+__device__ __forceinline__ void quantise16_x2(const f32x2* v, float global_scale, const float* inv_table,
+                                              uint32_t& stored_out, uint32_t& lo_out, uint32_t& hi_out) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        f2_unpack(v[i], a[2 * i], a[2 * i + 1]);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        amax = max3_abs_nan(amax, a[2 * i], a[2 * i + 1]);
+    }
+    const float sv = __fmul_rn(div_six_fast(amax), global_scale);
+    const uint32_t stored = e4m3_encode_finite(sv);
+    const float inv = inv_table[stored];
+    const float pmax = __fmul_rn(amax, inv);
+    const bool tiny = (amax < kDivSixExactFrom) && (amax > 0.0f);
+    if (!(fabsf(sv) <= 3.0e38f) || !(pmax < kE2m1FastLimit) || tiny) {
+        quantise16_rare(a, global_scale, stored_out, lo_out, hi_out);
+        return;
+    }
+    constexpr float kNudge = -4.33488326e-08f;   // see e2m1x2_fast
+    const f32x2 inv2 = f2_splat(inv);
+    const f32x2 nudge2 = f2_splat(kNudge);
+    uint32_t bytes[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const f32x2 p = f2_mul(v[i], inv2);
+        const f32x2 q = f2_fma(p, nudge2, p);
+        float first, second;
+        f2_unpack(q, first, second);
+        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
+            : "=r"(bytes[i])
+            : "f"(second), "f"(first));
+    }
+    stored_out = stored;
+    lo_out = bytes[0] | (bytes[1] << 8) | (bytes[2] << 16) | (bytes[3] << 24);
+    hi_out = bytes[4] | (bytes[5] << 8) | (bytes[6] << 16) | (bytes[7] << 24);
 }
 
 // --------------------------------------------------------------------------------------------
