@@ -384,7 +384,7 @@ int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, cons
     if (dtype == CLEF_BF16 && use_hot() && cols == 128 && aligned(x, 32) && aligned(gate, 32)) {
         static std::atomic<int> occ{0};
         const int per_sm = ctas_per_sm(gated_norm_quant_hot_kernel, 0, occ);
-        const size_t groups = ((size_t)rows + 31) / 32;   // 32 head rows per CTA step
+        const size_t groups = ((size_t)rows + 63) / 64;   // 64 head rows per CTA step
         gated_norm_quant_hot_kernel<<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
             (const uint16_t*)x, (const uint16_t*)gate, weight, packed, scales, rows_live, rows, eps, global_scale,
             blk_mn, chunk, vh, make_fast_div((uint32_t)vh), make_fast_div((uint32_t)blk_mn));

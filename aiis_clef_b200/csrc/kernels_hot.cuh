@@ -60,64 +60,70 @@ __device__ __forceinline__ void quad_squares(const f32x2* v, float* quad) {
     }
 }
 
-// Quad-pair layout -> natural order (rare path only).
-__device__ __forceinline__ void quadpairs_to_natural(const f32x2* v, float* a, bool negate) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        float x, z, y, w;
-        f2_unpack(v[2 * q], x, z);
-        f2_unpack(v[2 * q + 1], y, w);
-        a[4 * q] = negate ? -x : x;
-        a[4 * q + 1] = negate ? -y : y;
-        a[4 * q + 2] = negate ? -z : z;
-        a[4 * q + 3] = negate ? -w : w;
-    }
+// Eight scaled values -> 32 packed bits (first value in the lowest nibble) with the hardware
+// FP4 converter; see e2m1x2_fast in nvfp4_codec.cuh for why the inputs are nudged first.
+__device__ __forceinline__ uint32_t e2m1_pack8(float e0, float e1, float e2, float e3, float e4, float e5, float e6,
+                                               float e7) {
+    uint32_t r;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+        : "=r"(r)
+        : "f"(e0), "f"(e1), "f"(e2), "f"(e3), "f"(e4), "f"(e5), "f"(e6), "f"(e7));
+    return r;
 }
 
-// Block quantiser on the quad-pair layout. NEG: the pairs hold the NEGATED values (the SwiGLU fast
-// path produces -v); magnitudes are unaffected and the sign is restored by scaling with -inv_scale.
+// Block quantiser on the quad-pair layout, fast path only. Returns false, writing nothing, when the
+// block needs the literal path (a NaN or infinity, a scale argument that overflows, a scaled value of
+// 2^24 or more, or 0 < amax < 2^-100 where the short division by six is not exact); the caller then
+// runs its cold routine, which recomputes the block from global memory. Keeping the literal path out
+// of this function keeps address-taken arrays and call set-up out of the hot loop.
+// NEG: the pairs hold the NEGATED values (the SwiGLU fast path produces -v); magnitudes are unaffected
+// and the sign is restored by scaling with -inv_scale.
 template <bool NEG>
-__device__ __forceinline__ void quantise16_qp(const f32x2* v, float global_scale, const float* inv_table,
+__device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale, const float* inv_table,
                                               uint32_t& stored_out, uint32_t& lo_out, uint32_t& hi_out) {
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        float a, b;
-        f2_unpack(v[i], a, b);
-        amax = max3_abs_nan(amax, a, b);
+        amax = max3_abs_nan(amax, v[i].x, v[i].y);
     }
     const float sv = __fmul_rn(div_six_fast(amax), global_scale);
     const uint32_t stored = e4m3_encode_finite(sv);
     const float inv = inv_table[stored];
     const float pmax = __fmul_rn(amax, inv);
-    const bool tiny = (amax < kDivSixExactFrom) && (amax > 0.0f);
+    // 0 < amax < 2^-100 as one unsigned compare on the bit pattern (+0 wraps to the top)
+    const bool tiny = (__float_as_uint(amax) - 1u) < (__float_as_uint(kDivSixExactFrom) - 1u);
     if (!(fabsf(sv) <= 3.0e38f) || !(pmax < kE2m1FastLimit) || tiny) {
-        float a[16];
-        quadpairs_to_natural(v, a, NEG);
-        quantise16_rare(a, global_scale, stored_out, lo_out, hi_out);
-        return;
+        return false;
     }
     constexpr float kNudge = -4.33488326e-08f;   // see e2m1x2_fast
     const f32x2 inv2 = f2_splat(NEG ? -inv : inv);
     const f32x2 nudge2 = f2_splat(kNudge);
-    uint32_t bytes[8];
+    f32x2 p[8];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const f32x2 pa = f2_mul(v[2 * q], inv2);
-        const f32x2 pb = f2_mul(v[2 * q + 1], inv2);
-        float x, z, y, w;
-        f2_unpack(f2_fma(pa, nudge2, pa), x, z);
-        f2_unpack(f2_fma(pb, nudge2, pb), y, w);
-        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
-            : "=r"(bytes[2 * q])
-            : "f"(y), "f"(x));
-        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
-            : "=r"(bytes[2 * q + 1])
-            : "f"(w), "f"(z));
+    for (int i = 0; i < 8; ++i) {
+        const f32x2 t = f2_mul(v[i], inv2);
+        p[i] = f2_fma(t, nudge2, t);
     }
+    // quad q: p[2q] = (x, z), p[2q+1] = (y, w); element order x, y, z, w
     stored_out = stored;
-    lo_out = bytes[0] | (bytes[1] << 8) | (bytes[2] << 16) | (bytes[3] << 24);
-    hi_out = bytes[4] | (bytes[5] << 8) | (bytes[6] << 16) | (bytes[7] << 24);
+    lo_out = e2m1_pack8(p[0].x, p[1].x, p[0].y, p[1].y, p[2].x, p[3].x, p[2].y, p[3].y);
+    hi_out = e2m1_pack8(p[4].x, p[5].x, p[4].y, p[5].y, p[6].x, p[7].x, p[6].y, p[7].y);
+    return true;
+}
+
+// Cold path shared by the kernels: the caller has the block's 16 f32 values recomputed in natural
+// order; quantise them literally and store codes and scale.
+__device__ __noinline__ void quantise16_cold_store(const float* a, float global_scale, uint2* packed_dst,
+                                                   uint8_t* scale_dst) {
+    uint32_t stored, lo, hi;
+    quantise16_rare(a, global_scale, stored, lo, hi);
+    *packed_dst = make_uint2(lo, hi);
+    *scale_dst = (uint8_t)stored;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -159,27 +165,46 @@ __device__ __forceinline__ float row_tree_256(const float (&p)[2][4], int lane) 
     return u;
 }
 
+// 1 / sqrt(total / COLS + eps) for a power-of-two COLS: dividing by 2^k is the same rounding as
+// multiplying by 2^-k, and rcp.rn is the correctly rounded 1/x that div.rn(1, x) also returns, so this
+// equals the reference expression bit for bit at a fraction of the instructions.
+template <int COLS>
+__device__ __forceinline__ float inv_rms_pow2(float total, float eps) {
+    static_assert((COLS & (COLS - 1)) == 0, "COLS must be a power of two");
+    return __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(total, 1.0f / (float)COLS), eps)));
+}
+
+// Cold path of one RMSNorm block: recompute from global memory in natural order, literal quantiser.
+__device__ __noinline__ void rms_block_cold(const uint16_t* xblk, const float* wblk, float inv, float global_scale,
+                                            uint2* packed_dst, uint8_t* scale_dst) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = __uint_as_float((uint32_t)xblk[i] << 16) * inv * (1.0f + wblk[i]);
+    }
+    quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
+}
+
 #ifndef CLEF_RMS_MIN_CTAS
-#define CLEF_RMS_MIN_CTAS 3
+#define CLEF_RMS_MIN_CTAS 2
 #endif
 template <int NB>
-__global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? CLEF_RMS_MIN_CTAS : 2))
+__global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? CLEF_RMS_MIN_CTAS : 1))
 rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight,
                           uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows, int rows_total,
                           float eps, float global_scale, int blk_mn, int chunk, FastDiv atom_div) {
     constexpr int COLS = NB * 512;
     constexpr int BLOCKS = COLS / 16;
     __shared__ float s_inv[kInvScaleTableSize];
-    // (1 + w) in the quad-pair layout, transposed so lane L reads s_w[(4 j + q) * 32 + L] = the pairs
-    // (1+w_x, 1+w_z), (1+w_y, 1+w_w) of quad q of chunk L + 32 j.
+    // (1 + w) in the quad-pair layout, transposed so lane L reads s_w[(4 j + q) * 32 + L] =
+    // (1+w_x, 1+w_z, 1+w_y, 1+w_w) of quad q of chunk L + 32 j.
     extern __shared__ float4 s_w[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
 
     int row = blockIdx.x * 8 + warp;
     U8x32 d[NB];
-    bool loaded = row < rows;
-    if (loaded) {
+    if (row < rows) {
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
             d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
@@ -207,14 +232,8 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
             }
             continue;
         }
-        if (!loaded) {
-#pragma unroll
-            for (int j = 0; j < NB; ++j) {
-                d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
-            }
-        }
-        loaded = false;
-        // partial sums P[j & 1][k]: in-lane over j (stride 2, ascending), as the reference thread does
+        // Unpack once; partial sums P[j & 1][k] in-lane over j (stride 2, ascending), as the reference thread does.
+        f32x2 v[NB][8];
         float p[2][4];
 #pragma unroll
         for (int j0 = 0; j0 < 2; ++j0) {
@@ -223,32 +242,43 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
         }
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            f32x2 v[8];
             float quad[4];
-            unpack16_quadpairs(d[j], v);
-            quad_squares(v, quad);
+            unpack16_quadpairs(d[j], v[j]);
+            quad_squares(v[j], quad);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 p[j & 1][k] = __fadd_rn(p[j & 1][k], quad[k]);
             }
         }
-        const float inv = inv_rms(row_tree_256(p, lane), COLS, eps);
+        // The raw registers are free now: fetch this warp's next row while the current one is processed.
+        const int next = row + gridDim.x * 8;
+        if (next < rows) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                d[j] = ldg_stream_v8(x + (size_t)next * COLS + (size_t)(lane + 32 * j) * 16);
+            }
+        }
+        const float inv = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
+                                                   : inv_rms(row_tree_256(p, lane), COLS, eps);
         const f32x2 inv2 = f2_splat(inv);
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            f32x2 v[8];
-            unpack16_quadpairs(d[j], v);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float4 w = s_w[(4 * j + q) * 32 + lane];
-                v[2 * q] = f2_mul(f2_mul(v[2 * q], inv2), make_float2(w.x, w.y));
-                v[2 * q + 1] = f2_mul(f2_mul(v[2 * q + 1], inv2), make_float2(w.z, w.w));
+                v[j][2 * q] = f2_mul(f2_mul(v[j][2 * q], inv2), make_float2(w.x, w.y));
+                v[j][2 * q + 1] = f2_mul(f2_mul(v[j][2 * q + 1], inv2), make_float2(w.z, w.w));
             }
-            uint32_t stored, lo, hi;
-            quantise16_qp<false>(v, global_scale, s_inv, stored, lo, hi);
             const int b = lane + 32 * j;
-            *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(lo, hi);
-            srow[(size_t)(b >> 2) * chunk + (b & 3)] = (uint8_t)stored;
+            uint2* pdst = reinterpret_cast<uint2*>(prow + b * 8);
+            uint8_t* sdst = srow + (size_t)(b >> 2) * chunk + (b & 3);
+            uint32_t stored, lo, hi;
+            if (quantise16_qp<false>(v[j], global_scale, s_inv, stored, lo, hi)) {
+                *pdst = make_uint2(lo, hi);
+                *sdst = (uint8_t)stored;
+            } else {
+                rms_block_cold(x + (size_t)row * COLS + b * 16, weight + b * 16, inv, global_scale, pdst, sdst);
+            }
         }
     }
 }
@@ -259,27 +289,62 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
 // elements [512 u, 512 u + 512) of the dense [rows, cols] matrices, so only the scale address needs
 // the row. UNITS units are in flight per warp.
 //
-// silu(g) = g / (1 + __expf(-g)) with the IEEE division replaced, for bf16 g with |g| <= 44, by
-//   r = rcp.approx(-d), q0 = g * r, rem = fma(d, q0, g), q = fma(rem, r, q0)   (q = -g/d)
-// which equals div.rn.f32(g, d) negated for every such g (all 65536 bf16 patterns are compared on
-// the device by the tests; -0.0 gives +0.0, which the quantiser cannot tell apart). Blocks holding a
-// larger |g|, an infinity or a NaN take the literal expression.
+// silu(g) = g / (1 + __expf(-g)). For bf16 g with |g| <= 44 the block takes a short form:
+//   e = ex2.approx(g * -log2(e))     the intrinsic's range fix-ups cannot trigger for |g| <= 44
+//   d = 1 + e,  r = rcp.approx(d),  q0 = g * r,  rem = fma(-d, q0, g),  q = fma(rem, r, q0)
+// and q equals div.rn.f32(g, d) for every such g (all 65536 bf16 patterns are compared on the device
+// by the tests; -0.0 gives +0.0, which the quantiser cannot tell apart). Blocks holding a larger |g|,
+// an infinity or a NaN take the literal expression.
 // ---------------------------------------------------------------------------------------------
 constexpr float kSiluFastMaxAbs = 44.0f;
+constexpr float kNegLog2e = -1.4426950408889634f;
 
-// (g0, g1) -> (-silu(g0), -silu(g1)), fast form; see above for the domain.
-__device__ __forceinline__ f32x2 neg_silu_fast_x2(f32x2 g2) {
-    float g0, g1;
-    f2_unpack(g2, g0, g1);
-    const f32x2 d2 = f2_add(f2_splat(1.0f), f2_pack(__expf(-g0), __expf(-g1)));
-    float d0, d1, r0, r1;
-    f2_unpack(d2, d0, d1);
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(-d0));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(-d1));
-    const f32x2 r2 = f2_pack(r0, r1);
-    const f32x2 q0 = f2_mul(g2, r2);            // -(g * rcp(d))
-    const f32x2 rem = f2_fma(d2, q0, g2);       // g - d * (g * rcp(d)), exact
-    return f2_fma(rem, r2, q0);                 // -(q0' + rem * rcp(d))
+__device__ __forceinline__ float ex2_approx(float t) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+    return r;
+}
+__device__ __forceinline__ float rcp_approx(float d) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    return r;
+}
+
+// (g0, g1) -> (silu(g0), silu(g1)) with the IEEE quotient, short form; domain above.
+__device__ __forceinline__ f32x2 silu_ieee_fast_x2(f32x2 g2) {
+    const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));
+    const f32x2 d2 = f2_add(f2_splat(1.0f), make_float2(ex2_approx(t2.x), ex2_approx(t2.y)));
+    const f32x2 r2 = make_float2(rcp_approx(d2.x), rcp_approx(d2.y));
+    const f32x2 q0 = f2_mul(g2, r2);
+    const f32x2 rem = f2_fma(make_float2(-d2.x, -d2.y), q0, g2);   // exact remainder
+    return f2_fma(rem, r2, q0);
+}
+
+// (g0, g1) -> __fdividef(g, 1 + __expf(-g)) per lane, short form for |g| <= 44: g * rcp.approx(d).
+__device__ __forceinline__ f32x2 silu_approx_fast_x2(f32x2 g2) {
+    const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));
+    const f32x2 d2 = f2_add(f2_splat(1.0f), make_float2(ex2_approx(t2.x), ex2_approx(t2.y)));
+    return f2_mul(g2, make_float2(rcp_approx(d2.x), rcp_approx(d2.y)));
+}
+
+// max |g| over a block in the quad-pair layout, NaN if any value is NaN.
+__device__ __forceinline__ float block_abs_max(const f32x2* g) {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        m = max3_abs_nan(m, g[i].x, g[i].y);
+    }
+    return m;
+}
+
+__device__ __noinline__ void swiglu_block_cold(const uint16_t* gblk, const uint16_t* ublk, float global_scale,
+                                               uint2* packed_dst, uint8_t* scale_dst) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = silu_ieee_div(__uint_as_float((uint32_t)gblk[i] << 16)) * __uint_as_float((uint32_t)ublk[i] << 16);
+    }
+    quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
 }
 
 template <int UNITS>
@@ -306,19 +371,7 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
     fill_inv_scale_table(s_inv, global_scale);
     __syncthreads();
 
-    bool loaded = true;
     for (; unit0 < total_units; unit0 += UNITS * warps) {
-        if (!loaded) {
-#pragma unroll
-            for (int k = 0; k < UNITS; ++k) {
-                const uint32_t unit = unit0 + k * warps;
-                if (unit < live_units) {
-                    g[k] = ldg_stream_v8(gate + (size_t)unit * 512 + lane * 16);
-                    u[k] = ldg_stream_v8(up + (size_t)unit * 512 + lane * 16);
-                }
-            }
-        }
-        loaded = false;
 #pragma unroll
         for (int k = 0; k < UNITS; ++k) {
             const uint32_t unit = unit0 + k * warps;
@@ -331,135 +384,175 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
             const uint32_t m_atom = row - m_rest * (uint32_t)blk_mn;
             uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
             uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)unit * 256 + lane * 8);
-            uint32_t stored = 0, lo = 0, hi = 0;
-            if (unit < live_units) {
-                f32x2 gv[8], uv[8];
-                unpack16_quadpairs(g[k], gv);
-                unpack16_quadpairs(u[k], uv);
-                float gmax = 0.0f;
+            if (unit >= live_units) {
+                *pdst = make_uint2(0u, 0u);
+                *sdst = 0;
+                continue;
+            }
+            f32x2 gv[8], uv[8];
+            unpack16_quadpairs(g[k], gv);
+            unpack16_quadpairs(u[k], uv);
+            // The raw registers of this slot are free: fetch the unit this slot handles next.
+            const uint32_t next = unit + UNITS * warps;
+            if (next < live_units) {
+                g[k] = ldg_stream_v8(gate + (size_t)next * 512 + lane * 16);
+                u[k] = ldg_stream_v8(up + (size_t)next * 512 + lane * 16);
+            }
+            uint32_t stored, lo, hi;
+            bool done = false;
+            if (block_abs_max(gv) <= kSiluFastMaxAbs) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    float a, b;
-                    f2_unpack(gv[i], a, b);
-                    gmax = max3_abs_nan(gmax, a, b);
+                    gv[i] = f2_mul(silu_ieee_fast_x2(gv[i]), uv[i]);
                 }
-                if (gmax <= kSiluFastMaxAbs) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        gv[i] = f2_mul(neg_silu_fast_x2(gv[i]), uv[i]);   // -(silu(g) * u)
-                    }
-                    quantise16_qp<true>(gv, global_scale, s_inv, stored, lo, hi);
-                } else {
-                    float a[16], b[16];
-                    quadpairs_to_natural(gv, a, false);
-                    quadpairs_to_natural(uv, b, false);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        a[i] = silu_ieee_div(a[i]) * b[i];
-                    }
-                    quantise16(a, global_scale, s_inv, stored, lo, hi);
-                }
+                done = quantise16_qp<false>(gv, global_scale, s_inv, stored, lo, hi);
             }
-            *pdst = make_uint2(lo, hi);
-            *sdst = (uint8_t)stored;
+            if (done) {
+                *pdst = make_uint2(lo, hi);
+                *sdst = (uint8_t)stored;
+            } else {
+                swiglu_block_cold(gate + (size_t)unit * 512 + lane * 16, up + (size_t)unit * 512 + lane * 16, global_scale,
+                                  pdst, sdst);
+            }
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------------
 // Gated RMSNorm + NVFP4 quantiser for 128-wide heads (kernels/quantise.cu:57-121).
-// Eight lanes own one head row (8 chunks of 16), a warp handles 4 head rows per step.
-// Reference association: lane l of a warp holds quad l; tree 16,8,4,2,1 over l. Here lane m (of 8)
-// holds quads 4m + k: reduce-scatter over m bits 2,1 (keeping k bit 1, then k bit 0), butterfly over
-// m bit 0, then over k bit 1 (now lane bit 2) and k bit 0 (lane bit 1). 6 shuffles.
+// Four lanes own one head row: lane m holds chunks m and m + 4 (quads 4m + k and 16 + 4m + k), a warp
+// handles 8 head rows per step, and the next step's rows are fetched while the current ones are
+// processed. Reference association: lane l of a warp holds quad l; tree 16,8,4,2,1 over l. Here the
+// first level (l, l + 16) is in-lane; levels 8 and 4 (m bits 1, 0) are a reduce-scatter that keeps
+// k bit 1, then k bit 0; levels 2 and 1 (k bits) are butterflies over lane bits 1 and 0. 5 shuffles.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float head_tree_32(const float* quad, int lane) {
-    const bool m2 = lane & 4, m1 = lane & 2;
+__device__ __forceinline__ float head_tree_32(const float* quad_a, const float* quad_b, int lane) {
+    const bool m1 = lane & 2, m0 = lane & 1;
+    float p[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        p[k] = __fadd_rn(quad_a[k], quad_b[k]);            // reference lanes l, l + 16
+    }
     float s[2];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {   // level m bit 2: keep k bit 1 == m2
-        const float send = m2 ? quad[i] : quad[2 + i];
-        const float keep = m2 ? quad[2 + i] : quad[i];
-        s[i] = __fadd_rn(keep, __shfl_xor_sync(kFullMask, send, 4));
+    for (int i = 0; i < 2; ++i) {                          // l, l + 8: keep k bit 1 == m1
+        const float send = m1 ? p[i] : p[2 + i];
+        const float keep = m1 ? p[2 + i] : p[i];
+        s[i] = __fadd_rn(keep, __shfl_xor_sync(kFullMask, send, 2));
     }
-    // level m bit 1: keep k bit 0 == m1
-    float u = __fadd_rn(m1 ? s[1] : s[0], __shfl_xor_sync(kFullMask, m1 ? s[0] : s[1], 2));
-    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 1));   // level m bit 0
-    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 4));   // k ^ 2
-    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 2));   // k ^ 1
+    // l, l + 4: keep k bit 0 == m0
+    float u = __fadd_rn(m0 ? s[1] : s[0], __shfl_xor_sync(kFullMask, m0 ? s[0] : s[1], 1));
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 2));   // l, l + 2 (k bit 1 lives in lane bit 1 now)
+    u = __fadd_rn(u, __shfl_xor_sync(kFullMask, u, 1));   // l, l + 1
     return u;
 }
 
-__global__ void __launch_bounds__(kCtaThreads, 3)
+__device__ __noinline__ void gated_block_cold(const uint16_t* xblk, const uint16_t* gblk, const float* wblk, float inv,
+                                              float global_scale, uint2* packed_dst, uint8_t* scale_dst) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = __uint_as_float((uint32_t)xblk[i] << 16) * inv * wblk[i] *
+               silu_fast_div(__uint_as_float((uint32_t)gblk[i] << 16));
+    }
+    quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
+}
+
+__global__ void __launch_bounds__(kCtaThreads, 2)
 gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
                             const float* __restrict__ weight, uint8_t* __restrict__ packed,
                             uint8_t* __restrict__ scales, int rows_live, int rows_total, float eps,
                             float global_scale, int blk_mn, int chunk, int vh, FastDiv vh_div, FastDiv atom_div) {
     constexpr int COLS = 128;
     __shared__ float s_inv[kInvScaleTableSize];
+    // plain weight in the quad-pair layout: s_w[(h * 4 + q) * 4 + m] = (w_x, w_z, w_y, w_w) of quad q of chunk m + 4h
+    __shared__ float4 s_w[32];
     const int lane = threadIdx.x & 31;
-    const int m = lane & 7;
+    const int m = lane & 3;
     const int k1_count = (vh * (COLS / 16)) >> 2;
 
     // Head row handled by this lane group in step s: (global group index) + s * (groups in grid).
-    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 8);
-    uint32_t hrow = blockIdx.x * (kCtaThreads / 8) + (threadIdx.x >> 3);
+    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
+    uint32_t hrow = blockIdx.x * (kCtaThreads / 4) + (threadIdx.x >> 2);
 
-    U8x32 dx, dg;
+    U8x32 dx[2], dg[2];
     if (hrow < (uint32_t)rows_live) {
-        dx = ldg_stream_v8(x + (size_t)hrow * COLS + m * 16);
-        dg = ldg_stream_v8(gate + (size_t)hrow * COLS + m * 16);
-    }
-    f32x2 w[8];   // plain weight in the quad-pair layout
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float4 t = *reinterpret_cast<const float4*>(weight + m * 16 + 4 * q);
-        w[2 * q] = f2_pack(t.x, t.z);
-        w[2 * q + 1] = f2_pack(t.y, t.w);
+        for (int h = 0; h < 2; ++h) {
+            dx[h] = ldg_stream_v8(x + (size_t)hrow * COLS + (m + 4 * h) * 16);
+            dg[h] = ldg_stream_v8(gate + (size_t)hrow * COLS + (m + 4 * h) * 16);
+        }
+    }
+    if (threadIdx.x < 32) {
+        const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
+        const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
+        s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
     }
     fill_inv_scale_table(s_inv, global_scale);
     __syncthreads();
 
-    bool loaded = true;
     // Every lane of a warp runs the same number of steps (the shuffles need the full warp).
-    for (uint32_t base = hrow - (uint32_t)(lane >> 3); base < (uint32_t)rows_total; base += groups_in_grid, hrow += groups_in_grid) {
+    for (uint32_t base = hrow - (uint32_t)(lane >> 2); base < (uint32_t)rows_total; base += groups_in_grid, hrow += groups_in_grid) {
         const bool in_range = hrow < (uint32_t)rows_total;
         const bool live = hrow < (uint32_t)rows_live;
-        if (!loaded && live) {
-            dx = ldg_stream_v8(x + (size_t)hrow * COLS + m * 16);
-            dg = ldg_stream_v8(gate + (size_t)hrow * COLS + m * 16);
-        }
-        loaded = false;
-        f32x2 v[8];
-        float quad[4] = {0.f, 0.f, 0.f, 0.f};
+        f32x2 v[2][8], gv[2][8];
+        float quad[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         if (live) {
-            unpack16_quadpairs(dx, v);
-            quad_squares(v, quad);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                unpack16_quadpairs(dx[h], v[h]);
+                unpack16_quadpairs(dg[h], gv[h]);
+                quad_squares(v[h], quad[h]);
+            }
         }
-        const float total = head_tree_32(quad, lane);
+        const uint32_t next = hrow + groups_in_grid;
+        if (next < (uint32_t)rows_live) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                dx[h] = ldg_stream_v8(x + (size_t)next * COLS + (m + 4 * h) * 16);
+                dg[h] = ldg_stream_v8(gate + (size_t)next * COLS + (m + 4 * h) * 16);
+            }
+        }
+        const float total = head_tree_32(quad[0], quad[1], lane);
         if (!in_range) {
             continue;
         }
         const uint32_t token = fast_div(hrow, vh_div);
-        const uint32_t block = (hrow - token * (uint32_t)vh) * (COLS / 16) + m;
+        const uint32_t head_block = (hrow - token * (uint32_t)vh) * (COLS / 16);
         const uint32_t m_rest = fast_div(token, atom_div);
         const uint32_t m_atom = token - m_rest * (uint32_t)blk_mn;
-        uint32_t stored = 0, lo = 0, hi = 0;
-        if (live) {
-            const f32x2 inv2 = f2_splat(inv_rms(total, COLS, eps));
-            f32x2 gv[8];
-            unpack16_quadpairs(dg, gv);
+        const float inv = inv_rms_pow2<COLS>(total, eps);
+        const f32x2 inv2 = f2_splat(inv);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float g0, g1;
-                f2_unpack(gv[i], g0, g1);
-                const f32x2 s = f2_pack(silu_fast_div(g0), silu_fast_div(g1));
-                v[i] = f2_mul(f2_mul(f2_mul(v[i], inv2), w[i]), s);   // ((x * inv) * w) * silu(g)
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t block = head_block + m + 4 * h;
+            uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)hrow * (COLS / 2) + (m + 4 * h) * 8);
+            uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
+            if (!live) {
+                *pdst = make_uint2(0u, 0u);
+                *sdst = 0;
+                continue;
             }
-            quantise16_qp<false>(v, global_scale, s_inv, stored, lo, hi);
+            uint32_t stored, lo, hi;
+            bool done = false;
+            if (block_abs_max(gv[h]) <= kSiluFastMaxAbs) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 w = s_w[(h * 4 + q) * 4 + m];
+                    // ((x * inv) * w) * silu(g), left to right as the reference writes it
+                    v[h][2 * q] = f2_mul(f2_mul(f2_mul(v[h][2 * q], inv2), make_float2(w.x, w.y)), silu_approx_fast_x2(gv[h][2 * q]));
+                    v[h][2 * q + 1] = f2_mul(f2_mul(f2_mul(v[h][2 * q + 1], inv2), make_float2(w.z, w.w)), silu_approx_fast_x2(gv[h][2 * q + 1]));
+                }
+                done = quantise16_qp<false>(v[h], global_scale, s_inv, stored, lo, hi);
+            }
+            if (done) {
+                *pdst = make_uint2(lo, hi);
+                *sdst = (uint8_t)stored;
+            } else {
+                const size_t off = (size_t)hrow * COLS + (m + 4 * h) * 16;
+                gated_block_cold(x + off, gate + off, weight + (m + 4 * h) * 16, inv, global_scale, pdst, sdst);
+            }
         }
-        *reinterpret_cast<uint2*>(packed + (size_t)hrow * (COLS / 2) + m * 8) = make_uint2(lo, hi);
-        scales[((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3)] = (uint8_t)stored;
     }
 }
 

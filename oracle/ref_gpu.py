@@ -253,8 +253,23 @@ def probe_e4m3_decode(global_scale: float):
     return _read_results(buf, 2)
 
 
-def probe_blocks(values, global_scale: float):
-    """values: CUDA f32 tensor of n_blocks*16. Returns (results, want_scale, want_packed, got_scale, got_packed)."""
+def probe_silu_bf16():
+    buf = _result_buffer(2)
+    launch("ref_probe", "probe_silu_bf16", (256,), (256,), [buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 2)
+
+
+def probe_div_six():
+    buf = _result_buffer(1)
+    launch("ref_probe", "probe_div_six", (148 * 8,), (256,), [buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 1)
+
+
+def probe_blocks(values, global_scale: float, use_pairs: bool = False):
+    """values: CUDA f32 tensor of n_blocks*16. Returns (results, want_scale, want_packed, got_scale, got_packed).
+    use_pairs selects the tuned kernels' packed-pair quantiser (with its literal fallback)."""
     n = values.numel() // 16
     ws = torch.empty(n, dtype=torch.uint8, device="cuda")
     wp = torch.empty(n * 8, dtype=torch.uint8, device="cuda")
@@ -262,6 +277,6 @@ def probe_blocks(values, global_scale: float):
     gp = torch.empty_like(wp)
     buf = _result_buffer(2)
     launch("ref_probe", "probe_blocks", (min(148 * 8, (n + 255) // 256),), (256,),
-           [values, (n, ctypes.c_ulonglong), float(global_scale), ws, wp, gs, gp, buf])
+           [values, (n, ctypes.c_ulonglong), float(global_scale), ws, wp, gs, gp, buf, int(use_pairs)])
     torch.cuda.synchronize()
     return _read_results(buf, 2), ws, wp, gs, gp

@@ -12,6 +12,8 @@
 
 #include "nvfp4_quant.h"    // the reference's header (to_e2m1 / to_e4m3 / from_e4m3)
 #include "nvfp4_codec.cuh"  // this repo's codec (namespace clef)
+#include "kernels_generic.cuh"
+#include "kernels_hot.cuh"   // packed-pair quantiser and the short silu forms of the tuned kernels
 
 struct ProbeResult {
     unsigned long long checked;
@@ -113,7 +115,10 @@ extern "C" __global__ void probe_e4m3_decode(float global_scale, ProbeResult* re
 // result[0]: scale byte, result[1]: packed codes (counted per block). first_bad holds block indices.
 extern "C" __global__ void probe_blocks(const float* values, unsigned long long n_blocks, float global_scale,
                                         uint8_t* want_scale, uint8_t* want_packed, uint8_t* got_scale,
-                                        uint8_t* got_packed, ProbeResult* result) {
+                                        uint8_t* got_packed, ProbeResult* result, int use_pairs) {
+    __shared__ float inv_table[clef::kInvScaleTableSize];
+    clef::fill_inv_scale_table(inv_table, global_scale);
+    __syncthreads();
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
     for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += stride) {
         const float* src = values + b * 16;
@@ -136,7 +141,19 @@ extern "C" __global__ void probe_blocks(const float* values, unsigned long long 
             v[i] = src[i];
         }
         uint32_t got_stored, lo, hi;
-        clef::quantise16(v, global_scale, nullptr, got_stored, lo, hi);
+        if (use_pairs) {
+            // the tuned kernels' path: quad-pair layout, fast quantiser, literal routine when it declines
+            clef::f32x2 qp[8];
+            for (int q = 0; q < 4; ++q) {
+                qp[2 * q] = clef::f2_pack(v[4 * q], v[4 * q + 2]);
+                qp[2 * q + 1] = clef::f2_pack(v[4 * q + 1], v[4 * q + 3]);
+            }
+            if (!clef::quantise16_qp<false>(qp, global_scale, inv_table, got_stored, lo, hi)) {
+                clef::quantise16_rare(v, global_scale, got_stored, lo, hi);
+            }
+        } else {
+            clef::quantise16(v, global_scale, nullptr, got_stored, lo, hi);
+        }
         const unsigned long long got_bits = (unsigned long long)lo | ((unsigned long long)hi << 32);
         unsigned long long want_bits = 0;
         for (int pair = 0; pair < 8; ++pair) {
@@ -155,4 +172,56 @@ extern "C" __global__ void probe_blocks(const float* values, unsigned long long 
             report(&result[1], (uint32_t)b);
         }
     }
+}
+
+// The short silu forms of the tuned kernels against the reference expressions, for every bf16 pattern
+// inside their domain (|g| <= 44, NaN excluded). Zero results may differ in sign (the quantiser maps
+// both to code 0). result[0]: g / (1 + __expf(-g)); result[1]: __fdividef(g, 1 + __expf(-g)).
+extern "C" __global__ void probe_silu_bf16(ProbeResult* result) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 65536u) {
+        return;
+    }
+    const float g = __uint_as_float(i << 16);
+    if (!(fabsf(g) <= clef::kSiluFastMaxAbs)) {
+        return;
+    }
+    const float other = __uint_as_float(((i * 2654435761u) >> 16 & 0x3FFFu) << 16);   // a second in-domain value
+    const float want_ieee = g / (1.0f + __expf(-g));
+    const float want_fast = __fdividef(g, 1.0f + __expf(-g));
+    const clef::f32x2 a = clef::silu_ieee_fast_x2(clef::f2_pack(g, other));
+    const clef::f32x2 b = clef::silu_ieee_fast_x2(clef::f2_pack(other, g));
+    const clef::f32x2 c = clef::silu_approx_fast_x2(clef::f2_pack(g, other));
+    const clef::f32x2 d = clef::silu_approx_fast_x2(clef::f2_pack(other, g));
+    auto same = [](float x, float y) { return __float_as_uint(x) == __float_as_uint(y) || (x == 0.0f && y == 0.0f); };
+    atomicAdd(&result[0].checked, 1ull);
+    atomicAdd(&result[1].checked, 1ull);
+    if (!same(a.x, want_ieee) || !same(b.y, want_ieee)) {
+        report(&result[0], i);
+    }
+    if (!same(c.x, want_fast) || !same(d.y, want_fast)) {
+        report(&result[1], i);
+    }
+}
+
+// amax / 6.0f (kernels/quantise.cu:29) against the three-operation form, on the patterns the fast
+// quantiser uses it for: +0 and every finite x >= 2^-100.
+extern "C" __global__ void probe_div_six(ProbeResult* result) {
+    const unsigned long long first = __float_as_uint(clef::kDivSixExactFrom), last = 0x7F800000ull;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    unsigned long long checked = 0;
+    for (unsigned long long i = first + (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < last; i += stride) {
+        const float x = __uint_as_float((uint32_t)i);
+        ++checked;
+        if (__float_as_uint(clef::div_six_fast(x)) != __float_as_uint(x / 6.0f)) {
+            report(&result[0], (uint32_t)i);
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        ++checked;
+        if (__float_as_uint(clef::div_six_fast(0.0f)) != 0u) {
+            report(&result[0], 0u);
+        }
+    }
+    atomicAdd(&result[0].checked, checked);
 }

@@ -66,12 +66,13 @@ def _adversarial_blocks(rng):
     return out[: out.shape[0] // 4 * 4]
 
 
+@pytest.mark.parametrize("use_pairs", [False, True], ids=["scalar", "packed-pairs"])
 @pytest.mark.parametrize("global_scale", [1.0, 64.0, 215.0, 1.0 / 12.5, 2688.0, 1e-6, 1e6, 0.0, -3.0, 3e38])
-def test_block_quantiser_on_adversarial_blocks(global_scale):
+def test_block_quantiser_on_adversarial_blocks(global_scale, use_pairs):
     rng = np.random.default_rng(11)
     blocks = _adversarial_blocks(rng)
     vals = torch.from_numpy(blocks).cuda()
-    res, ws, wp, gs, gp = ref_gpu.probe_blocks(vals, global_scale)
+    res, ws, wp, gs, gp = ref_gpu.probe_blocks(vals, global_scale, use_pairs)
     assert res[0]["checked"] == blocks.shape[0]
     assert all(r["mismatches"] == 0 for r in res), f"global {global_scale}: " + _fmt(res)
     # the CPU oracle agrees with the reference header on the same blocks, non-finite ones included
@@ -83,9 +84,24 @@ def test_block_quantiser_on_adversarial_blocks(global_scale):
     assert np.array_equal(wp.cpu().numpy(), want_p[: rows * 32]), "CPU oracle codes differ from the reference header's"
 
 
-def test_block_quantiser_on_random_blocks_large():
+@pytest.mark.parametrize("use_pairs", [False, True], ids=["scalar", "packed-pairs"])
+def test_block_quantiser_on_random_blocks_large(use_pairs):
     rng = np.random.default_rng(12)
     x = rng.standard_normal((1 << 20, 16)).astype(np.float32)
     x[:, 3] *= 20.0
-    res, *_ = ref_gpu.probe_blocks(torch.from_numpy(x).cuda(), 448.0 * 6.0 / 100.0)
+    res, *_ = ref_gpu.probe_blocks(torch.from_numpy(x).cuda(), 448.0 * 6.0 / 100.0, use_pairs)
     assert all(r["mismatches"] == 0 for r in res), _fmt(res)
+
+
+def test_short_silu_forms_on_every_bf16_value():
+    """The tuned SwiGLU / gated-norm kernels replace g / (1 + __expf(-g)) and __fdividef(g, 1 + __expf(-g)) by
+    short sequences for |g| <= 44; both must equal the reference expressions for every bf16 g in that range."""
+    res = ref_gpu.probe_silu_bf16()
+    assert res[0]["checked"] == res[1]["checked"] and res[0]["checked"] > 30000
+    assert all(r["mismatches"] == 0 for r in res), _fmt(res)
+
+
+def test_short_division_by_six():
+    res = ref_gpu.probe_div_six()
+    assert res[0]["checked"] > 1_000_000_000
+    assert res[0]["mismatches"] == 0, _fmt(res)
