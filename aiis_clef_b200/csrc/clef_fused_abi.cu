@@ -10,6 +10,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "internal.hpp"
@@ -87,6 +88,32 @@ int ctas_per_sm(K kernel, size_t dyn_smem, std::atomic<int>& cache) {
     }
     cache.store(n, std::memory_order_relaxed);
     return n;
+}
+
+// Launch of a tuned kernel. With programmatic dependent launch (default; CLEF_PDL=0 turns it off) the
+// kernel may begin its argument-only prologue while the stream's previous kernel drains; the kernels
+// wait for that kernel before touching any activation or output (common.cuh, pdl_wait_prior_grids).
+bool pdl_enabled() {
+    static const int on = [] {
+        const char* v = getenv("CLEF_PDL");
+        return (v && v[0] == '0') ? 0 : 1;
+    }();
+    return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+void launch_hot(void (*kernel)(KArgs...), unsigned grid, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(clef::kCtaThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch
 }
 
 inline unsigned clamp_grid(size_t wanted, size_t cap) {
@@ -202,8 +229,8 @@ int clef_embed_gather(clef_stream_t stream, const void* table, const int32_t* id
     {                                                                                                            \
         static std::atomic<int> occ{0};                                                                          \
         const int per_sm = ctas_per_sm(embed_gather_hot_kernel<CH>, 0, occ);                                     \
-        embed_gather_hot_kernel<CH><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0,              \
-                                      as_stream(stream)>>>((const uint8_t*)table, ids, (uint8_t*)out, tokens);   \
+        launch_hot(embed_gather_hot_kernel<CH>, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, as_stream(stream), \
+                   (const uint8_t*)table, (const int*)ids, (uint8_t*)out, tokens);                                \
     }
         switch (row_bytes / 1024) {
             case 1: CLEF_EMBED_HOT(1) break;
@@ -290,13 +317,15 @@ int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const floa
         if (cols == 2048) {
             static std::atomic<int> occ{0};
             const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<4>, smem, occ);
-            rms_norm_quant_hot_kernel<4><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem, s>>>(
-                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk, atom_div);
+            launch_hot(rms_norm_quant_hot_kernel<4>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,
+                       (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk,
+                       atom_div);
         } else {
             static std::atomic<int> occ{0};
             const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<8>, smem, occ);
-            rms_norm_quant_hot_kernel<8><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem, s>>>(
-                (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk, atom_div);
+            launch_hot(rms_norm_quant_hot_kernel<8>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,
+                       (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk,
+                       atom_div);
         }
         return check_launch(what);
     }
@@ -385,9 +414,9 @@ int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, cons
         static std::atomic<int> occ{0};
         const int per_sm = ctas_per_sm(gated_norm_quant_hot_kernel, 0, occ);
         const size_t groups = ((size_t)rows + 63) / 64;   // 64 head rows per CTA step
-        gated_norm_quant_hot_kernel<<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
-            (const uint16_t*)x, (const uint16_t*)gate, weight, packed, scales, rows_live, rows, eps, global_scale,
-            blk_mn, chunk, vh, make_fast_div((uint32_t)vh), make_fast_div((uint32_t)blk_mn));
+        launch_hot(gated_norm_quant_hot_kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, s, (const uint16_t*)x,
+                   (const uint16_t*)gate, weight, packed, scales, rows_live, rows, eps, global_scale, blk_mn, chunk, vh,
+                   make_fast_div((uint32_t)vh), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {
@@ -494,9 +523,9 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
         const uint32_t segs = (uint32_t)(cols / 512);
         const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;
         const size_t ctas = ((size_t)total_units + kUnits * 8 - 1) / (kUnits * 8);
-        swiglu_quant_hot_kernel<kUnits><<<clamp_grid(ctas, (size_t)dev.sms * per_sm), kCtaThreads, 0, s>>>(
-            (const uint16_t*)gate, (const uint16_t*)up, packed, scales, live_units, total_units, cols, global_scale,
-            blk_mn, chunk, make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
+        launch_hot(swiglu_quant_hot_kernel<kUnits>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,
+                   (const uint16_t*)gate, (const uint16_t*)up, packed, scales, live_units, total_units, cols,
+                   global_scale, blk_mn, chunk, make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {
@@ -544,10 +573,10 @@ int clef_rope(clef_stream_t stream, void* out, const void* x, const float* cos_t
         aligned(x, 32) && aligned(out, 32)) {
         static std::atomic<int> occ{0};
         const int per_sm = ctas_per_sm(rope_hot_kernel, 0, occ);
-        rope_hot_kernel<<<clamp_grid((hot_items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), kCtaThreads,
-                          0, s>>>((uint16_t*)out, (const uint16_t*)x, cos_table, sin_table, (uint32_t)hot_items, heads,
-                                  head_dim, rotary_dim, seq_start, pos_base, pos_map,
-                                  make_fast_div((uint32_t)(head_dim / 32)), make_fast_div((uint32_t)heads));
+        launch_hot(rope_hot_kernel, clamp_grid((hot_items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0,
+                   s, (uint16_t*)out, (const uint16_t*)x, cos_table, sin_table, (uint32_t)hot_items, heads, head_dim,
+                   rotary_dim, (const int*)seq_start, (const int*)pos_base, (const int*)pos_map,
+                   make_fast_div((uint32_t)(head_dim / 32)), make_fast_div((uint32_t)heads));
         return check_launch(what);
     }
     const size_t items = (size_t)rows * heads * ((rotary_dim / 8) + (head_dim - rotary_dim) / 4);

@@ -74,6 +74,15 @@ __device__ __forceinline__ void stg_v2(void* p, uint2 v) {
     asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
+// Programmatic dependent launch (sm_90+). A kernel launched with the programmatic-serialisation
+// attribute may start while the previous kernel of the stream is still draining: it signals at once
+// that its own successor may be scheduled, does the work that depends on no earlier kernel (tables
+// built from launch arguments and from constant weights), and only then waits for every earlier grid
+// to have completed and flushed its writes. All reads of activations and all global writes come after
+// pdl_wait_prior_grids(). Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Load 4 consecutive activations (one "quad" = the reference's float4) as f32.
 template <typename T>
 __device__ __forceinline__ float4 load_quad(const typename T::storage* base, size_t quad_index);

@@ -202,6 +202,14 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
 
+    pdl_launch_dependents();
+    fill_inv_scale_table(s_inv, global_scale);
+    for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
+        const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
+        const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
+        s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
+    }
+    pdl_wait_prior_grids();
     int row = blockIdx.x * 8 + warp;
     U8x32 d[NB];
     if (row < rows) {
@@ -209,12 +217,6 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
         for (int j = 0; j < NB; ++j) {
             d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
         }
-    }
-    fill_inv_scale_table(s_inv, global_scale);
-    for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
-        const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
-        const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
-        s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
     }
     __syncthreads();
 
@@ -359,6 +361,9 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
     uint32_t unit0 = blockIdx.x * (kCtaThreads / 32) + (threadIdx.x >> 5);
     const int k1_count = cols >> 6;
 
+    pdl_launch_dependents();
+    fill_inv_scale_table(s_inv, global_scale);
+    pdl_wait_prior_grids();
     U8x32 g[UNITS], u[UNITS];
 #pragma unroll
     for (int k = 0; k < UNITS; ++k) {
@@ -368,7 +373,6 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
             u[k] = ldg_stream_v8(up + (size_t)unit * 512 + lane * 16);
         }
     }
-    fill_inv_scale_table(s_inv, global_scale);
     __syncthreads();
 
     for (; unit0 < total_units; unit0 += UNITS * warps) {
@@ -475,6 +479,14 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
     const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
     uint32_t hrow = blockIdx.x * (kCtaThreads / 4) + (threadIdx.x >> 2);
 
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
+        const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
+        s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
+    }
+    fill_inv_scale_table(s_inv, global_scale);
+    pdl_wait_prior_grids();
     U8x32 dx[2], dg[2];
     if (hrow < (uint32_t)rows_live) {
 #pragma unroll
@@ -483,12 +495,6 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
             dg[h] = ldg_stream_v8(gate + (size_t)hrow * COLS + (m + 4 * h) * 16);
         }
     }
-    if (threadIdx.x < 32) {
-        const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
-        const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
-        s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
-    }
-    fill_inv_scale_table(s_inv, global_scale);
     __syncthreads();
 
     // Every lane of a warp runs the same number of steps (the shuffles need the full warp).
@@ -568,6 +574,8 @@ rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, cons
                 const float* __restrict__ sin_t, uint32_t total_items, int heads, int head_dim, int rotary_dim,
                 const int* __restrict__ seq_start, const int* __restrict__ pos_base,
                 const int* __restrict__ pos_map, FastDiv items_div, FastDiv heads_div) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
     const uint32_t rot_items = rotary_dim >> 5;
     const uint32_t stride = gridDim.x * blockDim.x;
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_items; idx += stride) {
@@ -622,6 +630,8 @@ embed_gather_hot_kernel(const uint8_t* __restrict__ table, const int* __restrict
     constexpr size_t ROW_BYTES = (size_t)CH * 1024;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
     for (int t = blockIdx.x * 8 + warp; t < tokens; t += gridDim.x * 8) {
         const uint8_t* src = table + (size_t)__ldg(ids + t) * ROW_BYTES;
         uint8_t* dst = out + (size_t)t * ROW_BYTES;
