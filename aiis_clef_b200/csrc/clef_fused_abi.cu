@@ -284,6 +284,22 @@ int clef_rms_norm(clef_stream_t stream, const void* x, const float* weight, void
     if (rows == 0) return CLEF_OK;
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16 && use_hot() && (cols == 2048 || cols == 4096) && aligned(x, 32) && aligned(out, 32)) {
+        const size_t groups = ((size_t)rows + 7) / 8;
+        const size_t smem = (size_t)cols * sizeof(float);
+        if (cols == 2048) {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rms_norm_hot_kernel<4>, smem, occ);
+            launch_hot(rms_norm_hot_kernel<4>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, as_stream(stream),
+                       (const uint16_t*)x, weight, (uint16_t*)out, rows, eps);
+        } else {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rms_norm_hot_kernel<8>, smem, occ);
+            launch_hot(rms_norm_hot_kernel<8>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, as_stream(stream),
+                       (const uint16_t*)x, weight, (uint16_t*)out, rows, eps);
+        }
+        return check_launch("clef_rms_norm");
+    }
     if (dtype == CLEF_BF16) {
         launch_rms_norm_generic<Bf16, false>(as_stream(stream), dev, x, weight, out, nullptr, nullptr, rows, rows, cols,
                                              eps, 0.0f, 1, 4);
@@ -374,6 +390,15 @@ int clef_rms_norm_gated(clef_stream_t stream, const void* x, const void* gate, c
     if (rows == 0) return CLEF_OK;
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16 && use_hot() && cols == 128 && gate && weight && aligned(x, 32) && aligned(gate, 32) &&
+        aligned(out, 32)) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(gated_norm_hot_kernel, 0, occ);
+        const size_t groups = ((size_t)rows + 63) / 64;
+        launch_hot(gated_norm_hot_kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, as_stream(stream),
+                   (const uint16_t*)x, (const uint16_t*)gate, weight, (uint16_t*)out, rows, eps);
+        return check_launch(what);
+    }
     if (dtype == CLEF_BF16) {
         launch_gated_generic<Bf16, false>(as_stream(stream), dev, x, gate, weight, out, nullptr, nullptr, rows, rows,
                                           cols, eps, 0.0f, 1, 4, 1);
@@ -441,6 +466,21 @@ int clef_swiglu(clef_stream_t stream, const void* gate, const void* up, void* ou
     if (total == 0) return CLEF_OK;
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16 && use_hot() && total >= 16 && total / 16 < 0xffffffffull && aligned(gate, 32) &&
+        aligned(up, 32) && aligned(out, 32)) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(swiglu_hot_kernel, 0, occ);
+        const size_t blocks = total / 16;
+        launch_hot(swiglu_hot_kernel, clamp_grid((blocks + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0,
+                   as_stream(stream), (const uint16_t*)gate, (const uint16_t*)up, (uint16_t*)out, (uint32_t)blocks);
+        if (int r = check_launch(what)) return r;
+        const size_t done = blocks * 16;
+        if (done == total) return CLEF_OK;
+        gate = (const uint16_t*)gate + done;   // the last total % 16 values go through the shape-general kernel
+        up = (const uint16_t*)up + done;
+        out = (uint16_t*)out + done;
+        total -= done;
+    }
     const size_t quads = (total + 3) / 4;
     if (dtype == CLEF_BF16) {
         static std::atomic<int> occ{0};
@@ -488,6 +528,19 @@ int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, ui
     if (rows_total == 0) return CLEF_OK;
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16 && use_hot() && cols % 512 == 0 && (size_t)rows_total * (cols / 512) < 0x7fffffffull &&
+        aligned(x, 32)) {
+        constexpr int kUnits = 2;
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(quantise_hot_kernel<kUnits>, 0, occ);
+        const uint32_t segs = (uint32_t)(cols / 512);
+        const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;
+        const size_t ctas = ((size_t)total_units + kUnits * 8 - 1) / (kUnits * 8);
+        launch_hot(quantise_hot_kernel<kUnits>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, as_stream(stream),
+                   (const uint16_t*)x, packed, scales, live_units, total_units, cols, global_scale, blk_mn, chunk,
+                   make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
+        return check_launch(what);
+    }
     if (dtype == CLEF_BF16) {
         launch_quantise_generic<Bf16, false>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
                                              global_scale, blk_mn, chunk);

@@ -563,6 +563,281 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
 }
 
 // ---------------------------------------------------------------------------------------------
+// Plain NVFP4 quantiser (kernels/quantise.cu:6-53) for cols % 512 == 0: the SwiGLU kernel's unit
+// structure with one input.
+// ---------------------------------------------------------------------------------------------
+__device__ __noinline__ void quantise_block_cold(const uint16_t* xblk, float global_scale, uint2* packed_dst,
+                                                 uint8_t* scale_dst) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = __uint_as_float((uint32_t)xblk[i] << 16);
+    }
+    quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
+}
+
+template <int UNITS>
+__global__ void __launch_bounds__(kCtaThreads, 4)
+quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                    uint32_t live_units, uint32_t total_units, int cols, float global_scale, int blk_mn, int chunk,
+                    FastDiv seg_div, FastDiv atom_div) {
+    __shared__ float s_inv[kInvScaleTableSize];
+    const int lane = threadIdx.x & 31;
+    const uint32_t warps = gridDim.x * (kCtaThreads / 32);
+    uint32_t unit0 = blockIdx.x * (kCtaThreads / 32) + (threadIdx.x >> 5);
+    const int k1_count = cols >> 6;
+    pdl_launch_dependents();
+    fill_inv_scale_table(s_inv, global_scale);
+    pdl_wait_prior_grids();
+    U8x32 d[UNITS];
+#pragma unroll
+    for (int k = 0; k < UNITS; ++k) {
+        const uint32_t unit = unit0 + k * warps;
+        if (unit < live_units) {
+            d[k] = ldg_stream_v8(x + (size_t)unit * 512 + lane * 16);
+        }
+    }
+    __syncthreads();
+    for (; unit0 < total_units; unit0 += UNITS * warps) {
+#pragma unroll
+        for (int k = 0; k < UNITS; ++k) {
+            const uint32_t unit = unit0 + k * warps;
+            if (unit >= total_units) {
+                break;
+            }
+            const uint32_t row = fast_div(unit, seg_div);
+            const uint32_t block = (unit - row * seg_div.d) * 32 + lane;
+            const uint32_t m_rest = fast_div(row, atom_div);
+            const uint32_t m_atom = row - m_rest * (uint32_t)blk_mn;
+            uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
+            uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)unit * 256 + lane * 8);
+            if (unit >= live_units) {
+                *pdst = make_uint2(0u, 0u);
+                *sdst = 0;
+                continue;
+            }
+            f32x2 v[8];
+            unpack16_quadpairs(d[k], v);
+            const uint32_t next = unit + UNITS * warps;
+            if (next < live_units) {
+                d[k] = ldg_stream_v8(x + (size_t)next * 512 + lane * 16);
+            }
+            uint32_t stored, lo, hi;
+            if (quantise16_qp<false>(v, global_scale, s_inv, stored, lo, hi)) {
+                *pdst = make_uint2(lo, hi);
+                *sdst = (uint8_t)stored;
+            } else {
+                quantise_block_cold(x + (size_t)unit * 512 + lane * 16, global_scale, pdst, sdst);
+            }
+        }
+    }
+}
+
+// Quad-pair registers of one block -> 32 bytes of bf16 in natural order (round to nearest even).
+__device__ __forceinline__ U8x32 pack16_bf16(const f32x2* v) {
+    U8x32 o;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        o.w[2 * q] = pack_bf16x2(v[2 * q].x, v[2 * q + 1].x);       // (x, y)
+        o.w[2 * q + 1] = pack_bf16x2(v[2 * q].y, v[2 * q + 1].y);   // (z, w)
+    }
+    return o;
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm with bf16 output (kernels/elementwise.cu:4-68), cols = NB * 512: the quantising kernel's
+// row structure and summation tree, the normalised row rounded to bf16 instead of quantised, so the
+// result is the reference's f32 result rounded to nearest even.
+// ---------------------------------------------------------------------------------------------
+template <int NB>
+__global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? 2 : 1))
+rms_norm_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight, uint16_t* __restrict__ out,
+                    int rows, float eps) {
+    constexpr int COLS = NB * 512;
+    extern __shared__ float4 s_w[];   // (1 + w) or 1, quad-pair layout, transposed (see the quantising kernel)
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
+        const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (weight) {
+            w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
+        }
+        s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
+    }
+    pdl_wait_prior_grids();
+    int row = blockIdx.x * 8 + warp;
+    U8x32 d[NB];
+    if (row < rows) {
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
+        }
+    }
+    __syncthreads();
+    for (; row < rows; row += gridDim.x * 8) {
+        f32x2 v[NB][8];
+        float p[2][4];
+#pragma unroll
+        for (int j0 = 0; j0 < 2; ++j0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) p[j0][k] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            float quad[4];
+            unpack16_quadpairs(d[j], v[j]);
+            quad_squares(v[j], quad);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                p[j & 1][k] = __fadd_rn(p[j & 1][k], quad[k]);
+            }
+        }
+        const int next = row + gridDim.x * 8;
+        if (next < rows) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                d[j] = ldg_stream_v8(x + (size_t)next * COLS + (size_t)(lane + 32 * j) * 16);
+            }
+        }
+        const f32x2 inv2 = f2_splat(inv_rms_pow2<COLS>(row_tree_256(p, lane), eps));
+        uint16_t* orow = out + (size_t)row * COLS;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (weight) {   // without a weight the reference computes x * inv only (no multiply by 1)
+                    const float4 w = s_w[(4 * j + q) * 32 + lane];
+                    v[j][2 * q] = f2_mul(f2_mul(v[j][2 * q], inv2), make_float2(w.x, w.y));
+                    v[j][2 * q + 1] = f2_mul(f2_mul(v[j][2 * q + 1], inv2), make_float2(w.z, w.w));
+                } else {
+                    v[j][2 * q] = f2_mul(v[j][2 * q], inv2);
+                    v[j][2 * q + 1] = f2_mul(v[j][2 * q + 1], inv2);
+                }
+            }
+            stg_v8(orow + (size_t)(lane + 32 * j) * 16, pack16_bf16(v[j]));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU with bf16 output (kernels/elementwise.cu:225-241) over a flat array, 16 values per lane.
+// Blocks with max|g| <= 44 use the short exact quotient (see the quantising kernel); others the
+// literal expression. `blocks` = total / 16; a tail of total % 16 values is left to the caller
+// (the launcher runs the shape-general kernel on it).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kCtaThreads, 4)
+swiglu_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up, uint16_t* __restrict__ out,
+                  uint32_t blocks) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const uint32_t stride = gridDim.x * kCtaThreads;
+    uint32_t b = blockIdx.x * kCtaThreads + threadIdx.x;
+    U8x32 g, u;
+    if (b < blocks) {
+        g = ldg_stream_v8(gate + (size_t)b * 16);
+        u = ldg_stream_v8(up + (size_t)b * 16);
+    }
+    for (; b < blocks; b += stride) {
+        f32x2 gv[8], uv[8];
+        unpack16_quadpairs(g, gv);
+        unpack16_quadpairs(u, uv);
+        const uint32_t next = b + stride;
+        if (next < blocks) {
+            g = ldg_stream_v8(gate + (size_t)next * 16);
+            u = ldg_stream_v8(up + (size_t)next * 16);
+        }
+        if (block_abs_max(gv) <= kSiluFastMaxAbs) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                gv[i] = f2_mul(silu_ieee_fast_x2(gv[i]), uv[i]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                gv[i] = make_float2(silu_ieee_div(gv[i].x) * uv[i].x, silu_ieee_div(gv[i].y) * uv[i].y);
+            }
+        }
+        stg_v8(out + (size_t)b * 16, pack16_bf16(gv));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Gated RMSNorm with bf16 output for 128-wide rows (kernels/elementwise.cu:144-223): the quantising
+// kernel's layout (4 lanes per row) and tree; weight and gate are both present on this path.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kCtaThreads, 2)
+gated_norm_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
+                      const float* __restrict__ weight, uint16_t* __restrict__ out, int rows, float eps) {
+    constexpr int COLS = 128;
+    __shared__ float4 s_w[32];
+    const int lane = threadIdx.x & 31;
+    const int m = lane & 3;
+    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
+    uint32_t hrow = blockIdx.x * (kCtaThreads / 4) + (threadIdx.x >> 2);
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
+        const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
+        s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
+    }
+    pdl_wait_prior_grids();
+    U8x32 dx[2], dg[2];
+    if (hrow < (uint32_t)rows) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            dx[h] = ldg_stream_v8(x + (size_t)hrow * COLS + (m + 4 * h) * 16);
+            dg[h] = ldg_stream_v8(gate + (size_t)hrow * COLS + (m + 4 * h) * 16);
+        }
+    }
+    __syncthreads();
+    for (uint32_t base = hrow - (uint32_t)(lane >> 2); base < (uint32_t)rows; base += groups_in_grid, hrow += groups_in_grid) {
+        const bool live = hrow < (uint32_t)rows;
+        f32x2 v[2][8], gv[2][8];
+        float quad[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        if (live) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                unpack16_quadpairs(dx[h], v[h]);
+                unpack16_quadpairs(dg[h], gv[h]);
+                quad_squares(v[h], quad[h]);
+            }
+        }
+        const uint32_t next = hrow + groups_in_grid;
+        if (next < (uint32_t)rows) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                dx[h] = ldg_stream_v8(x + (size_t)next * COLS + (m + 4 * h) * 16);
+                dg[h] = ldg_stream_v8(gate + (size_t)next * COLS + (m + 4 * h) * 16);
+            }
+        }
+        const float total = head_tree_32(quad[0], quad[1], lane);
+        if (!live) {
+            continue;
+        }
+        const f32x2 inv2 = f2_splat(inv_rms_pow2<COLS>(total, eps));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const bool fast = block_abs_max(gv[h]) <= kSiluFastMaxAbs;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 w = s_w[(h * 4 + q) * 4 + m];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int i = 2 * q + e;
+                    const f32x2 wp = e == 0 ? make_float2(w.x, w.y) : make_float2(w.z, w.w);
+                    const f32x2 sl = fast ? silu_approx_fast_x2(gv[h][i])
+                                          : make_float2(silu_fast_div(gv[h][i].x), silu_fast_div(gv[h][i].y));
+                    v[h][i] = f2_mul(f2_mul(f2_mul(v[h][i], inv2), wp), sl);
+                }
+            }
+            stg_v8(out + (size_t)hrow * COLS + (m + 4 * h) * 16, pack16_bf16(v[h]));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Partial RoPE (kernels/elementwise.cu:276-315) for head_dim % 32 == 0, rotary_dim % 32 == 0.
 // A head row is head_dim/16 chunks of 32 bytes. Work items per head row: rotary_dim/32 "rotating"
 // items (chunk i of the lower half together with its partner chunk i + rotary_dim/32) followed by

@@ -156,7 +156,8 @@ def time_cpu(steps: int, warmup: int, budget_s: float = 25.0):
     """rows/s of the CPU restatement (oracle port) with every host thread, on the same 8,192-row step."""
     from oracle import binding as orc
 
-    threads = orc.max_threads()
+    # every host core this process may use (torchrun exports OMP_NUM_THREADS=1; the oracle takes the count explicitly)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     inp = host_inputs(ROWS, 1234)
     cos, sin = orc.rope_tables(np.arange(ROWS, dtype=np.int32), ROTARY, THETA)
     for _ in range(max(1, min(warmup, 2))):

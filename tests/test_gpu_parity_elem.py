@@ -60,8 +60,10 @@ def test_embed_gather(tokens, hidden, choice):
 
 
 # ---- rms_norm -------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("rows,cols", [(5, 128), (778, 2048), (129, 4096), (300, 256), (64, 1000), (33, 6144)])
-def test_rms_norm(rows, cols):
+def test_rms_norm(rows, cols, choice):
+    clef.set_kernel_choice(choice)
     rng = np.random.default_rng(rows + cols)
     x = normal_bf16(rng, (rows, cols), outlier_channels=4)
     w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
@@ -103,8 +105,10 @@ def test_rms_norm_reference_recipe():
 
 
 # ---- rms_norm_gated ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("rows,cols", [(5, 128), (778 * 16, 128), (77, 2048), (300, 256)])
-def test_rms_norm_gated(rows, cols):
+def test_rms_norm_gated(rows, cols, choice):
+    clef.set_kernel_choice(choice)
     rng = np.random.default_rng(rows + cols)
     x, g = normal_bf16(rng, (rows, cols)), normal_bf16(rng, (rows, cols))
     w = (1.0 + rng.standard_normal(cols) * 0.1).astype(np.float32)
@@ -132,8 +136,10 @@ def test_rms_norm_gated(rows, cols):
 
 
 # ---- swiglu --------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("total", [5 * 128, 5 * 128 - 1, 778 * 6144, 1, 3, 4099])
-def test_swiglu(total):
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
+@pytest.mark.parametrize("total", [5 * 128, 5 * 128 - 1, 778 * 6144, 1, 3, 4099, 16, 17])
+def test_swiglu(total, choice):
+    clef.set_kernel_choice(choice)
     rng = np.random.default_rng(total)
     pad = (total + 7) // 8 * 8
     g, u = normal_bf16(rng, (pad,), scale=3.0), normal_bf16(rng, (pad,))

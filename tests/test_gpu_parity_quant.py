@@ -43,9 +43,11 @@ def run_quant(entry, rows, cols, args_before, args_after, blk_mn=128):
 # ---------------------------------------------------------------------------------------------------------
 # quantise_nvfp4
 # ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("rows", ROWS)
 @pytest.mark.parametrize("cols", [64, 2048, 6144])
-def test_quantise_nvfp4(rows, cols):
+def test_quantise_nvfp4(rows, cols, choice):
+    clef.set_kernel_choice(choice)
     rng = np.random.default_rng(rows * 131 + cols)
     x = normal_bf16(rng, (rows, cols), outlier_channels=8)
     gs = 448.0 * 6.0 / 90.0
