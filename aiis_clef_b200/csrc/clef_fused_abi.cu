@@ -664,6 +664,27 @@ int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, 
     if (rows == 0) return CLEF_OK;
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16 && use_hot() && head_dim == 128 && rotary_dim == 64 && aligned(x, 32) && aligned(out, 32) &&
+        (!gate_out || aligned(gate_out, 32))) {
+        const size_t hot_groups = ((size_t)rows + 63) / 64;
+        const FastDiv heads_div = make_fast_div((uint32_t)heads);
+        if (gate_out) {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<true>, 0, occ);
+            launch_hot(qk_norm_rope_hot_kernel<true>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
+                       as_stream(stream), (const uint16_t*)x, weight, cos_table, sin_table, (uint16_t*)out,
+                       (uint16_t*)gate_out, (uint32_t)rows, eps, (const int*)seq_start, (const int*)pos_base,
+                       (const int*)pos_map, heads_div);
+        } else {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<false>, 0, occ);
+            launch_hot(qk_norm_rope_hot_kernel<false>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
+                       as_stream(stream), (const uint16_t*)x, weight, cos_table, sin_table, (uint16_t*)out,
+                       (uint16_t*)nullptr, (uint32_t)rows, eps, (const int*)seq_start, (const int*)pos_base,
+                       (const int*)pos_map, heads_div);
+        }
+        return check_launch(what);
+    }
     const size_t smem = (size_t)8 * head_dim * sizeof(float);
     const size_t groups = ((size_t)rows + 7) / 8;
     if (dtype == CLEF_BF16) {

@@ -895,6 +895,111 @@ rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, cons
 }
 
 // ---------------------------------------------------------------------------------------------
+// Per-head RMSNorm + partial RoPE (kernels/elementwise.cu:70-142) for head_dim 128, rotary_dim 64.
+// Four lanes own one head row: lane m holds chunk m (dims 16m .. 16m+15, inside the rotary span)
+// and chunk m + 4 (pass-through dims), a warp 8 head rows. The norm tree is the gated kernel's
+// (head_tree_32). The rotation pairs dims j and j + 32, i.e. chunk m of lanes m and m ^ 2: the
+// partner's RAW bf16 words cross by shuffle and both lanes normalise both halves. With `gate_out`
+// the input row is [q | gate] and the gate half is copied.
+// ---------------------------------------------------------------------------------------------
+template <bool GATE>
+__global__ void __launch_bounds__(kCtaThreads, 2)
+qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight,
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint16_t* __restrict__ out,
+                        uint16_t* __restrict__ gate_out, uint32_t rows, float eps, const int* __restrict__ seq_start,
+                        const int* __restrict__ pos_base, const int* __restrict__ pos_map, FastDiv heads_div) {
+    constexpr int HD = 128, ROT = 64, STRIDE = GATE ? 2 * HD : HD;
+    __shared__ float4 s_w[32];   // (1 + w), quad-pair layout: s_w[c * 4 + q] for chunk c, quad q
+    const int lane = threadIdx.x & 31;
+    const int m = lane & 3;
+    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
+    uint32_t hrow = blockIdx.x * (kCtaThreads / 4) + (threadIdx.x >> 2);
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        const float4 t = *reinterpret_cast<const float4*>(weight + threadIdx.x * 4);
+        s_w[threadIdx.x] = make_float4(1.0f + t.x, 1.0f + t.z, 1.0f + t.y, 1.0f + t.w);
+    }
+    pdl_wait_prior_grids();
+    U8x32 d[2], dgate[2];
+    if (hrow < rows) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            d[h] = ldg_stream_v8(x + (size_t)hrow * STRIDE + (m + 4 * h) * 16);
+            if (GATE) dgate[h] = ldg_stream_v8(x + (size_t)hrow * STRIDE + HD + (m + 4 * h) * 16);
+        }
+    }
+    __syncthreads();
+    for (uint32_t base = hrow - (uint32_t)(lane >> 2); base < rows; base += groups_in_grid, hrow += groups_in_grid) {
+        const bool live = hrow < rows;
+        f32x2 v[2][8], pv[8];
+        float quad[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        U8x32 praw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {   // partner's raw rotary chunk (lane m ^ 2)
+            praw.w[i] = __shfl_xor_sync(kFullMask, d[0].w[i], 2);
+        }
+        if (live) {
+            unpack16_quadpairs(d[0], v[0]);
+            unpack16_quadpairs(d[1], v[1]);
+            unpack16_quadpairs(praw, pv);
+            quad_squares(v[0], quad[0]);
+            quad_squares(v[1], quad[1]);
+            if (GATE) {
+                stg_v8(gate_out + (size_t)hrow * HD + m * 16, dgate[0]);
+                stg_v8(gate_out + (size_t)hrow * HD + (m + 4) * 16, dgate[1]);
+            }
+        }
+        const uint32_t next = hrow + groups_in_grid;
+        if (next < rows) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                d[h] = ldg_stream_v8(x + (size_t)next * STRIDE + (m + 4 * h) * 16);
+                if (GATE) dgate[h] = ldg_stream_v8(x + (size_t)next * STRIDE + HD + (m + 4 * h) * 16);
+            }
+        }
+        const float total = head_tree_32(quad[0], quad[1], lane);
+        if (!live) {
+            continue;
+        }
+        const f32x2 inv2 = f2_splat(inv_rms_pow2<HD>(total, eps));
+        const int pm = m ^ 2;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 wa = s_w[m * 4 + q], wb = s_w[(m + 4) * 4 + q], wp = s_w[pm * 4 + q];
+            v[0][2 * q] = f2_mul(f2_mul(v[0][2 * q], inv2), make_float2(wa.x, wa.y));
+            v[0][2 * q + 1] = f2_mul(f2_mul(v[0][2 * q + 1], inv2), make_float2(wa.z, wa.w));
+            v[1][2 * q] = f2_mul(f2_mul(v[1][2 * q], inv2), make_float2(wb.x, wb.y));
+            v[1][2 * q + 1] = f2_mul(f2_mul(v[1][2 * q + 1], inv2), make_float2(wb.z, wb.w));
+            pv[2 * q] = f2_mul(f2_mul(pv[2 * q], inv2), make_float2(wp.x, wp.y));
+            pv[2 * q + 1] = f2_mul(f2_mul(pv[2 * q + 1], inv2), make_float2(wp.z, wp.w));
+        }
+        const int token = (int)fast_div(hrow, heads_div);
+        const int pos = rope_position(token, seq_start, pos_base, pos_map);
+        const float* cp = cos_t + (size_t)pos * ROT + (m & 1) * 16;
+        const float* sp = sin_t + (size_t)pos * ROT + (m & 1) * 16;
+        const bool holds_lo = m < 2;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 c = __ldg(reinterpret_cast<const float4*>(cp) + q);
+            const float4 sn = __ldg(reinterpret_cast<const float4*>(sp) + q);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int i = 2 * q + e;
+                const f32x2 c2 = e == 0 ? make_float2(c.x, c.z) : make_float2(c.y, c.w);
+                const f32x2 s2 = e == 0 ? make_float2(sn.x, sn.z) : make_float2(sn.y, sn.w);
+                // lo' = fma(lo, c, -(hi * s));  hi' = fma(lo, s, hi * c)   (the reference build's contraction)
+                const f32x2 lo = holds_lo ? v[0][i] : pv[i];
+                const f32x2 hi = holds_lo ? pv[i] : v[0][i];
+                const f32x2 t = f2_mul(hi, holds_lo ? make_float2(-s2.x, -s2.y) : c2);
+                v[0][i] = f2_fma(lo, holds_lo ? c2 : s2, t);
+            }
+        }
+        stg_v8(out + (size_t)hrow * HD + m * 16, pack16_bf16(v[0]));
+        stg_v8(out + (size_t)hrow * HD + (m + 4) * 16, pack16_bf16(v[1]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Embedding gather (kernels/elementwise.cu:396-407) for rows of a multiple of 1 KiB: one warp per
 // token row, every lane moves CH chunks of 32 bytes.
 // ---------------------------------------------------------------------------------------------

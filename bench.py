@@ -49,8 +49,16 @@ BYTES_PER_ROW = {
     "rope_k": 2 * KV_HEADS * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,                        # 1,284
     "embed_gather": 4 + 2 * HIDDEN + 2 * HIDDEN,                                              # 8,196
     "rms_norm_gated_quantise_nvfp4": 2 * 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,             # 9,344
+    # the unfused entry points (what the engine runs when a fusion is switched off), bf16 in and out
+    "quantise_nvfp4": 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,                                # 5,248
+    "rms_norm": 2 * HIDDEN + 2 * HIDDEN,                                                      # 8,192
+    "swiglu": 3 * 2 * INTER,                                                                  # 36,864
+    "rms_norm_gated": 3 * 2 * HIDDEN,                                                         # 12,288
+    "qk_norm_rope_q": 2 * Q_HEADS * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,                 # 8,452
 }
 STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k"]
+FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k",
+                "rms_norm_gated_quantise_nvfp4"]     # config 4: the full fused chain over 130,712 rows
 DOMINANT = "swiglu_quantise_nvfp4"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel at 8,192 rows, from
 # the ncu capture summarised in profiles/. Reads equal the input bytes; part of the output is still in
@@ -264,7 +272,10 @@ def run_gpu_arm(args):
             "q_out": torch.empty(ROWS, Q_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
             "k_out": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
             "h": torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16, device="cuda"),
+            "act_i": torch.empty(ROWS, INTER, dtype=torch.bfloat16, device="cuda"),
+            "g_out": torch.empty(ROWS * VH, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
         })
+    w_head = (torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
 
     launchers = {
         "rms_norm_quantise_nvfp4": lambda d: lib.clef_rms_norm_quantise_nvfp4(
@@ -279,6 +290,15 @@ def run_gpu_arm(args):
         "rms_norm_gated_quantise_nvfp4": lambda d: lib.clef_rms_norm_gated_quantise_nvfp4(
             stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["pk_g"]), p(d["sc_g"]), rows_padded * VH, HEAD_DIM, EPS,
             GS_GATED, 128, 512, VH, ROWS * VH, 0),
+        "quantise_nvfp4": lambda d: lib.clef_quantise_nvfp4(stream(), p(d["x"]), p(d["pk_h"]), p(d["sc_h"]), ROWS, HIDDEN,
+                                                            GS_NORM, 128, 512, 0),
+        "rms_norm": lambda d: lib.clef_rms_norm(stream(), p(d["x"]), p(w_norm), p(d["h"]), ROWS, HIDDEN, EPS, 0),
+        "swiglu": lambda d: lib.clef_swiglu(stream(), p(d["gate"]), p(d["up"]), p(d["act_i"]), ROWS * INTER, 0),
+        "rms_norm_gated": lambda d: lib.clef_rms_norm_gated(stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["g_out"]),
+                                                            ROWS * VH, HEAD_DIM, EPS, 0),
+        "qk_norm_rope_q": lambda d: lib.clef_qk_norm_rope(stream(), p(d["q"]), p(w_head), p(cos), p(sin), p(d["q_out"]),
+                                                          None, ROWS * Q_HEADS, Q_HEADS, HEAD_DIM, ROTARY, EPS, None,
+                                                          None, p(cpos), 0),
     }
 
     def step_eager(d):
@@ -432,7 +452,7 @@ def full_pass(clef, lib, dev, world, rank, gen, p, stream, ok, w_norm, table):
 
     first, n = clef.shard_rows(FULL_ROWS, 128, world, rank)
     if n == 0:
-        return {k: 0.0 for k in BYTES_PER_ROW}
+        return {k: 0.0 for k in FULL_KERNELS}
 
     def randn_bf16(*shape):
         return torch.randn(*shape, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
@@ -479,7 +499,7 @@ def summarise_full(full_ms, world, peak):
     chain_ms = sum(full_ms.values())
     per_kernel = {k: {"ms": round(v, 4), "GBs_aggregate": round(BYTES_PER_ROW[k] * FULL_ROWS / (v * 1e-3) / 1e9, 1) if v else None}
                   for k, v in full_ms.items()}
-    total_bytes = sum(BYTES_PER_ROW.values()) * FULL_ROWS
+    total_bytes = sum(BYTES_PER_ROW[k] for k in FULL_KERNELS) * FULL_ROWS
     return {"n_gpus": world, "scaling": "strong (row-range shards aligned to the 128-row scale atom, max over ranks)",
             "chain_ms": round(chain_ms, 4), "rows_per_s": FULL_ROWS / (chain_ms * 1e-3) if chain_ms else None,
             "GBs_aggregate": round(total_bytes / (chain_ms * 1e-3) / 1e9, 1) if chain_ms else None,

@@ -218,10 +218,12 @@ def test_rope(rows, heads, head_dim, rot, mode, choice):
     assert_bytes_equal(outf.as_f32().view(np.uint32), ref.cpu().numpy().view(np.uint32), "f32 rope vs reference kernel")
 
 
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("with_gate", [False, True])
-@pytest.mark.parametrize("tokens,heads,head_dim,rot", [(7, 16, 256, 64), (300, 4, 256, 256), (64, 16, 128, 64), (33, 2, 128, 64), (9, 2, 512, 64)])
-def test_qk_norm_rope(tokens, heads, head_dim, rot, with_gate):
+@pytest.mark.parametrize("tokens,heads,head_dim,rot", [(7, 16, 256, 64), (300, 4, 256, 256), (64, 16, 128, 64), (33, 2, 128, 64), (9, 2, 512, 64), (778, 16, 128, 64), (1, 1, 128, 64)])
+def test_qk_norm_rope(tokens, heads, head_dim, rot, with_gate, choice):
     """src/cuda/mod.rs:6743-6806: the fused kernel equals split -> per-head rms_norm -> rope."""
+    clef.set_kernel_choice(choice)
     rng = np.random.default_rng(tokens + head_dim + int(with_gate))
     rows = tokens * heads
     stride = 2 * head_dim if with_gate else head_dim
