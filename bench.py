@@ -290,13 +290,14 @@ def run_gpu_arm(args):
         "rms_norm_gated_quantise_nvfp4": lambda d: lib.clef_rms_norm_gated_quantise_nvfp4(
             stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["pk_g"]), p(d["sc_g"]), rows_padded * VH, HEAD_DIM, EPS,
             GS_GATED, 128, 512, VH, ROWS * VH, 0),
-        "quantise_nvfp4": lambda d: lib.clef_quantise_nvfp4(stream(), p(d["x"]), p(d["pk_h"]), p(d["sc_h"]), ROWS, HIDDEN,
+        "quantise_nvfp4": lambda d: lib.clef_quantise_nvfp4(stream(), p(d["x"]), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN,
                                                             GS_NORM, 128, 512, 0),
         "rms_norm": lambda d: lib.clef_rms_norm(stream(), p(d["x"]), p(w_norm), p(d["h"]), ROWS, HIDDEN, EPS, 0),
         "swiglu": lambda d: lib.clef_swiglu(stream(), p(d["gate"]), p(d["up"]), p(d["act_i"]), ROWS * INTER, 0),
+        # (shares its output buffers with the gated quantiser above: neither is part of the checked step)
         "rms_norm_gated": lambda d: lib.clef_rms_norm_gated(stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["g_out"]),
                                                             ROWS * VH, HEAD_DIM, EPS, 0),
-        "qk_norm_rope_q": lambda d: lib.clef_qk_norm_rope(stream(), p(d["q"]), p(w_head), p(cos), p(sin), p(d["q_out"]),
+        "qk_norm_rope_q": lambda d: lib.clef_qk_norm_rope(stream(), p(d["q"]), p(w_head), p(cos), p(sin), p(d["h"]),
                                                           None, ROWS * Q_HEADS, Q_HEADS, HEAD_DIM, ROTARY, EPS, None,
                                                           None, p(cpos), 0),
     }
