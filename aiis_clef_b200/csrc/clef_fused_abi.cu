@@ -570,13 +570,15 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
     const size_t total_blocks = (size_t)rows_total * (cols / 16);
     if (dtype == CLEF_BF16 && use_hot() && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(gate, 32) &&
         aligned(up, 32)) {
-        constexpr int kUnits = 2;
-        static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(swiglu_quant_hot_kernel<kUnits>, 0, occ);
         const uint32_t segs = (uint32_t)(cols / 512);
         const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;
+        // One unit in flight per warp (plus its prefetched successor) at three CTAs per SM measured best on B200
+        // among 1-3 units x 2-5 CTAs (38.9 us against 40.7 to 45.3 us at 8,192 x 6144).
+        constexpr int kUnits = 1, kMinCtas = 3;
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(swiglu_quant_hot_kernel<kUnits, kMinCtas>, 0, occ);
         const size_t ctas = ((size_t)total_units + kUnits * 8 - 1) / (kUnits * 8);
-        launch_hot(swiglu_quant_hot_kernel<kUnits>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,
+        launch_hot(swiglu_quant_hot_kernel<kUnits, kMinCtas>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,
                    (const uint16_t*)gate, (const uint16_t*)up, packed, scales, live_units, total_units, cols,
                    global_scale, blk_mn, chunk, make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);

@@ -97,9 +97,9 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
     const float pmax = __fmul_rn(amax, inv);
     // 0 < amax < 2^-100 as one unsigned compare on the bit pattern (+0 wraps to the top)
     const bool tiny = (__float_as_uint(amax) - 1u) < (__float_as_uint(kDivSixExactFrom) - 1u);
-    if (!(fabsf(sv) <= 3.0e38f) || !(pmax < kE2m1FastLimit) || tiny) {
-        return false;
-    }
+    // No early exit: the codes are computed unconditionally (on values the fast path does not cover the
+    // result is simply not used), which leaves the compiler free to interleave several blocks.
+    const bool ok = (fabsf(sv) <= 3.0e38f) && (pmax < kE2m1FastLimit) && !tiny;
     constexpr float kNudge = -4.33488326e-08f;   // see e2m1x2_fast
     const f32x2 inv2 = f2_splat(NEG ? -inv : inv);
     const f32x2 nudge2 = f2_splat(kNudge);
@@ -113,7 +113,7 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
     stored_out = stored;
     lo_out = e2m1_pack8(p[0].x, p[1].x, p[0].y, p[1].y, p[2].x, p[3].x, p[2].y, p[3].y);
     hi_out = e2m1_pack8(p[4].x, p[5].x, p[4].y, p[5].y, p[6].x, p[7].x, p[6].y, p[7].y);
-    return true;
+    return ok;
 }
 
 // Cold path shared by the kernels: the caller has the block's 16 f32 values recomputed in natural
@@ -263,6 +263,8 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
         const float inv = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
                                                    : inv_rms(row_tree_256(p, lane), COLS, eps);
         const f32x2 inv2 = f2_splat(inv);
+        uint32_t stored[NB], lo[NB], hi[NB];
+        bool fast[NB];
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
 #pragma unroll
@@ -271,13 +273,16 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
                 v[j][2 * q] = f2_mul(f2_mul(v[j][2 * q], inv2), make_float2(w.x, w.y));
                 v[j][2 * q + 1] = f2_mul(f2_mul(v[j][2 * q + 1], inv2), make_float2(w.z, w.w));
             }
+            fast[j] = quantise16_qp<false>(v[j], global_scale, s_inv, stored[j], lo[j], hi[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
             const int b = lane + 32 * j;
             uint2* pdst = reinterpret_cast<uint2*>(prow + b * 8);
             uint8_t* sdst = srow + (size_t)(b >> 2) * chunk + (b & 3);
-            uint32_t stored, lo, hi;
-            if (quantise16_qp<false>(v[j], global_scale, s_inv, stored, lo, hi)) {
-                *pdst = make_uint2(lo, hi);
-                *sdst = (uint8_t)stored;
+            if (fast[j]) {
+                *pdst = make_uint2(lo[j], hi[j]);
+                *sdst = (uint8_t)stored[j];
             } else {
                 rms_block_cold(x + (size_t)row * COLS + b * 16, weight + b * 16, inv, global_scale, pdst, sdst);
             }
@@ -349,8 +354,8 @@ __device__ __noinline__ void swiglu_block_cold(const uint16_t* gblk, const uint1
     quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
 }
 
-template <int UNITS>
-__global__ void __launch_bounds__(kCtaThreads, 3)
+template <int UNITS, int MIN_CTAS>
+__global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
 swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up,
                         uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t live_units,
                         uint32_t total_units, int cols, float global_scale, int blk_mn, int chunk, FastDiv seg_div,
@@ -540,17 +545,15 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
                 continue;
             }
             uint32_t stored, lo, hi;
-            bool done = false;
-            if (block_abs_max(gv[h]) <= kSiluFastMaxAbs) {
+            const bool in_domain = block_abs_max(gv[h]) <= kSiluFastMaxAbs;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 w = s_w[(h * 4 + q) * 4 + m];
-                    // ((x * inv) * w) * silu(g), left to right as the reference writes it
-                    v[h][2 * q] = f2_mul(f2_mul(f2_mul(v[h][2 * q], inv2), make_float2(w.x, w.y)), silu_approx_fast_x2(gv[h][2 * q]));
-                    v[h][2 * q + 1] = f2_mul(f2_mul(f2_mul(v[h][2 * q + 1], inv2), make_float2(w.z, w.w)), silu_approx_fast_x2(gv[h][2 * q + 1]));
-                }
-                done = quantise16_qp<false>(v[h], global_scale, s_inv, stored, lo, hi);
+            for (int q = 0; q < 4; ++q) {
+                const float4 w = s_w[(h * 4 + q) * 4 + m];
+                // ((x * inv) * w) * silu(g), left to right as the reference writes it
+                v[h][2 * q] = f2_mul(f2_mul(f2_mul(v[h][2 * q], inv2), make_float2(w.x, w.y)), silu_approx_fast_x2(gv[h][2 * q]));
+                v[h][2 * q + 1] = f2_mul(f2_mul(f2_mul(v[h][2 * q + 1], inv2), make_float2(w.z, w.w)), silu_approx_fast_x2(gv[h][2 * q + 1]));
             }
+            const bool done = quantise16_qp<false>(v[h], global_scale, s_inv, stored, lo, hi) && in_domain;
             if (done) {
                 *pdst = make_uint2(lo, hi);
                 *sdst = (uint8_t)stored;
