@@ -13,6 +13,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "abi_support.cuh"
 #include "internal.hpp"
 #include "kernels_generic.cuh"
 #include "kernels_hot.cuh"
@@ -32,137 +33,16 @@ int fail(int code, const char* fmt, ...) {
 }  // namespace clef
 
 namespace {
-
-using clef::fail;
 std::atomic<int> g_kernel_choice{0};
-
-struct DeviceInfo {
-    int sms = 0;
-    int cc_major = 0;
-};
-
-// Per-device facts, looked up once per device (no allocation; attribute queries only).
-int device_info(DeviceInfo& out) {
-    static std::atomic<int> cached_sms[64];
-    static std::atomic<int> cached_cc[64];
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) {
-        return fail(CLEF_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-    }
-    if (dev < 0 || dev >= 64) {
-        return fail(CLEF_ERR_CUDA, "device ordinal %d out of range", dev);
-    }
-    int sms = cached_sms[dev].load(std::memory_order_relaxed);
-    int cc = cached_cc[dev].load(std::memory_order_relaxed);
-    if (sms == 0) {
-        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e == cudaSuccess) {
-            e = cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev);
-        }
-        if (e != cudaSuccess) {
-            return fail(CLEF_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
-        }
-        cached_sms[dev].store(sms, std::memory_order_relaxed);
-        cached_cc[dev].store(cc, std::memory_order_relaxed);
-    }
-    if (cc != 10) {
-        return fail(CLEF_ERR_CUDA, "this library holds sm_100a code only; device %d is compute capability %d.x", dev,
-                    cc);
-    }
-    out.sms = sms;
-    out.cc_major = cc;
-    return CLEF_OK;
 }
 
-// Resident CTAs per SM of a kernel (cached per kernel instantiation by the caller's static).
-template <typename K>
-int ctas_per_sm(K kernel, size_t dyn_smem, std::atomic<int>& cache) {
-    int n = cache.load(std::memory_order_relaxed);
-    if (n > 0) {
-        return n;
-    }
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, clef::kCtaThreads, dyn_smem) != cudaSuccess || n < 1) {
-        (void)cudaGetLastError();
-        n = 1;
-    }
-    cache.store(n, std::memory_order_relaxed);
-    return n;
-}
+namespace clef {
+int kernel_choice() { return g_kernel_choice.load(std::memory_order_relaxed); }
+}  // namespace clef
 
-// Launch of a tuned kernel. With programmatic dependent launch (default; CLEF_PDL=0 turns it off) the
-// kernel may begin its argument-only prologue while the stream's previous kernel drains; the kernels
-// wait for that kernel before touching any activation or output (common.cuh, pdl_wait_prior_grids).
-bool pdl_enabled() {
-    static const int on = [] {
-        const char* v = getenv("CLEF_PDL");
-        return (v && v[0] == '0') ? 0 : 1;
-    }();
-    return on != 0;
-}
-
-template <typename... KArgs, typename... Args>
-void launch_hot(void (*kernel)(KArgs...), unsigned grid, size_t smem, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(clef::kCtaThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch
-}
-
-inline unsigned clamp_grid(size_t wanted, size_t cap) {
-    size_t g = wanted < cap ? wanted : cap;
-    return (unsigned)(g < 1 ? 1 : g);
-}
-
-int check_launch(const char* what) {
-    const cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        return fail(CLEF_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
-    }
-    return CLEF_OK;
-}
-
-inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
-
-int check_dtype(int dtype, const char* what) {
-    if (dtype != CLEF_BF16 && dtype != CLEF_F32) {
-        return fail(CLEF_ERR_INVALID, "%s: dtype %d is neither CLEF_BF16 nor CLEF_F32", what, dtype);
-    }
-    return CLEF_OK;
-}
-
-int check_scale_layout(const char* what, int rows, int cols, int blk_mn, int chunk) {
-    if (rows < 0 || cols <= 0) {
-        return fail(CLEF_ERR_INVALID, "%s: rows %d / cols %d", what, rows, cols);
-    }
-    if (cols % 64 != 0) {
-        return fail(CLEF_ERR_INVALID,
-                    "%s: cols %d is not a multiple of 64 (four 16-value blocks fill one scale group)", what, cols);
-    }
-    if (blk_mn <= 0 || chunk != blk_mn * 4) {
-        return fail(CLEF_ERR_INVALID, "%s: scale atom blk_mn %d / chunk %d (chunk must be blk_mn * 4)", what, blk_mn,
-                    chunk);
-    }
-    return CLEF_OK;
-}
-
-inline bool use_hot() { return g_kernel_choice.load(std::memory_order_relaxed) == 0; }
-
-inline cudaStream_t as_stream(clef_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
-
-template <typename T>
-using Storage = typename T::storage;
-
-}  // namespace
 
 using namespace clef;
+using namespace clef::abi;
 
 extern "C" {
 
@@ -310,15 +190,18 @@ int clef_rms_norm(clef_stream_t stream, const void* x, const float* weight, void
     return check_launch("clef_rms_norm");
 }
 
-int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const float* weight, uint8_t* packed,
-                                 uint8_t* scales, int rows, int cols, float eps, float global_scale, int blk_mn,
-                                 int chunk, int dtype) {
-    const char* what = "clef_rms_norm_quantise_nvfp4";
+}  // extern "C"
+
+// RMSNorm + NVFP4 of x, or (addend != NULL) of the stored sum x + addend, which is also written to sum_out.
+static int rms_norm_quantise_impl(const char* what, clef_stream_t stream, const void* x, const void* addend,
+                                  void* sum_out, const float* weight, uint8_t* packed, uint8_t* scales, int rows,
+                                  int cols, float eps, float global_scale, int blk_mn, int chunk, int dtype) {
     if (int r = check_dtype(dtype, what)) return r;
     if (!x || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (addend && !sum_out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
-    if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(packed, 8)) {
-        return fail(CLEF_ERR_INVALID, "%s: x and weight must be 16-byte aligned, packed 8-byte aligned", what);
+    if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(packed, 8) || (addend && (!aligned(addend, 16) || !aligned(sum_out, 16)))) {
+        return fail(CLEF_ERR_INVALID, "%s: activations and weight must be 16-byte aligned, packed 8-byte aligned", what);
     }
     int rows_total = 0;
     if (int r = clef_nvfp4_sizes(rows, cols, blk_mn, &rows_total, nullptr, nullptr)) return r;
@@ -326,24 +209,30 @@ int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const floa
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
-    if (dtype == CLEF_BF16 && use_hot() && (cols == 2048 || cols == 4096) && aligned(x, 32)) {
+    if (dtype == CLEF_BF16 && use_hot() && (cols == 2048 || cols == 4096) && aligned(x, 32) &&
+        (!addend || (aligned(addend, 32) && aligned(sum_out, 32)))) {
         const size_t groups = ((size_t)rows_total + 7) / 8;
         const size_t smem = (size_t)cols * sizeof(float);
         const FastDiv atom_div = make_fast_div((uint32_t)blk_mn);
+#define CLEF_RMSQ_HOT(NB, ADD)                                                                                     \
+    {                                                                                                              \
+        static std::atomic<int> occ{0};                                                                            \
+        const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<NB, ADD>, smem, occ);                             \
+        launch_hot(rms_norm_quant_hot_kernel<NB, ADD>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,      \
+                   (const uint16_t*)x, (const uint16_t*)addend, (uint16_t*)sum_out, weight, packed, scales, rows,  \
+                   rows_total, eps, global_scale, blk_mn, chunk, atom_div);                                        \
+    }
         if (cols == 2048) {
-            static std::atomic<int> occ{0};
-            const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<4>, smem, occ);
-            launch_hot(rms_norm_quant_hot_kernel<4>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,
-                       (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk,
-                       atom_div);
+            if (addend) CLEF_RMSQ_HOT(4, true) else CLEF_RMSQ_HOT(4, false)
         } else {
-            static std::atomic<int> occ{0};
-            const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<8>, smem, occ);
-            launch_hot(rms_norm_quant_hot_kernel<8>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,
-                       (const uint16_t*)x, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk,
-                       atom_div);
+            if (addend) CLEF_RMSQ_HOT(8, true) else CLEF_RMSQ_HOT(8, false)
         }
+#undef CLEF_RMSQ_HOT
         return check_launch(what);
+    }
+    if (addend) {   // shape-general path: the add, then the norm + quantiser on the stored sum
+        if (int r = clef_add(stream, sum_out, x, addend, (size_t)rows * cols, dtype)) return r;
+        x = sum_out;
     }
     if (dtype == CLEF_BF16) {
         launch_rms_norm_generic<Bf16, true>(s, dev, x, weight, nullptr, packed, scales, rows, rows_total, cols, eps,
@@ -353,6 +242,23 @@ int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const floa
                                            global_scale, blk_mn, chunk);
     }
     return check_launch(what);
+}
+
+extern "C" {
+
+int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const float* weight, uint8_t* packed,
+                                 uint8_t* scales, int rows, int cols, float eps, float global_scale, int blk_mn,
+                                 int chunk, int dtype) {
+    return rms_norm_quantise_impl("clef_rms_norm_quantise_nvfp4", stream, x, nullptr, nullptr, weight, packed, scales,
+                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype);
+}
+
+int clef_add_rms_norm_quantise_nvfp4(clef_stream_t stream, void* sum_out, const void* a, const void* b,
+                                     const float* weight, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                                     float eps, float global_scale, int blk_mn, int chunk, int dtype) {
+    if (!b || !sum_out) return fail(CLEF_ERR_INVALID, "clef_add_rms_norm_quantise_nvfp4: null pointer");
+    return rms_norm_quantise_impl("clef_add_rms_norm_quantise_nvfp4", stream, a, b, sum_out, weight, packed, scales,
+                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype);
 }
 
 // ---- gated rms_norm family -------------------------------------------------------------------------
@@ -469,9 +375,9 @@ int clef_swiglu(clef_stream_t stream, const void* gate, const void* up, void* ou
     if (dtype == CLEF_BF16 && use_hot() && total >= 16 && total / 16 < 0xffffffffull && aligned(gate, 32) &&
         aligned(up, 32) && aligned(out, 32)) {
         static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(swiglu_hot_kernel, 0, occ);
+        const int per_sm = ctas_per_sm(swiglu_hot_kernel<kActSwiGLU>, 0, occ);
         const size_t blocks = total / 16;
-        launch_hot(swiglu_hot_kernel, clamp_grid((blocks + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0,
+        launch_hot(swiglu_hot_kernel<kActSwiGLU>, clamp_grid((blocks + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0,
                    as_stream(stream), (const uint16_t*)gate, (const uint16_t*)up, (uint16_t*)out, (uint32_t)blocks);
         if (int r = check_launch(what)) return r;
         const size_t done = blocks * 16;
@@ -497,22 +403,6 @@ int clef_swiglu(clef_stream_t stream, const void* gate, const void* up, void* ou
     }
     return check_launch(what);
 }
-
-}  // extern "C"
-
-template <typename T, bool SWIGLU>
-static void launch_quantise_generic(cudaStream_t stream, const DeviceInfo& dev, const void* a, const void* b,
-                                    uint8_t* packed, uint8_t* scales, int rows, int rows_total, int cols,
-                                    float global_scale, int blk_mn, int chunk) {
-    static std::atomic<int> occ{0};
-    auto kernel = quantise_generic_kernel<T, SWIGLU>;
-    const int per_sm = ctas_per_sm(kernel, 0, occ);
-    const size_t blocks = (size_t)rows_total * (cols / 16);
-    kernel<<<clamp_grid((blocks + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), kCtaThreads, 0, stream>>>(
-        (const Storage<T>*)a, (const Storage<T>*)b, packed, scales, rows, rows_total, cols, global_scale, blk_mn, chunk);
-}
-
-extern "C" {
 
 int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
                         float global_scale, int blk_mn, int chunk, int dtype) {
@@ -542,10 +432,10 @@ int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, ui
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {
-        launch_quantise_generic<Bf16, false>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
+        launch_quantise_generic<Bf16, kActNone>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
                                              global_scale, blk_mn, chunk);
     } else {
-        launch_quantise_generic<F32, false>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
+        launch_quantise_generic<F32, kActNone>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
                                             global_scale, blk_mn, chunk);
     }
     return check_launch(what);
@@ -576,18 +466,18 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
         // among 1-3 units x 2-5 CTAs (38.9 us against 40.7 to 45.3 us at 8,192 x 6144).
         constexpr int kUnits = 1, kMinCtas = 3;
         static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(swiglu_quant_hot_kernel<kUnits, kMinCtas>, 0, occ);
+        const int per_sm = ctas_per_sm(swiglu_quant_hot_kernel<kUnits, kMinCtas, kActSwiGLU>, 0, occ);
         const size_t ctas = ((size_t)total_units + kUnits * 8 - 1) / (kUnits * 8);
-        launch_hot(swiglu_quant_hot_kernel<kUnits, kMinCtas>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,
+        launch_hot(swiglu_quant_hot_kernel<kUnits, kMinCtas, kActSwiGLU>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,
                    (const uint16_t*)gate, (const uint16_t*)up, packed, scales, live_units, total_units, cols,
                    global_scale, blk_mn, chunk, make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {
-        launch_quantise_generic<Bf16, true>(s, dev, gate, up, packed, scales, rows, rows_total, cols, global_scale,
+        launch_quantise_generic<Bf16, kActSwiGLU>(s, dev, gate, up, packed, scales, rows, rows_total, cols, global_scale,
                                             blk_mn, chunk);
     } else {
-        launch_quantise_generic<F32, true>(s, dev, gate, up, packed, scales, rows, rows_total, cols, global_scale,
+        launch_quantise_generic<F32, kActSwiGLU>(s, dev, gate, up, packed, scales, rows, rows_total, cols, global_scale,
                                            blk_mn, chunk);
     }
     return check_launch(what);
@@ -627,11 +517,11 @@ int clef_rope(clef_stream_t stream, void* out, const void* x, const float* cos_t
     if (dtype == CLEF_BF16 && use_hot() && head_dim % 32 == 0 && rotary_dim % 32 == 0 && hot_items < 0x7fffffffull &&
         aligned(x, 32) && aligned(out, 32)) {
         static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(rope_hot_kernel, 0, occ);
-        launch_hot(rope_hot_kernel, clamp_grid((hot_items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0,
+        const int per_sm = ctas_per_sm(rope_hot_kernel<false>, 0, occ);
+        launch_hot(rope_hot_kernel<false>, clamp_grid((hot_items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0,
                    s, (uint16_t*)out, (const uint16_t*)x, cos_table, sin_table, (uint32_t)hot_items, heads, head_dim,
                    rotary_dim, (const int*)seq_start, (const int*)pos_base, (const int*)pos_map,
-                   make_fast_div((uint32_t)(head_dim / 32)), make_fast_div((uint32_t)heads));
+                   make_fast_div((uint32_t)(head_dim / 32)), make_fast_div((uint32_t)heads), KvCacheDest{});
         return check_launch(what);
     }
     const size_t items = (size_t)rows * heads * ((rotary_dim / 8) + (head_dim - rotary_dim) / 4);
@@ -672,18 +562,18 @@ int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, 
         const FastDiv heads_div = make_fast_div((uint32_t)heads);
         if (gate_out) {
             static std::atomic<int> occ{0};
-            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<true>, 0, occ);
-            launch_hot(qk_norm_rope_hot_kernel<true>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
+            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<true, false>, 0, occ);
+            launch_hot(qk_norm_rope_hot_kernel<true, false>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
                        as_stream(stream), (const uint16_t*)x, weight, cos_table, sin_table, (uint16_t*)out,
                        (uint16_t*)gate_out, (uint32_t)rows, eps, (const int*)seq_start, (const int*)pos_base,
-                       (const int*)pos_map, heads_div);
+                       (const int*)pos_map, heads_div, KvCacheDest{});
         } else {
             static std::atomic<int> occ{0};
-            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<false>, 0, occ);
-            launch_hot(qk_norm_rope_hot_kernel<false>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
+            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<false, false>, 0, occ);
+            launch_hot(qk_norm_rope_hot_kernel<false, false>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
                        as_stream(stream), (const uint16_t*)x, weight, cos_table, sin_table, (uint16_t*)out,
                        (uint16_t*)nullptr, (uint32_t)rows, eps, (const int*)seq_start, (const int*)pos_base,
-                       (const int*)pos_map, heads_div);
+                       (const int*)pos_map, heads_div, KvCacheDest{});
         }
         return check_launch(what);
     }
@@ -691,18 +581,20 @@ int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, 
     const size_t groups = ((size_t)rows + 7) / 8;
     if (dtype == CLEF_BF16) {
         static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(qk_norm_rope_generic_kernel<Bf16>, smem, occ);
-        qk_norm_rope_generic_kernel<Bf16><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem,
+        const int per_sm = ctas_per_sm(qk_norm_rope_generic_kernel<Bf16, Bf16, false>, smem, occ);
+        qk_norm_rope_generic_kernel<Bf16, Bf16, false><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem,
                                             as_stream(stream)>>>((const uint16_t*)x, weight, cos_table, sin_table,
                                                                  (uint16_t*)out, (uint16_t*)gate_out, rows, heads,
-                                                                 head_dim, rotary_dim, eps, seq_start, pos_base, pos_map);
+                                                                 head_dim, rotary_dim, eps, seq_start, pos_base, pos_map,
+                                                                 nullptr, nullptr);
     } else {
         static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(qk_norm_rope_generic_kernel<F32>, smem, occ);
-        qk_norm_rope_generic_kernel<F32><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem,
+        const int per_sm = ctas_per_sm(qk_norm_rope_generic_kernel<F32, F32, false>, smem, occ);
+        qk_norm_rope_generic_kernel<F32, F32, false><<<clamp_grid(groups, (size_t)dev.sms * per_sm), kCtaThreads, smem,
                                            as_stream(stream)>>>((const float*)x, weight, cos_table, sin_table,
                                                                 (float*)out, (float*)gate_out, rows, heads, head_dim,
-                                                                rotary_dim, eps, seq_start, pos_base, pos_map);
+                                                                rotary_dim, eps, seq_start, pos_base, pos_map, nullptr,
+                                                                nullptr);
     }
     return check_launch(what);
 }

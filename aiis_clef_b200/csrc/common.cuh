@@ -207,4 +207,15 @@ __host__ __device__ __forceinline__ int ref_threads_per_row(int cols) {
 __device__ __forceinline__ float silu_ieee_div(float g) { return __fdiv_rn(g, __fadd_rn(1.0f, __expf(-g))); }
 __device__ __forceinline__ float silu_fast_div(float g) { return __fdividef(g, __fadd_rn(1.0f, __expf(-g))); }
 
+// The two gated products that share one kernel structure. First input g, second input x:
+//   kActSwiGLU      (g / (1 + __expf(-g))) * x          kernels/elementwise.cu:225-241, g = gate, x = up
+//   kActSigmoidMul  x * 1.0f / (1.0f + __expf(-g))      kernels/elementwise.cu:344-353, g = gate, x = attention output
+enum GatedAct { kActNone = -1, kActSwiGLU = 0, kActSigmoidMul = 1 };
+
+template <int ACT>
+__device__ __forceinline__ float gated_literal(float g, float x) {
+    return ACT == kActSwiGLU ? silu_ieee_div(g) * x : __fdiv_rn(x * 1.0f, __fadd_rn(1.0f, __expf(-g)));
+}
+
+
 }  // namespace clef

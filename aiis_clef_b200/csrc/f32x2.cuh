@@ -33,4 +33,11 @@ __device__ __forceinline__ float max3_abs_nan(float acc, float a, float b) {
     return r;
 }
 
+// 3-input minimum of magnitudes: min(acc, |a|, |b|); a NaN input is ignored.
+__device__ __forceinline__ float min3_abs(float acc, float a, float b) {
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(acc), "f"(fabsf(a)), "f"(fabsf(b)));
+    return r;
+}
+
 }  // namespace clef

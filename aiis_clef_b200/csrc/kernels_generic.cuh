@@ -235,10 +235,11 @@ swiglu_generic_kernel(const typename T::storage* __restrict__ gate, const typena
 }
 
 // ---------------------------------------------------------------------------------------------
-// quantise_nvfp4 (kernels/quantise.cu:6-53) and swiglu_quantise_nvfp4 (kernels/quantise.cu:523-591):
+// quantise_nvfp4 (kernels/quantise.cu:6-53), swiglu_quantise_nvfp4 (kernels/quantise.cu:523-591) and
+// sigmoid_mul (kernels/elementwise.cu:344-359) followed by quantise_nvfp4:
 // one thread per 16-value block, rows in [0, rows_total) written, pad rows zeroed.
 // ---------------------------------------------------------------------------------------------
-template <typename T, bool SWIGLU>
+template <typename T, int ACT>
 __global__ void __launch_bounds__(kCtaThreads)
 quantise_generic_kernel(const typename T::storage* __restrict__ a, const typename T::storage* __restrict__ b,
                         uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows, int rows_total, int cols,
@@ -256,12 +257,12 @@ quantise_generic_kernel(const typename T::storage* __restrict__ a, const typenam
         if (row < rows) {
             float v[16];
             load_block16<T>(a + (size_t)row * cols + blk * 16, v);
-            if (SWIGLU) {
+            if (ACT != kActNone) {   // a = gate, b = up (SwiGLU) or the gated values (sigmoid_mul)
                 float u[16];
                 load_block16<T>(b + (size_t)row * cols + blk * 16, u);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    v[i] = silu_ieee_div(v[i]) * u[i];
+                    v[i] = gated_literal<(ACT == kActNone ? kActSwiGLU : ACT)>(v[i], u[i]);
                 }
             }
             quantise16(v, global_scale, s_inv, stored, lo, hi);
@@ -323,14 +324,17 @@ rope_generic_kernel(typename T::storage* __restrict__ out, const typename T::sto
 // qk_norm_rope (kernels/elementwise.cu:70-142), any head_dim: one warp per head row; the row is
 // normalised with the (1 + w) weight, staged in shared memory, rotated, and written; with
 // gate_out the input row is [q | gate] and the gate half is copied out.
-template <typename T>
+// TO is the storage type of `out` (T itself, or Bf16 when the rows go to a KV cache); with KV the head rows of
+// token t are written at cache row cache_map[t], or t + *cache_len without a map (kernels/attention_mma.cu:118-171).
+template <typename T, typename TO, bool KV>
 __global__ void __launch_bounds__(kCtaThreads)
 qk_norm_rope_generic_kernel(const typename T::storage* __restrict__ x, const float* __restrict__ weight,
                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                            typename T::storage* __restrict__ out, typename T::storage* __restrict__ gate_out,
+                            typename TO::storage* __restrict__ out, typename T::storage* __restrict__ gate_out,
                             int rows, int heads, int head_dim, int rotary_dim, float eps,
                             const int* __restrict__ seq_start, const int* __restrict__ pos_base,
-                            const int* __restrict__ pos_map) {
+                            const int* __restrict__ pos_map, const int* __restrict__ cache_map,
+                            const int* __restrict__ cache_len) {
     extern __shared__ float s_rows[];   // 8 warps x head_dim floats
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -386,9 +390,14 @@ qk_norm_rope_generic_kernel(const typename T::storage* __restrict__ x, const flo
             r[p + half] = ohi;
         }
         __syncwarp();
-        typename T::storage* orow = out + (size_t)row * head_dim;
+        size_t out_row = (size_t)row;
+        if (KV) {
+            const size_t cache_row = cache_map ? (size_t)cache_map[t] : (size_t)t + (size_t)(cache_len ? cache_len[0] : 0);
+            out_row = cache_row * (size_t)heads + (size_t)(row - t * heads);
+        }
+        typename TO::storage* orow = out + out_row * head_dim;
         for (int i = lane; i < c4; i += 32) {
-            store_quad<T>(orow, i, *reinterpret_cast<const float4*>(r + 4 * i));
+            store_quad<TO>(orow, i, *reinterpret_cast<const float4*>(r + 4 * i));
         }
         if (gate_out) {
             typename T::storage* grow = gate_out + (size_t)row * head_dim;
@@ -405,7 +414,7 @@ qk_norm_rope_generic_kernel(const typename T::storage* __restrict__ x, const flo
 }
 
 // embed_gather (kernels/elementwise.cu:396-407): out[t, :] = table[ids[t], :], 16 bytes per thread.
-__global__ void __launch_bounds__(kCtaThreads)
+static __global__ void __launch_bounds__(kCtaThreads)
 embed_gather_generic_kernel(const uint8_t* __restrict__ table, const int* __restrict__ ids, uint8_t* __restrict__ out,
                             int tokens, size_t row_bytes) {
     const size_t vecs_per_row = row_bytes >> 4;
@@ -420,7 +429,7 @@ embed_gather_generic_kernel(const uint8_t* __restrict__ table, const int* __rest
 }
 
 // rope_tables (kernels/elementwise.cu:446-462): cos/sin of pos / theta^(2i/rot), both halves alike.
-__global__ void __launch_bounds__(kCtaThreads)
+static __global__ void __launch_bounds__(kCtaThreads)
 rope_tables_kernel(const int* __restrict__ positions, float* __restrict__ cos_out, float* __restrict__ sin_out,
                    int rows, int rotary_dim, float theta) {
     const int half = rotary_dim / 2;

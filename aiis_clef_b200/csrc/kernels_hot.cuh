@@ -47,6 +47,17 @@ __device__ __forceinline__ void unpack16_quadpairs(const U8x32& d, f32x2* v) {
     }
 }
 
+// Quad-pair registers of one block -> 32 bytes of bf16 in natural order (round to nearest even).
+__device__ __forceinline__ U8x32 pack16_bf16(const f32x2* v) {
+    U8x32 o;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        o.w[2 * q] = pack_bf16x2(v[2 * q].x, v[2 * q + 1].x);       // (x, y)
+        o.w[2 * q + 1] = pack_bf16x2(v[2 * q].y, v[2 * q + 1].y);   // (z, w)
+    }
+    return o;
+}
+
 // Sum of squares of the 4 quads of a block, reference association and contraction:
 // quad = fma(x,x,y*y) + fma(z,z,w*w).
 __device__ __forceinline__ void quad_squares(const f32x2* v, float* quad) {
@@ -118,7 +129,7 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
 
 // Cold path shared by the kernels: the caller has the block's 16 f32 values recomputed in natural
 // order; quantise them literally and store codes and scale.
-__device__ __noinline__ void quantise16_cold_store(const float* a, float global_scale, uint2* packed_dst,
+static __device__ __noinline__ void quantise16_cold_store(const float* a, float global_scale, uint2* packed_dst,
                                                    uint8_t* scale_dst) {
     uint32_t stored, lo, hi;
     quantise16_rare(a, global_scale, stored, lo, hi);
@@ -175,7 +186,7 @@ __device__ __forceinline__ float inv_rms_pow2(float total, float eps) {
 }
 
 // Cold path of one RMSNorm block: recompute from global memory in natural order, literal quantiser.
-__device__ __noinline__ void rms_block_cold(const uint16_t* xblk, const float* wblk, float inv, float global_scale,
+static __device__ __noinline__ void rms_block_cold(const uint16_t* xblk, const float* wblk, float inv, float global_scale,
                                             uint2* packed_dst, uint8_t* scale_dst) {
     float a[16];
 #pragma unroll
@@ -188,11 +199,16 @@ __device__ __noinline__ void rms_block_cold(const uint16_t* xblk, const float* w
 #ifndef CLEF_RMS_MIN_CTAS
 #define CLEF_RMS_MIN_CTAS 2
 #endif
-template <int NB>
+// With ADD the row that is normalised is bf16(x + addend) (the residual add of kernels/head.cu:117-129 fused
+// in front); that sum is also written to sum_out, which may be x itself. The sum is rounded to bf16 before
+// the norm, so the result equals the add followed by the plain kernel on the stored residual. This variant
+// loads at the top of each row instead of one row ahead (two inputs would not fit the register budget).
+template <int NB, bool ADD>
 __global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? CLEF_RMS_MIN_CTAS : 1))
-rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight,
-                          uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows, int rows_total,
-                          float eps, float global_scale, int blk_mn, int chunk, FastDiv atom_div) {
+rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ addend, uint16_t* sum_out,
+                          const float* __restrict__ weight, uint8_t* __restrict__ packed,
+                          uint8_t* __restrict__ scales, int rows, int rows_total, float eps, float global_scale,
+                          int blk_mn, int chunk, FastDiv atom_div) {
     constexpr int COLS = NB * 512;
     constexpr int BLOCKS = COLS / 16;
     __shared__ float s_inv[kInvScaleTableSize];
@@ -212,7 +228,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
     pdl_wait_prior_grids();
     int row = blockIdx.x * 8 + warp;
     U8x32 d[NB];
-    if (row < rows) {
+    if (!ADD && row < rows) {
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
             d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
@@ -242,10 +258,29 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
 #pragma unroll
             for (int k = 0; k < 4; ++k) p[j0][k] = 0.0f;
         }
+        U8x32 e[ADD ? NB : 1];
+        if (ADD) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
+                e[j] = ldg_stream_v8(addend + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
+            }
+        }
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
             float quad[4];
             unpack16_quadpairs(d[j], v[j]);
+            if (ADD) {
+                f32x2 t[8];
+                unpack16_quadpairs(e[j], t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    v[j][i] = f2_add(v[j][i], t[i]);
+                }
+                const U8x32 sum = pack16_bf16(v[j]);
+                stg_v8(sum_out + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16, sum);
+                unpack16_quadpairs(sum, v[j]);
+            }
             quad_squares(v[j], quad);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -254,7 +289,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
         }
         // The raw registers are free now: fetch this warp's next row while the current one is processed.
         const int next = row + gridDim.x * 8;
-        if (next < rows) {
+        if (!ADD && next < rows) {
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
                 d[j] = ldg_stream_v8(x + (size_t)next * COLS + (size_t)(lane + 32 * j) * 16);
@@ -284,7 +319,9 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const float* __restric
                 *pdst = make_uint2(lo[j], hi[j]);
                 *sdst = (uint8_t)stored[j];
             } else {
-                rms_block_cold(x + (size_t)row * COLS + b * 16, weight + b * 16, inv, global_scale, pdst, sdst);
+                // ADD: this lane stored the block's sum above, so it reads its own bytes back.
+                rms_block_cold((ADD ? (const uint16_t*)sum_out : x) + (size_t)row * COLS + b * 16, weight + b * 16, inv,
+                               global_scale, pdst, sdst);
             }
         }
     }
@@ -334,6 +371,20 @@ __device__ __forceinline__ f32x2 silu_approx_fast_x2(f32x2 g2) {
     return f2_mul(g2, make_float2(rcp_approx(d2.x), rcp_approx(d2.y)));
 }
 
+// (g, x) -> x / (1 + __expf(-g)) per lane with the IEEE quotient (kernels/elementwise.cu:344-353, the
+// vector path), short form: the construction of silu_ieee_fast_x2 with numerator x. Domain: bf16 g
+// with |g| <= 44 and bf16 x that is zero or has 2^-60 <= |x| < inf, which keeps the quotient and the
+// remainder normal numbers (all such pairs are compared on the device by the tests).
+constexpr float kSigmoidMulMinAbs = 8.67361738e-19f;   // 2^-60
+__device__ __forceinline__ f32x2 sigmoid_mul_fast_x2(f32x2 g2, f32x2 x2) {
+    const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));
+    const f32x2 d2 = f2_add(f2_splat(1.0f), make_float2(ex2_approx(t2.x), ex2_approx(t2.y)));
+    const f32x2 r2 = make_float2(rcp_approx(d2.x), rcp_approx(d2.y));
+    const f32x2 q0 = f2_mul(x2, r2);
+    const f32x2 rem = f2_fma(make_float2(-d2.x, -d2.y), q0, x2);
+    return f2_fma(rem, r2, q0);
+}
+
 // max |g| over a block in the quad-pair layout, NaN if any value is NaN.
 __device__ __forceinline__ float block_abs_max(const f32x2* g) {
     float m = 0.0f;
@@ -344,17 +395,65 @@ __device__ __forceinline__ float block_abs_max(const f32x2* g) {
     return m;
 }
 
-__device__ __noinline__ void swiglu_block_cold(const uint16_t* gblk, const uint16_t* ublk, float global_scale,
-                                               uint2* packed_dst, uint8_t* scale_dst) {
+__device__ __forceinline__ float block_abs_min(const f32x2* x) {
+    float m = INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        m = min3_abs(m, x[i].x, x[i].y);
+    }
+    return m;
+}
+
+// True if a block of 16 bf16 values holds a non-zero value of magnitude below kSigmoidMulMinAbs. Rarely
+// evaluated, so it re-reads the block from global memory instead of tying up the caller's registers.
+static __device__ __noinline__ bool block_has_tiny_nonzero(const uint16_t* xblk) {
+    constexpr uint32_t kMinBits = 0x2180u;   // bf16 pattern of 2^-60
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t m = xblk[i] & 0x7fffu;
+        bad |= (m - 1u) < (kMinBits - 1u);
+    }
+    return bad;
+}
+
+// Whether a block may take the short form; xblk addresses the block's x values in global memory.
+// FINITE_X: also require finite x (kernels whose result is not checked by the quantiser afterwards).
+template <int ACT, bool FINITE_X>
+__device__ __forceinline__ bool gated_fast_domain(const f32x2* g, const f32x2* x, const uint16_t* xblk) {
+    bool ok = block_abs_max(g) <= kSiluFastMaxAbs;
+    if (ACT == kActSigmoidMul) {
+        if (FINITE_X) {
+            ok = ok && block_abs_max(x) < INFINITY;
+        }
+        if (ok && block_abs_min(x) < kSigmoidMulMinAbs) {
+            ok = !block_has_tiny_nonzero(xblk);
+        }
+    }
+    return ok;
+}
+
+// g <- act(g, x) for a block inside the short form's domain.
+template <int ACT>
+__device__ __forceinline__ void gated_fast(f32x2* g, const f32x2* x) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        g[i] = ACT == kActSwiGLU ? f2_mul(silu_ieee_fast_x2(g[i]), x[i]) : sigmoid_mul_fast_x2(g[i], x[i]);
+    }
+}
+
+template <int ACT>
+__device__ __noinline__ void gated_act_block_cold(const uint16_t* gblk, const uint16_t* xblk, float global_scale,
+                                                  uint2* packed_dst, uint8_t* scale_dst) {
     float a[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        a[i] = silu_ieee_div(__uint_as_float((uint32_t)gblk[i] << 16)) * __uint_as_float((uint32_t)ublk[i] << 16);
+        a[i] = gated_literal<ACT>(__uint_as_float((uint32_t)gblk[i] << 16), __uint_as_float((uint32_t)xblk[i] << 16));
     }
     quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
 }
 
-template <int UNITS, int MIN_CTAS>
+template <int UNITS, int MIN_CTAS, int ACT>
 __global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
 swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up,
                         uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t live_units,
@@ -409,18 +508,15 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
             }
             uint32_t stored, lo, hi;
             bool done = false;
-            if (block_abs_max(gv) <= kSiluFastMaxAbs) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    gv[i] = f2_mul(silu_ieee_fast_x2(gv[i]), uv[i]);
-                }
+            if (gated_fast_domain<ACT, false>(gv, uv, up + (size_t)unit * 512 + lane * 16)) {
+                gated_fast<ACT>(gv, uv);
                 done = quantise16_qp<false>(gv, global_scale, s_inv, stored, lo, hi);
             }
             if (done) {
                 *pdst = make_uint2(lo, hi);
                 *sdst = (uint8_t)stored;
             } else {
-                swiglu_block_cold(gate + (size_t)unit * 512 + lane * 16, up + (size_t)unit * 512 + lane * 16, global_scale,
+                gated_act_block_cold<ACT>(gate + (size_t)unit * 512 + lane * 16, up + (size_t)unit * 512 + lane * 16, global_scale,
                                   pdst, sdst);
             }
         }
@@ -456,7 +552,7 @@ __device__ __forceinline__ float head_tree_32(const float* quad_a, const float* 
     return u;
 }
 
-__device__ __noinline__ void gated_block_cold(const uint16_t* xblk, const uint16_t* gblk, const float* wblk, float inv,
+static __device__ __noinline__ void gated_block_cold(const uint16_t* xblk, const uint16_t* gblk, const float* wblk, float inv,
                                               float global_scale, uint2* packed_dst, uint8_t* scale_dst) {
     float a[16];
 #pragma unroll
@@ -467,7 +563,7 @@ __device__ __noinline__ void gated_block_cold(const uint16_t* xblk, const uint16
     quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
 }
 
-__global__ void __launch_bounds__(kCtaThreads, 2)
+static __global__ void __launch_bounds__(kCtaThreads, 2)
 gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
                             const float* __restrict__ weight, uint8_t* __restrict__ packed,
                             uint8_t* __restrict__ scales, int rows_live, int rows_total, float eps,
@@ -569,7 +665,7 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
 // Plain NVFP4 quantiser (kernels/quantise.cu:6-53) for cols % 512 == 0: the SwiGLU kernel's unit
 // structure with one input.
 // ---------------------------------------------------------------------------------------------
-__device__ __noinline__ void quantise_block_cold(const uint16_t* xblk, float global_scale, uint2* packed_dst,
+static __device__ __noinline__ void quantise_block_cold(const uint16_t* xblk, float global_scale, uint2* packed_dst,
                                                  uint8_t* scale_dst) {
     float a[16];
 #pragma unroll
@@ -634,17 +730,6 @@ quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed
             }
         }
     }
-}
-
-// Quad-pair registers of one block -> 32 bytes of bf16 in natural order (round to nearest even).
-__device__ __forceinline__ U8x32 pack16_bf16(const f32x2* v) {
-    U8x32 o;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        o.w[2 * q] = pack_bf16x2(v[2 * q].x, v[2 * q + 1].x);       // (x, y)
-        o.w[2 * q + 1] = pack_bf16x2(v[2 * q].y, v[2 * q + 1].y);   // (z, w)
-    }
-    return o;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -730,6 +815,7 @@ rms_norm_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
 // literal expression. `blocks` = total / 16; a tail of total % 16 values is left to the caller
 // (the launcher runs the shape-general kernel on it).
 // ---------------------------------------------------------------------------------------------
+template <int ACT>
 __global__ void __launch_bounds__(kCtaThreads, 4)
 swiglu_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up, uint16_t* __restrict__ out,
                   uint32_t blocks) {
@@ -751,15 +837,12 @@ swiglu_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict_
             g = ldg_stream_v8(gate + (size_t)next * 16);
             u = ldg_stream_v8(up + (size_t)next * 16);
         }
-        if (block_abs_max(gv) <= kSiluFastMaxAbs) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                gv[i] = f2_mul(silu_ieee_fast_x2(gv[i]), uv[i]);
-            }
+        if (gated_fast_domain<ACT, true>(gv, uv, up + (size_t)b * 16)) {
+            gated_fast<ACT>(gv, uv);
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                gv[i] = make_float2(silu_ieee_div(gv[i].x) * uv[i].x, silu_ieee_div(gv[i].y) * uv[i].y);
+                gv[i] = make_float2(gated_literal<ACT>(gv[i].x, uv[i].x), gated_literal<ACT>(gv[i].y, uv[i].y));
             }
         }
         stg_v8(out + (size_t)b * 16, pack16_bf16(gv));
@@ -770,7 +853,7 @@ swiglu_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict_
 // Gated RMSNorm with bf16 output for 128-wide rows (kernels/elementwise.cu:144-223): the quantising
 // kernel's layout (4 lanes per row) and tree; weight and gate are both present on this path.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kCtaThreads, 2)
+static __global__ void __launch_bounds__(kCtaThreads, 2)
 gated_norm_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
                       const float* __restrict__ weight, uint16_t* __restrict__ out, int rows, float eps) {
     constexpr int COLS = 128;
@@ -847,22 +930,49 @@ gated_norm_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict
 // (head_dim - rotary_dim)/32 "copy" items (two pass-through chunks each); one lane per item, so
 // every lane moves 64 bytes in and 64 bytes out.
 // ---------------------------------------------------------------------------------------------
+// Where a token's key / value row goes in a KV cache of bf16 rows (kernels/attention_mma.cu:118-171): row
+// cache_map[token] when a map is given, else token + *cache_len (0 without a length).
+struct KvCacheDest {
+    const int* cache_map;
+    const int* cache_len;
+    const uint16_t* v;    // value rows, same [tokens, heads, head_dim] shape as the keys
+    uint16_t* cache_v;
+};
+__device__ __forceinline__ size_t kv_cache_row(int token, const int* cache_map, const int* cache_len) {
+    return cache_map ? (size_t)cache_map[token] : (size_t)token + (size_t)(cache_len ? cache_len[0] : 0);
+}
+
+// With KV: `out` is the key cache; total_items counts the items of the key rows followed by as many items of
+// the value rows kv.v (every item of a value row is a copy item), and both land at the token's cache row.
+template <bool KV>
 __global__ void __launch_bounds__(kCtaThreads)
 rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, const float* __restrict__ cos_t,
                 const float* __restrict__ sin_t, uint32_t total_items, int heads, int head_dim, int rotary_dim,
                 const int* __restrict__ seq_start, const int* __restrict__ pos_base,
-                const int* __restrict__ pos_map, FastDiv items_div, FastDiv heads_div) {
+                const int* __restrict__ pos_map, FastDiv items_div, FastDiv heads_div, KvCacheDest kv) {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
     const uint32_t rot_items = rotary_dim >> 5;
     const uint32_t stride = gridDim.x * blockDim.x;
+    const uint32_t key_head_rows = KV ? fast_div(total_items >> 1, items_div) : 0u;
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_items; idx += stride) {
-        const uint32_t head_row = fast_div(idx, items_div);
-        const uint32_t item = idx - head_row * items_div.d;
-        const uint16_t* xr = x + (size_t)head_row * head_dim;
+        uint32_t head_row = fast_div(idx, items_div);
+        uint32_t item = idx - head_row * items_div.d;
+        const bool is_value = KV && head_row >= key_head_rows;
+        if (is_value) {
+            head_row -= key_head_rows;
+            item += rot_items;   // a copy item; its column offset is corrected below
+        }
+        const uint16_t* xr = (is_value ? kv.v : x) + (size_t)head_row * head_dim;
         uint16_t* orow = out + (size_t)head_row * head_dim;
+        int row = 0;
+        if (KV) {
+            row = (int)fast_div(head_row, heads_div);
+            orow = (is_value ? kv.cache_v : out) +
+                   (kv_cache_row(row, kv.cache_map, kv.cache_len) * (size_t)heads + (head_row - (uint32_t)row * heads)) * head_dim;
+        }
         if (item < rot_items) {
-            const int row = (int)fast_div(head_row, heads_div);
+            if (!KV) row = (int)fast_div(head_row, heads_div);
             const int pos = rope_position(row, seq_start, pos_base, pos_map);
             const int half = rotary_dim >> 1;
             const U8x32 dlo = ldg_stream_v8(xr + item * 16);
@@ -888,7 +998,7 @@ rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, cons
             stg_v8(orow + item * 16, olo);
             stg_v8(orow + half + item * 16, ohi);
         } else {
-            const int c0 = rotary_dim + (int)(item - rot_items) * 32;
+            const int c0 = (is_value ? 0 : rotary_dim) + (int)(item - rot_items) * 32;
             const U8x32 a = ldg_stream_v8(xr + c0);
             const U8x32 b = ldg_stream_v8(xr + c0 + 16);
             stg_v8(orow + c0, a);
@@ -905,13 +1015,20 @@ rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, cons
 // partner's RAW bf16 words cross by shuffle and both lanes normalise both halves. With `gate_out`
 // the input row is [q | gate] and the gate half is copied.
 // ---------------------------------------------------------------------------------------------
-template <bool GATE>
+// With KV (GATE must be false, rows % 8 == 0): `out` is the key cache, the head rows of token t are written at
+// cache row kv_cache_row(t), and the value rows ride along as head rows [rows, 2 rows) that are copied to the
+// value cache at the same cache row, so one launch fills both caches.
+template <bool GATE, bool KV>
 __global__ void __launch_bounds__(kCtaThreads, 2)
 qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint16_t* __restrict__ out,
                         uint16_t* __restrict__ gate_out, uint32_t rows, float eps, const int* __restrict__ seq_start,
-                        const int* __restrict__ pos_base, const int* __restrict__ pos_map, FastDiv heads_div) {
+                        const int* __restrict__ pos_base, const int* __restrict__ pos_map, FastDiv heads_div,
+                        KvCacheDest kv) {
+    static_assert(!(GATE && KV), "the key side has no gate half");
     constexpr int HD = 128, ROT = 64, STRIDE = GATE ? 2 * HD : HD;
+    const uint32_t key_rows = rows;
+    if (KV) rows *= 2;
     __shared__ float4 s_w[32];   // (1 + w), quad-pair layout: s_w[c * 4 + q] for chunk c, quad q
     const int lane = threadIdx.x & 31;
     const int m = lane & 3;
@@ -923,17 +1040,35 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
         s_w[threadIdx.x] = make_float4(1.0f + t.x, 1.0f + t.z, 1.0f + t.y, 1.0f + t.w);
     }
     pdl_wait_prior_grids();
+    auto row_ptr = [&](uint32_t r) {
+        return (KV && r >= key_rows) ? kv.v + (size_t)(r - key_rows) * HD : x + (size_t)r * STRIDE;
+    };
     U8x32 d[2], dgate[2];
     if (hrow < rows) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            d[h] = ldg_stream_v8(x + (size_t)hrow * STRIDE + (m + 4 * h) * 16);
+            d[h] = ldg_stream_v8(row_ptr(hrow) + (m + 4 * h) * 16);
             if (GATE) dgate[h] = ldg_stream_v8(x + (size_t)hrow * STRIDE + HD + (m + 4 * h) * 16);
         }
     }
     __syncthreads();
     for (uint32_t base = hrow - (uint32_t)(lane >> 2); base < rows; base += groups_in_grid, hrow += groups_in_grid) {
         const bool live = hrow < rows;
+        if (KV && base >= key_rows) {   // a warp of value rows (warp-uniform: key_rows % 8 == 0): copy and go on
+            if (live) {
+                const uint32_t vrow = hrow - key_rows;
+                const int token = (int)fast_div(vrow, heads_div);
+                const size_t dst = (kv_cache_row(token, kv.cache_map, kv.cache_len) * heads_div.d + (vrow - (uint32_t)token * heads_div.d)) * HD;
+                stg_v8(kv.cache_v + dst + m * 16, d[0]);
+                stg_v8(kv.cache_v + dst + (m + 4) * 16, d[1]);
+            }
+            const uint32_t next_v = hrow + groups_in_grid;
+            if (next_v < rows) {
+                d[0] = ldg_stream_v8(row_ptr(next_v) + m * 16);
+                d[1] = ldg_stream_v8(row_ptr(next_v) + (m + 4) * 16);
+            }
+            continue;
+        }
         f32x2 v[2][8], pv[8];
         float quad[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         U8x32 praw;
@@ -956,7 +1091,7 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
         if (next < rows) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                d[h] = ldg_stream_v8(x + (size_t)next * STRIDE + (m + 4 * h) * 16);
+                d[h] = ldg_stream_v8(row_ptr(next) + (m + 4 * h) * 16);
                 if (GATE) dgate[h] = ldg_stream_v8(x + (size_t)next * STRIDE + HD + (m + 4 * h) * 16);
             }
         }
@@ -997,8 +1132,10 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
                 v[0][i] = f2_fma(lo, holds_lo ? c2 : s2, t);
             }
         }
-        stg_v8(out + (size_t)hrow * HD + m * 16, pack16_bf16(v[0]));
-        stg_v8(out + (size_t)hrow * HD + (m + 4) * 16, pack16_bf16(v[1]));
+        const size_t orow = KV ? (kv_cache_row(token, kv.cache_map, kv.cache_len) * heads_div.d + (hrow - (uint32_t)token * heads_div.d)) * HD
+                               : (size_t)hrow * HD;
+        stg_v8(out + orow + m * 16, pack16_bf16(v[0]));
+        stg_v8(out + orow + (m + 4) * 16, pack16_bf16(v[1]));
     }
 }
 

@@ -143,7 +143,7 @@ __device__ __forceinline__ float amax_nan(float acc, float v) {
 
 // Literal path for one block of 16: the reference recipe with NaN-ignoring fmaxf, the literal
 // E2M1 rule and a literal walk of the E4M3 encoder for a non-finite scale argument.
-__device__ __noinline__ void quantise16_rare(const float* v, float global_scale, uint32_t& stored_out,
+static __device__ __noinline__ void quantise16_rare(const float* v, float global_scale, uint32_t& stored_out,
                                              uint32_t& lo_out, uint32_t& hi_out) {
     float amax = 0.0f;
 #pragma unroll

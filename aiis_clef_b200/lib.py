@@ -47,6 +47,14 @@ SYMBOLS = {
     "clef_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
     "clef_rms_norm_gated_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I, _I, _I]),
     "clef_swiglu_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
+    "clef_to_bf16": (_I, [_P, _P, _P, _SZ, _P, _I, _I]),
+    "clef_to_bf16_scatter": (_I, [_P, _P, _P, _SZ, _P, _I, _I]),
+    "clef_rope_kv_write": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I]),
+    "clef_qk_norm_rope_kv_write": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _I]),
+    "clef_sigmoid_mul": (_I, [_P, _P, _P, _P, _SZ, _I]),
+    "clef_sigmoid_mul_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
+    "clef_add": (_I, [_P, _P, _P, _P, _SZ, _I]),
+    "clef_add_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
     "clef_set_kernel_choice": (None, [_I]),
 }
 
@@ -280,6 +288,92 @@ class Device:
                                                             _ptr(scales), rows, cols, global_scale, blk_mn, chunk,
                                                             _dtype_code(gate)), "clef_swiglu_quantise_nvfp4")
         return None if st == CLEF_DECLINED else (packed, scales)
+
+    # ==== the steps either side of the fused quantisers ==========================================
+
+    # -- src/cuda/mod.rs:1462-1465, 3201-3227 (to_bf16_kernel) ---------------------------------
+    def to_bf16_dev(self, x, total: int, out=None, off_tokens=None, off_stride: int = 0):
+        """bf16 copy of `x`; with `out` (a cache) and `off_tokens` it is written at *off_tokens * off_stride."""
+        _dev_tensor(x, "x")
+        if out is None:
+            out = self._empty((total,), torch.bfloat16)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_to_bf16(_stream(), _ptr(out), _ptr(x), total, _ptr(off_tokens), off_stride,
+                                         _dtype_code(x)), "clef_to_bf16")
+        return out
+
+    # -- src/cuda/mod.rs:3201-3227 (to_bf16_scatter_kernel) ------------------------------------
+    def to_bf16_scatter_dev(self, out, x, total: int, pos_map, stride: int):
+        _dev_tensor(x, "x"), _dev_tensor(out, "out")
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_to_bf16_scatter(_stream(), _ptr(out), _ptr(x), total, _ptr(pos_map), stride,
+                                                 _dtype_code(x)), "clef_to_bf16_scatter")
+        return out
+
+    def rope_kv_write_dev(self, cache_k, cache_v, k, v, cos, sin, tokens: int, kv_heads: int, head_dim: int,
+                          rotary_dim: int, seq_start=None, pos_base=None, pos_map=None, cache_map=None,
+                          cache_len=None):
+        """rope_apply_dev on k, then k and v into the bf16 caches (in place), one launch."""
+        _dev_tensor(k, "k"), _dev_tensor(v, "v"), _dev_tensor(cache_k, "cache_k"), _dev_tensor(cache_v, "cache_v")
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rope_kv_write(_stream(), _ptr(cache_k), _ptr(cache_v), _ptr(k), _ptr(v), _ptr(cos),
+                                               _ptr(sin), tokens, kv_heads, head_dim, rotary_dim, _ptr(seq_start),
+                                               _ptr(pos_base), _ptr(pos_map), _ptr(cache_map), _ptr(cache_len),
+                                               _dtype_code(k)), "clef_rope_kv_write")
+
+    def qk_norm_rope_kv_write_dev(self, cache_k, cache_v, k_raw, v, weight, cos, sin, tokens: int, kv_heads: int,
+                                  head_dim: int, rotary_dim: int, eps: float, seq_start=None, pos_base=None,
+                                  pos_map=None, cache_map=None, cache_len=None):
+        """qk_norm_rope_dev on k_raw, then k and v into the bf16 caches (in place)."""
+        _dev_tensor(k_raw, "k_raw"), _dev_tensor(v, "v"), _dev_tensor(cache_k, "cache_k"), _dev_tensor(cache_v, "cache_v")
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_qk_norm_rope_kv_write(_stream(), _ptr(cache_k), _ptr(cache_v), _ptr(k_raw), _ptr(v),
+                                                       _ptr(weight), _ptr(cos), _ptr(sin), tokens, kv_heads, head_dim,
+                                                       rotary_dim, eps, _ptr(seq_start), _ptr(pos_base), _ptr(pos_map),
+                                                       _ptr(cache_map), _ptr(cache_len), _dtype_code(k_raw)),
+                   "clef_qk_norm_rope_kv_write")
+
+    # -- src/cuda/mod.rs:2838-2856 ------------------------------------------------------------
+    def sigmoid_mul_dev(self, x, gate, total: int):
+        _dev_tensor(x, "x"), _dev_tensor(gate, "gate")
+        out = self._empty((total,), x.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_sigmoid_mul(_stream(), _ptr(out), _ptr(x), _ptr(gate), total, _dtype_code(x)),
+                   "clef_sigmoid_mul")
+        return out
+
+    def sigmoid_mul_quantise_nvfp4_dev(self, x, gate, rows: int, cols: int, global_scale: float, tile_m: int):
+        """sigmoid_mul_dev followed by quantise_nvfp4_dev, one launch."""
+        _dev_tensor(x, "x"), _dev_tensor(gate, "gate")
+        blk_mn, chunk, _, packed, scales = self._quant_outputs(rows, cols, tile_m)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_sigmoid_mul_quantise_nvfp4(_stream(), _ptr(x), _ptr(gate), _ptr(packed), _ptr(scales),
+                                                            rows, cols, global_scale, blk_mn, chunk, _dtype_code(x)),
+                   "clef_sigmoid_mul_quantise_nvfp4")
+        return packed, scales
+
+    # -- src/cuda/mod.rs:1686-1704 ------------------------------------------------------------
+    def add_dev(self, a, b, total: int, out=None):
+        _dev_tensor(a, "a"), _dev_tensor(b, "b")
+        if out is None:
+            out = self._empty((total,), a.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_add(_stream(), _ptr(out), _ptr(a), _ptr(b), total, _dtype_code(a)), "clef_add")
+        return out
+
+    def add_rms_norm_quantise_nvfp4_dev(self, a, b, weight, rows: int, cols: int, eps: float, global_scale: float,
+                                        tile_m: int, sum_out=None):
+        """add_dev followed by rms_norm_quantise_nvfp4_dev on the stored sum, one pass; returns (sum, packed, scales)."""
+        _dev_tensor(a, "a"), _dev_tensor(b, "b")
+        if sum_out is None:
+            sum_out = self._empty((rows, cols), a.dtype)
+        blk_mn, chunk, _, packed, scales = self._quant_outputs(rows, cols, tile_m)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_add_rms_norm_quantise_nvfp4(_stream(), _ptr(sum_out), _ptr(a), _ptr(b), _ptr(weight),
+                                                             _ptr(packed), _ptr(scales), rows, cols, eps, global_scale,
+                                                             blk_mn, chunk, _dtype_code(a)),
+                   "clef_add_rms_norm_quantise_nvfp4")
+        return sum_out, packed, scales
 
 
 # =================================================================================================

@@ -137,6 +137,68 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
                                uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
                                int dtype);
 
+/* ------------------------------------------------------------------------------------------------
+ * The steps either side of the fused quantisers in a layer.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* to_bf16_kernel (kernels/attention_mma.cu:118-146), launched by Device::attention_dev for q and, without
+ * a position map, for k and v (src/cuda/mod.rs:3201-3227): out[off + i] = bf16(x[i]), i < n,
+ * off = *off_tokens_dev * off_stride (0 when the pointer is NULL). Round to nearest even. With
+ * CLEF_BF16 input this is a copy to the offset. out is always bf16. */
+int clef_to_bf16(clef_stream_t stream, void* out, const void* x, size_t n, const int32_t* off_tokens_dev,
+                 int off_stride, int dtype);
+
+/* to_bf16_scatter_kernel (kernels/attention_mma.cu:148-171; KvCache::pos_map, src/cuda/mod.rs:5344-5354,
+ * the engine's `cpos`, src/gpu.rs:1157): token t = i / stride is written at row pos_map[t] of the cache:
+ * out[pos_map[t] * stride + c] = bf16(x[t * stride + c]). stride % 8 == 0, n % stride == 0. */
+int clef_to_bf16_scatter(clef_stream_t stream, void* out, const void* x, size_t n, const int32_t* pos_map,
+                         int stride, int dtype);
+
+/* The key/value side of Device::attention_dev's prologue in one launch: rope_kernel on k
+ * (as clef_rope, same position arguments) followed by the bf16 cache write of k and v
+ * (src/cuda/mod.rs:3201-3227). k, v: [tokens, kv_heads, head_dim]; cache_k, cache_v: bf16 caches with
+ * rows of kv_heads * head_dim values. Token t lands at cache row cache_map[t] (to_bf16_scatter_kernel),
+ * or, with cache_map NULL, at t + *cache_len (to_bf16_kernel; cache_len NULL means 0). Bytes equal
+ * clef_rope into an f32 buffer followed by clef_to_bf16(_scatter). No counterpart as ONE kernel in the
+ * reference. */
+int clef_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_v, const void* k, const void* v,
+                       const float* cos_table, const float* sin_table, int tokens, int kv_heads, int head_dim,
+                       int rotary_dim, const int32_t* seq_start, const int32_t* pos_base, const int32_t* pos_map,
+                       const int32_t* cache_map, const int32_t* cache_len, int dtype);
+
+/* As clef_rope_kv_write with the per-head RMSNorm of qk_norm_rope_kernel in front of the rotation
+ * (the k call of src/gpu.rs:1711-1713): k_raw -> norm with (1 + weight) -> RoPE -> bf16 -> cache. */
+int clef_qk_norm_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_v, const void* k_raw, const void* v,
+                               const float* weight, const float* cos_table, const float* sin_table, int tokens,
+                               int kv_heads, int head_dim, int rotary_dim, float eps, const int32_t* seq_start,
+                               const int32_t* pos_base, const int32_t* pos_map, const int32_t* cache_map,
+                               const int32_t* cache_len, int dtype);
+
+/* sigmoid_mul_kernel (kernels/elementwise.cu:344-359), Device::sigmoid_mul_dev (src/cuda/mod.rs:2838-2856):
+ * out[i] = x[i] * sigmoid(gate[i]) in the reference's two forms (x * 1 / (1 + __expf(-g)) for whole
+ * quads, x * (1 / (1 + __expf(-g))) for the total % 4 tail). */
+int clef_sigmoid_mul(clef_stream_t stream, void* out, const void* x, const void* gate, size_t total, int dtype);
+
+/* sigmoid_mul_kernel followed by quantise_nvfp4_kernel without the round trip: the gated attention output
+ * as the NVFP4 operand of o_proj (src/gpu.rs:1750-1753 with run_projection_dev's quantiser). x and gate
+ * are dense [rows, cols]; bytes equal clef_sigmoid_mul (f32) followed by clef_quantise_nvfp4.
+ * cols % 64 == 0. No counterpart as ONE kernel in the reference. */
+int clef_sigmoid_mul_quantise_nvfp4(clef_stream_t stream, const void* x, const void* gate, uint8_t* packed,
+                                    uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                                    int dtype);
+
+/* add_kernel (kernels/head.cu:117-129), Device::add_dev (src/cuda/mod.rs:1686-1704): out = a + b.
+ * out may be a or b. */
+int clef_add(clef_stream_t stream, void* out, const void* a, const void* b, size_t total, int dtype);
+
+/* The residual add and the next layer's norm + quantiser in one pass over the row: sum = a + b is
+ * written to sum_out (which may be a) in the activation dtype, and rms_norm_quantise_nvfp4 of that stored
+ * sum to packed/scales. Bytes equal clef_add followed by clef_rms_norm_quantise_nvfp4 on sum_out.
+ * No counterpart as ONE kernel in the reference. */
+int clef_add_rms_norm_quantise_nvfp4(clef_stream_t stream, void* sum_out, const void* a, const void* b,
+                                     const float* weight, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                                     float eps, float global_scale, int blk_mn, int chunk, int dtype);
+
 /* Kernel selection for tests and measurements: 0 = automatic (tuned kernel when the shape has one),
  * 1 = always the shape-general kernel. Process-wide; not part of the reference interface. */
 void clef_set_kernel_choice(int choice);

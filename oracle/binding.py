@@ -321,3 +321,39 @@ def swiglu_quantise_nvfp4(gate, up, rows, cols, global_scale, blk_mn=128, chunk=
     load().oracle_swiglu_quantise_nvfp4(_p(gate), _p(up), _p(packed), _p(scales), rows, cols, _f(global_scale),
                                         blk_mn, chunk, _dtype_code(gate), _p(pre), nthreads)
     return (packed, scales, pre) if want_pre else (packed, scales)
+
+
+# ---- the steps either side of the fused quantisers -----------------------------------------------------
+
+def to_bf16_rows(x, out_bits, pos_map=None, off_tokens=None, stride=0):
+    """In place on `out_bits` (uint16 cache): kernels/attention_mma.cu:118-171."""
+    x = _c(x)
+    pos_map = None if pos_map is None else _c(pos_map, np.int32)
+    off = None if off_tokens is None else _c(np.asarray([off_tokens]), np.int32)
+    load().oracle_to_bf16_rows(_p(x), _p(out_bits), _sz(x.size), _p(pos_map), _p(off), int(stride), _dtype_code(x))
+    return out_bits
+
+
+def sigmoid_mul(x, gate, nthreads=0):
+    x, gate = _c(x), _c(gate)
+    f32 = np.empty(x.shape, np.float32)
+    out = np.empty(x.shape, x.dtype)
+    load().oracle_sigmoid_mul(_p(x), _p(gate), _sz(x.size), _dtype_code(x), _p(f32), _p(out), nthreads)
+    return f32, out
+
+
+def sigmoid_mul_quantise_nvfp4(x, gate, rows, cols, global_scale, blk_mn=128, chunk=512, want_pre=False, nthreads=0):
+    x, gate = _c(x), _c(gate)
+    _, packed, scales = _quant_out(rows, cols, blk_mn)
+    pre = np.empty((rows, cols), np.float32) if want_pre else None
+    load().oracle_sigmoid_mul_quantise_nvfp4(_p(x), _p(gate), _p(packed), _p(scales), rows, cols, _f(global_scale),
+                                             blk_mn, chunk, _dtype_code(x), _p(pre), nthreads)
+    return (packed, scales, pre) if want_pre else (packed, scales)
+
+
+def add(a, b):
+    a, b = _c(a), _c(b)
+    f32 = np.empty(a.shape, np.float32)
+    out = np.empty(a.shape, a.dtype)
+    load().oracle_add(_p(a), _p(b), _sz(a.size), _dtype_code(a), _p(f32), _p(out))
+    return f32, out

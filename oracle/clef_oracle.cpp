@@ -55,7 +55,7 @@ inline uint16_t f32_to_bf16_bits(float f) {
     uint32_t u;
     std::memcpy(&u, &f, 4);
     if ((u & 0x7FFFFFFFu) > 0x7F800000u) {
-        return (uint16_t)((u >> 16) | 0x0040u);
+        return (uint16_t)0x7FFFu;   // cvt.rn.bf16.f32 / __float2bfloat16 return the canonical NaN
     }
     return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
 }
@@ -746,6 +746,88 @@ ORACLE_API void oracle_swiglu_quantise_nvfp4(const void* gate, const void* up, u
                 zero_pad_row(r, cols, blk_mn, chunk, packed, scales);
             }
         }
+    }
+}
+
+// kernels/attention_mma.cu:118-171 to_bf16_kernel / to_bf16_scatter_kernel: token t = i / stride of x goes to
+// cache row pos_map[t], or (no map) to t + *off_tokens; out is bf16 (round to nearest even).
+ORACLE_API void oracle_to_bf16_rows(const void* x, uint16_t* out, size_t n, const int32_t* pos_map,
+                                    const int32_t* off_tokens, int stride, int dtype) {
+    const size_t base = (!pos_map && off_tokens) ? (size_t)off_tokens[0] * (size_t)stride : 0;
+    for (size_t i = 0; i < n; ++i) {
+        float v;
+        widen_row(x, i, 1, dtype, &v);
+        size_t dst = base + i;
+        if (pos_map) {
+            const size_t t = i / (size_t)stride;
+            dst = (size_t)pos_map[t] * (size_t)stride + (i - t * (size_t)stride);
+        }
+        out[dst] = f32_to_bf16_bits(v);
+    }
+}
+
+// kernels/elementwise.cu:344-359 sigmoid_mul_kernel: x * 1.0f / (1.0f + exp(-g)) for whole quads and
+// x * (1.0f / (1.0f + exp(-g))) for the total % 4 tail (exp stands in for __expf, see the header).
+inline float sigmoid_mul_main(float x, float g) { return x * 1.0f / (1.0f + std::exp(-g)); }
+inline float sigmoid_mul_tail(float x, float g) { return x * (1.0f / (1.0f + std::exp(-g))); }
+
+ORACLE_API void oracle_sigmoid_mul(const void* x, const void* gate, size_t total, int dtype, float* out_f32, void* out,
+                                   int nthreads) {
+    const int nt = pick_threads(nthreads);
+    const size_t step = 4096;
+    const long nchunks = (long)((total + step - 1) / step);
+    const size_t whole = total & ~(size_t)3;
+#pragma omp parallel num_threads(nt)
+    {
+        std::vector<float> g(step), v(step), y(step);
+#pragma omp for schedule(static)
+        for (long c = 0; c < nchunks; ++c) {
+            const size_t off = (size_t)c * step;
+            const int n = (int)std::min(step, total - off);
+            widen_row(gate, off, n, dtype, g.data());
+            widen_row(x, off, n, dtype, v.data());
+            for (int i = 0; i < n; ++i) {
+                y[i] = (off + i < whole) ? sigmoid_mul_main(v[i], g[i]) : sigmoid_mul_tail(v[i], g[i]);
+            }
+            if (out_f32) std::memcpy(out_f32 + off, y.data(), (size_t)n * 4);
+            if (out) narrow_row(y.data(), n, dtype, out, off);
+        }
+    }
+}
+
+// sigmoid_mul_kernel then quantise_nvfp4_kernel (kernels/quantise.cu:6-53) on dense [rows, cols].
+ORACLE_API void oracle_sigmoid_mul_quantise_nvfp4(const void* x, const void* gate, uint8_t* packed, uint8_t* scales,
+                                                  int rows, int cols, float global_scale, int blk_mn, int chunk,
+                                                  int dtype, float* pre_f32, int nthreads) {
+    const int nt = pick_threads(nthreads);
+    const int rows_padded = round_up_i(rows, blk_mn);
+#pragma omp parallel num_threads(nt)
+    {
+        std::vector<float> g(cols), v(cols), y(cols);
+#pragma omp for schedule(static)
+        for (int r = 0; r < rows_padded; ++r) {
+            if (r < rows) {
+                widen_row(gate, (size_t)r * cols, cols, dtype, g.data());
+                widen_row(x, (size_t)r * cols, cols, dtype, v.data());
+                for (int i = 0; i < cols; ++i) y[i] = sigmoid_mul_main(v[i], g[i]);
+                if (pre_f32) std::memcpy(pre_f32 + (size_t)r * cols, y.data(), (size_t)cols * 4);
+                quantise_row(y.data(), r, cols, global_scale, blk_mn, chunk, packed, scales);
+            } else {
+                zero_pad_row(r, cols, blk_mn, chunk, packed, scales);
+            }
+        }
+    }
+}
+
+// kernels/head.cu:117-129 add_kernel.
+ORACLE_API void oracle_add(const void* a, const void* b, size_t total, int dtype, float* out_f32, void* out) {
+    for (size_t i = 0; i < total; ++i) {
+        float x, y;
+        widen_row(a, i, 1, dtype, &x);
+        widen_row(b, i, 1, dtype, &y);
+        const float s = x + y;
+        if (out_f32) out_f32[i] = s;
+        if (out) narrow_row(&s, 1, dtype, out, i);
     }
 }
 

@@ -1,7 +1,8 @@
 """Launch the REFERENCE's own CUDA kernels (oracle/_ref/*.cubin) on torch tensors.
 
 TEST INFRASTRUCTURE. The cubins are compiled by oracle/Makefile from the reference's unmodified
-kernels/elementwise.cu and kernels/quantise.cu for sm_100a; this module only loads them with the
+kernels/elementwise.cu, kernels/quantise.cu, kernels/head.cu and kernels/attention_mma.cu (for its
+bf16 conversion kernels) for sm_100a; this module only loads them with the
 CUDA driver API (cuda-python) and launches them with the grid/block shapes the reference's
 launch layer uses (aiis-clef src/cuda/mod.rs, cited per function). The reference kernels take
 f32 activations; bf16 test inputs are widened exactly before the call.
@@ -19,7 +20,7 @@ _functions: dict[tuple[str, str], object] = {}
 
 
 def available() -> bool:
-    return all((_DIR / f"{n}.cubin").exists() for n in ("elementwise", "quantise", "ref_probe"))
+    return all((_DIR / f"{n}.cubin").exists() for n in ("elementwise", "quantise", "ref_probe", "head", "to_bf16"))
 
 
 def _cu():
@@ -89,6 +90,37 @@ def _row_blocks(rows: int, cols: int) -> int:
 
 def _round_up(v, n):
     return -(-v // n) * n
+
+
+# ---- the steps either side of the fused quantisers -----------------------------------------------
+def sigmoid_mul(x, gate, total):
+    """src/cuda/mod.rs:2838-2856."""
+    out = torch.empty(total, dtype=torch.float32, device=x.device)
+    launch("elementwise", "sigmoid_mul_kernel", ((total + 1023) // 1024,), (256,), [out, x, gate, total])
+    return out
+
+
+def add(a, b, total):
+    """src/cuda/mod.rs:1686-1704 (kernels/head.cu add_kernel)."""
+    out = torch.empty(total, dtype=torch.float32, device=a.device)
+    launch("head", "add_kernel", ((total + 1023) // 1024,), (256,), [out, a, b, total])
+    return out
+
+
+def to_bf16(x, out, n, off_tokens=None, off_stride=0):
+    """src/cuda/mod.rs:3201-3227, the arm without a position map (kernels/attention_mma.cu to_bf16_kernel).
+    x f32; out a bf16 tensor written in place. The reference sizes its grid from n / 8 (its n is always a
+    multiple of 8); here the grid is sized from ceil(n / 8) so the kernel's scalar tail branch has a thread."""
+    blocks = max(1, (((n + 7) // 8) + 255) // 256)
+    launch("to_bf16", "to_bf16_kernel", (blocks,), (256,), [x, out, (n, ctypes.c_longlong), off_tokens, int(off_stride)])
+    return out
+
+
+def to_bf16_scatter(x, out, n, pos_map, stride):
+    """src/cuda/mod.rs:3201-3227, the arm with KvCache::pos_map (to_bf16_scatter_kernel)."""
+    blocks = max(1, ((n // 8) + 255) // 256)
+    launch("to_bf16", "to_bf16_scatter_kernel", (blocks,), (256,), [x, out, (n, ctypes.c_longlong), pos_map, int(stride)])
+    return out
 
 
 # ---- elementwise.cu ------------------------------------------------------------------------------
@@ -256,6 +288,13 @@ def probe_e4m3_decode(global_scale: float):
 def probe_silu_bf16():
     buf = _result_buffer(2)
     launch("ref_probe", "probe_silu_bf16", (256,), (256,), [buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 2)
+
+
+def probe_sigmoid_mul_bf16():
+    buf = _result_buffer(2)
+    launch("ref_probe", "probe_sigmoid_mul_bf16", (256,), (256,), [buf])
     torch.cuda.synchronize()
     return _read_results(buf, 2)
 

@@ -204,6 +204,44 @@ extern "C" __global__ void probe_silu_bf16(ProbeResult* result) {
     }
 }
 
+// The short form of x * 1.0f / (1.0f + __expf(-g)) (kernels/elementwise.cu:350-353) for every pair of a
+// bf16 g with |g| <= 44 and a finite bf16 x: 2^16 threads (one per g) each walk all x. Zero results may
+// differ in sign. result[0]: all pairs; result[1]: the pairs of the tuned kernels' domain, x == 0 or |x| >= 2^-60.
+extern "C" __global__ void probe_sigmoid_mul_bf16(ProbeResult* result) {
+    const uint32_t gi = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= 65536u) {
+        return;
+    }
+    const float g = __uint_as_float(gi << 16);
+    if (!(fabsf(g) <= clef::kSiluFastMaxAbs)) {
+        return;
+    }
+    const float d = 1.0f + __expf(-g);
+    unsigned long long checked = 0, checked_normal = 0;
+    for (uint32_t xi = 0; xi < 65536u; ++xi) {
+        const float x = __uint_as_float(xi << 16);
+        if (!(fabsf(x) < INFINITY)) {
+            continue;
+        }
+        const float want = x * 1.0f / d;
+        const clef::f32x2 a = clef::sigmoid_mul_fast_x2(clef::f2_pack(g, 1.0f), clef::f2_pack(x, 2.0f));
+        const clef::f32x2 b = clef::sigmoid_mul_fast_x2(clef::f2_pack(1.0f, g), clef::f2_pack(2.0f, x));
+        const bool ok = (__float_as_uint(a.x) == __float_as_uint(want) || (a.x == 0.0f && want == 0.0f)) &&
+                        (__float_as_uint(b.y) == __float_as_uint(want) || (b.y == 0.0f && want == 0.0f));
+        const bool normal = x == 0.0f || fabsf(x) >= clef::kSigmoidMulMinAbs;
+        ++checked;
+        checked_normal += normal;
+        if (!ok) {
+            report(&result[0], (gi << 16) | xi);
+            if (normal) {
+                report(&result[1], (gi << 16) | xi);
+            }
+        }
+    }
+    atomicAdd(&result[0].checked, checked);
+    atomicAdd(&result[1].checked, checked_normal);
+}
+
 // amax / 6.0f (kernels/quantise.cu:29) against the three-operation form, on the patterns the fast
 // quantiser uses it for: +0 and every finite x >= 2^-100.
 extern "C" __global__ void probe_div_six(ProbeResult* result) {

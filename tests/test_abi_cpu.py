@@ -63,7 +63,19 @@ def test_bad_arguments_are_refused_before_cuda(clef_lib):
     assert lib.clef_rms_norm_gated_quantise_nvfp4(None, p, p, p, p, p, 160, 128, 1e-6, 1.0, 128, 512, 16, 64, 0) == -1
     assert b"blk_mn" in lib.clef_last_error()
     assert lib.clef_embed_gather(None, p, p, p, 4, 7, 0) == -1
+    assert lib.clef_to_bf16_scatter(None, p, p, 64, p, 12, 1) == -1                               # stride % 8
+    assert lib.clef_to_bf16_scatter(None, p, p, 64, None, 32, 1) == -1                            # no position map
+    assert lib.clef_rope_kv_write(None, p, p, p, p, p, p, 4, 2, 100, 64, None, None, None, None, None, 0) == -1   # head_dim % 8
+    assert lib.clef_rope_kv_write(None, p, None, p, p, p, p, 4, 2, 128, 64, None, None, None, None, None, 0) == -1
+    assert lib.clef_qk_norm_rope_kv_write(None, p, p, p, p, p, p, p, 4, 2, 4096, 64, 1e-6, None, None, None, None, None, 0) == -3
+    assert lib.clef_sigmoid_mul_quantise_nvfp4(None, p, p, p, p, 4, 100, 1.0, 128, 512, 0) == -1
+    assert lib.clef_add_rms_norm_quantise_nvfp4(None, None, p, p, p, p, p, 4, 2048, 1e-6, 1.0, 128, 512, 0) == -1
+    assert lib.clef_add(None, p, p, ctypes.c_void_p(0x1004), 64, 0) == -1
     # zero-sized work is accepted without a device
+    assert lib.clef_sigmoid_mul(None, p, p, p, 0, 0) == 0
+    assert lib.clef_add(None, p, p, p, 0, 1) == 0
+    assert lib.clef_to_bf16(None, p, p, 0, None, 0, 1) == 0
+    assert lib.clef_rope_kv_write(None, p, p, p, p, p, p, 0, 2, 128, 64, None, None, None, None, None, 0) == 0
     assert lib.clef_quantise_nvfp4(None, p, p, p, 0, 128, 1.0, 128, 512, 0) == 0
     assert lib.clef_swiglu(None, p, p, p, 0, 0) == 0
     assert lib.clef_embed_gather(None, p, p, p, 0, 2048, 0) == 0

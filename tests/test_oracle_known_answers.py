@@ -297,3 +297,42 @@ def test_bf16_round_trip_helpers():
     # ties to even: 1 + 2^-8 is half way between two bf16 values -> even mantissa (1.0)
     assert orc.f32_to_bf16(np.array([1.0 + 2.0 ** -8], np.float32))[0] == 0x3F80
     assert orc.f32_to_bf16(np.array([1.0 + 3 * 2.0 ** -8], np.float32))[0] == 0x3F82
+
+
+# ---- the steps either side of the fused quantisers --------------------------------------------------------------------
+def test_to_bf16_rows_known_answers():
+    """kernels/attention_mma.cu:118-171: the offset form and the scatter form, NaN -> 0x7FFF as __float2bfloat16."""
+    x = np.array([1.0, -2.0, 0.5, np.inf, 1.0 + 2.0 ** -8, 1.0 + 3 * 2.0 ** -8, np.nan, -0.0], np.float32)
+    out = np.full(24, 0xBF80, np.uint16)
+    orc.to_bf16_rows(x, out, off_tokens=2, stride=8)
+    assert (out[:16] == 0xBF80).all()
+    assert list(out[16:]) == [0x3F80, 0xC000, 0x3F00, 0x7F80, 0x3F80, 0x3F82, 0x7FFF, 0x8000]
+    rows = np.arange(32, dtype=np.float32).reshape(4, 8)
+    cache = np.zeros(6 * 8, np.uint16)
+    orc.to_bf16_rows(rows, cache, pos_map=[5, 0, 3, 1], stride=8)
+    got = orc.bf16_to_f32(cache).reshape(6, 8)
+    assert np.array_equal(got[5], rows[0]) and np.array_equal(got[0], rows[1])
+    assert np.array_equal(got[3], rows[2]) and np.array_equal(got[1], rows[3])
+    assert not got[2].any() and not got[4].any()
+
+
+def test_sigmoid_mul_and_add_known_answers():
+    """kernels/elementwise.cu:344-359 (two forms) and kernels/head.cu:117-129."""
+    x = np.array([2.0, -3.0, 0.0, 1.5, 7.0, 1.0, -1.0], np.float32)
+    g = np.array([0.0, 0.0, 5.0, 100.0, -100.0, 1.0, -1.0], np.float32)
+    f32, _ = orc.sigmoid_mul(x, g)
+    assert f32[0] == 1.0 and f32[1] == -1.5 and f32[2] == 0.0 and f32[3] == 1.5 and f32[4] < 1e-40
+    # element 4 is the last of the whole quad; 5 and 6 are the tail, computed as x * (1 / (1 + e))
+    e = np.exp(np.float32(-1.0))
+    assert f32[5] == np.float32(1.0) * (np.float32(1.0) / (np.float32(1.0) + e))
+    s, bits = orc.add(np.array([1.0, 2.5, -0.0], np.float32), np.array([2.0 ** -30, -2.5, 0.0], np.float32))
+    assert s[0] == 1.0 and s[1] == 0.0 and s[2] == 0.0
+    # the fused restatement equals sigmoid_mul followed by the quantiser
+    rows, cols = 3, 256
+    rng = np.random.default_rng(11)
+    xv = rng.standard_normal((rows, cols)).astype(np.float32)
+    gv = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+    act, _ = orc.sigmoid_mul(xv, gv)
+    pc, sc = orc.quantise_nvfp4(act, rows, cols, 48.0)
+    pf, sf = orc.sigmoid_mul_quantise_nvfp4(xv, gv, rows, cols, 48.0)
+    assert np.array_equal(pf, pc) and np.array_equal(sf, sc)
