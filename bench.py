@@ -55,6 +55,13 @@ BYTES_PER_ROW = {
     "swiglu": 3 * 2 * INTER,                                                                  # 36,864
     "rms_norm_gated": 3 * 2 * HIDDEN,                                                         # 12,288
     "qk_norm_rope_q": 2 * Q_HEADS * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,                 # 8,452
+    # the steps either side of the fused quantisers (attention width = Q_HEADS * HEAD_DIM = HIDDEN here)
+    "rope_kv_write": 4 * KV_HEADS * HEAD_DIM * 2 + 8 + 2 * (ROTARY // 2) * 4,                 # 2,312 (k, v in; both caches out)
+    "qk_norm_rope_kv_write": 4 * KV_HEADS * HEAD_DIM * 2 + 8 + 2 * (ROTARY // 2) * 4,         # 2,312
+    "sigmoid_mul_quantise_nvfp4": 2 * 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,                # 9,344
+    "sigmoid_mul": 3 * 2 * HIDDEN,                                                            # 12,288
+    "add": 3 * 2 * HIDDEN,                                                                    # 12,288
+    "add_rms_norm_quantise_nvfp4": 3 * 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,               # 13,440
 }
 STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k"]
 FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k",
@@ -274,7 +281,12 @@ def run_gpu_arm(args):
             "h": torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16, device="cuda"),
             "act_i": torch.empty(ROWS, INTER, dtype=torch.bfloat16, device="cuda"),
             "g_out": torch.empty(ROWS * VH, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
+            "v": randn_bf16(ROWS, KV_HEADS, HEAD_DIM), "res": randn_bf16(ROWS, HIDDEN),
+            "cache_k": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
+            "cache_v": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
+            "sum": torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16, device="cuda"),
         })
+    cache_map = torch.randperm(ROWS, device="cuda", generator=gen).to(torch.int32)   # the engine's cpos: a slot per token
     w_head = (torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
 
     launchers = {
@@ -300,6 +312,20 @@ def run_gpu_arm(args):
         "qk_norm_rope_q": lambda d: lib.clef_qk_norm_rope(stream(), p(d["q"]), p(w_head), p(cos), p(sin), p(d["h"]),
                                                           None, ROWS * Q_HEADS, Q_HEADS, HEAD_DIM, ROTARY, EPS, None,
                                                           None, p(cpos), 0),
+        "rope_kv_write": lambda d: lib.clef_rope_kv_write(
+            stream(), p(d["cache_k"]), p(d["cache_v"]), p(d["k"]), p(d["v"]), p(cos), p(sin), ROWS, KV_HEADS, HEAD_DIM,
+            ROTARY, None, None, p(cpos), p(cache_map), None, 0),
+        "qk_norm_rope_kv_write": lambda d: lib.clef_qk_norm_rope_kv_write(
+            stream(), p(d["cache_k"]), p(d["cache_v"]), p(d["k"]), p(d["v"]), p(w_head), p(cos), p(sin), ROWS, KV_HEADS,
+            HEAD_DIM, ROTARY, EPS, None, None, p(cpos), p(cache_map), None, 0),
+        # attention output (q-shaped) gated by a same-shaped gate, as the operand of o_proj
+        "sigmoid_mul_quantise_nvfp4": lambda d: lib.clef_sigmoid_mul_quantise_nvfp4(
+            stream(), p(d["q"]), p(d["res"]), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, GS_NORM, 128, 512, 0),
+        "sigmoid_mul": lambda d: lib.clef_sigmoid_mul(stream(), p(d["sum"]), p(d["q"]), p(d["res"]), ROWS * HIDDEN, 0),
+        "add": lambda d: lib.clef_add(stream(), p(d["sum"]), p(d["x"]), p(d["res"]), ROWS * HIDDEN, 0),
+        "add_rms_norm_quantise_nvfp4": lambda d: lib.clef_add_rms_norm_quantise_nvfp4(
+            stream(), p(d["sum"]), p(d["x"]), p(d["res"]), p(w_norm), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, EPS,
+            GS_NORM, 128, 512, 0),
     }
 
     def step_eager(d):
