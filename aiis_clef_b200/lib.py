@@ -55,6 +55,10 @@ SYMBOLS = {
     "clef_sigmoid_mul_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
     "clef_add": (_I, [_P, _P, _P, _P, _SZ, _I]),
     "clef_add_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
+    "clef_quantise_fp8": (_I, [_P, _P, _P, _P, _I, _I, _I]),
+    "clef_swiglu_quantise_fp8": (_I, [_P, _P, _P, _P, _P, _I, _I, _I]),
+    "clef_rms_norm_fp8_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I]),
+    "clef_rms_norm_gated_quantise_fp8": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
     "clef_set_kernel_choice": (None, [_I]),
 }
 
@@ -374,6 +378,47 @@ class Device:
                                                              blk_mn, chunk, _dtype_code(a)),
                    "clef_add_rms_norm_quantise_nvfp4")
         return sum_out, packed, scales
+
+    # ==== FP8 (E4M3) activation quantisers ======================================================
+
+    # -- src/cuda/mod.rs:2246-2266 ------------------------------------------------------------
+    def quantise_fp8_dev(self, x, rows: int, cols: int):
+        _dev_tensor(x, "x")
+        out, scales = self._empty((rows, cols), torch.uint8), self._empty((rows,), torch.int16)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_quantise_fp8(_stream(), _ptr(x), _ptr(out), _ptr(scales), rows, cols, _dtype_code(x)),
+                   "clef_quantise_fp8")
+        return out, scales
+
+    # -- src/cuda/mod.rs:2402-2427 ------------------------------------------------------------
+    def swiglu_quantise_fp8_dev(self, gate, up, rows: int, cols: int):
+        _dev_tensor(gate, "gate"), _dev_tensor(up, "up")
+        out, scales = self._empty((rows, cols), torch.uint8), self._empty((rows,), torch.int16)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_swiglu_quantise_fp8(_stream(), _ptr(gate), _ptr(up), _ptr(out), _ptr(scales), rows, cols,
+                                                     _dtype_code(gate)), "clef_swiglu_quantise_fp8")
+        return out, scales
+
+    # -- src/cuda/mod.rs:2330-2358 ------------------------------------------------------------
+    def rms_norm_fp8_bf16_dev(self, x, weight, rows: int, cols: int, eps: float):
+        """(codes, row scales, bf16 copy) of the normalised rows."""
+        _dev_tensor(x, "x")
+        q, qs = self._empty((rows, cols), torch.uint8), self._empty((rows,), torch.int16)
+        bf = self._empty((rows, cols), torch.bfloat16)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rms_norm_fp8_bf16(_stream(), _ptr(x), _ptr(weight), _ptr(q), _ptr(qs), _ptr(bf), rows, cols,
+                                                   eps, _dtype_code(x)), "clef_rms_norm_fp8_bf16")
+        return q, qs, bf
+
+    # -- src/cuda/mod.rs:2304-2328 ------------------------------------------------------------
+    def rms_norm_gated_quantise_fp8_dev(self, x, gate, weight, rows: int, cols: int, vh: int, eps: float):
+        _dev_tensor(x, "x"), _dev_tensor(gate, "gate")
+        out, scales = self._empty((rows, cols), torch.uint8), self._empty((rows // vh,), torch.int16)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rms_norm_gated_quantise_fp8(_stream(), _ptr(x), _ptr(gate), _ptr(weight), _ptr(out),
+                                                             _ptr(scales), rows, cols, eps, vh, rows, _dtype_code(x)),
+                   "clef_rms_norm_gated_quantise_fp8")
+        return out, scales
 
 
 # =================================================================================================

@@ -199,6 +199,40 @@ int clef_add_rms_norm_quantise_nvfp4(clef_stream_t stream, void* sum_out, const 
                                      const float* weight, uint8_t* packed, uint8_t* scales, int rows, int cols,
                                      float eps, float global_scale, int blk_mn, int chunk, int dtype);
 
+/* ------------------------------------------------------------------------------------------------
+ * FP8 (E4M3) activation quantisers, for the FP8 projections of a mixed NVFP4 + FP8 checkpoint.
+ * Per quantised row: scale = amax / 448, stored as the upper 16 bits of that f32 (one uint16 per row);
+ * code = e4m3(|v| / scale) with the sign bit, one byte per value, dense [rows, cols]. cols % 8 == 0,
+ * cols <= 16384.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* quantise_fp8_kernel (kernels/quantise.cu:454-514), Device::quantise_fp8_dev (src/cuda/mod.rs:2246-2266).
+ * Every row is quantised from its own values; the reference kernel reads row blockIdx.x for all rows of
+ * a block, which is the same thing only when a row has a CTA to itself (cols > 1792). */
+int clef_quantise_fp8(clef_stream_t stream, const void* x, uint8_t* out, uint16_t* scales, int rows, int cols,
+                      int dtype);
+
+/* swiglu_quantise_fp8_kernel (kernels/quantise.cu:390-452), Device::swiglu_quantise_fp8_dev
+ * (src/cuda/mod.rs:2402-2427): clef_swiglu followed by clef_quantise_fp8. The reference declines
+ * cols > 12288. */
+int clef_swiglu_quantise_fp8(clef_stream_t stream, const void* gate, const void* up, uint8_t* out, uint16_t* scales,
+                             int rows, int cols, int dtype);
+
+/* rms_norm_fp8_bf16_kernel (kernels/quantise.cu:273-381), Device::rms_norm_fp8_bf16_dev
+ * (src/cuda/mod.rs:2330-2358): one pass gives the FP8 codes and row scales of the normalised row AND its
+ * bf16 copy (bf_out, [rows, cols]; may be NULL). Equals clef_rms_norm -> clef_quantise_fp8 / clef_to_bf16.
+ * The reference declines cols != 4096. */
+int clef_rms_norm_fp8_bf16(clef_stream_t stream, const void* x, const float* weight, uint8_t* q_out,
+                           uint16_t* q_scales, uint16_t* bf_out, int rows, int cols, float eps, int dtype);
+
+/* rms_norm_gated_quantise_fp8_kernel (kernels/quantise.cu:123-191), Device::rms_norm_gated_quantise_fp8_dev
+ * (src/cuda/mod.rs:2304-2328): `rows` head rows of width `cols` (vh per token, rows % vh == 0), one scale
+ * per TOKEN (rows / vh of them); head rows >= rows_live hold no data and are not written. The reference
+ * serves cols == 128 and vh <= 32; here cols <= 256, vh <= 64. */
+int clef_rms_norm_gated_quantise_fp8(clef_stream_t stream, const void* x, const void* gate, const float* weight,
+                                     uint8_t* out, uint16_t* scales, int rows, int cols, float eps, int vh,
+                                     int rows_live, int dtype);
+
 /* Kernel selection for tests and measurements: 0 = automatic (tuned kernel when the shape has one),
  * 1 = always the shape-general kernel. Process-wide; not part of the reference interface. */
 void clef_set_kernel_choice(int choice);

@@ -357,3 +357,39 @@ def add(a, b):
     out = np.empty(a.shape, a.dtype)
     load().oracle_add(_p(a), _p(b), _sz(a.size), _dtype_code(a), _p(f32), _p(out))
     return f32, out
+
+
+# ---- FP8 (E4M3) activation quantisers --------------------------------------------------------------------
+
+def _fp8_rows(mode, a, b, w, rows, cols, eps, want_bf16, fma_mode, nthreads):
+    a = _c(a)
+    b = None if b is None else _c(b)
+    w = None if w is None else _c(w, np.float32)
+    out = np.empty((rows, cols), np.uint8)
+    scales = np.empty(rows, np.uint16)
+    bf = np.empty((rows, cols), np.uint16) if want_bf16 else None
+    load().oracle_fp8_rows(mode, _p(a), _p(b), _p(w), _p(out), _p(scales), _p(bf), rows, cols, _f(eps), _dtype_code(a),
+                           SUMSQ_FMA if fma_mode is None else fma_mode, nthreads)
+    return (out, scales, bf) if want_bf16 else (out, scales)
+
+
+def quantise_fp8(x, rows, cols, nthreads=0):
+    return _fp8_rows(0, x, None, None, rows, cols, 0.0, False, None, nthreads)
+
+
+def swiglu_quantise_fp8(gate, up, rows, cols, nthreads=0):
+    return _fp8_rows(1, gate, up, None, rows, cols, 0.0, False, None, nthreads)
+
+
+def rms_norm_fp8_bf16(x, w, rows, cols, eps, fma_mode=None, nthreads=0):
+    return _fp8_rows(2, x, None, w, rows, cols, eps, True, fma_mode, nthreads)
+
+
+def rms_norm_gated_quantise_fp8(x, g, w, rows, cols, vh, eps, rows_live=None, fma_mode=None, nthreads=0):
+    x, g, w = _c(x), _c(g), _c(w, np.float32)
+    out = np.zeros((rows, cols), np.uint8)
+    scales = np.empty(rows // vh, np.uint16)
+    load().oracle_rms_norm_gated_quantise_fp8(_p(x), _p(g), _p(w), _p(out), _p(scales), rows, cols, _f(eps), vh,
+                                              rows if rows_live is None else rows_live, _dtype_code(x),
+                                              SUMSQ_FMA if fma_mode is None else fma_mode, nthreads)
+    return out, scales

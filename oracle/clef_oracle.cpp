@@ -831,6 +831,96 @@ ORACLE_API void oracle_add(const void* a, const void* b, size_t total, int dtype
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// FP8 (E4M3) activation quantisers (kernels/quantise.cu:123-191, 273-514). Shared row recipe:
+// scale = amax / 448 (amax with fmaxf semantics), the row's scale word is the upper half of that f32,
+// code = to_e4m3(|v| * inv) | sign with inv = scale > 0 ? 1 / scale : 0.
+// ---------------------------------------------------------------------------------------------
+inline void fp8_quantise_span(const float* const* parts, const int* lens, int nparts, uint8_t* const* outs,
+                              uint16_t* scale_word) {
+    float amax = 0.0f;
+    for (int p = 0; p < nparts; ++p) {
+        for (int i = 0; i < lens[p]; ++i) amax = std::fmax(amax, std::fabs(parts[p][i]));
+    }
+    const float scale = amax / 448.0f;
+    uint32_t bits;
+    std::memcpy(&bits, &scale, 4);
+    *scale_word = (uint16_t)(bits >> 16);
+    const float inv = (scale > 0.0f) ? 1.0f / scale : 0.0f;
+    for (int p = 0; p < nparts; ++p) {
+        if (!outs[p]) continue;
+        for (int i = 0; i < lens[p]; ++i) {
+            const float t = parts[p][i];
+            outs[p][i] = (uint8_t)(to_e4m3(std::fabs(t) * inv) | ((t < 0.0f) ? 0x80u : 0x00u));
+        }
+    }
+}
+
+// mode 0: quantise_fp8_kernel (:454-514, every row from its own values); 1: swiglu_quantise_fp8_kernel
+// (:390-452, a = gate, b = up); 2: rms_norm_fp8_bf16_kernel (:273-381, bf_out optional bf16 twin).
+ORACLE_API void oracle_fp8_rows(int mode, const void* a, const void* b, const float* weight, uint8_t* out,
+                                uint16_t* scales, uint16_t* bf_out, int rows, int cols, float eps, int dtype,
+                                int fma_mode, int nthreads) {
+    const int nt = pick_threads(nthreads);
+#pragma omp parallel num_threads(nt)
+    {
+        std::vector<float> x(cols), u(cols), y(cols);
+#pragma omp for schedule(static)
+        for (int r = 0; r < rows; ++r) {
+            widen_row(a, (size_t)r * cols, cols, dtype, x.data());
+            if (mode == 1) {
+                widen_row(b, (size_t)r * cols, cols, dtype, u.data());
+                for (int i = 0; i < cols; ++i) y[i] = silu_div_ieee(x[i]) * u[i];
+            } else if (mode == 2) {
+                rms_norm_row(x.data(), weight, cols, eps, fma_mode, y.data());
+                if (bf_out) {
+                    for (int i = 0; i < cols; ++i) bf_out[(size_t)r * cols + i] = f32_to_bf16_bits(y[i]);
+                }
+            } else {
+                y = x;
+            }
+            const float* parts[1] = {y.data()};
+            uint8_t* outs[1] = {out + (size_t)r * cols};
+            fp8_quantise_span(parts, &cols, 1, outs, scales + r);
+        }
+    }
+}
+
+// rms_norm_gated_quantise_fp8_kernel (:123-191): one scale per token over its vh head rows; head rows
+// >= rows_live hold no data (they add 0 to the amax and are not written).
+ORACLE_API void oracle_rms_norm_gated_quantise_fp8(const void* x, const void* gate, const float* weight, uint8_t* out,
+                                                   uint16_t* scales, int rows, int cols, float eps, int vh,
+                                                   int rows_live, int dtype, int fma_mode, int nthreads) {
+    const int nt = pick_threads(nthreads);
+    const int tokens = rows / vh;
+#pragma omp parallel num_threads(nt)
+    {
+        std::vector<float> xin(cols), gin(cols), y((size_t)vh * cols);
+        std::vector<const float*> parts(vh);
+        std::vector<uint8_t*> outs(vh);
+        std::vector<int> lens(vh);
+#pragma omp for schedule(static)
+        for (int t = 0; t < tokens; ++t) {
+            for (int h = 0; h < vh; ++h) {
+                const int row = t * vh + h;
+                float* yh = y.data() + (size_t)h * cols;
+                parts[h] = yh;
+                lens[h] = cols;
+                if (row < rows_live) {
+                    widen_row(x, (size_t)row * cols, cols, dtype, xin.data());
+                    widen_row(gate, (size_t)row * cols, cols, dtype, gin.data());
+                    rms_norm_gated_row(xin.data(), gin.data(), weight, cols, eps, fma_mode, yh);
+                    outs[h] = out + (size_t)row * cols;
+                } else {
+                    std::fill(yh, yh + cols, 0.0f);
+                    outs[h] = nullptr;
+                }
+            }
+            fp8_quantise_span(parts.data(), lens.data(), vh, outs.data(), scales + t);
+        }
+    }
+}
+
 // Quantise rows of f32 values that were produced elsewhere (for instance a GPU f32 result), so a
 // test can separate "same pre-quantisation values" from "same quantiser".
 ORACLE_API void oracle_quantise_rows_f32(const float* v, uint8_t* packed, uint8_t* scales, int rows, int cols,

@@ -123,6 +123,50 @@ def to_bf16_scatter(x, out, n, pos_map, stride):
     return out
 
 
+# ---- FP8 quantisers (quantise.cu) ----------------------------------------------------------------
+def quantise_fp8(x, rows, cols):
+    """src/cuda/mod.rs:2246-2266. Meaningful for cols > 1792 only (one row per CTA): for narrower rows the
+    reference kernel reads row blockIdx.x for every row of the block."""
+    assert cols > 1792
+    out = torch.empty(rows * cols, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(rows, dtype=torch.int16, device=x.device)
+    launch("quantise", "quantise_fp8_kernel", (_row_blocks(rows, cols),), (256,), [x, out, scales, rows, cols])
+    return out.view(rows, cols), scales
+
+
+def swiglu_quantise_fp8(gate, up, rows, cols):
+    """src/cuda/mod.rs:2402-2427."""
+    assert cols <= 768 * 16
+    out = torch.empty(rows * cols, dtype=torch.uint8, device=gate.device)
+    scales = torch.empty(rows, dtype=torch.int16, device=gate.device)
+    launch("quantise", "swiglu_quantise_fp8_kernel", (rows,), (768,), [gate, up, out, scales, rows, cols])
+    return out.view(rows, cols), scales
+
+
+def rms_norm_fp8_bf16(x, weight, rows, cols, eps):
+    """src/cuda/mod.rs:2330-2358 (cols 4096 only)."""
+    assert cols == 4096
+    q = torch.empty(rows * cols, dtype=torch.uint8, device=x.device)
+    qs = torch.empty(rows, dtype=torch.int16, device=x.device)
+    bf = torch.empty(rows * cols, dtype=torch.bfloat16, device=x.device)
+    launch("quantise", "rms_norm_fp8_bf16_kernel", (rows,), (256,), [x, weight, q, qs, bf, rows, cols, float(eps)])
+    return q.view(rows, cols), qs, bf.view(rows, cols)
+
+
+def rms_norm_gated_quantise_fp8(x, gate, weight, rows, cols, vh, eps):
+    """src/cuda/mod.rs:2304-2328 (cols 128, vh <= 32)."""
+    assert cols == 128 and vh <= 32
+    tokens = rows // vh
+    out = torch.zeros(rows * cols, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(tokens, dtype=torch.int16, device=x.device)
+    # The reference launches 1,024 threads: warp w of block t takes head row t * vh + w, so with vh < 32 the
+    # surplus warps would also quantise rows of token t + 1 with token t's scale, racing with block t + 1.
+    # One warp per head row is launched here, which is the reference launch itself at vh = 32.
+    launch("quantise", "rms_norm_gated_quantise_fp8_kernel", (tokens,), (32 * vh,),
+           [x, gate, weight, out, scales, rows, cols, float(eps), vh, rows])
+    return out.view(rows, cols), scales
+
+
 # ---- elementwise.cu ------------------------------------------------------------------------------
 def rms_norm(x, weight, rows, cols, eps):
     """src/cuda/mod.rs:2718-2739."""
@@ -271,11 +315,12 @@ def probe_e2m1(base: int, count: int):
 
 
 def probe_e4m3(base: int, count: int):
-    buf = _result_buffer(1)
+    """[scale encoder e4m3_encode_finite (+inf literal), element encoder e4m3_encode_any] against to_e4m3."""
+    buf = _result_buffer(2)
     launch("ref_probe", "probe_e4m3", (148 * 8,), (256,),
            [(base, ctypes.c_ulonglong), (count, ctypes.c_ulonglong), buf])
     torch.cuda.synchronize()
-    return _read_results(buf, 1)
+    return _read_results(buf, 2)
 
 
 def probe_e4m3_decode(global_scale: float):

@@ -14,6 +14,7 @@
 #include "nvfp4_codec.cuh"  // this repo's codec (namespace clef)
 #include "kernels_generic.cuh"
 #include "kernels_hot.cuh"   // packed-pair quantiser and the short silu forms of the tuned kernels
+#include "kernels_fp8.cuh"   // e4m3_encode_any, the FP8 quantisers' element encoder
 
 struct ProbeResult {
     unsigned long long checked;
@@ -74,7 +75,7 @@ extern "C" __global__ void probe_e2m1(unsigned long long base, unsigned long lon
     atomicAdd(&result[2].checked, checked_all);
 }
 
-// result[0]: scale encoder on every pattern. +inf goes through the literal branch of the rare path
+// result[0] (and result[1], see below): scale encoder on every pattern. +inf goes through the literal branch of the rare path
 // (clef::quantise16_rare handles it the same way), everything else through e4m3_encode_finite.
 extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long long count, ProbeResult* result) {
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
@@ -88,8 +89,12 @@ extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long lon
         if (got != want) {
             report(&result[0], bits);
         }
+        if (clef::e4m3_encode_any(v) != want) {   // the FP8 quantisers' element encoder, every pattern
+            report(&result[1], bits);
+        }
     }
     atomicAdd(&result[0].checked, checked);
+    atomicAdd(&result[1].checked, checked);
 }
 
 // result[0]: decoder on all 256 bytes (bit-exact f32); result[1]: inv_scale for `global_scale`.
