@@ -33,6 +33,13 @@ __device__ __forceinline__ float max3_abs_nan(float acc, float a, float b) {
     return r;
 }
 
+// NaN-propagating 2-input maximum.
+__device__ __forceinline__ float fmaxf_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+
 // 3-input minimum of magnitudes: min(acc, |a|, |b|); a NaN input is ignored.
 __device__ __forceinline__ float min3_abs(float acc, float a, float b) {
     float r;

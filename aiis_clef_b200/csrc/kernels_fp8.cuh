@@ -13,6 +13,7 @@
 #pragma once
 
 #include "kernels_generic.cuh"
+#include "kernels_hot.cuh"
 
 namespace clef {
 
@@ -223,6 +224,487 @@ fp8_gated_kernel(const typename T::storage* __restrict__ x, const typename T::st
                                            (fp8_code(t.z, inv_scale) << 16) | (fp8_code(t.w, inv_scale) << 24);
                         *reinterpret_cast<uint32_t*>(out + (size_t)row * cols + 4 * i) = q;
                     }
+                }
+            }
+        }
+    }
+}
+
+
+// =============================================================================================
+// Tuned bf16 kernels.
+// =============================================================================================
+
+// Magnitude code of p for 0 <= p < 464 (finite), the reference encoder in 6 operations:
+//   n = ((bits(p) + half step) >> 20) - 960      the normal-range code; below 8 (even negative) under 2^-6
+//   k = floor(min(p * 512 + 0.5, 8 - ulp))       the subnormal code min(int(p*512 + 0.5), 7); 7 for larger p
+// and the code is max(n, k): where the normal branch applies n >= 8 > k, and where the subnormal branch
+// applies n <= k (n counts eighths of 2^-7 above 2^-7, k halves of them above 4, rounded). Compared with the
+// reference encoder for every f32 pattern of the domain (oracle/ref_probe.cu).
+__device__ __forceinline__ uint32_t e4m3_mag_fast(float p) {
+    const int n = (int)(__float_as_uint(p) + (0x00080000u - (960u << 20))) >> 20;
+    const float s = fminf(__fmaf_rn(p, 512.0f, 0.5f), 7.99999952f);
+    const int u = __float_as_int(__fadd_rz(s, 8388608.0f));
+    return (uint32_t)__viaddmax_s32(u, -0x4B000000, n);
+}
+
+// Largest and smallest non-zero row maximum the short encoder is used for: the row scale amax / 448 and its
+// reciprocal are then normal numbers and every |t| * inv is finite and below 464.
+constexpr float kFp8FastMinAmax = 7.888609052e-31f;   // 2^-100
+constexpr float kFp8FastMaxAmax = 3.0e38f;
+
+// 16 values of a row in the quad-pair layout -> 16 code bytes in natural order. `inv2` = splat(1 / scale).
+// Signs come from t + 0.0f, which turns -0.0 into +0.0 (the reference's (t < 0) is false for it) and changes
+// nothing else; NaN rows never get here.
+__device__ __forceinline__ uint4 fp8_encode16_qp(const f32x2* v, f32x2 inv2) {
+    uint32_t word[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const f32x2 a = f2_add(v[2 * q], f2_splat(0.0f)), b = f2_add(v[2 * q + 1], f2_splat(0.0f));   // (x, z), (y, w)
+        const uint32_t cx = e4m3_mag_fast(__fmul_rn(fabsf(a.x), inv2.x)), cy = e4m3_mag_fast(__fmul_rn(fabsf(b.x), inv2.x));
+        const uint32_t cz = e4m3_mag_fast(__fmul_rn(fabsf(a.y), inv2.x)), cw = e4m3_mag_fast(__fmul_rn(fabsf(b.y), inv2.x));
+        const uint32_t mags = cx | (cy << 8) | (cz << 16) | (cw << 24);
+        // top bytes of x, y, z, w -> bytes 0..3
+        const uint32_t xy = __byte_perm(__float_as_uint(a.x), __float_as_uint(b.x), 0x0073);
+        const uint32_t zw = __byte_perm(__float_as_uint(a.y), __float_as_uint(b.y), 0x0073);
+        const uint32_t tops = __byte_perm(xy, zw, 0x5410);
+        word[q] = mags | (tops & 0x80808080u);
+    }
+    return make_uint4(word[0], word[1], word[2], word[3]);
+}
+
+// Literal encoder for one block of a row that left the short encoder's domain: values recomputed from global
+// memory in natural order. MODE as in fp8_rows_kernel; inv_norm is the row's 1 / rms (RMSNorm only).
+template <int MODE>
+static __device__ __noinline__ void fp8_block_cold(const uint16_t* ablk, const uint16_t* bblk, const float* wblk,
+                                                   float inv_norm, float inv_scale, uint4* dst) {
+    uint32_t word[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float t = __uint_as_float((uint32_t)ablk[i] << 16);
+        if (MODE == kFp8SwiGLU) {
+            t = silu_ieee_div(t) * __uint_as_float((uint32_t)bblk[i] << 16);
+        } else if (MODE == kFp8RmsNorm) {
+            t = t * inv_norm * (1.0f + wblk[i]);
+        }
+        word[i >> 2] |= fp8_code(t, inv_scale) << (8 * (i & 3));
+    }
+    *dst = make_uint4(word[0], word[1], word[2], word[3]);
+}
+
+// max |v| over a block, NaN if any value is NaN (the fast path's detector) / NaN ignored (the recipe's amax).
+__device__ __forceinline__ float block_abs_max_ignoring_nan(const f32x2* v) {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        m = fmaxf(m, fmaxf(fabsf(v[i].x), fabsf(v[i].y)));
+    }
+    return m;
+}
+
+// quantise_fp8 (MODE plain) and rms_norm_fp8_bf16 (MODE RmsNorm, bf_out optional) for cols = NB * 512, one warp
+// per row: the row structure, prefetch and summation tree of rms_norm_quant_hot_kernel; the row maximum is a
+// 5-step butterfly, the row scale is computed by every lane, each lane encodes its NB blocks (16 bytes each).
+template <int NB, int MODE>
+__global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? 2 : 1))
+fp8_rows_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight, uint8_t* __restrict__ out,
+                    uint16_t* __restrict__ scales, uint16_t* __restrict__ bf_out, int rows, float eps) {
+    constexpr int COLS = NB * 512;
+    extern __shared__ float4 s_w[];   // (1 + w), quad-pair layout, as in rms_norm_quant_hot_kernel
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    if (MODE == kFp8RmsNorm) {
+        for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
+            const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
+            const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
+            s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
+        }
+    }
+    pdl_wait_prior_grids();
+    int row = blockIdx.x * 8 + warp;
+    U8x32 d[NB];
+    if (row < rows) {
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
+        }
+    }
+    __syncthreads();
+    for (; row < rows; row += gridDim.x * 8) {
+        f32x2 v[NB][8];
+        float p[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            unpack16_quadpairs(d[j], v[j]);
+            if (MODE == kFp8RmsNorm) {
+                float quad[4];
+                quad_squares(v[j], quad);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    p[j & 1][k] = __fadd_rn(p[j & 1][k], quad[k]);
+                }
+            }
+        }
+        const int next = row + gridDim.x * 8;
+        if (next < rows) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                d[j] = ldg_stream_v8(x + (size_t)next * COLS + (size_t)(lane + 32 * j) * 16);
+            }
+        }
+        float inv_norm = 0.0f;
+        if (MODE == kFp8RmsNorm) {
+            inv_norm = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
+                                                : inv_rms(row_tree_256(p, lane), COLS, eps);
+            const f32x2 inv2 = f2_splat(inv_norm);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 w = s_w[(4 * j + q) * 32 + lane];
+                    v[j][2 * q] = f2_mul(f2_mul(v[j][2 * q], inv2), make_float2(w.x, w.y));
+                    v[j][2 * q + 1] = f2_mul(f2_mul(v[j][2 * q + 1], inv2), make_float2(w.z, w.w));
+                }
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            amax = fmaxf_nan(amax, block_abs_max(v[j]));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            amax = fmaxf_nan(amax, __shfl_xor_sync(kFullMask, amax, off));
+        }
+        uint8_t* orow = out + (size_t)row * COLS;
+        const bool fast = amax == 0.0f || (amax >= kFp8FastMinAmax && amax <= kFp8FastMaxAmax);   // false for NaN
+        if (fast) {
+            const float scale = __fdiv_rn(amax, 448.0f);
+            if (lane == 0) {
+                scales[row] = (uint16_t)(__float_as_uint(scale) >> 16);
+            }
+            const f32x2 inv2 = f2_splat((scale > 0.0f) ? __frcp_rn(scale) : 0.0f);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                *reinterpret_cast<uint4*>(orow + (size_t)(lane + 32 * j) * 16) = fp8_encode16_qp(v[j], inv2);
+            }
+        } else {
+            // A NaN, an infinity or a tiny maximum in the row: the recipe's own maximum (NaN ignored), literal codes.
+            float m = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                m = fmaxf(m, block_abs_max_ignoring_nan(v[j]));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                m = fmaxf(m, __shfl_xor_sync(kFullMask, m, off));
+            }
+            const float scale = __fdiv_rn(m, 448.0f);
+            if (lane == 0) {
+                scales[row] = (uint16_t)(__float_as_uint(scale) >> 16);
+            }
+            const float inv_scale = (scale > 0.0f) ? __fdiv_rn(1.0f, scale) : 0.0f;
+            for (int j = 0; j < NB; ++j) {
+                const int b = lane + 32 * j;
+                fp8_block_cold<MODE>(x + (size_t)row * COLS + b * 16, nullptr, weight + b * 16, inv_norm, inv_scale,
+                                     reinterpret_cast<uint4*>(orow + (size_t)b * 16));
+            }
+        }
+        if (MODE == kFp8RmsNorm && bf_out) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                stg_v8(bf_out + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16, pack16_bf16(v[j]));
+            }
+        }
+    }
+}
+
+
+// A barrier over the WPR warps of one team (named barrier 1 + team; barrier 0 is __syncthreads).
+template <int WPR>
+__device__ __forceinline__ void team_barrier(int team) {
+    if (WPR > 1) {
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(WPR * 32) : "memory");
+    }
+}
+
+// quantise_fp8 (MODE plain) and swiglu_quantise_fp8 for cols = 512 * WPR * BPL: a team of WPR warps owns a row
+// (8 / WPR rows per CTA at a time), lane l of team warp w holds the 16-value blocks (32 w + l) + 32 WPR j, j < BPL,
+// keeps their f32 values in registers, and the team's row maximum goes through shared memory: one named barrier
+// per row, the slots double-buffered by row parity so a fast warp's next row cannot overwrite a slow warp's read.
+template <int MODE, int BPL, int WPR>
+__global__ void __launch_bounds__(kCtaThreads, 2)
+fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, uint8_t* __restrict__ out,
+                    uint16_t* __restrict__ scales, int rows) {
+    constexpr int COLS = 512 * WPR * BPL;
+    constexpr int TEAMS = (kCtaThreads / 32) / WPR;
+    __shared__ float s_max[2][2][kCtaThreads / 32];   // [fast | literal][row parity][warp]
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int team = warp / WPR, wt = warp % WPR;
+    const int first_block = wt * 32 + lane;
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    int row = blockIdx.x * TEAMS + team;
+    U8x32 da[BPL], db[MODE == kFp8SwiGLU ? BPL : 1];
+    if (row < rows) {
+#pragma unroll
+        for (int j = 0; j < BPL; ++j) {
+            const size_t off = (size_t)row * COLS + (size_t)(first_block + 32 * WPR * j) * 16;
+            da[j] = ldg_stream_v8(a + off);
+            if (MODE == kFp8SwiGLU) db[j] = ldg_stream_v8(b + off);
+        }
+    }
+    int parity = 0;
+    for (; row < rows; row += gridDim.x * TEAMS, parity ^= 1) {
+        f32x2 v[BPL][8];
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < BPL; ++j) {
+            unpack16_quadpairs(da[j], v[j]);
+            if (MODE == kFp8SwiGLU) {
+                f32x2 u[8];
+                unpack16_quadpairs(db[j], u);
+                if (gated_fast_domain<kActSwiGLU, false>(v[j], u, nullptr)) {
+                    gated_fast<kActSwiGLU>(v[j], u);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        v[j][i] = make_float2(gated_literal<kActSwiGLU>(v[j][i].x, u[i].x), gated_literal<kActSwiGLU>(v[j][i].y, u[i].y));
+                    }
+                }
+            }
+            amax = fmaxf_nan(amax, block_abs_max(v[j]));
+        }
+        const int next = row + gridDim.x * TEAMS;
+        if (next < rows) {
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) {
+                const size_t off = (size_t)next * COLS + (size_t)(first_block + 32 * WPR * j) * 16;
+                da[j] = ldg_stream_v8(a + off);
+                if (MODE == kFp8SwiGLU) db[j] = ldg_stream_v8(b + off);
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            amax = fmaxf_nan(amax, __shfl_xor_sync(kFullMask, amax, off));
+        }
+        if (WPR > 1) {
+            if (lane == 0) s_max[0][parity][warp] = amax;
+            team_barrier<WPR>(team);
+            amax = s_max[0][parity][team * WPR];
+#pragma unroll
+            for (int w = 1; w < WPR; ++w) {
+                amax = fmaxf_nan(amax, s_max[0][parity][team * WPR + w]);
+            }
+        }
+        uint8_t* orow = out + (size_t)row * COLS;
+        const bool fast = amax == 0.0f || (amax >= kFp8FastMinAmax && amax <= kFp8FastMaxAmax);   // false for NaN
+        if (fast) {
+            const float scale = __fdiv_rn(amax, 448.0f);
+            if (wt == 0 && lane == 0) {
+                scales[row] = (uint16_t)(__float_as_uint(scale) >> 16);
+            }
+            const f32x2 inv2 = f2_splat((scale > 0.0f) ? __frcp_rn(scale) : 0.0f);
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) {
+                *reinterpret_cast<uint4*>(orow + (size_t)(first_block + 32 * WPR * j) * 16) = fp8_encode16_qp(v[j], inv2);
+            }
+        } else {
+            float m = 0.0f;
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) {
+                m = fmaxf(m, block_abs_max_ignoring_nan(v[j]));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                m = fmaxf(m, __shfl_xor_sync(kFullMask, m, off));
+            }
+            if (WPR > 1) {
+                if (lane == 0) s_max[1][parity][warp] = m;
+                team_barrier<WPR>(team);
+                m = s_max[1][parity][team * WPR];
+#pragma unroll
+                for (int w = 1; w < WPR; ++w) {
+                    m = fmaxf(m, s_max[1][parity][team * WPR + w]);
+                }
+            }
+            const float scale = __fdiv_rn(m, 448.0f);
+            if (wt == 0 && lane == 0) {
+                scales[row] = (uint16_t)(__float_as_uint(scale) >> 16);
+            }
+            const float inv_scale = (scale > 0.0f) ? __fdiv_rn(1.0f, scale) : 0.0f;
+            for (int j = 0; j < BPL; ++j) {
+                const size_t off = (size_t)row * COLS + (size_t)(first_block + 32 * WPR * j) * 16;
+                fp8_block_cold<MODE>(a + off, MODE == kFp8SwiGLU ? b + off : nullptr, nullptr, 0.0f, inv_scale,
+                                     reinterpret_cast<uint4*>(out + off));
+            }
+        }
+    }
+}
+
+
+// Literal values and codes of one 16-value block of the gated norm (kernels/quantise.cu:149-157, 185-190).
+static __device__ __noinline__ void fp8_gated_block_cold(const uint16_t* xblk, const uint16_t* gblk, const float* wblk,
+                                                         float inv_norm, float inv_scale, uint4* dst) {
+    uint32_t word[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float t = __uint_as_float((uint32_t)xblk[i] << 16) * inv_norm * wblk[i] *
+                        silu_fast_div(__uint_as_float((uint32_t)gblk[i] << 16));
+        word[i >> 2] |= fp8_code(t, inv_scale) << (8 * (i & 3));
+    }
+    *dst = make_uint4(word[0], word[1], word[2], word[3]);
+}
+
+// rms_norm_gated_quantise_fp8 for 128-wide heads, vh = 8 * STEPS * WPT head rows per token, every head row live:
+// WPT warps own a token; in each of its STEPS steps a warp normalises 8 head rows with the lane layout and the
+// summation tree of gated_norm_quant_hot_kernel (4 lanes per head row); the values stay in registers until the
+// token's maximum is known (butterfly, then the team exchange of fp8_team_hot_kernel).
+template <int STEPS, int WPT>
+__global__ void __launch_bounds__(kCtaThreads, 2)
+fp8_gated_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, const float* __restrict__ weight,
+                     uint8_t* __restrict__ out, uint16_t* __restrict__ scales, int tokens, float eps) {
+    constexpr int COLS = 128;
+    constexpr int VH = 8 * STEPS * WPT;
+    constexpr int TEAMS = (kCtaThreads / 32) / WPT;
+    __shared__ float s_max[2][2][kCtaThreads / 32];
+    __shared__ float4 s_w[32];   // plain weight, quad-pair layout: s_w[(h * 4 + q) * 4 + m]
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int m = lane & 3;
+    const int team = warp / WPT, wt = warp % WPT;
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
+        const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
+        s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
+    }
+    pdl_wait_prior_grids();
+    __syncthreads();
+    // Head row of this lane group in step s of token t: t * VH + (wt * STEPS + s) * 8 + (lane >> 2).
+    auto head_row = [&](int token, int step) { return (size_t)token * VH + (size_t)(wt * STEPS + step) * 8 + (lane >> 2); };
+    int token = blockIdx.x * TEAMS + team;
+    U8x32 dx[2], dg[2];
+    if (token < tokens) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            dx[h] = ldg_stream_v8(x + head_row(token, 0) * COLS + (m + 4 * h) * 16);
+            dg[h] = ldg_stream_v8(gate + head_row(token, 0) * COLS + (m + 4 * h) * 16);
+        }
+    }
+    int parity = 0;
+    for (; token < tokens; token += gridDim.x * TEAMS, parity ^= 1) {
+        f32x2 v[STEPS][2][8];
+        float inv_norm[STEPS];
+        float amax = 0.0f;
+#pragma unroll
+        for (int step = 0; step < STEPS; ++step) {
+            f32x2 gv[2][8];
+            float quad[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                unpack16_quadpairs(dx[h], v[step][h]);
+                unpack16_quadpairs(dg[h], gv[h]);
+                quad_squares(v[step][h], quad[h]);
+            }
+            // fetch the next step (of this token, or the first of this team's next token)
+            const int ntoken = (step + 1 < STEPS) ? token : token + gridDim.x * TEAMS;
+            const int nstep = (step + 1 < STEPS) ? step + 1 : 0;
+            if (ntoken < tokens) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    dx[h] = ldg_stream_v8(x + head_row(ntoken, nstep) * COLS + (m + 4 * h) * 16);
+                    dg[h] = ldg_stream_v8(gate + head_row(ntoken, nstep) * COLS + (m + 4 * h) * 16);
+                }
+            }
+            inv_norm[step] = inv_rms_pow2<COLS>(head_tree_32(quad[0], quad[1], lane), eps);
+            const f32x2 inv2 = f2_splat(inv_norm[step]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (block_abs_max(gv[h]) <= kSiluFastMaxAbs) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 w = s_w[(h * 4 + q) * 4 + m];
+                        v[step][h][2 * q] = f2_mul(f2_mul(f2_mul(v[step][h][2 * q], inv2), make_float2(w.x, w.y)),
+                                                   silu_approx_fast_x2(gv[h][2 * q]));
+                        v[step][h][2 * q + 1] = f2_mul(f2_mul(f2_mul(v[step][h][2 * q + 1], inv2), make_float2(w.z, w.w)),
+                                                       silu_approx_fast_x2(gv[h][2 * q + 1]));
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 w = s_w[(h * 4 + q) * 4 + m];
+                        f32x2& a = v[step][h][2 * q];
+                        f32x2& b = v[step][h][2 * q + 1];
+                        a = make_float2(a.x * inv_norm[step] * w.x * silu_fast_div(gv[h][2 * q].x),
+                                        a.y * inv_norm[step] * w.y * silu_fast_div(gv[h][2 * q].y));
+                        b = make_float2(b.x * inv_norm[step] * w.z * silu_fast_div(gv[h][2 * q + 1].x),
+                                        b.y * inv_norm[step] * w.w * silu_fast_div(gv[h][2 * q + 1].y));
+                    }
+                }
+                amax = fmaxf_nan(amax, block_abs_max(v[step][h]));
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            amax = fmaxf_nan(amax, __shfl_xor_sync(kFullMask, amax, off));
+        }
+        if (WPT > 1) {
+            if (lane == 0) s_max[0][parity][warp] = amax;
+            team_barrier<WPT>(team);
+            amax = s_max[0][parity][team * WPT];
+#pragma unroll
+            for (int w = 1; w < WPT; ++w) {
+                amax = fmaxf_nan(amax, s_max[0][parity][team * WPT + w]);
+            }
+        }
+        const bool fast = amax == 0.0f || (amax >= kFp8FastMinAmax && amax <= kFp8FastMaxAmax);
+        if (fast) {
+            const float scale = __fdiv_rn(amax, 448.0f);
+            if (wt == 0 && lane == 0) {
+                scales[token] = (uint16_t)(__float_as_uint(scale) >> 16);
+            }
+            const f32x2 inv2 = f2_splat((scale > 0.0f) ? __frcp_rn(scale) : 0.0f);
+#pragma unroll
+            for (int step = 0; step < STEPS; ++step) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    *reinterpret_cast<uint4*>(out + head_row(token, step) * COLS + (m + 4 * h) * 16) =
+                        fp8_encode16_qp(v[step][h], inv2);
+                }
+            }
+        } else {
+            float mx = 0.0f;
+#pragma unroll
+            for (int step = 0; step < STEPS; ++step) {
+                mx = fmaxf(mx, fmaxf(block_abs_max_ignoring_nan(v[step][0]), block_abs_max_ignoring_nan(v[step][1])));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, off));
+            }
+            if (WPT > 1) {
+                if (lane == 0) s_max[1][parity][warp] = mx;
+                team_barrier<WPT>(team);
+                mx = s_max[1][parity][team * WPT];
+#pragma unroll
+                for (int w = 1; w < WPT; ++w) {
+                    mx = fmaxf(mx, s_max[1][parity][team * WPT + w]);
+                }
+            }
+            const float scale = __fdiv_rn(mx, 448.0f);
+            if (wt == 0 && lane == 0) {
+                scales[token] = (uint16_t)(__float_as_uint(scale) >> 16);
+            }
+            const float inv_scale = (scale > 0.0f) ? __fdiv_rn(1.0f, scale) : 0.0f;
+#pragma unroll
+            for (int step = 0; step < STEPS; ++step) {
+                for (int h = 0; h < 2; ++h) {
+                    const size_t off = head_row(token, step) * COLS + (m + 4 * h) * 16;
+                    fp8_gated_block_cold(x + off, gate + off, weight + (m + 4 * h) * 16, inv_norm[step], inv_scale,
+                                         reinterpret_cast<uint4*>(out + off));
                 }
             }
         }

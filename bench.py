@@ -62,6 +62,11 @@ BYTES_PER_ROW = {
     "sigmoid_mul": 3 * 2 * HIDDEN,                                                            # 12,288
     "add": 3 * 2 * HIDDEN,                                                                    # 12,288
     "add_rms_norm_quantise_nvfp4": 3 * 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,               # 13,440
+    # FP8 (E4M3) quantisers: one code byte per value, one 2-byte scale per row
+    "quantise_fp8": 2 * HIDDEN + HIDDEN + 2,                                                  # 6,146
+    "rms_norm_fp8_bf16": 2 * HIDDEN + HIDDEN + 2 + 2 * HIDDEN,                                # 10,242 (codes + bf16 twin)
+    "swiglu_quantise_fp8": 2 * 2 * INTER + INTER + 2,                                         # 30,722
+    "rms_norm_gated_quantise_fp8": 2 * 2 * HIDDEN + HIDDEN + 2,                               # 10,242
 }
 STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k"]
 FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k",
@@ -285,6 +290,9 @@ def run_gpu_arm(args):
             "cache_k": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
             "cache_v": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
             "sum": torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16, device="cuda"),
+            "q8_h": torch.empty(ROWS, HIDDEN, dtype=torch.uint8, device="cuda"),
+            "q8_i": torch.empty(ROWS, INTER, dtype=torch.uint8, device="cuda"),
+            "s8": torch.empty(ROWS, dtype=torch.int16, device="cuda"),
         })
     cache_map = torch.randperm(ROWS, device="cuda", generator=gen).to(torch.int32)   # the engine's cpos: a slot per token
     w_head = (torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
@@ -326,6 +334,13 @@ def run_gpu_arm(args):
         "add_rms_norm_quantise_nvfp4": lambda d: lib.clef_add_rms_norm_quantise_nvfp4(
             stream(), p(d["sum"]), p(d["x"]), p(d["res"]), p(w_norm), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, EPS,
             GS_NORM, 128, 512, 0),
+        "quantise_fp8": lambda d: lib.clef_quantise_fp8(stream(), p(d["x"]), p(d["q8_h"]), p(d["s8"]), ROWS, HIDDEN, 0),
+        "rms_norm_fp8_bf16": lambda d: lib.clef_rms_norm_fp8_bf16(stream(), p(d["x"]), p(w_norm), p(d["q8_h"]), p(d["s8"]),
+                                                                  p(d["sum"]), ROWS, HIDDEN, EPS, 0),
+        "swiglu_quantise_fp8": lambda d: lib.clef_swiglu_quantise_fp8(stream(), p(d["gate"]), p(d["up"]), p(d["q8_i"]),
+                                                                      p(d["s8"]), ROWS, INTER, 0),
+        "rms_norm_gated_quantise_fp8": lambda d: lib.clef_rms_norm_gated_quantise_fp8(
+            stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["q8_h"]), p(d["s8"]), ROWS * VH, HEAD_DIM, EPS, VH, ROWS * VH, 0),
     }
 
     def step_eager(d):

@@ -79,7 +79,7 @@ extern "C" __global__ void probe_e2m1(unsigned long long base, unsigned long lon
 // (clef::quantise16_rare handles it the same way), everything else through e4m3_encode_finite.
 extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long long count, ProbeResult* result) {
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-    unsigned long long checked = 0;
+    unsigned long long checked = 0, checked_fast = 0;
     for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         const uint32_t bits = (uint32_t)(base + i);
         const float v = __uint_as_float(bits);
@@ -92,9 +92,16 @@ extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long lon
         if (clef::e4m3_encode_any(v) != want) {   // the FP8 quantisers' element encoder, every pattern
             report(&result[1], bits);
         }
+        if (bits < 0x43E80000u) {                 // the tuned FP8 kernels' short encoder on its domain, +0 <= v < 464
+            ++checked_fast;
+            if (clef::e4m3_mag_fast(v) != want) {
+                report(&result[2], bits);
+            }
+        }
     }
     atomicAdd(&result[0].checked, checked);
     atomicAdd(&result[1].checked, checked);
+    atomicAdd(&result[2].checked, checked_fast);
 }
 
 // result[0]: decoder on all 256 bytes (bit-exact f32); result[1]: inv_scale for `global_scale`.

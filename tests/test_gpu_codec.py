@@ -27,7 +27,8 @@ def test_e4m3_encoder_all_patterns():
     """Both encoders (the block-scale one and the FP8 quantisers' element one) against the reference's to_e4m3."""
     res = ref_gpu.probe_e4m3(0, 1 << 32)
     assert res[0]["checked"] == 1 << 32 and res[1]["checked"] == 1 << 32
-    assert res[0]["mismatches"] == 0 and res[1]["mismatches"] == 0, _fmt(res)
+    assert res[2]["checked"] == 0x43E80000            # every pattern of [+0, 464)
+    assert all(r["mismatches"] == 0 for r in res), _fmt(res)
 
 
 @pytest.mark.parametrize("global_scale", [1.0, 64.0, 215.0, 1.0 / 12.5, 2688.0, 1e-3])
