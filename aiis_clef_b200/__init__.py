@@ -5,4 +5,4 @@ holds its build step and a ctypes binding whose `Device` class mirrors the refer
 """
 from .lib import (CLEF_BF16, CLEF_F32, ClefError, Device, HostDevice, load, load_host, nvfp4_m_tile_for,  # noqa: F401
                   nvfp4_sizes, pass_geometries, pass_maps, rungs_decompose, shard_rows,
-                  set_kernel_choice, sf_atom_for_tile_m)
+                  set_kernel_choice, set_scale_layout, sf_atom_for_tile_m, SF_ACTIVATION, SF_INTERLEAVED)

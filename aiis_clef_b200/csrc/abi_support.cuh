@@ -134,6 +134,9 @@ inline int check_scale_layout(const char* what, int rows, int cols, int blk_mn, 
 
 inline bool use_hot() { return kernel_choice() == 0; }
 
+// chunk as the kernels take it: negated when the interleaved tile order is selected (nvfp4_codec.cuh, SfLayout).
+inline int fold_scale_layout(int chunk) { return scale_layout() == CLEF_SF_INTERLEAVED ? -chunk : chunk; }
+
 inline cudaStream_t as_stream(clef_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 template <typename T>

@@ -34,10 +34,12 @@ int fail(int code, const char* fmt, ...) {
 
 namespace {
 std::atomic<int> g_kernel_choice{0};
+std::atomic<int> g_scale_layout{0};
 }
 
 namespace clef {
 int kernel_choice() { return g_kernel_choice.load(std::memory_order_relaxed); }
+int scale_layout() { return g_scale_layout.load(std::memory_order_relaxed); }
 }  // namespace clef
 
 
@@ -51,6 +53,14 @@ const char* clef_last_error(void) { return g_error; }
 int clef_version(void) { return 100; }
 
 void clef_set_kernel_choice(int choice) { g_kernel_choice.store(choice == 1 ? 1 : 0, std::memory_order_relaxed); }
+
+int clef_set_scale_layout(int layout) {
+    if (layout != CLEF_SF_ACTIVATION && layout != CLEF_SF_INTERLEAVED) {
+        return fail(CLEF_ERR_INVALID, "clef_set_scale_layout: layout %d", layout);
+    }
+    g_scale_layout.store(layout, std::memory_order_relaxed);
+    return CLEF_OK;
+}
 
 int clef_sf_atom_for_tile_m(int tile_m, int* blk_mn, int* chunk) {
     if (tile_m <= 0) {
@@ -200,6 +210,7 @@ static int rms_norm_quantise_impl(const char* what, clef_stream_t stream, const 
     if (!x || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (addend && !sum_out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
+    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
     if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(packed, 8) || (addend && (!aligned(addend, 16) || !aligned(sum_out, 16)))) {
         return fail(CLEF_ERR_INVALID, "%s: activations and weight must be 16-byte aligned, packed 8-byte aligned", what);
     }
@@ -330,6 +341,7 @@ int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, cons
                     rows_live);
     }
     if (int r = check_scale_layout(what, rows / vh, vh * cols, blk_mn, chunk)) return r;
+    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
     if ((rows / vh) % blk_mn != 0) {
         return fail(CLEF_ERR_INVALID, "%s: rows/vh = %d tokens is not a multiple of blk_mn %d (rows counts padding)", what,
                     rows / vh, blk_mn);
@@ -410,6 +422,7 @@ int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, ui
     if (int r = check_dtype(dtype, what)) return r;
     if (!x || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
+    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
     if (!aligned(x, 16) || !aligned(packed, 8)) {
         return fail(CLEF_ERR_INVALID, "%s: x must be 16-byte aligned, packed 8-byte aligned", what);
     }
@@ -448,6 +461,7 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
     if (int r = check_dtype(dtype, what)) return r;
     if (!gate || !up || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
+    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
     if (!aligned(gate, 16) || !aligned(up, 16) || !aligned(packed, 8)) {
         return fail(CLEF_ERR_INVALID, "%s: gate and up must be 16-byte aligned, packed 8-byte aligned", what);
     }

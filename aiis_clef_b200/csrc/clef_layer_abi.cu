@@ -243,6 +243,7 @@ int clef_sigmoid_mul_quantise_nvfp4(clef_stream_t stream, const void* x, const v
     if (int r = check_dtype(dtype, what)) return r;
     if (!x || !gate || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
+    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
     if (!aligned(x, 16) || !aligned(gate, 16) || !aligned(packed, 8)) {
         return fail(CLEF_ERR_INVALID, "%s: x and gate must be 16-byte aligned, packed 8-byte aligned", what);
     }

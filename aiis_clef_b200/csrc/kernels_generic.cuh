@@ -40,7 +40,8 @@ __device__ __forceinline__ float team_sum_squares(const typename T::storage* xro
     }
     __syncthreads();
     const int first = (warp / wpr) * wpr;
-    float t = (lane < wpr) ? s_part[first + lane] : 0.0f;
+    // (a CTA whose 8 warps do not divide into teams leaves a partial last team: it reads in range and its sum is unused)
+    float t = (lane < wpr && first + lane < kCtaThreads / 32) ? s_part[first + lane] : 0.0f;
 #pragma unroll
     for (int off = 4; off > 0; off >>= 1) {
         t = __fadd_rn(t, __shfl_xor_sync(kFullMask, t, off));
@@ -80,10 +81,17 @@ rms_norm_generic_kernel(const typename T::storage* __restrict__ x, const float* 
     }
     const int groups = (rows_total + rpb - 1) / rpb;
     for (int group = blockIdx.x; group < groups; group += gridDim.x) {
+        // Threads beyond the last whole team (tpr = 160, 192 or 224 does not divide 256) take no row. The reference
+        // kernels let them run as a partial team on the NEXT block's first row, racing with that block; the intended
+        // arithmetic, one team of tpr threads per row, is what is computed here.
+        const bool in_team = team < rpb;
         const int row = group * rpb + team;
-        const bool live = row < rows;
+        const bool live = in_team && row < rows;
         const typename T::storage* xrow = x + (size_t)row * cols;
         const float total = team_sum_squares<T>(xrow, live, cols, tpr, s_part);
+        if (!in_team) {
+            continue;
+        }
         if (!QUANT) {
             if (live) {
                 const float inv = inv_rms(total, cols, eps);
@@ -153,11 +161,15 @@ rms_norm_gated_generic_kernel(const typename T::storage* __restrict__ x, const t
     }
     const int groups = (rows_total + rpb - 1) / rpb;
     for (int group = blockIdx.x; group < groups; group += gridDim.x) {
+        const bool in_team = team < rpb;   // see rms_norm_generic_kernel
         const int row = group * rpb + team;
-        const bool live = row < rows_live;
+        const bool live = in_team && row < rows_live;
         const typename T::storage* xrow = x + (size_t)row * cols;
         const typename T::storage* grow = gate ? gate + (size_t)row * cols : nullptr;
         const float total = team_sum_squares<T>(xrow, live, cols, tpr, s_part);
+        if (!in_team) {
+            continue;
+        }
         if (!QUANT) {
             if (live) {
                 const float inv = inv_rms(total, cols, eps);

@@ -212,6 +212,8 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
     constexpr int COLS = NB * 512;
     constexpr int BLOCKS = COLS / 16;
     __shared__ float s_inv[kInvScaleTableSize];
+    const SfLayout sf = sf_layout_of(blk_mn, chunk);   // a negated chunk selects the interleaved tile order
+    chunk = sf.chunk;
     // (1 + w) in the quad-pair layout, transposed so lane L reads s_w[(4 j + q) * 32 + L] =
     // (1+w_x, 1+w_z, 1+w_y, 1+w_w) of quad q of chunk L + 32 j.
     extern __shared__ float4 s_w[];
@@ -239,7 +241,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
     for (; row < rows_total; row += gridDim.x * 8) {
         uint8_t* prow = packed + (size_t)row * (COLS / 2);
         const uint32_t m_rest = fast_div((uint32_t)row, atom_div);
-        const uint32_t m_atom = (uint32_t)row - m_rest * (uint32_t)blk_mn;
+        const uint32_t m_atom = sf_row_slot((uint32_t)row - m_rest * (uint32_t)blk_mn, sf);
         uint8_t* srow = scales + (size_t)m_rest * (BLOCKS / 4) * (size_t)chunk + (size_t)m_atom * 4;
         if (row >= rows) {
 #pragma unroll
@@ -460,6 +462,8 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
                         uint32_t total_units, int cols, float global_scale, int blk_mn, int chunk, FastDiv seg_div,
                         FastDiv atom_div) {
     __shared__ float s_inv[kInvScaleTableSize];
+    const SfLayout sf = sf_layout_of(blk_mn, chunk);   // a negated chunk selects the interleaved tile order
+    chunk = sf.chunk;
     const int lane = threadIdx.x & 31;
     const uint32_t warps = gridDim.x * (kCtaThreads / 32);
     uint32_t unit0 = blockIdx.x * (kCtaThreads / 32) + (threadIdx.x >> 5);
@@ -489,7 +493,7 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
             const uint32_t row = fast_div(unit, seg_div);
             const uint32_t block = (unit - row * seg_div.d) * 32 + lane;
             const uint32_t m_rest = fast_div(row, atom_div);
-            const uint32_t m_atom = row - m_rest * (uint32_t)blk_mn;
+            const uint32_t m_atom = sf_row_slot(row - m_rest * (uint32_t)blk_mn, sf);
             uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
             uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)unit * 256 + lane * 8);
             if (unit >= live_units) {
@@ -570,6 +574,8 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
                             float global_scale, int blk_mn, int chunk, int vh, FastDiv vh_div, FastDiv atom_div) {
     constexpr int COLS = 128;
     __shared__ float s_inv[kInvScaleTableSize];
+    const SfLayout sf = sf_layout_of(blk_mn, chunk);   // a negated chunk selects the interleaved tile order
+    chunk = sf.chunk;
     // plain weight in the quad-pair layout: s_w[(h * 4 + q) * 4 + m] = (w_x, w_z, w_y, w_w) of quad q of chunk m + 4h
     __shared__ float4 s_w[32];
     const int lane = threadIdx.x & 31;
@@ -627,7 +633,7 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
         const uint32_t token = fast_div(hrow, vh_div);
         const uint32_t head_block = (hrow - token * (uint32_t)vh) * (COLS / 16);
         const uint32_t m_rest = fast_div(token, atom_div);
-        const uint32_t m_atom = token - m_rest * (uint32_t)blk_mn;
+        const uint32_t m_atom = sf_row_slot(token - m_rest * (uint32_t)blk_mn, sf);
         const float inv = inv_rms_pow2<COLS>(total, eps);
         const f32x2 inv2 = f2_splat(inv);
 #pragma unroll
@@ -681,6 +687,8 @@ quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed
                     uint32_t live_units, uint32_t total_units, int cols, float global_scale, int blk_mn, int chunk,
                     FastDiv seg_div, FastDiv atom_div) {
     __shared__ float s_inv[kInvScaleTableSize];
+    const SfLayout sf = sf_layout_of(blk_mn, chunk);   // a negated chunk selects the interleaved tile order
+    chunk = sf.chunk;
     const int lane = threadIdx.x & 31;
     const uint32_t warps = gridDim.x * (kCtaThreads / 32);
     uint32_t unit0 = blockIdx.x * (kCtaThreads / 32) + (threadIdx.x >> 5);
@@ -707,7 +715,7 @@ quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed
             const uint32_t row = fast_div(unit, seg_div);
             const uint32_t block = (unit - row * seg_div.d) * 32 + lane;
             const uint32_t m_rest = fast_div(row, atom_div);
-            const uint32_t m_atom = row - m_rest * (uint32_t)blk_mn;
+            const uint32_t m_atom = sf_row_slot(row - m_rest * (uint32_t)blk_mn, sf);
             uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
             uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)unit * 256 + lane * 8);
             if (unit >= live_units) {

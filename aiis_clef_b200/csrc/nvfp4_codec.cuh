@@ -253,13 +253,30 @@ __device__ __forceinline__ void quantise16_x2(const f32x2* v, float global_scale
 
 // --------------------------------------------------------------------------------------------
 // Scale addressing (activation side, kernels/quantise.cu:34-41): tiles of [blk_mn rows x 4
-// blocks] = `chunk` bytes, row-major inside, ordered (row tile, group of 4 blocks).
+// blocks] = `chunk` bytes, ordered (row tile, group of 4 blocks). Inside a tile the reference's
+// activation side stores row r at byte 4 r ("conflict-free", src/swizzle.rs:64-65); the standard
+// block-scaled layout of a tcgen05 GEMM stores it at 4 ((r % 32) * (blk_mn / 32) + r / 32)
+// (src/swizzle.rs:66-68, the weight side's order). Kernels receive the choice folded into their
+// `chunk` argument: a NEGATED chunk selects the interleaved order (chunk is always 4 * blk_mn, so
+// the sign is free); sf_layout_of undoes the folding.
 // --------------------------------------------------------------------------------------------
-__device__ __forceinline__ size_t scale_offset(int row, int block, int blocks_per_row, int blk_mn, int chunk) {
+struct SfLayout {
+    int chunk;   // bytes per tile
+    int sub;     // blk_mn / 32 for the interleaved order, 0 for the reference's activation-side order
+};
+__device__ __forceinline__ SfLayout sf_layout_of(int blk_mn, int chunk_arg) {
+    return chunk_arg < 0 ? SfLayout{-chunk_arg, blk_mn >> 5} : SfLayout{chunk_arg, 0};
+}
+__device__ __forceinline__ uint32_t sf_row_slot(uint32_t row_in_tile, const SfLayout& sf) {
+    return sf.sub ? (row_in_tile & 31u) * (uint32_t)sf.sub + (row_in_tile >> 5) : row_in_tile;
+}
+
+__device__ __forceinline__ size_t scale_offset(int row, int block, int blocks_per_row, int blk_mn, int chunk_arg) {
+    const SfLayout sf = sf_layout_of(blk_mn, chunk_arg);
     const int k1_count = blocks_per_row >> 2;
     const int m_rest = row / blk_mn;
-    const int m_atom = row - m_rest * blk_mn;
-    return ((size_t)m_rest * k1_count + (size_t)(block >> 2)) * (size_t)chunk + (size_t)m_atom * 4 + (size_t)(block & 3);
+    const uint32_t m_atom = sf_row_slot((uint32_t)(row - m_rest * blk_mn), sf);
+    return ((size_t)m_rest * k1_count + (size_t)(block >> 2)) * (size_t)sf.chunk + (size_t)m_atom * 4 + (size_t)(block & 3);
 }
 
 }  // namespace clef

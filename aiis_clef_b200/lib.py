@@ -59,6 +59,7 @@ SYMBOLS = {
     "clef_swiglu_quantise_fp8": (_I, [_P, _P, _P, _P, _P, _I, _I, _I]),
     "clef_rms_norm_fp8_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I]),
     "clef_rms_norm_gated_quantise_fp8": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
+    "clef_set_scale_layout": (_I, [_I]),
     "clef_set_kernel_choice": (None, [_I]),
 }
 
@@ -146,6 +147,15 @@ def nvfp4_m_tile_for(m: int) -> int:
 def set_kernel_choice(choice: int) -> None:
     """0: tuned kernel when the shape has one (default); 1: always the shape-general kernel."""
     load().clef_set_kernel_choice(int(choice))
+
+
+SF_ACTIVATION, SF_INTERLEAVED = 0, 1
+
+
+def set_scale_layout(layout: int) -> None:
+    """Row order inside a scale tile for every NVFP4 entry point: SF_ACTIVATION (the reference's activation side,
+    default) or SF_INTERLEAVED (the 32 x 4 x 4 order of src/swizzle.rs:66-68, read directly by block-scaled GEMMs)."""
+    _check(load().clef_set_scale_layout(int(layout)), "clef_set_scale_layout")
 
 
 class Device:

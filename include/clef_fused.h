@@ -233,6 +233,16 @@ int clef_rms_norm_gated_quantise_fp8(clef_stream_t stream, const void* x, const 
                                      uint8_t* out, uint16_t* scales, int rows, int cols, float eps, int vh,
                                      int rows_live, int dtype);
 
+/* Order of the rows inside a [blk_mn rows x 4 blocks] scale tile, for every NVFP4 entry point of the process:
+ *   CLEF_SF_ACTIVATION   row r at byte 4 r: the reference's activation-side ("conflict-free") order,
+ *                        kernels/quantise.cu:34-41, src/swizzle.rs:64-65. Default.
+ *   CLEF_SF_INTERLEAVED  row r at byte 4 ((r % 32) * (blk_mn / 32) + r / 32): the 32 x 4 x 4 order of
+ *                        src/swizzle.rs:66-68 that block-scaled tensor-core GEMMs (tcgen05) read directly.
+ * It is a property of the GEMM that consumes the operands, so it is set once, not per call. */
+#define CLEF_SF_ACTIVATION 0
+#define CLEF_SF_INTERLEAVED 1
+int clef_set_scale_layout(int layout);
+
 /* Kernel selection for tests and measurements: 0 = automatic (tuned kernel when the shape has one),
  * 1 = always the shape-general kernel. Process-wide; not part of the reference interface. */
 void clef_set_kernel_choice(int choice);

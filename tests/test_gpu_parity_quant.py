@@ -125,6 +125,32 @@ def test_rms_norm_quantise_nvfp4(rows, cols, choice):
         assert_bytes_equal(f_s, want_s, "f32 input scales")
 
 
+@pytest.mark.parametrize("rows", [1, 65, 300])
+@pytest.mark.parametrize("cols", [1088, 1536, 1792])
+def test_widths_whose_reference_team_does_not_divide_the_cta(rows, cols):
+    """cols in (1024, 1792]: the reference assigns 160, 192 or 224 threads to a row, which does not divide its
+    256-thread block; its surplus threads then work on the next block's row as a partial team and race with that
+    block, so the reference kernels are not an arbiter here. The CPU oracle (one team per row) is, and the result
+    must be the same on every call."""
+    rng = np.random.default_rng(rows + cols)
+    x = normal_bf16(rng, (rows, cols), outlier_channels=4)
+    w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
+    eps, gs = 1e-6, 64.0
+    dx, dw = dev_bf16(x), torch.from_numpy(w).cuda()
+    want_p, want_s = orc.rms_norm_quantise_nvfp4(x, w, rows, cols, eps, gs)
+    for trial in range(3):
+        got_p, got_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(dx), ptr(dw)],
+                                 [rows, cols, eps, gs, 128, 512, BF16])
+        assert_bytes_equal(got_s, want_s, f"scales vs CPU oracle (call {trial})")
+        assert_bytes_equal(got_p, want_p, f"packed vs CPU oracle (call {trial})")
+    dev = clef.Device(0)
+    _, want = orc.rms_norm(x, w, rows, cols, eps)
+    out = dev.rms_norm_dev(dx, dw, rows, cols, eps)
+    torch.cuda.synchronize()
+    d = np.abs(orc.bf16_bits(out.cpu()).astype(np.int32).reshape(-1) - want.astype(np.int32).reshape(-1))
+    assert d.max() <= 1
+
+
 def test_rms_norm_quantise_96_row_atom():
     rows, cols = 200, 2048
     rng = np.random.default_rng(5)
