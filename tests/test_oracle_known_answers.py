@@ -336,3 +336,31 @@ def test_sigmoid_mul_and_add_known_answers():
     pc, sc = orc.quantise_nvfp4(act, rows, cols, 48.0)
     pf, sf = orc.sigmoid_mul_quantise_nvfp4(xv, gv, rows, cols, 48.0)
     assert np.array_equal(pf, pc) and np.array_equal(sf, sc)
+
+
+def test_config_0_chain_on_the_cpu_restatement():
+    """The CPU-runnable configuration: 778 rows, embedding gather (table 32768 x 2048, N(0, 0.02), 8 outlier channels
+    x20) -> RMSNorm (eps 1e-6, weight 1 + N(0, 0.1)) -> NVFP4 -> dequantised check with src/dequant.rs semantics."""
+    from util import to_bf16_bits
+    rows, hidden, vocab = 778, 2048, 32768
+    rng = np.random.default_rng(7780)
+    tf = (rng.standard_normal((vocab, hidden)) * 0.02).astype(np.float32)
+    tf[:, rng.choice(hidden, 8, replace=False)] *= 20.0
+    table = to_bf16_bits(tf)
+    ids = rng.integers(0, vocab, rows).astype(np.int32)
+    w = (rng.standard_normal(hidden) * 0.1).astype(np.float32)
+    h = orc.embed_gather(table, ids, rows, hidden)
+    assert np.array_equal(h, table[ids])
+    normed, _ = orc.rms_norm(h, w, rows, hidden, 1e-6)
+    gs = float(np.float32(448.0 * 6.0) / np.abs(normed).max())
+    fused_p, fused_s = orc.rms_norm_quantise_nvfp4(h, w, rows, hidden, 1e-6, gs)
+    chain_p, chain_s = orc.quantise_nvfp4(normed, rows, hidden, gs)
+    assert np.array_equal(fused_p, chain_p) and np.array_equal(fused_s, chain_s)
+    rows_padded, blocks = 896, hidden // 16
+    assert fused_p.size == rows_padded * hidden // 2 and not fused_p[rows * hidden // 2:].any()
+    row_major = orc.unswizzle_tiled(fused_s, rows_padded, blocks, 128, conflict_free=True)[: rows * blocks].reshape(rows, blocks)
+    scale_f32 = orc.e4m3_table()[row_major]
+    deq = orc.dequantise(fused_p[: rows * hidden // 2], scale_f32, gs, hidden, rows).reshape(rows, hidden)
+    unit = np.repeat(scale_f32 / np.float32(gs), 16, axis=1)
+    assert (np.abs(deq - normed) <= unit + 1e-12).all()
+    assert np.linalg.norm(deq - normed) / np.linalg.norm(normed) < 0.2
