@@ -40,8 +40,11 @@ struct clef_device {
     cudaEvent_t slot_free[kStreams] = {nullptr, nullptr};
     void* arena[kStreams] = {nullptr, nullptr};
     size_t arena_bytes[kStreams] = {0, 0};
-    void* consts = nullptr;       // small operands of the current call (weights, tables, maps)
+    void* consts = nullptr;       // small operands (weights, tables): two halves, used by alternate calls
     size_t consts_bytes = 0;
+    int consts_gen = 0;           // the half the current call uses
+    cudaEvent_t gen_done[2][kStreams] = {{nullptr, nullptr}, {nullptr, nullptr}};   // last work that read a half
+    bool pipelined = false;       // host-slice calls return once their work is enqueued (clef_device_set_pipelined)
     std::mutex lock;              // one host-slice call at a time per handle
 };
 
@@ -151,7 +154,13 @@ int run_tiled(clef_device* dev, int rows, int atom, int tile_rows, std::vector<R
         CLEF_CUDA(cudaEventRecord(dev->slot_free[s], st));
     }
     for (int s = 0; s < kStreams; ++s) {
-        CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
+        // the half of the constants arena this call read may be rewritten once this point is reached
+        CLEF_CUDA(cudaEventRecord(dev->gen_done[dev->consts_gen][s], dev->streams[s]));
+    }
+    if (!dev->pipelined) {
+        for (int s = 0; s < kStreams; ++s) {
+            CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
+        }
     }
     return CLEF_OK;
 }
@@ -175,8 +184,16 @@ int upload_consts(clef_device* dev, std::initializer_list<std::pair<const void*,
                   std::vector<void*>& device_ptrs) {
     size_t total = 0;
     for (const auto& it : items) total += round_up(it.second, 256);
-    if (int rc = ensure_consts(dev, total)) return rc;
-    size_t off = 0;
+    const size_t half = round_up(total, 1 << 16);
+    if (int rc = ensure_consts(dev, 2 * half)) return rc;
+    // Alternate calls use alternate halves, so that (in pipelined mode) this call's constants can be uploaded while
+    // the previous call's kernels still read theirs; the half is free once the call before that has passed the
+    // events recorded at its end.
+    dev->consts_gen ^= 1;
+    for (int s = 0; s < kStreams; ++s) {
+        CLEF_CUDA(cudaStreamWaitEvent(dev->streams[0], dev->gen_done[dev->consts_gen][s], 0));
+    }
+    size_t off = (size_t)dev->consts_gen * (dev->consts_bytes / 2);
     for (const auto& it : items) {
         void* dst = static_cast<char*>(dev->consts) + off;
         device_ptrs.push_back(it.first ? dst : nullptr);
@@ -223,6 +240,8 @@ int clef_device_open(int ordinal, clef_device** out) {
     for (int s = 0; s < kStreams; ++s) {
         CLEF_CUDA(cudaStreamCreateWithPriority(&dev->streams[s], cudaStreamNonBlocking, greatest));
         CLEF_CUDA(cudaEventCreateWithFlags(&dev->slot_free[s], cudaEventDisableTiming));
+        CLEF_CUDA(cudaEventCreateWithFlags(&dev->gen_done[0][s], cudaEventDisableTiming));
+        CLEF_CUDA(cudaEventCreateWithFlags(&dev->gen_done[1][s], cudaEventDisableTiming));
     }
     *out = dev;
     return CLEF_OK;
@@ -238,6 +257,8 @@ int clef_device_close(clef_device* dev) {
                 cudaStreamDestroy(dev->streams[s]);
             }
             if (dev->slot_free[s]) cudaEventDestroy(dev->slot_free[s]);
+            if (dev->gen_done[0][s]) cudaEventDestroy(dev->gen_done[0][s]);
+            if (dev->gen_done[1][s]) cudaEventDestroy(dev->gen_done[1][s]);
             if (dev->arena[s]) cudaFree(dev->arena[s]);
         }
         if (dev->consts) cudaFree(dev->consts);
@@ -255,6 +276,19 @@ int clef_device_synchronize(clef_device* dev) {
     DeviceScope scope(dev);
     for (int s = 0; s < kStreams; ++s) {
         CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
+    }
+    return CLEF_OK;
+}
+
+int clef_device_set_pipelined(clef_device* dev, int on) {
+    if (int rc = check_handle(dev, "clef_device_set_pipelined")) return rc;
+    std::lock_guard<std::mutex> guard(dev->lock);
+    dev->pipelined = on != 0;
+    if (!dev->pipelined) {
+        DeviceScope scope(dev);
+        for (int s = 0; s < kStreams; ++s) {
+            CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
+        }
     }
     return CLEF_OK;
 }
@@ -476,12 +510,19 @@ int clef_host_rope(clef_device* dev, void* out, const void* x, const float* cos_
     std::vector<RowStream> in{{x, nullptr, row, 0}, {pos_map, nullptr, sizeof(int32_t), 0}};
     std::vector<RowStream> outs{{nullptr, out, row, 0}};
     const int tile = pick_tile_rows(rows, 128, 2 * row);
-    return run_tiled(dev, rows, 1, tile, in, outs, false,
-                     [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
-                         return clef_rope(st, base + outs[0].offset, base + in[0].offset, (const float*)consts[0],
-                                          (const float*)consts[1], n_live, heads, head_dim, rotary_dim, nullptr, nullptr,
-                                          (const int32_t*)(base + in[1].offset), dtype);
-                     });
+    const int rc = run_tiled(dev, rows, 1, tile, in, outs, false,
+                             [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
+                                 return clef_rope(st, base + outs[0].offset, base + in[0].offset, (const float*)consts[0],
+                                                  (const float*)consts[1], n_live, heads, head_dim, rotary_dim, nullptr,
+                                                  nullptr, (const int32_t*)(base + in[1].offset), dtype);
+                             });
+    if (rc == CLEF_OK && dev->pipelined && !iota.empty()) {
+        // the position map of this call lives in a local buffer: its uploads must finish before it goes away
+        for (int s = 0; s < kStreams; ++s) {
+            CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
+        }
+    }
+    return rc;
 }
 
 // ---- per-token maps -----------------------------------------------------------------------------------------

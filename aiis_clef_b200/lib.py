@@ -453,6 +453,7 @@ HOST_SYMBOLS = {
     "clef_device_ordinal": (_I, [_P]),
     "clef_device_stream": (_P, [_P]),
     "clef_device_synchronize": (_I, [_P]),
+    "clef_device_set_pipelined": (_I, [_P, _I]),
     "clef_device_alloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
     "clef_device_free": (_I, [_P, _P]),
     "clef_device_upload": (_I, [_P, _P, _P, _SZ]),
@@ -570,6 +571,14 @@ class HostDevice:
         if self.handle:
             self.lib.clef_device_close(self.handle)
             self.handle = None
+
+    def set_pipelined(self, on: bool):
+        """Pipelined mode: the calls below return once enqueued; `synchronize()` completes them. Every buffer passed
+        to a call (weights included) must stay alive and unchanged until then."""
+        _check(self.lib.clef_device_set_pipelined(self.handle, int(bool(on))), "clef_device_set_pipelined")
+
+    def synchronize(self):
+        _check(self.lib.clef_device_synchronize(self.handle), "clef_device_synchronize")
 
     def __del__(self):
         try:

@@ -421,7 +421,11 @@ def run_gpu_arm(args):
         hd.swiglu_quantise_nvfp4(host["gate"], host["up"], out["pk_i"], out["sc_i"], ROWS, INTER, GS_SWIGLU)
         hd.rope(out["q"], host["q"], host_cos, host_sin, ROWS, ROWS, Q_HEADS, HEAD_DIM, ROTARY, host["cpos"])
         hd.rope(out["k"], host["k"], host_cos, host_sin, ROWS, ROWS, KV_HEADS, HEAD_DIM, ROTARY, host["cpos"])
+        hd.synchronize()     # every output of the step is in host memory from here on
 
+    # Pipelined host-slice mode: the four calls of a step are enqueued back to back (uploads of one call run under
+    # the downloads of the previous one) and the step ends with one synchronisation.
+    hd.set_pipelined(True)
     h2d = sum(host[k].numel() * host[k].element_size() for k in ("x", "gate", "up", "q", "k")) + 2 * host["cpos"].numel() * 4 \
         + host_w.nbytes + 2 * 2 * host_cos.numel() * 4
     d2h = sum(t.numel() * t.element_size() for t in out.values())
@@ -472,7 +476,8 @@ def run_gpu_arm(args):
                          "algorithmic_bytes_per_launch": BYTES_PER_ROW[DOMINANT] * ROWS},
             "e2e": {"value": world * ROWS * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "steps": e2e_steps, "outputs_equal_device_path": e2e_ok,
-                    "api": "clef_host_* (host-slice C-ABI, pinned host buffers, two-stream row tiles)"},
+                    "api": "clef_host_* (host-slice C-ABI, pinned host buffers, two-stream row tiles, pipelined mode: "
+                           "one clef_device_synchronize per step)"},
             "gpu_launches": len(STEP_KERNELS) * args.steps,
             "clocks": clocks,
             "kernels": kernels,

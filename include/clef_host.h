@@ -39,6 +39,11 @@ int clef_device_ordinal(const clef_device* dev);
 /* The stream every *_dev call of this handle should be given (a cudaStream_t). */
 clef_stream_t clef_device_stream(clef_device* dev);
 int clef_device_synchronize(clef_device* dev);
+/* Pipelined mode (off by default): a host-slice call (clef_host_*) returns as soon as its copies and launches are
+ * enqueued, so consecutive calls overlap (the uploads of the next call run under the downloads of the previous
+ * one); outputs are complete in host memory after clef_device_synchronize. The caller keeps every host buffer of a
+ * call, inputs and weights included, alive and unchanged until then. Switching it off synchronises. */
+int clef_device_set_pipelined(clef_device* dev, int on);
 /* Stream-ordered device memory (src/cuda/mod.rs:3971-4051); not for use inside a stream capture. */
 int clef_device_alloc(clef_device* dev, size_t bytes, void** out);
 int clef_device_free(clef_device* dev, void* ptr);

@@ -103,3 +103,38 @@ def test_host_rope_and_embed(host_dev):
     got = np.zeros((tokens, hidden), np.uint16)
     host_dev.embed_gather(dev_bf16(table), ids, got, tokens, hidden)
     assert_bytes_equal(got, table[ids], "host embed gather")
+
+
+def test_pipelined_mode_gives_the_same_bytes(host_dev):
+    """clef_device_set_pipelined: calls return once enqueued and overlap; after clef_device_synchronize every output
+    equals the synchronous mode's, also when the same call sequence runs several times over the same buffers."""
+    rows, hidden, inter = 3000, 2048, 1024
+    rng = np.random.default_rng(31)
+    x, g, u = (orc.bits_to_torch_bf16(normal_bf16(rng, shape)).pin_memory() for shape in ((rows, hidden), (rows, inter), (rows, inter)))
+    w1 = (rng.standard_normal(hidden) * 0.1).astype(np.float32)
+    w2 = (rng.standard_normal(hidden) * 0.3).astype(np.float32)
+    rp = (rows + 127) // 128 * 128
+
+    def outputs():
+        return [torch.empty(rp * hidden // 2, dtype=torch.uint8).pin_memory(), torch.empty(rp * hidden // 16, dtype=torch.uint8).pin_memory(),
+                torch.empty(rp * hidden // 2, dtype=torch.uint8).pin_memory(), torch.empty(rp * hidden // 16, dtype=torch.uint8).pin_memory(),
+                torch.empty(rp * inter // 2, dtype=torch.uint8).pin_memory(), torch.empty(rp * inter // 16, dtype=torch.uint8).pin_memory()]
+
+    def sequence(o):
+        host_dev.rms_norm_quantise_nvfp4(x, w1, o[0], o[1], rows, hidden, 1e-6, 64.0)
+        host_dev.rms_norm_quantise_nvfp4(x, w2, o[2], o[3], rows, hidden, 1e-6, 64.0)     # different weights, same arena
+        host_dev.swiglu_quantise_nvfp4(g, u, o[4], o[5], rows, inter, 48.0)
+
+    want = outputs()
+    sequence(want)
+    host_dev.set_pipelined(True)
+    try:
+        got = outputs()
+        for _ in range(3):
+            sequence(got)
+        host_dev.synchronize()
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+    finally:
+        host_dev.set_pipelined(False)
+    assert not torch.equal(want[0], want[2])
