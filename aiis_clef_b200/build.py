@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libclef_fused.so"
-SOURCES = ["clef_fused_abi.cu", "clef_layer_abi.cu", "clef_fp8_abi.cu", "clef_host.cu"]
+SOURCES = ["clef_fused_abi.cu", "clef_layer_abi.cu", "clef_fp8_abi.cu", "clef_gdn_prep_abi.cu", "clef_host.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -107,6 +107,28 @@ __device__ __forceinline__ void store_quad<F32>(float* base, size_t quad_index, 
 }
 
 // Load one 16-value block as f32.
+// One activation value widened to f32 / narrowed from f32 (round to nearest even).
+template <typename T>
+__device__ __forceinline__ float load_scalar(const typename T::storage* p);
+template <>
+__device__ __forceinline__ float load_scalar<Bf16>(const uint16_t* p) {
+    return __uint_as_float((uint32_t)(*p) << 16);
+}
+template <>
+__device__ __forceinline__ float load_scalar<F32>(const float* p) {
+    return *p;
+}
+template <typename T>
+__device__ __forceinline__ void store_scalar(typename T::storage* p, float v);
+template <>
+__device__ __forceinline__ void store_scalar<Bf16>(uint16_t* p, float v) {
+    *p = (uint16_t)(pack_bf16x2(v, 0.0f) & 0xffffu);
+}
+template <>
+__device__ __forceinline__ void store_scalar<F32>(float* p, float v) {
+    *p = v;
+}
+
 template <typename T>
 __device__ __forceinline__ void load_block16(const typename T::storage* p, float* v);
 template <>

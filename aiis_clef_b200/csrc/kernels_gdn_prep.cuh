@@ -1,0 +1,221 @@
+// Elementwise kernels in front of the Gated-DeltaNet scan: the causal depthwise convolution + silu driven by
+// the per-token maps (seq_start, slot_map) and the convolution history, the history save, the gate transform,
+// and the q/k/v splitting copies (kernels/elementwise.cu:243-274, 361-445, 463-485). T = Bf16 or F32 is the
+// storage type of the activations; weights, biases and the two gate outputs are f32.
+#pragma once
+
+#include "kernels_fp8.cuh"   // load8<T>
+
+namespace clef {
+
+template <typename T>
+__device__ __forceinline__ void store8(typename T::storage* p, const float* v);
+template <>
+__device__ __forceinline__ void store8<Bf16>(uint16_t* p, const float* v) {
+    stg_v4(p, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+}
+template <>
+__device__ __forceinline__ void store8<F32>(float* p, const float* v) {
+    stg_v4(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
+    stg_v4(p + 4, make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
+}
+
+// ---------------------------------------------------------------------------------------------
+// causal_conv_silu (kernels/elementwise.cu:243-274): out[t, c] = silu(sum over taps of w[c, tap] * x[t - (K-1) + tap, c]),
+// the taps added in ascending order by fused multiply-add (the reference build contracts `acc += w * x`), a tap
+// whose source row lies before the token's sequence start (seq_start[t]) taken from the convolution history of
+// the token's slot (history[slot_map[t]], K - 1 rows per slot) when there is one and skipped otherwise;
+// silu(a) = a / (1 + __expf(-a)) with the IEEE quotient.
+// A thread owns 8 channels and R consecutive rows and slides a K-row window over them, so every x value is
+// loaded once. channels % 8 == 0.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int K, int R>
+__global__ void __launch_bounds__(kCtaThreads)
+causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T::storage* __restrict__ x,
+                        const float* __restrict__ w, int rows, int channels, const int* __restrict__ seq_start,
+                        const typename T::storage* __restrict__ history, const int* __restrict__ slot_map,
+                        FastDiv cvecs_div) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const uint32_t cvecs = cvecs_div.d;
+    const uint32_t strips = ((uint32_t)rows + R - 1) / R;
+    const uint32_t total = strips * cvecs;
+    const uint32_t step = gridDim.x * kCtaThreads;
+    for (uint32_t idx = blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
+        const uint32_t strip = fast_div(idx, cvecs_div);
+        const int c0 = (int)(idx - strip * cvecs) * 8;
+        const int t0 = (int)strip * R;
+        float wt[8][K];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int tap = 0; tap < K; ++tap) {
+                wt[j][tap] = __ldg(w + (size_t)(c0 + j) * K + tap);
+            }
+        }
+        float win[K][8];   // win[i] = x[t - (K-1) + i] for the current row t; win[K-1] is the row itself
+#pragma unroll
+        for (int i = 0; i < K - 1; ++i) {
+            const int src = t0 - (K - 1) + i;
+            if (src >= 0) {
+                load8<T>(x + (size_t)src * channels + c0, win[i + 1]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) win[i + 1][j] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int t = t0 + r;
+            if (t >= rows) {
+                break;
+            }
+#pragma unroll
+            for (int i = 0; i < K - 1; ++i) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) win[i][j] = win[i + 1][j];
+            }
+            load8<T>(x + (size_t)t * channels + c0, win[K - 1]);
+            const int lo = seq_start ? seq_start[t] : 0;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int tap = 0; tap < K; ++tap) {
+                const int src = t - (K - 1) + tap;
+                if (src >= lo) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(wt[j][tap], win[tap][j], acc[j]);
+                } else if (history && src >= lo - (K - 1)) {
+                    const int slot = slot_map ? slot_map[t] : 0;
+                    float h[8];
+                    load8<T>(history + ((size_t)slot * (K - 1) + (size_t)(src - lo + (K - 1))) * channels + c0, h);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(wt[j][tap], h[j], acc[j]);
+                }
+            }
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = silu_ieee_div(acc[j]);
+            store8<T>(out + (size_t)t * channels + c0, o);
+        }
+    }
+}
+
+// The same arithmetic for any tap count and any channel count: one thread per (row, channel).
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads)
+causal_conv_silu_generic_kernel(typename T::storage* __restrict__ out, const typename T::storage* __restrict__ x,
+                                const float* __restrict__ w, int rows, int channels, int k,
+                                const int* __restrict__ seq_start, const typename T::storage* __restrict__ history,
+                                const int* __restrict__ slot_map) {
+    const size_t total = (size_t)rows * channels;
+    const size_t step = (size_t)gridDim.x * kCtaThreads;
+    for (size_t idx = (size_t)blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
+        const int t = (int)(idx / channels);
+        const int ch = (int)(idx - (size_t)t * channels);
+        const int lo = seq_start ? seq_start[t] : 0;
+        float acc = 0.0f;
+        for (int tap = 0; tap < k; ++tap) {
+            const int src = t - (k - 1) + tap;
+            float v;
+            if (src >= lo) {
+                v = load_scalar<T>(x + (size_t)src * channels + ch);
+            } else if (history && src >= lo - (k - 1)) {
+                const int slot = slot_map ? slot_map[t] : 0;
+                v = load_scalar<T>(history + ((size_t)slot * (k - 1) + (size_t)(src - lo + (k - 1))) * channels + ch);
+            } else {
+                continue;
+            }
+            acc = __fmaf_rn(w[(size_t)ch * k + tap], v, acc);
+        }
+        store_scalar<T>(out + idx, silu_ieee_div(acc));
+    }
+}
+
+// conv_hist_save (kernels/elementwise.cu:463-485): for each (row, slot) pair of `saves`, the K - 1 rows ending at
+// `row` become the history of `slot`. One CTA per pair, 16 bytes per thread per step.
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads)
+conv_hist_save_kernel(const typename T::storage* __restrict__ src, typename T::storage* __restrict__ hist,
+                      const int* __restrict__ saves, int n_saves, int rows, int k, int channels) {
+    const int i = blockIdx.x;
+    if (i >= n_saves) return;
+    const int row = saves[2 * i], slot = saves[2 * i + 1];
+    const int hist_rows = k - 1;
+    const size_t per_slot = (size_t)hist_rows * channels;
+    const int first = row + 1 - hist_rows;
+    if (row < 0 || first < 0 || row >= rows) return;
+    const typename T::storage* s = src + (size_t)first * channels;
+    typename T::storage* d = hist + (size_t)slot * per_slot;
+    constexpr int kPer = 16 / T::kBytes;
+    const size_t vecs = per_slot / kPer;
+    for (size_t v = threadIdx.x; v < vecs; v += kCtaThreads) {
+        stg_v4(d + v * kPer, ldg_stream_v4(s + v * kPer));
+    }
+    for (size_t c = vecs * kPer + threadIdx.x; c < per_slot; c += kCtaThreads) {
+        d[c] = s[c];
+    }
+}
+
+// gdn_gates (kernels/elementwise.cu:361-377): beta = 1 / (1 + __expf(-b)); decay = -__expf(a_log[h]) * softplus(a + dt_bias[h])
+// with softplus(x) = x above 20 and log1pf(__expf(x)) otherwise. Outputs are f32.
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads)
+gdn_gates_kernel(const typename T::storage* __restrict__ a, const typename T::storage* __restrict__ b,
+                 const float* __restrict__ a_log, const float* __restrict__ dt_bias, float* __restrict__ decay,
+                 float* __restrict__ beta, int total, int heads) {
+    const int step = gridDim.x * kCtaThreads;
+    for (int i = blockIdx.x * kCtaThreads + threadIdx.x; i < total; i += step) {
+        const int h = i % heads;
+        beta[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, __expf(-load_scalar<T>(b + i))));
+        const float xv = __fadd_rn(load_scalar<T>(a + i), dt_bias[h]);
+        const float sp = (xv > 20.0f) ? xv : log1pf(__expf(xv));
+        decay[i] = __fmul_rn(-__expf(a_log[h]), sp);
+    }
+}
+
+// The three splitting copies (kernels/elementwise.cu:378-445), 16 bytes per thread. `segs` describes, per input
+// row of `in_width` values, up to three consecutive column ranges and where each goes.
+struct SplitPlan {
+    int in_width;        // values per input row
+    int n_out;           // outputs in use
+    int start[3];        // first input column of each range
+    int width[3];        // its width (also the output's row width)
+};
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads)
+split_rows_kernel(const typename T::storage* __restrict__ in, typename T::storage* __restrict__ out0,
+                  typename T::storage* __restrict__ out1, typename T::storage* __restrict__ out2, size_t rows,
+                  SplitPlan plan) {
+    constexpr int kPer = 16 / T::kBytes;
+    const size_t vec_per_row = (size_t)plan.in_width / kPer;
+    const size_t total = rows * vec_per_row;
+    const size_t step = (size_t)gridDim.x * kCtaThreads;
+    for (size_t idx = (size_t)blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
+        const size_t row = idx / vec_per_row;
+        const int col = (int)(idx - row * vec_per_row) * kPer;
+        const uint4 v = ldg_stream_v4(in + row * plan.in_width + col);
+        typename T::storage* dst = out0;
+        int which = 0;
+        if (plan.n_out > 1 && col >= plan.start[1]) { dst = out1; which = 1; }
+        if (plan.n_out > 2 && col >= plan.start[2]) { dst = out2; which = 2; }
+        stg_v4(dst + row * plan.width[which] + (col - plan.start[which]), v);
+    }
+}
+
+// repeat_interleave (kernels/elementwise.cu:429-445): out[t, h * ratio + r, :] = src[t, h, :].
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads)
+repeat_interleave_kernel(const typename T::storage* __restrict__ src, typename T::storage* __restrict__ out,
+                         size_t head_rows_out, int ratio, int dim) {
+    constexpr int kPer = 16 / T::kBytes;
+    const size_t vec_per_row = (size_t)dim / kPer;
+    const size_t total = head_rows_out * vec_per_row;
+    const size_t step = (size_t)gridDim.x * kCtaThreads;
+    for (size_t idx = (size_t)blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
+        const size_t orow = idx / vec_per_row;                  // t * (kh * ratio) + oh
+        const size_t v = idx - orow * vec_per_row;
+        stg_v4(out + orow * dim + v * kPer, ldg_stream_v4(src + (orow / ratio) * dim + v * kPer));
+    }
+}
+
+}  // namespace clef

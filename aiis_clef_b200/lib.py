@@ -59,6 +59,12 @@ SYMBOLS = {
     "clef_swiglu_quantise_fp8": (_I, [_P, _P, _P, _P, _P, _I, _I, _I]),
     "clef_rms_norm_fp8_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I]),
     "clef_rms_norm_gated_quantise_fp8": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
+    "clef_causal_conv_silu": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I]),
+    "clef_conv_hist_save": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I]),
+    "clef_gdn_gates": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I]),
+    "clef_split_q_gate": (_I, [_P, _P, _P, _P, _I, _I, _I, _I]),
+    "clef_split_qkv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
+    "clef_repeat_interleave": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
     "clef_set_scale_layout": (_I, [_I]),
     "clef_set_kernel_choice": (None, [_I]),
 }
@@ -429,6 +435,61 @@ class Device:
                                                              _ptr(scales), rows, cols, eps, vh, rows, _dtype_code(x)),
                    "clef_rms_norm_gated_quantise_fp8")
         return out, scales
+
+    # ==== elementwise kernels in front of the GDN scan ==========================================
+
+    # -- src/cuda/mod.rs:2784-2812 ------------------------------------------------------------
+    def causal_conv_silu_dev(self, x, w, rows: int, channels: int, k: int, seq_start=None, history=None, slot_map=None):
+        _dev_tensor(x, "x")
+        out = self._empty((rows, channels), x.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_causal_conv_silu(_stream(), _ptr(out), _ptr(x), _ptr(w), rows, channels, k, _ptr(seq_start),
+                                                  _ptr(history), _ptr(slot_map), _dtype_code(x)), "clef_causal_conv_silu")
+        return out
+
+    # -- src/cuda/mod.rs:2814-2836 ------------------------------------------------------------
+    def conv_hist_save_dev(self, src, hist, saves, n_saves: int, rows: int, k: int, channels: int):
+        _dev_tensor(src, "src"), _dev_tensor(hist, "hist")
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_conv_hist_save(_stream(), _ptr(hist), _ptr(src), _ptr(saves), n_saves, rows, k, channels,
+                                                _dtype_code(src)), "clef_conv_hist_save")
+
+    # -- src/cuda/mod.rs:2858-2882 ------------------------------------------------------------
+    def gdn_gates_dev(self, a, b, a_log, dt_bias, tokens: int, heads: int):
+        _dev_tensor(a, "a"), _dev_tensor(b, "b")
+        decay, beta = self._empty((tokens, heads), torch.float32), self._empty((tokens, heads), torch.float32)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_gdn_gates(_stream(), _ptr(a), _ptr(b), _ptr(a_log), _ptr(dt_bias), _ptr(decay), _ptr(beta),
+                                           tokens, heads, _dtype_code(a)), "clef_gdn_gates")
+        return decay, beta
+
+    # -- src/cuda/mod.rs:2884-2906 ------------------------------------------------------------
+    def split_q_gate_dev(self, qg, tokens: int, heads: int, head_dim: int):
+        _dev_tensor(qg, "qg")
+        q, gate = self._empty((tokens, heads, head_dim), qg.dtype), self._empty((tokens, heads, head_dim), qg.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_split_q_gate(_stream(), _ptr(qg), _ptr(q), _ptr(gate), tokens, heads, head_dim,
+                                              _dtype_code(qg)), "clef_split_q_gate")
+        return q, gate
+
+    # -- src/cuda/mod.rs:2930-2958 ------------------------------------------------------------
+    def split_qkv_dev(self, mixed, tokens: int, kh: int, kd: int, vh: int, vd: int):
+        _dev_tensor(mixed, "mixed")
+        q, k = self._empty((tokens, kh * kd), mixed.dtype), self._empty((tokens, kh * kd), mixed.dtype)
+        v = self._empty((tokens, vh * vd), mixed.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_split_qkv(_stream(), _ptr(mixed), _ptr(q), _ptr(k), _ptr(v), tokens, kh, kd, vh, vd,
+                                           _dtype_code(mixed)), "clef_split_qkv")
+        return q, k, v
+
+    # -- src/cuda/mod.rs:2959-2982 ------------------------------------------------------------
+    def repeat_interleave_dev(self, src, tokens: int, kh: int, ratio: int, dim: int):
+        _dev_tensor(src, "src")
+        out = self._empty((tokens, kh * ratio, dim), src.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_repeat_interleave(_stream(), _ptr(src), _ptr(out), tokens, kh, ratio, dim,
+                                                   _dtype_code(src)), "clef_repeat_interleave")
+        return out
 
 
 # =================================================================================================

@@ -233,6 +233,44 @@ int clef_rms_norm_gated_quantise_fp8(clef_stream_t stream, const void* x, const 
                                      uint8_t* out, uint16_t* scales, int rows, int cols, float eps, int vh,
                                      int rows_live, int dtype);
 
+/* ------------------------------------------------------------------------------------------------
+ * Elementwise kernels in front of the Gated-DeltaNet scan.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* causal_conv_silu_kernel (kernels/elementwise.cu:243-274), Device::causal_conv_silu_dev
+ * (src/cuda/mod.rs:2784-2812): depthwise causal convolution over the token axis with k taps, then silu.
+ * x, out [rows, channels]; w [channels, k] f32. seq_start[t] (optional) is the first row of token t's sequence:
+ * taps before it come from history [slots, k - 1, channels] of slot slot_map[t] (slot 0 without a map) when
+ * history is given, and are skipped otherwise. out must not alias x. */
+int clef_causal_conv_silu(clef_stream_t stream, void* out, const void* x, const float* w, int rows, int channels, int k,
+                          const int32_t* seq_start, const void* history, const int32_t* slot_map, int dtype);
+
+/* conv_hist_save_kernel (kernels/elementwise.cu:463-485), Device::conv_hist_save_dev (src/cuda/mod.rs:2814-2836):
+ * for each pair saves[2 i] = row, saves[2 i + 1] = slot (the pass maps' hist_save), rows row - (k - 2) .. row of src
+ * become the history of the slot. Pairs with a row outside [k - 2, rows) are ignored, as in the reference. */
+int clef_conv_hist_save(clef_stream_t stream, void* hist, const void* src, const int32_t* saves, int n_saves, int rows,
+                        int k, int channels, int dtype);
+
+/* gdn_gates_kernel (kernels/elementwise.cu:361-377), Device::gdn_gates_dev (src/cuda/mod.rs:2858-2882):
+ * beta = sigmoid(b), decay = -exp(a_log[h]) * softplus(a + dt_bias[h]) for a, b [tokens, heads]; outputs are f32. */
+int clef_gdn_gates(clef_stream_t stream, const void* a, const void* b, const float* a_log, const float* dt_bias,
+                   float* decay, float* beta, int tokens, int heads, int dtype);
+
+/* split_q_gate_kernel (kernels/elementwise.cu:378-395), Device::split_q_gate_dev (src/cuda/mod.rs:2884-2906):
+ * qg [tokens, heads, 2 * head_dim] -> q and gate [tokens, heads, head_dim]. */
+int clef_split_q_gate(clef_stream_t stream, const void* qg, void* q, void* gate, int tokens, int heads, int head_dim,
+                      int dtype);
+
+/* split_qkv_kernel (kernels/elementwise.cu:409-427), Device::split_qkv_dev (src/cuda/mod.rs:2930-2958):
+ * mixed [tokens, 2 kh kd + vh vd] -> q, k [tokens, kh kd] and v [tokens, vh vd]. */
+int clef_split_qkv(clef_stream_t stream, const void* mixed, void* q, void* k, void* v, int tokens, int kh, int kd, int vh,
+                   int vd, int dtype);
+
+/* repeat_interleave_kernel (kernels/elementwise.cu:429-445), Device::repeat_interleave_dev
+ * (src/cuda/mod.rs:2959-2982): out[t, h * ratio + r, :] = src[t, h, :] for r < ratio. */
+int clef_repeat_interleave(clef_stream_t stream, const void* src, void* out, int tokens, int kh, int ratio, int dim,
+                           int dtype);
+
 /* Order of the rows inside a [blk_mn rows x 4 blocks] scale tile, for every NVFP4 entry point of the process:
  *   CLEF_SF_ACTIVATION   row r at byte 4 r: the reference's activation-side ("conflict-free") order,
  *                        kernels/quantise.cu:34-41, src/swizzle.rs:64-65. Default.

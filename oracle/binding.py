@@ -393,3 +393,27 @@ def rms_norm_gated_quantise_fp8(x, g, w, rows, cols, vh, eps, rows_live=None, fm
                                               rows if rows_live is None else rows_live, _dtype_code(x),
                                               SUMSQ_FMA if fma_mode is None else fma_mode, nthreads)
     return out, scales
+
+
+# ---- elementwise kernels in front of the GDN scan ------------------------------------------------------------
+
+def causal_conv_silu(x, w, rows, channels, k, seq_start=None, history=None, slot_map=None, nthreads=0):
+    """(f32 result, result in x's dtype, f32 pre-activation sums)."""
+    x, w = _c(x), _c(w, np.float32)
+    seq_start = None if seq_start is None else _c(seq_start, np.int32)
+    slot_map = None if slot_map is None else _c(slot_map, np.int32)
+    history = None if history is None else _c(history)
+    f32 = np.empty((rows, channels), np.float32)
+    acc = np.empty((rows, channels), np.float32)
+    out = np.empty((rows, channels), x.dtype)
+    load().oracle_causal_conv_silu(_p(x), _p(w), _p(f32), _p(out), rows, channels, k, _p(seq_start), _p(history),
+                                   _p(slot_map), _dtype_code(x), _p(acc), nthreads)
+    return f32, out, acc
+
+
+def gdn_gates(a, b, a_log, dt_bias, tokens, heads):
+    a, b = _c(a), _c(b)
+    decay, beta = np.empty((tokens, heads), np.float32), np.empty((tokens, heads), np.float32)
+    load().oracle_gdn_gates(_p(a), _p(b), _p(_c(a_log, np.float32)), _p(_c(dt_bias, np.float32)), _p(decay), _p(beta),
+                            tokens, heads, _dtype_code(a))
+    return decay, beta

@@ -921,6 +921,55 @@ ORACLE_API void oracle_rms_norm_gated_quantise_fp8(const void* x, const void* ga
     }
 }
 
+// kernels/elementwise.cu:243-274 causal_conv_silu_kernel: taps in ascending order, each added by a fused multiply-add
+// (the reference build contracts `acc += w * x`), taps before the token's sequence start taken from the slot's history
+// when there is one and skipped otherwise; silu with exp and the IEEE quotient (exp stands in for __expf).
+ORACLE_API void oracle_causal_conv_silu(const void* x, const float* w, float* out_f32, void* out, int rows, int channels,
+                                        int k, const int32_t* seq_start, const void* history, const int32_t* slot_map,
+                                        int dtype, float* acc_f32, int nthreads) {
+    const int nt = pick_threads(nthreads);
+#pragma omp parallel for schedule(static) num_threads(nt)
+    for (int t = 0; t < rows; ++t) {
+        const int lo = seq_start ? seq_start[t] : 0;
+        for (int ch = 0; ch < channels; ++ch) {
+            float acc = 0.0f;
+            for (int tap = 0; tap < k; ++tap) {
+                const int src = t - (k - 1) + tap;
+                float v;
+                if (src >= lo) {
+                    widen_row(x, (size_t)src * channels + ch, 1, dtype, &v);
+                } else if (history && src >= lo - (k - 1)) {
+                    const int slot = slot_map ? slot_map[t] : 0;
+                    widen_row(history, ((size_t)slot * (k - 1) + (size_t)(src - lo + (k - 1))) * channels + ch, 1, dtype, &v);
+                } else {
+                    continue;
+                }
+                acc = std::fmaf(w[(size_t)ch * k + tap], v, acc);
+            }
+            const size_t i = (size_t)t * channels + ch;
+            if (acc_f32) acc_f32[i] = acc;
+            const float y = silu_div_ieee(acc);
+            if (out_f32) out_f32[i] = y;
+            if (out) narrow_row(&y, 1, dtype, out, i);
+        }
+    }
+}
+
+// kernels/elementwise.cu:361-377 gdn_gates_kernel (exp / log1p stand in for the device's __expf / log1pf).
+ORACLE_API void oracle_gdn_gates(const void* a, const void* b, const float* a_log, const float* dt_bias, float* decay,
+                                 float* beta, int tokens, int heads, int dtype) {
+    for (int i = 0; i < tokens * heads; ++i) {
+        const int h = i % heads;
+        float av, bv;
+        widen_row(a, (size_t)i, 1, dtype, &av);
+        widen_row(b, (size_t)i, 1, dtype, &bv);
+        beta[i] = 1.0f / (1.0f + std::exp(-bv));
+        const float xv = av + dt_bias[h];
+        const float sp = (xv > 20.0f) ? xv : std::log1p(std::exp(xv));
+        decay[i] = -std::exp(a_log[h]) * sp;
+    }
+}
+
 // Quantise rows of f32 values that were produced elsewhere (for instance a GPU f32 result), so a
 // test can separate "same pre-quantisation values" from "same quantiser".
 ORACLE_API void oracle_quantise_rows_f32(const float* v, uint8_t* packed, uint8_t* scales, int rows, int cols,

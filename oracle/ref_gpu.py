@@ -123,6 +123,56 @@ def to_bf16_scatter(x, out, n, pos_map, stride):
     return out
 
 
+# ---- elementwise kernels in front of the GDN scan ------------------------------------------------
+def causal_conv_silu(x, w, rows, channels, k, seq_start=None, history=None, slot_map=None):
+    """src/cuda/mod.rs:2784-2812."""
+    out = torch.empty(rows * channels, dtype=torch.float32, device=x.device)
+    launch("elementwise", "causal_conv_silu_kernel", ((channels + 127) // 128, min(rows, 65535), -(-rows // 65535)), (128,),
+           [x, w, out, rows, channels, k, seq_start, history, slot_map])
+    return out.view(rows, channels)
+
+
+def conv_hist_save(src, hist, saves, n_saves, rows, k, channels):
+    """src/cuda/mod.rs:2814-2836 (hist is written in place)."""
+    launch("elementwise", "conv_hist_save_kernel", (n_saves,), (128,), [src, hist, saves, n_saves, rows, k, channels])
+    return hist
+
+
+def gdn_gates(a, b, a_log, dt_bias, tokens, heads):
+    """src/cuda/mod.rs:2858-2882."""
+    decay = torch.empty(tokens * heads, dtype=torch.float32, device=a.device)
+    beta = torch.empty(tokens * heads, dtype=torch.float32, device=a.device)
+    launch("elementwise", "gdn_gates_kernel", ((tokens * heads + 255) // 256,), (256,), [a, b, a_log, dt_bias, decay, beta, tokens, heads])
+    return decay.view(tokens, heads), beta.view(tokens, heads)
+
+
+def split_q_gate(qg, tokens, heads, head_dim):
+    """src/cuda/mod.rs:2884-2906."""
+    total = tokens * heads * head_dim
+    q = torch.empty(total, dtype=torch.float32, device=qg.device)
+    gate = torch.empty(total, dtype=torch.float32, device=qg.device)
+    launch("elementwise", "split_q_gate_kernel", ((total + 255) // 256,), (256,), [qg, q, gate, tokens, heads, head_dim])
+    return q.view(tokens, heads, head_dim), gate.view(tokens, heads, head_dim)
+
+
+def split_qkv(mixed, tokens, kh, kd, vh, vd):
+    """src/cuda/mod.rs:2930-2958."""
+    total = tokens * (2 * kh * kd + vh * vd)
+    q = torch.empty(tokens * kh * kd, dtype=torch.float32, device=mixed.device)
+    k = torch.empty(tokens * kh * kd, dtype=torch.float32, device=mixed.device)
+    v = torch.empty(tokens * vh * vd, dtype=torch.float32, device=mixed.device)
+    launch("elementwise", "split_qkv_kernel", ((total + 255) // 256,), (256,), [mixed, q, k, v, tokens, kh, kd, vh, vd])
+    return q.view(tokens, kh * kd), k.view(tokens, kh * kd), v.view(tokens, vh * vd)
+
+
+def repeat_interleave(src, tokens, kh, ratio, dim):
+    """src/cuda/mod.rs:2959-2982."""
+    total = tokens * kh * ratio * dim
+    out = torch.empty(total, dtype=torch.float32, device=src.device)
+    launch("elementwise", "repeat_interleave_kernel", ((total + 255) // 256,), (256,), [src, out, tokens, kh, ratio, dim])
+    return out.view(tokens, kh * ratio, dim)
+
+
 # ---- FP8 quantisers (quantise.cu) ----------------------------------------------------------------
 def quantise_fp8(x, rows, cols):
     """src/cuda/mod.rs:2246-2266. Meaningful for cols > 1792 only (one row per CTA): for narrower rows the

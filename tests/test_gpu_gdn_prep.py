@@ -1,0 +1,176 @@
+"""Parity of the elementwise kernels in front of the Gated-DeltaNet scan through the C-ABI against the reference's
+own kernels on the same GPU (oracle/_ref/elementwise.cubin; bf16 inputs widened exactly to the f32 those kernels
+take) and against the CPU oracle: causal convolution + silu with sequence starts, history and slot maps built by
+the pass maps, the history save, the gate transform, the splitting copies."""
+import numpy as np
+import pytest
+import torch
+
+import aiis_clef_b200 as clef
+from oracle import binding as orc
+from oracle import ref_gpu
+from gpu_util import dev_bf16, dev_f32_from_bits
+from util import bf16_ulp_distance, normal_bf16, to_bf16_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _cleanup():
+    clef.set_kernel_choice(0)
+    yield
+    clef.set_kernel_choice(0)
+    torch.cuda.empty_cache()
+
+
+def i32(a):
+    return torch.from_numpy(np.ascontiguousarray(a, np.int32)).cuda()
+
+
+def bits(t):
+    return orc.bf16_bits(t.cpu())
+
+
+def packed_sequences(rng, rows, n_seq):
+    """seq_start per row for n_seq sequences packed back to back, and a slot per row."""
+    cuts = np.sort(rng.choice(np.arange(1, rows), n_seq - 1, replace=False)) if n_seq > 1 else np.array([], int)
+    starts = np.concatenate([[0], cuts]).astype(np.int32)
+    seq_start = np.zeros(rows, np.int32)
+    slot_map = np.zeros(rows, np.int32)
+    for i, s in enumerate(starts):
+        e = starts[i + 1] if i + 1 < len(starts) else rows
+        seq_start[s:e] = s
+        slot_map[s:e] = (i * 3 + 1) % n_seq
+    return seq_start, slot_map
+
+
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
+@pytest.mark.parametrize("mode", ["plain", "sequences", "history"])
+@pytest.mark.parametrize("rows,channels,k", [(1, 64, 4), (7, 128, 4), (778, 1024, 4), (300, 8192, 4), (65, 96, 3), (40, 40, 2), (129, 256, 5)])
+def test_causal_conv_silu(rows, channels, k, mode, choice):
+    clef.set_kernel_choice(choice)
+    rng = np.random.default_rng(rows * 31 + channels + k)
+    xb = normal_bf16(rng, (rows, channels))
+    w = (rng.standard_normal((channels, k)) * 0.5).astype(np.float32)
+    n_seq = min(4, rows)
+    seq_start = slot_map = hist = None
+    if mode != "plain":
+        seq_start, slot_map = packed_sequences(rng, rows, n_seq)
+    if mode == "history":
+        hist = normal_bf16(rng, (n_seq, k - 1, channels))
+    dw = torch.from_numpy(w).cuda()
+    d_ss = None if seq_start is None else i32(seq_start)
+    d_sm = None if slot_map is None or hist is None else i32(slot_map)
+    dev = clef.Device(0)
+    ref = ref_gpu.causal_conv_silu(dev_f32_from_bits(xb), dw, rows, channels, k, d_ss,
+                                   None if hist is None else dev_f32_from_bits(hist), d_sm)
+    # f32: bit-exact against the reference kernel
+    out_f = dev.causal_conv_silu_dev(dev_f32_from_bits(xb), dw, rows, channels, k, d_ss,
+                                     None if hist is None else dev_f32_from_bits(hist), d_sm)
+    torch.cuda.synchronize()
+    assert torch.equal(out_f.view(torch.int32), ref.view(torch.int32))
+    # bf16: the reference f32 result rounded to nearest even
+    out_b = dev.causal_conv_silu_dev(dev_bf16(xb), dw, rows, channels, k, d_ss, None if hist is None else dev_bf16(hist), d_sm)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(out_b), bits(ref.to(torch.bfloat16)))
+    # CPU oracle: the pre-activation sums are exact arithmetic; the silu differs by the exp approximation only
+    f32, cpu_b, acc = orc.causal_conv_silu(xb, w, rows, channels, k, seq_start, hist, slot_map if hist is not None else None)
+    assert bf16_ulp_distance(bits(out_b).reshape(-1), cpu_b.reshape(-1)).max() <= 1
+    np.testing.assert_allclose(out_f.cpu().numpy(), f32, rtol=2e-6, atol=1e-30)
+
+
+def test_causal_conv_silu_with_pass_maps_and_history_round_trip():
+    """Two passes over the same requests: the first pass saves each request's last k - 1 rows as its history
+    (hist_save of the pass maps), the second continues the requests; a request continued this way must equal the
+    same request run in one piece."""
+    k, channels, capacity = 4, 512, 4096
+    rng = np.random.default_rng(5)
+    lens = [192, 128, 320]
+    first = [128, 64, 192]
+    reqs = [rng.integers(0, 1000, n).astype(np.uint32) for n in lens]
+    xs = [normal_bf16(rng, (n, channels)) for n in lens]
+    w = (rng.standard_normal((channels, k)) * 0.5).astype(np.float32)
+    dw = torch.from_numpy(w).cuda()
+    dev = clef.Device(0)
+    whole = [dev.causal_conv_silu_dev(dev_bf16(x), dw, x.shape[0], channels, k) for x in xs]
+    hist = torch.zeros(len(lens), k - 1, channels, dtype=torch.bfloat16, device="cuda")
+    # pass 1: the first part of every request, coalesced
+    m1 = clef.pass_maps([(reqs[i], 0, i, first[i]) for i in range(3)], capacity)
+    x1 = dev_bf16(np.concatenate([xs[i][: first[i]] for i in range(3)]))
+    rows1 = int(m1["total"])
+    out1 = dev.causal_conv_silu_dev(x1, dw, rows1, channels, k, i32(m1["seq_start"]), hist, i32(m1["slot_map"]))
+    saves = i32(m1["hist_save"].astype(np.int32).reshape(-1))
+    dev.conv_hist_save_dev(x1, hist, saves, 3, rows1, k, channels)
+    ref_hist = ref_gpu.conv_hist_save(x1.float(), torch.zeros(3, k - 1, channels, device="cuda"), saves, 3, rows1, k, channels)
+    assert torch.equal(hist.float(), ref_hist)
+    # pass 2: the rest of every request
+    rest = [lens[i] - first[i] for i in range(3)]
+    m2 = clef.pass_maps([(reqs[i], first[i], i, rest[i]) for i in range(3)], capacity)
+    x2 = dev_bf16(np.concatenate([xs[i][first[i]:] for i in range(3)]))
+    out2 = dev.causal_conv_silu_dev(x2, dw, int(m2["total"]), channels, k, i32(m2["seq_start"]), hist, i32(m2["slot_map"]))
+    torch.cuda.synchronize()
+    for i in range(3):
+        o1, o2 = int(m1["offs"][i]), int(m2["offs"][i])
+        assert torch.equal(out1[o1:o1 + first[i]], whole[i][: first[i]])
+        assert torch.equal(out2[o2:o2 + rest[i]], whole[i][first[i]:])
+
+
+@pytest.mark.parametrize("tokens,heads", [(1, 32), (778, 32), (8192, 16), (65, 5)])
+def test_gdn_gates(tokens, heads):
+    rng = np.random.default_rng(tokens + heads)
+    ab = to_bf16_bits((rng.standard_normal((tokens, heads)) * 6).astype(np.float32))
+    bb = to_bf16_bits((rng.standard_normal((tokens, heads)) * 3).astype(np.float32))
+    ab.reshape(-1)[:4] = to_bf16_bits(np.array([30.0, 19.9, -60.0, 0.0], np.float32))[: min(4, ab.size)]
+    a_log = (rng.standard_normal(heads) * 0.5).astype(np.float32)
+    dt_bias = (rng.standard_normal(heads) * 0.5).astype(np.float32)
+    dal, ddt = torch.from_numpy(a_log).cuda(), torch.from_numpy(dt_bias).cuda()
+    dev = clef.Device(0)
+    rd, rb = ref_gpu.gdn_gates(dev_f32_from_bits(ab), dev_f32_from_bits(bb), dal, ddt, tokens, heads)
+    for a_in, b_in in ((dev_f32_from_bits(ab), dev_f32_from_bits(bb)), (dev_bf16(ab), dev_bf16(bb))):
+        decay, beta = dev.gdn_gates_dev(a_in, b_in, dal, ddt, tokens, heads)
+        torch.cuda.synchronize()
+        assert torch.equal(decay.view(torch.int32), rd.view(torch.int32)) and torch.equal(beta.view(torch.int32), rb.view(torch.int32))
+    cd, cb = orc.gdn_gates(ab, bb, a_log, dt_bias, tokens, heads)
+    np.testing.assert_allclose(decay.cpu().numpy(), cd, rtol=3e-6, atol=1e-30)
+    np.testing.assert_allclose(beta.cpu().numpy(), cb, rtol=3e-6, atol=1e-30)
+
+
+@pytest.mark.parametrize("tokens", [1, 778, 4099])
+def test_splitting_copies(tokens):
+    rng = np.random.default_rng(tokens)
+    dev = clef.Device(0)
+    heads, hd = 16, 128
+    qg = normal_bf16(rng, (tokens, heads, 2 * hd))
+    q, gate = dev.split_q_gate_dev(dev_bf16(qg), tokens, heads, hd)
+    rq, rg = ref_gpu.split_q_gate(dev_f32_from_bits(qg), tokens, heads, hd)
+    assert np.array_equal(bits(q), qg[:, :, :hd]) and np.array_equal(bits(gate), qg[:, :, hd:])          # elementwise.cu:386-394
+    assert torch.equal(q.float(), rq) and torch.equal(gate.float(), rg)
+    qf, gf = dev.split_q_gate_dev(dev_f32_from_bits(qg), tokens, heads, hd)
+    assert torch.equal(qf, rq) and torch.equal(gf, rg)
+    kh, kd, vh, vd = 16, 128, 32, 128
+    mixed = normal_bf16(rng, (tokens, 2 * kh * kd + vh * vd))
+    q, k, v = dev.split_qkv_dev(dev_bf16(mixed), tokens, kh, kd, vh, vd)
+    rq, rk, rv = ref_gpu.split_qkv(dev_f32_from_bits(mixed), tokens, kh, kd, vh, vd)
+    assert np.array_equal(bits(q), mixed[:, : kh * kd]) and np.array_equal(bits(k), mixed[:, kh * kd: 2 * kh * kd])
+    assert np.array_equal(bits(v), mixed[:, 2 * kh * kd:])                                                      # elementwise.cu:417-425
+    assert torch.equal(q.float(), rq) and torch.equal(k.float(), rk) and torch.equal(v.float(), rv)
+    src = normal_bf16(rng, (tokens, kh, kd))
+    out = dev.repeat_interleave_dev(dev_bf16(src), tokens, kh, 2, kd)
+    ro = ref_gpu.repeat_interleave(dev_f32_from_bits(src), tokens, kh, 2, kd)
+    assert np.array_equal(bits(out), np.repeat(src, 2, axis=1))                                                 # elementwise.cu:437-444
+    assert torch.equal(out.float(), ro)
+    outf = dev.repeat_interleave_dev(dev_f32_from_bits(src), tokens, kh, 2, kd)
+    assert torch.equal(outf, ro)
+
+
+def test_gdn_prep_argument_errors():
+    lib = clef.load()
+    from gpu_util import ptr, stream
+    x = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(64, 4, device="cuda")
+    assert lib.clef_causal_conv_silu(stream(), ptr(x), ptr(x), ptr(w), 64, 64, 4, None, None, None, 0) == -1     # out aliases x
+    assert lib.clef_causal_conv_silu(stream(), None, ptr(x), ptr(w), 64, 64, 4, None, None, None, 0) == -1
+    assert lib.clef_split_q_gate(stream(), ptr(x), ptr(x), ptr(x), 4, 2, 12, 0) == -1                              # 12 values < 16 bytes
+    assert lib.clef_repeat_interleave(stream(), ptr(x), ptr(x), 4, 2, 2, 12, 0) == -1
+    assert lib.clef_gdn_gates(stream(), ptr(x), ptr(x), ptr(w), ptr(w), None, ptr(w), 4, 2, 0) == -1
+    assert lib.clef_conv_hist_save(stream(), ptr(x), ptr(x), None, 0, 64, 4, 64, 0) == 0                          # nothing to save
