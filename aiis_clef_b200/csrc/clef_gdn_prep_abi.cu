@@ -19,7 +19,7 @@ template <typename T>
 void launch_conv(cudaStream_t s, const DeviceInfo& dev, void* out, const void* x, const float* w, int rows, int channels,
                  int k, const int32_t* seq_start, const void* history, const int32_t* slot_map) {
     if (k == 4 && channels % 8 == 0 && use_hot()) {
-        constexpr int kRows = 8;
+        constexpr int kRows = T::kBytes == 2 ? 8 : 4;   // rows per thread: 11 (bf16) or 7 (f32) 16/32-byte loads in flight
         static std::atomic<int> occ{0};
         auto kernel = causal_conv_silu_kernel<T, 4, kRows>;
         const int per_sm = ctas_per_sm(kernel, 0, occ);

@@ -20,6 +20,45 @@ __device__ __forceinline__ void store8<F32>(float* p, const float* v) {
     stg_v4(p + 4, make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
 }
 
+// 8 consecutive activations as loaded (16 or 32 bytes), widened later.
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<Bf16> {
+    uint4 a = make_uint4(0u, 0u, 0u, 0u);
+};
+template <>
+struct Raw8<F32> {
+    uint4 a = make_uint4(0u, 0u, 0u, 0u), b = make_uint4(0u, 0u, 0u, 0u);
+};
+template <typename T>
+__device__ __forceinline__ Raw8<T> load8_raw(const typename T::storage* p);
+template <>
+__device__ __forceinline__ Raw8<Bf16> load8_raw<Bf16>(const uint16_t* p) {
+    Raw8<Bf16> r;
+    r.a = ldg_stream_v4(p);
+    return r;
+}
+template <>
+__device__ __forceinline__ Raw8<F32> load8_raw<F32>(const float* p) {
+    Raw8<F32> r;
+    r.a = ldg_stream_v4(p);
+    r.b = ldg_stream_v4(p + 4);
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ void unpack8(const Raw8<T>& r, float* v);
+template <>
+__device__ __forceinline__ void unpack8<Bf16>(const Raw8<Bf16>& r, float* v) {
+    v[0] = bf16_lo(r.a.x), v[1] = bf16_hi(r.a.x), v[2] = bf16_lo(r.a.y), v[3] = bf16_hi(r.a.y);
+    v[4] = bf16_lo(r.a.z), v[5] = bf16_hi(r.a.z), v[6] = bf16_lo(r.a.w), v[7] = bf16_hi(r.a.w);
+}
+template <>
+__device__ __forceinline__ void unpack8<F32>(const Raw8<F32>& r, float* v) {
+    v[0] = __uint_as_float(r.a.x), v[1] = __uint_as_float(r.a.y), v[2] = __uint_as_float(r.a.z), v[3] = __uint_as_float(r.a.w);
+    v[4] = __uint_as_float(r.b.x), v[5] = __uint_as_float(r.b.y), v[6] = __uint_as_float(r.b.z), v[7] = __uint_as_float(r.b.w);
+}
+
 // ---------------------------------------------------------------------------------------------
 // causal_conv_silu (kernels/elementwise.cu:243-274): out[t, c] = silu(sum over taps of w[c, tap] * x[t - (K-1) + tap, c]),
 // the taps added in ascending order by fused multiply-add (the reference build contracts `acc += w * x`), a tap
@@ -46,23 +85,41 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
         const int c0 = (int)(idx - strip * cvecs) * 8;
         const int t0 = (int)strip * R;
         float wt[8][K];
+        if (K == 4) {   // a channel's four taps are one 16-byte load
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 8; ++j) {
+                const float4 t4 = __ldg(reinterpret_cast<const float4*>(w) + (c0 + j));
+                wt[j][0] = t4.x, wt[j][1] = t4.y, wt[j][2 % K] = t4.z, wt[j][3 % K] = t4.w;
+            }
+        } else {
 #pragma unroll
-            for (int tap = 0; tap < K; ++tap) {
-                wt[j][tap] = __ldg(w + (size_t)(c0 + j) * K + tap);
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int tap = 0; tap < K; ++tap) {
+                    wt[j][tap] = __ldg(w + (size_t)(c0 + j) * K + tap);
+                }
+            }
+        }
+        int lo_of[R];   // the sequence start of every row of the strip, requested up front as well
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            lo_of[r] = (seq_start && t0 + r < rows) ? __ldg(seq_start + t0 + r) : 0;
+        }
+        // All R + K - 1 rows of the strip are requested before any is used, so a thread has that many loads in flight.
+        Raw8<T> raw[R + K - 1];
+#pragma unroll
+        for (int i = 0; i < R + K - 1; ++i) {
+            const int src = t0 - (K - 1) + i;
+            if (src >= 0 && src < rows) {
+                raw[i] = load8_raw<T>(x + (size_t)src * channels + c0);
+            } else {
+                raw[i] = Raw8<T>{};
             }
         }
         float win[K][8];   // win[i] = x[t - (K-1) + i] for the current row t; win[K-1] is the row itself
 #pragma unroll
         for (int i = 0; i < K - 1; ++i) {
-            const int src = t0 - (K - 1) + i;
-            if (src >= 0) {
-                load8<T>(x + (size_t)src * channels + c0, win[i + 1]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) win[i + 1][j] = 0.0f;
-            }
+            unpack8<T>(raw[i], win[i + 1]);
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -75,8 +132,8 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
 #pragma unroll
                 for (int j = 0; j < 8; ++j) win[i][j] = win[i + 1][j];
             }
-            load8<T>(x + (size_t)t * channels + c0, win[K - 1]);
-            const int lo = seq_start ? seq_start[t] : 0;
+            unpack8<T>(raw[r + K - 1], win[K - 1]);
+            const int lo = lo_of[r];
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int tap = 0; tap < K; ++tap) {
@@ -93,8 +150,21 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
                 }
             }
             float o[8];
+            float amax = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = silu_ieee_div(acc[j]);
+            for (int j = 0; j < 8; j += 2) amax = max3_abs_nan(amax, acc[j], acc[j + 1]);
+            if (amax <= kSiluFastMaxAbs) {   // the short exact quotient (every f32 of the domain is compared on the device)
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const f32x2 y = silu_ieee_fast_f32_x2(f2_pack(acc[j], acc[j + 1]));
+                    // a zero quotient takes the sign of the sum, as the division gives it (the short form returns +0)
+                    o[j] = (y.x == 0.0f) ? __uint_as_float(__float_as_uint(acc[j]) & 0x80000000u) : y.x;
+                    o[j + 1] = (y.y == 0.0f) ? __uint_as_float(__float_as_uint(acc[j + 1]) & 0x80000000u) : y.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = silu_ieee_div(acc[j]);
+            }
             store8<T>(out + (size_t)t * channels + c0, o);
         }
     }

@@ -35,6 +35,7 @@ ROWS = 8192
 HIDDEN, INTER = 2048, 6144
 Q_HEADS, KV_HEADS, HEAD_DIM, ROTARY, THETA = 16, 2, 128, 64, 1e7
 VH = 16                      # GDN value heads (x 128) of the gated RMSNorm, reported under "kernels"
+CONV_DIM, CONV_K = 8192, 4   # GDN convolution: 2 x 16 x 128 (q, k) + 32 x 128 (v) channels, 4 taps
 VOCAB = 32768
 EPS = 1e-6
 GS_NORM, GS_SWIGLU, GS_GATED = 64.0, 48.0, 96.0     # per-projection input_global_scale stand-ins
@@ -67,6 +68,8 @@ BYTES_PER_ROW = {
     "rms_norm_fp8_bf16": 2 * HIDDEN + HIDDEN + 2 + 2 * HIDDEN,                                # 10,242 (codes + bf16 twin)
     "swiglu_quantise_fp8": 2 * 2 * INTER + INTER + 2,                                         # 30,722
     "rms_norm_gated_quantise_fp8": 2 * 2 * HIDDEN + HIDDEN + 2,                               # 10,242
+    # in front of the GDN scan: causal convolution (4 taps) + silu over the 8,192 mixed q/k/v channels
+    "causal_conv_silu": 2 * 2 * CONV_DIM + 4,                                                 # 32,772
 }
 STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k"]
 FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k",
@@ -293,7 +296,10 @@ def run_gpu_arm(args):
             "q8_h": torch.empty(ROWS, HIDDEN, dtype=torch.uint8, device="cuda"),
             "q8_i": torch.empty(ROWS, INTER, dtype=torch.uint8, device="cuda"),
             "s8": torch.empty(ROWS, dtype=torch.int16, device="cuda"),
+            "mixed": randn_bf16(ROWS, CONV_DIM), "conv_out": torch.empty(ROWS, CONV_DIM, dtype=torch.bfloat16, device="cuda"),
         })
+    w_conv = (torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5).contiguous()
+    seq_start = torch.zeros(ROWS, dtype=torch.int32, device="cuda")
     cache_map = torch.randperm(ROWS, device="cuda", generator=gen).to(torch.int32)   # the engine's cpos: a slot per token
     w_head = (torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
 
@@ -341,6 +347,8 @@ def run_gpu_arm(args):
                                                                       p(d["s8"]), ROWS, INTER, 0),
         "rms_norm_gated_quantise_fp8": lambda d: lib.clef_rms_norm_gated_quantise_fp8(
             stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["q8_h"]), p(d["s8"]), ROWS * VH, HEAD_DIM, EPS, VH, ROWS * VH, 0),
+        "causal_conv_silu": lambda d: lib.clef_causal_conv_silu(stream(), p(d["conv_out"]), p(d["mixed"]), p(w_conv), ROWS,
+                                                                CONV_DIM, CONV_K, p(seq_start), None, None, 0),
     }
 
     def step_eager(d):

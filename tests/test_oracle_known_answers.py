@@ -364,3 +364,40 @@ def test_config_0_chain_on_the_cpu_restatement():
     unit = np.repeat(scale_f32 / np.float32(gs), 16, axis=1)
     assert (np.abs(deq - normed) <= unit + 1e-12).all()
     assert np.linalg.norm(deq - normed) / np.linalg.norm(normed) < 0.2
+
+
+def test_causal_conv_silu_known_answers():
+    """kernels/elementwise.cu:243-274: taps before a sequence start are skipped without history and taken from the
+    slot's history with it; sequences packed in one pass do not see each other."""
+    k, channels = 4, 2
+    x = np.arange(1, 13, dtype=np.float32).reshape(6, 2)          # rows 0..5
+    w = np.tile(np.array([[0.5, -1.0, 2.0, 1.0]], np.float32), (channels, 1))
+    silu = lambda a: a / (1.0 + np.exp(-a))
+    # one sequence, no history: row 0 sees only its own tap (weight 1.0), row 3 sees all four
+    f32, _, acc = orc.causal_conv_silu(x, w, 6, channels, k)
+    assert acc[0, 0] == 1.0 * x[0, 0]
+    assert acc[3, 1] == np.float32(0.5 * x[0, 1] - 1.0 * x[1, 1] + 2.0 * x[2, 1] + 1.0 * x[3, 1])
+    np.testing.assert_allclose(f32, silu(acc.astype(np.float64)), rtol=1e-6)
+    # two sequences (rows 0-2 and 3-5): row 3 starts afresh
+    seq_start = np.array([0, 0, 0, 3, 3, 3], np.int32)
+    _, _, acc2 = orc.causal_conv_silu(x, w, 6, channels, k, seq_start=seq_start)
+    assert acc2[3, 0] == 1.0 * x[3, 0] and acc2[4, 0] == np.float32(2.0 * x[3, 0] + 1.0 * x[4, 0])
+    assert np.array_equal(acc2[:3], acc[:3])
+    # history of slot 1 continues the second sequence: its three rows stand in for rows "before 3"
+    hist = np.zeros((2, k - 1, channels), np.float32)
+    hist[1] = np.array([[10, 20], [30, 40], [50, 60]], np.float32)
+    slot_map = np.array([0, 0, 0, 1, 1, 1], np.int32)
+    _, _, acc3 = orc.causal_conv_silu(x, w, 6, channels, k, seq_start=seq_start, history=hist, slot_map=slot_map)
+    assert acc3[3, 0] == np.float32(0.5 * 10 - 1.0 * 30 + 2.0 * 50 + 1.0 * x[3, 0])
+    assert acc3[4, 1] == np.float32(0.5 * 40 - 1.0 * 60 + 2.0 * x[3, 1] + 1.0 * x[4, 1])
+    assert np.array_equal(acc3[:3], acc[:3])                       # slot 0's history is all zeros
+
+
+def test_gdn_gates_known_answers():
+    """kernels/elementwise.cu:361-377."""
+    a = np.array([[0.0, 25.0]], np.float32)
+    b = np.array([[0.0, -30.0]], np.float32)
+    decay, beta = orc.gdn_gates(a, b, np.array([0.0, 1.0], np.float32), np.array([0.0, 0.0], np.float32), 1, 2)
+    assert beta[0, 0] == 0.5 and beta[0, 1] < 1e-12
+    np.testing.assert_allclose(decay[0, 0], -np.log(2.0), rtol=1e-6)       # -exp(0) * log1p(exp(0))
+    np.testing.assert_allclose(decay[0, 1], -np.e * 25.0, rtol=1e-6)      # softplus(x) = x above 20
