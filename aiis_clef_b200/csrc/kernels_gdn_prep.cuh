@@ -150,21 +150,8 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
                 }
             }
             float o[8];
-            float amax = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) amax = max3_abs_nan(amax, acc[j], acc[j + 1]);
-            if (amax <= kSiluFastMaxAbs) {   // the short exact quotient (every f32 of the domain is compared on the device)
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    const f32x2 y = silu_ieee_fast_f32_x2(f2_pack(acc[j], acc[j + 1]));
-                    // a zero quotient takes the sign of the sum, as the division gives it (the short form returns +0)
-                    o[j] = (y.x == 0.0f) ? __uint_as_float(__float_as_uint(acc[j]) & 0x80000000u) : y.x;
-                    o[j + 1] = (y.y == 0.0f) ? __uint_as_float(__float_as_uint(acc[j + 1]) & 0x80000000u) : y.y;
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = silu_ieee_div(acc[j]);
-            }
+            for (int j = 0; j < 8; ++j) o[j] = silu_ieee_div(acc[j]);
             store8<T>(out + (size_t)t * channels + c0, o);
         }
     }

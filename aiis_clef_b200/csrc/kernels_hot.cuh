@@ -366,20 +366,6 @@ __device__ __forceinline__ f32x2 silu_ieee_fast_x2(f32x2 g2) {
     return f2_fma(rem, r2, q0);
 }
 
-// The same quotient for ANY f32 g with |g| <= 44 (not only bf16 values): the reciprocal is refined by one Newton step
-// before the quotient and its exact-remainder correction. Compared with div.rn on every f32 pattern of the domain
-// (the form above differs from div.rn for two f32 inputs, none of them a bf16 value).
-__device__ __forceinline__ f32x2 silu_ieee_fast_f32_x2(f32x2 g2) {
-    const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));
-    const f32x2 d2 = f2_add(f2_splat(1.0f), make_float2(ex2_approx(t2.x), ex2_approx(t2.y)));
-    const f32x2 nd2 = make_float2(-d2.x, -d2.y);
-    const f32x2 r0 = make_float2(rcp_approx(d2.x), rcp_approx(d2.y));
-    const f32x2 r2 = f2_fma(f2_fma(nd2, r0, f2_splat(1.0f)), r0, r0);
-    const f32x2 q0 = f2_mul(g2, r2);
-    const f32x2 rem = f2_fma(nd2, q0, g2);
-    return f2_fma(rem, r2, q0);
-}
-
 // (g0, g1) -> __fdividef(g, 1 + __expf(-g)) per lane, short form for |g| <= 44: g * rcp.approx(d).
 __device__ __forceinline__ f32x2 silu_approx_fast_x2(f32x2 g2) {
     const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));

@@ -395,14 +395,6 @@ def probe_sigmoid_mul_bf16():
     return _read_results(buf, 2)
 
 
-def probe_silu_f32():
-    """[silu_ieee_fast_x2, silu_ieee_fast_f32_x2] against g / (1 + __expf(-g)) on every f32 with |g| <= 44."""
-    buf = _result_buffer(2)
-    launch("ref_probe", "probe_silu_f32", (148 * 8,), (256,), [buf])
-    torch.cuda.synchronize()
-    return _read_results(buf, 2)
-
-
 def probe_div_six():
     buf = _result_buffer(1)
     launch("ref_probe", "probe_div_six", (148 * 8,), (256,), [buf])

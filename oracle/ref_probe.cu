@@ -254,38 +254,6 @@ extern "C" __global__ void probe_sigmoid_mul_bf16(ProbeResult* result) {
     atomicAdd(&result[1].checked, checked_normal);
 }
 
-// The short IEEE-quotient silu form against g / (1 + __expf(-g)) for EVERY f32 pattern with |g| <= 44 (the causal
-// convolution applies it to f32 sums, not to bf16 values). Zero results may differ in sign. result[0]: the form used
-// for bf16 inputs (silu_ieee_fast_x2); result[1]: the form with a refined reciprocal (silu_ieee_fast_f32_x2).
-extern "C" __global__ void probe_silu_f32(ProbeResult* result) {
-    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-    unsigned long long checked = 0;
-    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < (1ull << 32); i += stride) {
-        const float g = __uint_as_float((uint32_t)i);
-        if (!(fabsf(g) <= clef::kSiluFastMaxAbs)) {
-            continue;
-        }
-        ++checked;
-        const float want = g / (1.0f + __expf(-g));
-        const clef::f32x2 a = clef::silu_ieee_fast_x2(clef::f2_pack(g, 1.0f));
-        const clef::f32x2 b = clef::silu_ieee_fast_x2(clef::f2_pack(1.0f, g));
-        const bool ok = (__float_as_uint(a.x) == __float_as_uint(want) || (a.x == 0.0f && want == 0.0f)) &&
-                        (__float_as_uint(b.y) == __float_as_uint(want) || (b.y == 0.0f && want == 0.0f));
-        if (!ok) {
-            report(&result[0], (uint32_t)i);
-        }
-        const clef::f32x2 c = clef::silu_ieee_fast_f32_x2(clef::f2_pack(g, 1.0f));
-        const clef::f32x2 e = clef::silu_ieee_fast_f32_x2(clef::f2_pack(1.0f, g));
-        const bool ok2 = (__float_as_uint(c.x) == __float_as_uint(want) || (c.x == 0.0f && want == 0.0f)) &&
-                         (__float_as_uint(e.y) == __float_as_uint(want) || (e.y == 0.0f && want == 0.0f));
-        if (!ok2) {
-            report(&result[1], (uint32_t)i);
-        }
-    }
-    atomicAdd(&result[0].checked, checked);
-    atomicAdd(&result[1].checked, checked);
-}
-
 // amax / 6.0f (kernels/quantise.cu:29) against the three-operation form, on the patterns the fast
 // quantiser uses it for: +0 and every finite x >= 2^-100.
 extern "C" __global__ void probe_div_six(ProbeResult* result) {

@@ -31,14 +31,6 @@ def test_e4m3_encoder_all_patterns():
     assert all(r["mismatches"] == 0 for r in res), _fmt(res)
 
 
-def test_short_silu_quotients_on_every_f32_of_their_domain():
-    """g / (1 + __expf(-g)) for all 2.2e9 f32 patterns with |g| <= 44: the form with a refined reciprocal (used on f32
-    sums) is exact everywhere; the shorter form (used on bf16 values only) differs for two f32 inputs, neither a bf16."""
-    short, refined = ref_gpu.probe_silu_f32()
-    assert refined["checked"] > 2_200_000_000 and refined["mismatches"] == 0, refined
-    assert short["mismatches"] <= 2 and all(b & 0xFFFF for b in short["first_bad"]), short
-
-
 @pytest.mark.parametrize("global_scale", [1.0, 64.0, 215.0, 1.0 / 12.5, 2688.0, 1e-3])
 def test_e4m3_decoder_and_inverse_scale(global_scale):
     res = ref_gpu.probe_e4m3_decode(global_scale)
