@@ -391,6 +391,30 @@ int clef_host_quantise_nvfp4(clef_device* dev, const void* x, uint8_t* packed, u
                      });
 }
 
+// Device::quantise_fp8 (src/cuda/mod.rs:1065-1092): FP8 codes [rows, cols] and one u16 scale word per row.
+int clef_host_quantise_fp8(clef_device* dev, const void* x, uint8_t* out, uint16_t* scales, int rows, int cols,
+                           int dtype) {
+    const char* what = "clef_host_quantise_fp8";
+    if (int rc = check_handle(dev, what)) return rc;
+    if (dtype != CLEF_BF16 && dtype != CLEF_F32) return fail(CLEF_ERR_INVALID, "%s: dtype %d", what, dtype);
+    if (rows < 0 || cols <= 0 || cols % 8 != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: rows %d, cols %d (cols must be a multiple of 8)", what, rows, cols);
+    }
+    if (!x || !out || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (rows == 0) return CLEF_OK;
+    std::lock_guard<std::mutex> guard(dev->lock);
+    DeviceScope scope(dev);
+    const size_t row_in = (size_t)cols * elem_bytes(dtype);
+    std::vector<RowStream> in{{x, nullptr, row_in, 0}};
+    std::vector<RowStream> outs{{nullptr, out, (size_t)cols, 0}, {nullptr, scales, sizeof(uint16_t), 0}};
+    const int tile = pick_tile_rows(rows, 128, row_in + cols + 2);
+    return run_tiled(dev, rows, 1, tile, in, outs, false,
+                     [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
+                         return clef_quantise_fp8(st, base + in[0].offset, (uint8_t*)(base + outs[0].offset),
+                                                  (uint16_t*)(base + outs[1].offset), n_live, cols, dtype);
+                     });
+}
+
 int clef_host_rms_norm_quantise_nvfp4(clef_device* dev, const void* x, const float* weight, uint8_t* packed,
                                       uint8_t* scales, int rows, int cols, float eps, float global_scale, int tile_m,
                                       int dtype) {

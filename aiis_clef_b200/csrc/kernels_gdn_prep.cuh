@@ -68,8 +68,10 @@ __device__ __forceinline__ void unpack8<F32>(const Raw8<F32>& r, float* v) {
 // A thread owns 8 channels and R consecutive rows and slides a K-row window over them, so every x value is
 // loaded once. channels % 8 == 0.
 // ---------------------------------------------------------------------------------------------
+// Two CTAs per SM (128 registers) measured best: one CTA (145 registers) or three and four (spills) are 20 to 60 %
+// slower, and so was keeping the next strip's loads in flight during the arithmetic (159 registers).
 template <typename T, int K, int R>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, 2)
 causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T::storage* __restrict__ x,
                         const float* __restrict__ w, int rows, int channels, const int* __restrict__ seq_start,
                         const typename T::storage* __restrict__ history, const int* __restrict__ slot_map,

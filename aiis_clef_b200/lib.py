@@ -522,6 +522,7 @@ HOST_SYMBOLS = {
     "clef_host_alloc_pinned": (_I, [_SZ, ctypes.POINTER(_P)]),
     "clef_host_free_pinned": (_I, [_P]),
     "clef_host_embed_gather": (_I, [_P, _P, _P, _P, _I, _I, _I]),
+    "clef_host_quantise_fp8": (_I, [_P, _P, _P, _P, _I, _I, _I]),
     "clef_host_quantise_nvfp4": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _I]),
     "clef_host_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I]),
     "clef_host_swiglu_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I]),
@@ -669,6 +670,10 @@ class HostDevice:
     def embed_gather(self, table_dev: torch.Tensor, ids, out, tokens: int, hidden: int):
         _check(self.lib.clef_host_embed_gather(self.handle, _ptr(table_dev), self._hp(ids), self._hp(out), tokens,
                                                hidden, _dtype_code(table_dev)), "clef_host_embed_gather")
+
+    def quantise_fp8(self, x, out, scales, rows, cols):
+        _check(self.lib.clef_host_quantise_fp8(self.handle, self._hp(x), self._hp(out), self._hp(scales), rows, cols,
+                                               self._code(x)), "clef_host_quantise_fp8")
 
     def quantise_nvfp4(self, x, packed, scales, rows, cols, global_scale, tile_m=128):
         _check(self.lib.clef_host_quantise_nvfp4(self.handle, self._hp(x), self._hp(packed), self._hp(scales), rows,

@@ -60,6 +60,8 @@ int clef_host_embed_gather(clef_device* dev, const void* table_device, const int
                            int hidden, int dtype);   /* the table stays on the device (it is a model weight) */
 int clef_host_quantise_nvfp4(clef_device* dev, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
                              float global_scale, int tile_m, int dtype);
+int clef_host_quantise_fp8(clef_device* dev, const void* x, uint8_t* out, uint16_t* scales, int rows, int cols,
+                           int dtype);             /* Device::quantise_fp8, src/cuda/mod.rs:1065-1092 */
 int clef_host_rms_norm_quantise_nvfp4(clef_device* dev, const void* x, const float* weight, uint8_t* packed,
                                       uint8_t* scales, int rows, int cols, float eps, float global_scale, int tile_m,
                                       int dtype);

@@ -138,3 +138,16 @@ def test_pipelined_mode_gives_the_same_bytes(host_dev):
     finally:
         host_dev.set_pipelined(False)
     assert not torch.equal(want[0], want[2])
+
+
+@pytest.mark.parametrize("rows", [1, 778, 20000])
+def test_host_quantise_fp8(host_dev, rows):
+    """Device::quantise_fp8 (src/cuda/mod.rs:1065-1092) through the host-slice launcher, against the CPU oracle."""
+    cols = 2048
+    rng = np.random.default_rng(rows + 8)
+    x = normal_bf16(rng, (rows, cols), outlier_channels=4)
+    out, scales = pinned(np.full(rows * cols, 0xA5, np.uint8)), pinned(np.zeros(rows, np.uint16))
+    host_dev.quantise_fp8(orc.bits_to_torch_bf16(x).pin_memory(), out, scales, rows, cols)
+    want_q, want_s = orc.quantise_fp8(x, rows, cols)
+    assert_bytes_equal(out.numpy(), want_q.reshape(-1), "host fp8 codes")
+    assert_bytes_equal(scales.numpy(), want_s, "host fp8 scales")
