@@ -133,6 +133,77 @@ int clef_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_v, const
     return check_launch(what);
 }
 
+// q and k rotated in one launch; with caches, k goes to its cache rows and v is copied to its own.
+static int rope_qkv_impl(const char* what, clef_stream_t stream, void* q_out, const void* q, int q_heads, void* k_dst,
+                         void* cache_v, const void* k, const void* v, int kv_heads, const float* cos_table,
+                         const float* sin_table, int rows, int head_dim, int rotary_dim, const int32_t* seq_start,
+                         const int32_t* pos_base, const int32_t* pos_map, const int32_t* cache_map,
+                         const int32_t* cache_len, bool to_cache, int dtype) {
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!q_out || !q || !k_dst || !k || !cos_table || !sin_table || (to_cache && (!cache_v || !v))) {
+        return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    }
+    if (q_heads <= 0) return fail(CLEF_ERR_INVALID, "%s: q_heads %d", what, q_heads);
+    if (int r = check_kv_shape(what, rows, kv_heads, head_dim, rotary_dim)) return r;
+    if (q_out == q || (!to_cache && k_dst == k)) return fail(CLEF_ERR_INVALID, "%s: an output must not alias its input", what);
+    if (rows == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    const size_t per_row = (size_t)(head_dim / 32);
+    const size_t q_items = (size_t)rows * q_heads * per_row, k_items = (size_t)rows * kv_heads * per_row;
+    const size_t items = q_items + k_items * (to_cache ? 2 : 1);
+    const bool all32 = aligned(q, 32) && aligned(q_out, 32) && aligned(k, 32) && aligned(k_dst, 32) &&
+                       (!to_cache || (aligned(v, 32) && aligned(cache_v, 32)));
+    if (dtype == CLEF_BF16 && use_hot() && head_dim % 32 == 0 && rotary_dim % 32 == 0 && items < 0x7fffffffull && all32) {
+        RopeSegments segs{};
+        segs.seg[0] = RopeSegment{(const uint16_t*)q, (uint16_t*)q_out, (uint32_t)q_items, q_heads,
+                                  make_fast_div((uint32_t)q_heads), 1, 0};
+        segs.seg[1] = RopeSegment{(const uint16_t*)k, (uint16_t*)k_dst, (uint32_t)(q_items + k_items), kv_heads,
+                                  make_fast_div((uint32_t)kv_heads), 1, to_cache ? 1 : 0};
+        segs.seg[2] = RopeSegment{(const uint16_t*)v, (uint16_t*)cache_v, (uint32_t)items, kv_heads,
+                                  make_fast_div((uint32_t)kv_heads), 0, 1};
+        const size_t ctas = (items + kCtaThreads - 1) / kCtaThreads;
+        if (to_cache) {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rope_multi_hot_kernel<3>, 0, occ);
+            launch_hot(rope_multi_hot_kernel<3>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, as_stream(stream), segs, cos_table,
+                       sin_table, head_dim, rotary_dim, (const int*)seq_start, (const int*)pos_base, (const int*)pos_map,
+                       (const int*)cache_map, (const int*)cache_len, make_fast_div((uint32_t)per_row));
+        } else {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rope_multi_hot_kernel<2>, 0, occ);
+            launch_hot(rope_multi_hot_kernel<2>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, as_stream(stream), segs, cos_table,
+                       sin_table, head_dim, rotary_dim, (const int*)seq_start, (const int*)pos_base, (const int*)pos_map,
+                       (const int*)nullptr, (const int*)nullptr, make_fast_div((uint32_t)per_row));
+        }
+        return check_launch(what);
+    }
+    // Other shapes and f32: the calls this entry point stands for.
+    if (int r = clef_rope(stream, q_out, q, cos_table, sin_table, rows, q_heads, head_dim, rotary_dim, seq_start, pos_base,
+                          pos_map, dtype)) return r;
+    if (to_cache) {
+        return clef_rope_kv_write(stream, k_dst, cache_v, k, v, cos_table, sin_table, rows, kv_heads, head_dim, rotary_dim,
+                                  seq_start, pos_base, pos_map, cache_map, cache_len, dtype);
+    }
+    return clef_rope(stream, k_dst, k, cos_table, sin_table, rows, kv_heads, head_dim, rotary_dim, seq_start, pos_base,
+                     pos_map, dtype);
+}
+
+int clef_rope_qk(clef_stream_t stream, void* q_out, const void* q, int q_heads, void* k_out, const void* k, int kv_heads,
+                 const float* cos_table, const float* sin_table, int rows, int head_dim, int rotary_dim,
+                 const int32_t* seq_start, const int32_t* pos_base, const int32_t* pos_map, int dtype) {
+    return rope_qkv_impl("clef_rope_qk", stream, q_out, q, q_heads, k_out, nullptr, k, nullptr, kv_heads, cos_table, sin_table,
+                         rows, head_dim, rotary_dim, seq_start, pos_base, pos_map, nullptr, nullptr, false, dtype);
+}
+
+int clef_rope_qkv_write(clef_stream_t stream, void* q_out, const void* q, int q_heads, void* cache_k, void* cache_v,
+                        const void* k, const void* v, int kv_heads, const float* cos_table, const float* sin_table,
+                        int tokens, int head_dim, int rotary_dim, const int32_t* seq_start, const int32_t* pos_base,
+                        const int32_t* pos_map, const int32_t* cache_map, const int32_t* cache_len, int dtype) {
+    return rope_qkv_impl("clef_rope_qkv_write", stream, q_out, q, q_heads, cache_k, cache_v, k, v, kv_heads, cos_table, sin_table,
+                         tokens, head_dim, rotary_dim, seq_start, pos_base, pos_map, cache_map, cache_len, true, dtype);
+}
+
 int clef_qk_norm_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_v, const void* k_raw, const void* v,
                                const float* weight, const float* cos_table, const float* sin_table, int tokens,
                                int kv_heads, int head_dim, int rotary_dim, float eps, const int32_t* seq_start,

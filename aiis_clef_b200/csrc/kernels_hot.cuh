@@ -1015,6 +1015,95 @@ rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, cons
     }
 }
 
+// Several [rows, heads_i, head_dim] tensors of one token set in ONE launch of the RoPE item structure above: q and k
+// rotated with the same positions (the reference's two rope_kernel launches, src/gpu.rs:1722-1725), optionally with
+// k going to its bf16 cache rows and v copied to its cache rows (the three conversion launches of attention_dev,
+// src/cuda/mod.rs:3201-3227). Work items of the segments follow each other; an item finds its segment by comparing
+// with the segments' end items.
+struct RopeSegment {
+    const uint16_t* x;
+    uint16_t* out;
+    uint32_t end_item;    // one past this segment's last item in the launch's item numbering
+    int heads;
+    FastDiv heads_div;
+    int rotate;           // 0: every item is a copy item (value rows)
+    int to_cache;         // 1: token t's rows are written at cache row kv_cache_row(t)
+};
+struct RopeSegments {
+    RopeSegment seg[3];
+};
+__device__ __forceinline__ void rope_segment_item(const RopeSegment& sg, uint32_t local, const float* __restrict__ cos_t,
+                                                  const float* __restrict__ sin_t, int head_dim, int rotary_dim,
+                                                  const int* seq_start, const int* pos_base, const int* pos_map,
+                                                  const int* cache_map, const int* cache_len, const FastDiv& items_div) {
+    const int half = rotary_dim >> 1;
+    const uint32_t head_row = fast_div(local, items_div);
+    const uint32_t item = local - head_row * items_div.d;
+    const uint32_t rot_items = sg.rotate ? (uint32_t)rotary_dim >> 5 : 0u;
+    const int row = (int)fast_div(head_row, sg.heads_div);
+    const uint16_t* xr = sg.x + (size_t)head_row * head_dim;
+    uint16_t* orow = sg.out + (sg.to_cache ? (kv_cache_row(row, cache_map, cache_len) * (size_t)sg.heads +
+                                              (head_row - (uint32_t)row * sg.heads)) * head_dim
+                                           : (size_t)head_row * head_dim);
+    if (item < rot_items) {
+        const int pos = rope_position(row, seq_start, pos_base, pos_map);
+        const U8x32 dlo = ldg_stream_v8(xr + item * 16);
+        const U8x32 dhi = ldg_stream_v8(xr + half + item * 16);
+        const float* cp = cos_t + (size_t)pos * rotary_dim + item * 16;
+        const float* sp = sin_t + (size_t)pos * rotary_dim + item * 16;
+        U8x32 olo, ohi;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 c = __ldg(reinterpret_cast<const float4*>(cp) + q);
+            const float4 s = __ldg(reinterpret_cast<const float4*>(sp) + q);
+            const uint32_t l0 = dlo.w[2 * q], l1 = dlo.w[2 * q + 1], h0 = dhi.w[2 * q], h1 = dhi.w[2 * q + 1];
+            float a0, b0, a1, b1, a2, b2, a3, b3;
+            rope_pair(bf16_lo(l0), bf16_lo(h0), c.x, s.x, a0, b0);
+            rope_pair(bf16_hi(l0), bf16_hi(h0), c.y, s.y, a1, b1);
+            rope_pair(bf16_lo(l1), bf16_lo(h1), c.z, s.z, a2, b2);
+            rope_pair(bf16_hi(l1), bf16_hi(h1), c.w, s.w, a3, b3);
+            olo.w[2 * q] = pack_bf16x2(a0, a1);
+            olo.w[2 * q + 1] = pack_bf16x2(a2, a3);
+            ohi.w[2 * q] = pack_bf16x2(b0, b1);
+            ohi.w[2 * q + 1] = pack_bf16x2(b2, b3);
+        }
+        stg_v8(orow + item * 16, olo);
+        stg_v8(orow + half + item * 16, ohi);
+    } else {
+        // copy item: two 32-byte chunks past the rotary span (or anywhere in a value row)
+        const int c0 = (sg.rotate ? rotary_dim : 0) + (int)(item - rot_items) * 32;
+        const U8x32 a = ldg_stream_v8(xr + c0);
+        const U8x32 b = ldg_stream_v8(xr + c0 + 16);
+        stg_v8(orow + c0, a);
+        stg_v8(orow + c0 + 16, b);
+    }
+}
+
+template <int NSEG>
+__global__ void __launch_bounds__(kCtaThreads)
+rope_multi_hot_kernel(RopeSegments segs, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int head_dim,
+                      int rotary_dim, const int* __restrict__ seq_start, const int* __restrict__ pos_base,
+                      const int* __restrict__ pos_map, const int* __restrict__ cache_map,
+                      const int* __restrict__ cache_len, FastDiv items_div) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const uint32_t total_items = segs.seg[NSEG - 1].end_item;
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_items; idx += stride) {
+        // (the segments are addressed with constant indices: kernel parameters cannot be indexed dynamically)
+        if (idx < segs.seg[0].end_item) {
+            rope_segment_item(segs.seg[0], idx, cos_t, sin_t, head_dim, rotary_dim, seq_start, pos_base, pos_map, cache_map,
+                              cache_len, items_div);
+        } else if (NSEG == 2 || idx < segs.seg[1].end_item) {
+            rope_segment_item(segs.seg[1], idx - segs.seg[0].end_item, cos_t, sin_t, head_dim, rotary_dim, seq_start, pos_base,
+                              pos_map, cache_map, cache_len, items_div);
+        } else {
+            rope_segment_item(segs.seg[NSEG - 1], idx - segs.seg[1].end_item, cos_t, sin_t, head_dim, rotary_dim, seq_start,
+                              pos_base, pos_map, cache_map, cache_len, items_div);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Per-head RMSNorm + partial RoPE (kernels/elementwise.cu:70-142) for head_dim 128, rotary_dim 64.
 // Four lanes own one head row: lane m holds chunk m (dims 16m .. 16m+15, inside the rotary span)

@@ -50,6 +50,8 @@ SYMBOLS = {
     "clef_to_bf16": (_I, [_P, _P, _P, _SZ, _P, _I, _I]),
     "clef_to_bf16_scatter": (_I, [_P, _P, _P, _SZ, _P, _I, _I]),
     "clef_rope_kv_write": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I]),
+    "clef_rope_qk": (_I, [_P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I]),
+    "clef_rope_qkv_write": (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I]),
     "clef_qk_norm_rope_kv_write": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _I]),
     "clef_sigmoid_mul": (_I, [_P, _P, _P, _P, _SZ, _I]),
     "clef_sigmoid_mul_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
@@ -340,6 +342,30 @@ class Device:
                                                _ptr(sin), tokens, kv_heads, head_dim, rotary_dim, _ptr(seq_start),
                                                _ptr(pos_base), _ptr(pos_map), _ptr(cache_map), _ptr(cache_len),
                                                _dtype_code(k)), "clef_rope_kv_write")
+
+    def rope_qk_dev(self, q, k, cos, sin, rows: int, q_heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
+                    seq_start=None, pos_base=None, pos_map=None):
+        """rope_apply_dev on q and on k in one launch; returns (q_out, k_out)."""
+        _dev_tensor(q, "q"), _dev_tensor(k, "k")
+        q_out, k_out = self._empty((rows, q_heads, head_dim), q.dtype), self._empty((rows, kv_heads, head_dim), k.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rope_qk(_stream(), _ptr(q_out), _ptr(q), q_heads, _ptr(k_out), _ptr(k), kv_heads, _ptr(cos),
+                                         _ptr(sin), rows, head_dim, rotary_dim, _ptr(seq_start), _ptr(pos_base), _ptr(pos_map),
+                                         _dtype_code(q)), "clef_rope_qk")
+        return q_out, k_out
+
+    def rope_qkv_write_dev(self, q, cache_k, cache_v, k, v, cos, sin, tokens: int, q_heads: int, kv_heads: int,
+                           head_dim: int, rotary_dim: int, seq_start=None, pos_base=None, pos_map=None, cache_map=None,
+                           cache_len=None):
+        """rope_apply_dev on q (returned) and rope_kv_write_dev on k, v (caches written in place), one launch."""
+        _dev_tensor(q, "q"), _dev_tensor(k, "k"), _dev_tensor(v, "v")
+        q_out = self._empty((tokens, q_heads, head_dim), q.dtype)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_rope_qkv_write(_stream(), _ptr(q_out), _ptr(q), q_heads, _ptr(cache_k), _ptr(cache_v), _ptr(k),
+                                                _ptr(v), kv_heads, _ptr(cos), _ptr(sin), tokens, head_dim, rotary_dim,
+                                                _ptr(seq_start), _ptr(pos_base), _ptr(pos_map), _ptr(cache_map),
+                                                _ptr(cache_len), _dtype_code(q)), "clef_rope_qkv_write")
+        return q_out
 
     def qk_norm_rope_kv_write_dev(self, cache_k, cache_v, k_raw, v, weight, cos, sin, tokens: int, kv_heads: int,
                                   head_dim: int, rotary_dim: int, eps: float, seq_start=None, pos_base=None,

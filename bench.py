@@ -48,6 +48,7 @@ BYTES_PER_ROW = {
     "swiglu_quantise_nvfp4": 2 * 2 * INTER + INTER // 2 + INTER // 16,                        # 28,032
     "rope_q": 2 * Q_HEADS * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,                         # 8,452
     "rope_k": 2 * KV_HEADS * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,                        # 1,284
+    "rope_qk": 2 * (Q_HEADS + KV_HEADS) * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,           # 9,476 (q and k, one launch)
     "embed_gather": 4 + 2 * HIDDEN + 2 * HIDDEN,                                              # 8,196
     "rms_norm_gated_quantise_nvfp4": 2 * 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,             # 9,344
     # the unfused entry points (what the engine runs when a fusion is switched off), bf16 in and out
@@ -71,7 +72,9 @@ BYTES_PER_ROW = {
     # in front of the GDN scan: causal convolution (4 taps) + silu over the 8,192 mixed q/k/v channels
     "causal_conv_silu": 2 * 2 * CONV_DIM + 4,                                                 # 32,772
 }
-STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k"]
+# The step: RMSNorm+NVFP4, SwiGLU+NVFP4, and the partial RoPE of the q and the k heads, which share their positions
+# and go out as one launch (clef_rope_qk); rope_q / rope_k alone are reported under "kernels".
+STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk"]
 FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k",
                 "rms_norm_gated_quantise_nvfp4"]     # config 4: the full fused chain over 130,712 rows
 DOMINANT = "swiglu_quantise_nvfp4"
@@ -310,6 +313,8 @@ def run_gpu_arm(args):
             stream(), p(d["gate"]), p(d["up"]), p(d["pk_i"]), p(d["sc_i"]), ROWS, INTER, GS_SWIGLU, 128, 512, 0),
         "rope_q": lambda d: lib.clef_rope(stream(), p(d["q_out"]), p(d["q"]), p(cos), p(sin), ROWS, Q_HEADS, HEAD_DIM,
                                           ROTARY, None, None, p(cpos), 0),
+        "rope_qk": lambda d: lib.clef_rope_qk(stream(), p(d["q_out"]), p(d["q"]), Q_HEADS, p(d["k_out"]), p(d["k"]), KV_HEADS,
+                                              p(cos), p(sin), ROWS, HEAD_DIM, ROTARY, None, None, p(cpos), 0),
         "rope_k": lambda d: lib.clef_rope(stream(), p(d["k_out"]), p(d["k"]), p(cos), p(sin), ROWS, KV_HEADS, HEAD_DIM,
                                           ROTARY, None, None, p(cpos), 0),
         "embed_gather": lambda d: lib.clef_embed_gather(stream(), p(table), p(d["ids"]), p(d["h"]), ROWS, HIDDEN, 0),

@@ -174,6 +174,20 @@ int clef_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_v, const
                        int rotary_dim, const int32_t* seq_start, const int32_t* pos_base, const int32_t* pos_map,
                        const int32_t* cache_map, const int32_t* cache_len, int dtype);
 
+/* The two rope_kernel launches of a layer (q, then k, same positions: src/gpu.rs:1722-1725) as one launch.
+ * q [rows, q_heads, head_dim] -> q_out, k [rows, kv_heads, head_dim] -> k_out; position arguments as clef_rope. */
+int clef_rope_qk(clef_stream_t stream, void* q_out, const void* q, int q_heads, void* k_out, const void* k, int kv_heads,
+                 const float* cos_table, const float* sin_table, int rows, int head_dim, int rotary_dim,
+                 const int32_t* seq_start, const int32_t* pos_base, const int32_t* pos_map, int dtype);
+
+/* clef_rope on q plus clef_rope_kv_write on k and v in one launch: the whole RoPE + KV-cache prologue of an attention
+ * layer (two rope_kernel launches and the k / v conversion launches of the reference). q_out has the activation dtype,
+ * the caches are bf16. */
+int clef_rope_qkv_write(clef_stream_t stream, void* q_out, const void* q, int q_heads, void* cache_k, void* cache_v,
+                        const void* k, const void* v, int kv_heads, const float* cos_table, const float* sin_table,
+                        int tokens, int head_dim, int rotary_dim, const int32_t* seq_start, const int32_t* pos_base,
+                        const int32_t* pos_map, const int32_t* cache_map, const int32_t* cache_len, int dtype);
+
 /* As clef_rope_kv_write with the per-head RMSNorm of qk_norm_rope_kernel in front of the rotation
  * (the k call of src/gpu.rs:1711-1713): k_raw -> norm with (1 + weight) -> RoPE -> bf16 -> cache. */
 int clef_qk_norm_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_v, const void* k_raw, const void* v,

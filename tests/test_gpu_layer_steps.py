@@ -360,3 +360,42 @@ def test_add_rms_norm_quantise_equals_the_chain(rows, cols, dtype, choice):
         torch.cuda.synchronize()
         assert_bytes_equal(orc.bf16_bits(da.cpu()).reshape(-1), cpu_sum.reshape(-1), "in-place residual")
         assert_bytes_equal(packed2.bytes(), want_p, "packed codes, in-place residual")
+
+
+# ---- q and k (and the KV-cache write) in one launch ---------------------------------------------------------------
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
+@pytest.mark.parametrize("dtype", [BF16, F32], ids=["bf16", "f32"])
+@pytest.mark.parametrize("rows,q_heads,kv_heads,hd,rot", [(1, 16, 2, 128, 64), (778, 16, 2, 128, 64), (129, 8, 2, 256, 64),
+                                                           (65, 4, 4, 64, 64), (33, 3, 1, 40, 16), (8192, 16, 2, 128, 64)])
+def test_rope_qk_and_rope_qkv_write_equal_the_separate_calls(rows, q_heads, kv_heads, hd, rot, dtype, choice):
+    """clef_rope_qk == clef_rope(q), clef_rope(k); clef_rope_qkv_write == clef_rope(q), clef_rope_kv_write(k, v): byte for
+    byte (the separate calls are compared with the reference kernels above and in test_gpu_parity_elem.py)."""
+    clef.set_kernel_choice(choice)
+    rng = np.random.default_rng(rows * 13 + hd + q_heads)
+    tdt = torch.bfloat16 if dtype == BF16 else torch.float32
+    mk = (lambda b: dev_bf16(b)) if dtype == BF16 else (lambda b: dev_f32_from_bits(b))
+    q, k, v = (mk(normal_bf16(rng, (rows, h, hd))) for h in (q_heads, kv_heads, kv_heads))
+    pos, cos, sin = rope_setup(rng, rows, rot, 700)
+    dpos = i32(pos)
+    dev = clef.Device(0)
+    want_q = dev.rope_apply_dev(q, cos, sin, rows, q_heads, hd, rot, pos_map=dpos)
+    want_k = dev.rope_apply_dev(k, cos, sin, rows, kv_heads, hd, rot, pos_map=dpos)
+    got_q, got_k = dev.rope_qk_dev(q, k, cos, sin, rows, q_heads, kv_heads, hd, rot, pos_map=dpos)
+    torch.cuda.synchronize()
+    assert got_q.dtype == tdt and torch.equal(got_q, want_q) and torch.equal(got_k, want_k)
+    cache_rows = rows + 11
+    cmap = i32(cache_case(rng, rows, cache_rows))
+    caches = [torch.full((cache_rows, kv_heads, hd), -1.0, dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    dev.rope_kv_write_dev(caches[0], caches[1], k, v, cos, sin, rows, kv_heads, hd, rot, pos_map=dpos, cache_map=cmap)
+    got_q2 = dev.rope_qkv_write_dev(q, caches[2], caches[3], k, v, cos, sin, rows, q_heads, kv_heads, hd, rot, pos_map=dpos,
+                                    cache_map=cmap)
+    torch.cuda.synchronize()
+    assert torch.equal(got_q2, want_q) and torch.equal(caches[2], caches[0]) and torch.equal(caches[3], caches[1])
+    # without a map: rows land at *cache_len + t
+    clen = i32([7])
+    c2 = [torch.full((cache_rows, kv_heads, hd), -1.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    dev.rope_qkv_write_dev(q, c2[0], c2[1], k, v, cos, sin, min(rows, 4), q_heads, kv_heads, hd, rot, pos_map=dpos, cache_len=clen)
+    torch.cuda.synchronize()
+    n = min(rows, 4)
+    assert torch.equal(c2[0][7:7 + n], want_k[:n].to(torch.bfloat16)) and torch.equal(c2[1][7:7 + n], v[:n].to(torch.bfloat16))
+    assert (c2[0][:7].float() == -1.0).all() and (c2[0][7 + n:].float() == -1.0).all()
