@@ -75,7 +75,7 @@ BYTES_PER_ROW = {
 # The step: RMSNorm+NVFP4, SwiGLU+NVFP4, and the partial RoPE of the q and the k heads, which share their positions
 # and go out as one launch (clef_rope_qk); rope_q / rope_k alone are reported under "kernels".
 STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk"]
-FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_q", "rope_k",
+FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk",
                 "rms_norm_gated_quantise_nvfp4"]     # config 4: the full fused chain over 130,712 rows
 DOMINANT = "swiglu_quantise_nvfp4"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel at 8,192 rows, from
@@ -533,8 +533,8 @@ def full_pass(clef, lib, dev, world, rank, gen, p, stream, ok, w_norm, table):
     calls = {
         "rms_norm_quantise_nvfp4": lambda: lib.clef_rms_norm_quantise_nvfp4(stream(), p(x), p(w_norm), p(pkh), p(sch), n, HIDDEN, EPS, GS_NORM, 128, 512, 0),
         "swiglu_quantise_nvfp4": lambda: lib.clef_swiglu_quantise_nvfp4(stream(), p(gate), p(up), p(pki), p(sci), n, INTER, GS_SWIGLU, 128, 512, 0),
-        "rope_q": lambda: lib.clef_rope(stream(), p(qo), p(q), p(cos), p(sin), n, Q_HEADS, HEAD_DIM, ROTARY, None, None, p(cpos), 0),
-        "rope_k": lambda: lib.clef_rope(stream(), p(ko), p(k), p(cos), p(sin), n, KV_HEADS, HEAD_DIM, ROTARY, None, None, p(cpos), 0),
+        "rope_qk": lambda: lib.clef_rope_qk(stream(), p(qo), p(q), Q_HEADS, p(ko), p(k), KV_HEADS, p(cos), p(sin), n, HEAD_DIM,
+                                            ROTARY, None, None, p(cpos), 0),
         "embed_gather": lambda: lib.clef_embed_gather(stream(), p(table), p(ids), p(h), n, HIDDEN, 0),
         "rms_norm_gated_quantise_nvfp4": lambda: lib.clef_rms_norm_gated_quantise_nvfp4(
             stream(), p(o), p(z), p(w_gated), p(pkg), p(scg), rp * VH, HEAD_DIM, EPS, GS_GATED, 128, 512, VH, n * VH, 0),
