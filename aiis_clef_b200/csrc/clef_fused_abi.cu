@@ -570,24 +570,25 @@ int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, 
     if (rows == 0) return CLEF_OK;
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
-    if (dtype == CLEF_BF16 && use_hot() && head_dim == 128 && rotary_dim == 64 && aligned(x, 32) && aligned(out, 32) &&
-        (!gate_out || aligned(gate_out, 32))) {
-        const size_t hot_groups = ((size_t)rows + 63) / 64;
+    if (dtype == CLEF_BF16 && use_hot() && (head_dim == 128 || head_dim == 256) && rotary_dim == 64 && rows < 0x3fffffff &&
+        aligned(x, 32) && aligned(out, 32) && (!gate_out || aligned(gate_out, 32))) {
+        // head_dim 256 with a gate: the gate halves are copy items after the normed rows (from a multiple of 8)
+        const size_t hot_items = (head_dim == 256 && gate_out) ? (((size_t)rows + 7) & ~(size_t)7) + rows : (size_t)rows;
+        const size_t hot_groups = (hot_items + 63) / 64;
         const FastDiv heads_div = make_fast_div((uint32_t)heads);
-        if (gate_out) {
-            static std::atomic<int> occ{0};
-            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<true, false>, 0, occ);
-            launch_hot(qk_norm_rope_hot_kernel<true, false>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
-                       as_stream(stream), (const uint16_t*)x, weight, cos_table, sin_table, (uint16_t*)out,
-                       (uint16_t*)gate_out, (uint32_t)rows, eps, (const int*)seq_start, (const int*)pos_base,
-                       (const int*)pos_map, heads_div, KvCacheDest{});
+        auto launch = [&](auto kernel, std::atomic<int>& occ) {
+            const int per_sm = ctas_per_sm(kernel, 0, occ);
+            launch_hot(kernel, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0, as_stream(stream), (const uint16_t*)x,
+                       weight, cos_table, sin_table, (uint16_t*)out, (uint16_t*)gate_out, (uint32_t)rows, eps,
+                       (const int*)seq_start, (const int*)pos_base, (const int*)pos_map, heads_div, KvCacheDest{});
+        };
+        static std::atomic<int> occ[4];
+        if (head_dim == 128) {
+            if (gate_out) launch(qk_norm_rope_hot_kernel<true, false>, occ[0]);
+            else launch(qk_norm_rope_hot_kernel<false, false>, occ[1]);
         } else {
-            static std::atomic<int> occ{0};
-            const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<false, false>, 0, occ);
-            launch_hot(qk_norm_rope_hot_kernel<false, false>, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0,
-                       as_stream(stream), (const uint16_t*)x, weight, cos_table, sin_table, (uint16_t*)out,
-                       (uint16_t*)nullptr, (uint32_t)rows, eps, (const int*)seq_start, (const int*)pos_base,
-                       (const int*)pos_map, heads_div, KvCacheDest{});
+            if (gate_out) launch(qk_norm_rope_hd256_hot_kernel<true, false>, occ[2]);
+            else launch(qk_norm_rope_hd256_hot_kernel<false, false>, occ[3]);
         }
         return check_launch(what);
     }

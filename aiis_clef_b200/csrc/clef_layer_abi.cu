@@ -225,16 +225,19 @@ int clef_qk_norm_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
-    if (dtype == CLEF_BF16 && use_hot() && head_dim == 128 && rotary_dim == 64 && rows % 8 == 0 && aligned(k_raw, 32) &&
-        aligned(v, 32) && aligned(cache_k, 32) && aligned(cache_v, 32)) {
-        static std::atomic<int> occ{0};
-        const int per_sm = ctas_per_sm(qk_norm_rope_hot_kernel<false, true>, 0, occ);
+    if (dtype == CLEF_BF16 && use_hot() && (head_dim == 128 || head_dim == 256) && rotary_dim == 64 && rows % 8 == 0 &&
+        aligned(k_raw, 32) && aligned(v, 32) && aligned(cache_k, 32) && aligned(cache_v, 32)) {
         const size_t groups = (2 * rows + 63) / 64;
-        launch_hot(qk_norm_rope_hot_kernel<false, true>, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, s,
-                   (const uint16_t*)k_raw, weight, cos_table, sin_table, (uint16_t*)cache_k, (uint16_t*)nullptr,
-                   (uint32_t)rows, eps, (const int*)seq_start, (const int*)pos_base, (const int*)pos_map,
-                   make_fast_div((uint32_t)kv_heads),
-                   KvCacheDest{(const int*)cache_map, (const int*)cache_len, (const uint16_t*)v, (uint16_t*)cache_v});
+        auto launch = [&](auto kernel, std::atomic<int>& occ) {
+            const int per_sm = ctas_per_sm(kernel, 0, occ);
+            launch_hot(kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, s, (const uint16_t*)k_raw, weight, cos_table,
+                       sin_table, (uint16_t*)cache_k, (uint16_t*)nullptr, (uint32_t)rows, eps, (const int*)seq_start,
+                       (const int*)pos_base, (const int*)pos_map, make_fast_div((uint32_t)kv_heads),
+                       KvCacheDest{(const int*)cache_map, (const int*)cache_len, (const uint16_t*)v, (uint16_t*)cache_v});
+        };
+        static std::atomic<int> occ[2];
+        if (head_dim == 128) launch(qk_norm_rope_hot_kernel<false, true>, occ[0]);
+        else launch(qk_norm_rope_hd256_hot_kernel<false, true>, occ[1]);
         return check_launch(what);
     }
     // Shape-general path: the value rows as a cache write of their own, then the fused key kernel.

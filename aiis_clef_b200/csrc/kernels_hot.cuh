@@ -1237,6 +1237,143 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same step for head_dim 256, rotary_dim 64 (the head shape src/cuda/mod.rs:6743 serves). Four lanes own one
+// head row again: lane m holds chunks m (rotary), m + 4, m + 8 and m + 12. The reference's norm team for 256
+// columns is one warp whose thread l adds quad l and then quad l + 32, so the halves are added quad by quad
+// before the head_tree_32 tree. The raw words of a row stay in registers across the tree and are unpacked chunk
+// by chunk afterwards; rows that are only copied are items of their own. No software prefetch: two resident CTAs
+// of independent row loads cover the latency.
+// ---------------------------------------------------------------------------------------------
+template <bool GATE, bool KV>
+__global__ void __launch_bounds__(kCtaThreads, 2)
+qk_norm_rope_hd256_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight,
+                              const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint16_t* __restrict__ out,
+                              uint16_t* __restrict__ gate_out, uint32_t rows, float eps, const int* __restrict__ seq_start,
+                              const int* __restrict__ pos_base, const int* __restrict__ pos_map, FastDiv heads_div,
+                              KvCacheDest kv) {
+    static_assert(!(GATE && KV), "the key side has no gate half");
+    constexpr int HD = 256, ROT = 64, NCH = 4, STRIDE = GATE ? 2 * HD : HD;
+    constexpr bool COPIES = GATE || KV;
+    // Rows that are only copied (the gate halves, or the value rows of a KV write) follow the normed rows as
+    // items of their own, from the next multiple of 8 so that a warp holds one kind.
+    const uint32_t copy_base = (rows + 7u) & ~7u;
+    const uint32_t items = COPIES ? copy_base + rows : rows;
+    __shared__ float4 s_w[HD / 4];   // (1 + w), quad-pair layout: s_w[c * 4 + q] for chunk c, quad q
+    const int lane = threadIdx.x & 31;
+    const int m = lane & 3;
+    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
+    uint32_t item = blockIdx.x * (kCtaThreads / 4) + (threadIdx.x >> 2);
+    pdl_launch_dependents();
+    if (threadIdx.x < HD / 4) {
+        const float4 t = *reinterpret_cast<const float4*>(weight + threadIdx.x * 4);
+        s_w[threadIdx.x] = make_float4(1.0f + t.x, 1.0f + t.z, 1.0f + t.y, 1.0f + t.w);
+    }
+    pdl_wait_prior_grids();
+    __syncthreads();
+    for (uint32_t base = item - (uint32_t)(lane >> 2); base < items; base += groups_in_grid, item += groups_in_grid) {
+        if (COPIES && base >= copy_base) {
+            const uint32_t crow = item - copy_base;
+            if (crow < rows) {
+                const uint16_t* src = GATE ? x + (size_t)crow * STRIDE + HD : kv.v + (size_t)crow * HD;
+                U8x32 c[NCH];
+#pragma unroll
+                for (int h = 0; h < NCH; ++h) c[h] = ldg_stream_v8(src + (m + 4 * h) * 16);
+                uint16_t* dst;
+                if (GATE) {
+                    dst = gate_out + (size_t)crow * HD;
+                } else {
+                    const int token = (int)fast_div(crow, heads_div);
+                    dst = kv.cache_v + (kv_cache_row(token, kv.cache_map, kv.cache_len) * heads_div.d + (crow - (uint32_t)token * heads_div.d)) * HD;
+                }
+#pragma unroll
+                for (int h = 0; h < NCH; ++h) stg_v8(dst + (m + 4 * h) * 16, c[h]);
+            }
+            continue;
+        }
+        const uint32_t hrow = item;
+        const bool live = hrow < rows;
+        U8x32 d[NCH];
+#pragma unroll
+        for (int h = 0; h < NCH; ++h) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) d[h].w[i] = 0u;
+        }
+        if (live) {
+#pragma unroll
+            for (int h = 0; h < NCH; ++h) d[h] = ldg_stream_v8(x + (size_t)hrow * STRIDE + (m + 4 * h) * 16);
+        }
+        f32x2 v[8], pv[8];
+        float quad[NCH][4];
+#pragma unroll
+        for (int h = 0; h < NCH; ++h) {
+            unpack16_quadpairs(d[h], v);
+            quad_squares(v, quad[h]);
+        }
+        U8x32 praw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {   // partner's raw rotary chunk (lane m ^ 2)
+            praw.w[i] = __shfl_xor_sync(kFullMask, d[0].w[i], 2);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // reference thread l adds quad l, then quad l + 32 (dims + 128), before the tree
+            quad[0][k] = __fadd_rn(quad[0][k], quad[2][k]);
+            quad[1][k] = __fadd_rn(quad[1][k], quad[3][k]);
+        }
+        const float total = head_tree_32(quad[0], quad[1], lane);
+        if (!live) {
+            continue;
+        }
+        const f32x2 inv2 = f2_splat(inv_rms_pow2<HD>(total, eps));
+        const int token = (int)fast_div(hrow, heads_div);
+        uint16_t* orow = out + (KV ? (kv_cache_row(token, kv.cache_map, kv.cache_len) * heads_div.d + (hrow - (uint32_t)token * heads_div.d)) * HD
+                                   : (size_t)hrow * HD);
+#pragma unroll
+        for (int h = 1; h < NCH; ++h) {   // pass-through chunks
+            unpack16_quadpairs(d[h], v);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 w = s_w[(m + 4 * h) * 4 + q];
+                v[2 * q] = f2_mul(f2_mul(v[2 * q], inv2), make_float2(w.x, w.y));
+                v[2 * q + 1] = f2_mul(f2_mul(v[2 * q + 1], inv2), make_float2(w.z, w.w));
+            }
+            stg_v8(orow + (m + 4 * h) * 16, pack16_bf16(v));
+        }
+        unpack16_quadpairs(d[0], v);
+        unpack16_quadpairs(praw, pv);
+        const int pm = m ^ 2;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 wa = s_w[m * 4 + q], wp = s_w[pm * 4 + q];
+            v[2 * q] = f2_mul(f2_mul(v[2 * q], inv2), make_float2(wa.x, wa.y));
+            v[2 * q + 1] = f2_mul(f2_mul(v[2 * q + 1], inv2), make_float2(wa.z, wa.w));
+            pv[2 * q] = f2_mul(f2_mul(pv[2 * q], inv2), make_float2(wp.x, wp.y));
+            pv[2 * q + 1] = f2_mul(f2_mul(pv[2 * q + 1], inv2), make_float2(wp.z, wp.w));
+        }
+        const int pos = rope_position(token, seq_start, pos_base, pos_map);
+        const float* cp = cos_t + (size_t)pos * ROT + (m & 1) * 16;
+        const float* sp = sin_t + (size_t)pos * ROT + (m & 1) * 16;
+        const bool holds_lo = m < 2;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 c = __ldg(reinterpret_cast<const float4*>(cp) + q);
+            const float4 sn = __ldg(reinterpret_cast<const float4*>(sp) + q);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int i = 2 * q + e;
+                const f32x2 c2 = e == 0 ? make_float2(c.x, c.z) : make_float2(c.y, c.w);
+                const f32x2 s2 = e == 0 ? make_float2(sn.x, sn.z) : make_float2(sn.y, sn.w);
+                // lo' = fma(lo, c, -(hi * s));  hi' = fma(lo, s, hi * c)   (the reference build's contraction)
+                const f32x2 lo = holds_lo ? v[i] : pv[i];
+                const f32x2 hi = holds_lo ? pv[i] : v[i];
+                const f32x2 t = f2_mul(hi, holds_lo ? make_float2(-s2.x, -s2.y) : c2);
+                v[i] = f2_fma(lo, holds_lo ? c2 : s2, t);
+            }
+        }
+        stg_v8(orow + m * 16, pack16_bf16(v));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Embedding gather (kernels/elementwise.cu:396-407) for rows of a multiple of 1 KiB: one warp per
 // token row, every lane moves CH chunks of 32 bytes.
 // ---------------------------------------------------------------------------------------------

@@ -158,7 +158,7 @@ def test_rope_kv_write_equals_the_reference_chain(tokens, heads, hd, rot, mode, 
 @pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("dtype", [BF16, F32], ids=["bf16", "f32"])
 @pytest.mark.parametrize("mode", ["map", "len"])
-@pytest.mark.parametrize("tokens,heads,hd,rot", [(4, 2, 128, 64), (778, 2, 128, 64), (129, 2, 256, 64), (65, 3, 128, 64), (40, 4, 64, 32)])
+@pytest.mark.parametrize("tokens,heads,hd,rot", [(4, 2, 128, 64), (778, 2, 128, 64), (129, 2, 256, 64), (776, 2, 256, 64), (4, 2, 256, 64), (65, 3, 128, 64), (40, 4, 64, 32)])
 def test_qk_norm_rope_kv_write_equals_the_unfused_calls(tokens, heads, hd, rot, mode, dtype, choice):
     """k_raw -> clef_qk_norm_rope (itself checked against the reference kernels elsewhere) -> to_bf16(_scatter)
     must equal the one-launch entry point byte for byte; the f32 path is additionally the reference chain."""

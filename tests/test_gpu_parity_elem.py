@@ -263,6 +263,43 @@ def test_qk_norm_rope(tokens, heads, head_dim, rot, with_gate, choice):
                 assert_bytes_equal(gate.as_bf16_bits(), want_gate, "gate half")
 
 
+@pytest.mark.parametrize("with_gate", [False, True])
+@pytest.mark.parametrize("tokens,heads,head_dim", [(778, 16, 256), (4099, 16, 256), (129, 2, 256), (1, 1, 256), (4099, 16, 128), (65, 3, 128)])
+def test_qk_norm_rope_bf16_rounds_the_reference_f32_result(tokens, heads, head_dim, with_gate):
+    """bf16 in and out: the tuned kernels (head_dim 128 and 256, rotary 64) and the general kernel must both give
+    the reference fused f32 kernel's result rounded once to bf16, byte for byte (bf16 widens to f32 exactly)."""
+    rot = 64
+    rng = np.random.default_rng(tokens * 3 + head_dim + int(with_gate))
+    rows = tokens * heads
+    stride = 2 * head_dim if with_gate else head_dim
+    x = normal_bf16(rng, (rows, stride))
+    x[rng.integers(0, rows, 8)] = 0                      # all-zero head rows
+    w = (rng.standard_normal(head_dim) * 0.1).astype(np.float32)
+    table_len = 2048
+    dev = clef.Device(0)
+    cos, sin = dev.rope_tables_dev(torch.arange(table_len, dtype=torch.int32, device="cuda"), table_len, rot, 1e7)
+    pos_map = torch.from_numpy(rng.integers(0, table_len, tokens).astype(np.int32)).cuda()
+    dw, xf = torch.from_numpy(w).cuda(), dev_f32_from_bits(x)
+    if head_dim == 256:
+        fused, _ = ref_gpu.qk_norm_rope(xf, dw, cos, sin, rows, heads, head_dim, rot, 1e-6, None, None, pos_map, with_gate)
+    else:   # the reference gates its fused kernel on head_dim 256; the chain it replaces is the arbiter elsewhere
+        q_f = xf.view(rows, stride)[:, :head_dim].contiguous()
+        fused = ref_gpu.rope(ref_gpu.rms_norm(q_f, dw, rows, head_dim, 1e-6), cos, sin, tokens, heads, head_dim, rot, None, None, pos_map)
+    want = f32_to_bf16_bits_gpu(fused)
+    for choice in (0, 1):
+        clef.set_kernel_choice(choice)
+        out = out_buffer(rows * head_dim, BF16)
+        gate = out_buffer(rows * head_dim, BF16) if with_gate else None
+        assert call("clef_qk_norm_rope", stream(), ptr(dev_bf16(x)), ptr(dw), ptr(cos), ptr(sin), out.ptr,
+                    gate.ptr if gate else None, rows, heads, head_dim, rot, 1e-6, None, None, ptr(pos_map), BF16) == 0
+        torch.cuda.synchronize()
+        out.check_guards("qk_norm_rope")
+        assert_bytes_equal(out.as_bf16_bits(), want, f"bf16 qk_norm_rope, kernel choice {choice}")
+        if with_gate:
+            gate.check_guards("qk gate")
+            assert_bytes_equal(gate.as_bf16_bits(), x.reshape(rows, stride)[:, head_dim:], "gate half")
+
+
 def test_rope_contraction_matches_the_reference_build():
     """Which FMA contraction the reference build applies to lo*c - hi*s and to hi*c + lo*s (each
     expression on its own): the modes the CPU oracle uses must reproduce rope_kernel's f32 output."""
