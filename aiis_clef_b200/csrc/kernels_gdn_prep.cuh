@@ -68,6 +68,104 @@ __device__ __forceinline__ void unpack8<F32>(const Raw8<F32>& r, float* v) {
 // A thread owns 8 channels and R consecutive rows and slides a K-row window over them, so every x value is
 // loaded once. channels % 8 == 0.
 // ---------------------------------------------------------------------------------------------
+struct Float8 {
+    float v[8];
+};
+// The literal silu of 8 accumulators, out of line: taken when one of them is outside the short form's domain.
+static __device__ __noinline__ Float8 silu8_literal(float a0, float a1, float a2, float a3, float a4, float a5, float a6,
+                                                    float a7) {
+    Float8 r;
+    r.v[0] = silu_ieee_div(a0), r.v[1] = silu_ieee_div(a1), r.v[2] = silu_ieee_div(a2), r.v[3] = silu_ieee_div(a3);
+    r.v[4] = silu_ieee_div(a4), r.v[5] = silu_ieee_div(a5), r.v[6] = silu_ieee_div(a6), r.v[7] = silu_ieee_div(a7);
+    return r;
+}
+
+// One output value by the literal expression, reading its taps from global memory: the general kernel's element and
+// the tuned kernel's path for strips that touch a sequence start.
+template <typename T>
+__device__ __forceinline__ float causal_conv_silu_element(const typename T::storage* __restrict__ x, const float* __restrict__ w,
+                                                          int t, int ch, int channels, int k, const int* __restrict__ seq_start,
+                                                          const typename T::storage* __restrict__ history,
+                                                          const int* __restrict__ slot_map) {
+    const int lo = seq_start ? seq_start[t] : 0;
+    float acc = 0.0f;
+    for (int tap = 0; tap < k; ++tap) {
+        const int src = t - (k - 1) + tap;
+        float v;
+        if (src >= lo) {
+            v = load_scalar<T>(x + (size_t)src * channels + ch);
+        } else if (history && src >= lo - (k - 1)) {
+            const int slot = slot_map ? slot_map[t] : 0;
+            v = load_scalar<T>(history + ((size_t)slot * (k - 1) + (size_t)(src - lo + (k - 1))) * channels + ch);
+        } else {
+            continue;
+        }
+        acc = __fmaf_rn(w[(size_t)ch * k + tap], v, acc);
+    }
+    return silu_ieee_div(acc);
+}
+
+// Rows [t0, t1) of 8 channels with every tap tested against the row's sequence start, out of line; a tap's 8
+// values are one vector load from x or from the history.
+template <typename T, int K>
+static __device__ __noinline__ void causal_conv_silu_strip_literal(typename T::storage* __restrict__ out,
+                                                                   const typename T::storage* __restrict__ x,
+                                                                   const float* __restrict__ w, int t0, int t1, int c0,
+                                                                   int channels, const int* __restrict__ seq_start,
+                                                                   const typename T::storage* __restrict__ history,
+                                                                   const int* __restrict__ slot_map) {
+#pragma unroll 2
+    for (int t = t0; t < t1; ++t) {
+        const int lo = seq_start ? seq_start[t] : 0;
+        constexpr int k = K;
+        const int slot = (history && slot_map) ? slot_map[t] : 0;
+        Raw8<T> raw[K];   // the K taps are requested together
+        bool live[K];
+#pragma unroll
+        for (int tap = 0; tap < K; ++tap) {
+            const int src = t - (k - 1) + tap;
+            const typename T::storage* p = nullptr;
+            if (src >= lo) {
+                p = x + (size_t)src * channels + c0;
+            } else if (history && src >= lo - (k - 1)) {
+                p = history + ((size_t)slot * (k - 1) + (size_t)(src - lo + (k - 1))) * channels + c0;
+            }
+            live[tap] = p != nullptr;
+            if (live[tap]) raw[tap] = load8_raw<T>(p);
+        }
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int tap = 0; tap < K; ++tap) {
+            if (live[tap]) {
+                float v[8];
+                unpack8<T>(raw[tap], v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(__ldg(w + (size_t)(c0 + j) * k + tap), v[j], acc[j]);
+            }
+        }
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = silu_ieee_div(acc[j]);
+        store8<T>(out + (size_t)t * channels + c0, o);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack8_pairs(const Raw8<T>& r, f32x2* v);
+template <>
+__device__ __forceinline__ void unpack8_pairs<Bf16>(const Raw8<Bf16>& r, f32x2* v) {
+    v[0] = f2_pack(bf16_lo(r.a.x), bf16_hi(r.a.x)), v[1] = f2_pack(bf16_lo(r.a.y), bf16_hi(r.a.y));
+    v[2] = f2_pack(bf16_lo(r.a.z), bf16_hi(r.a.z)), v[3] = f2_pack(bf16_lo(r.a.w), bf16_hi(r.a.w));
+}
+template <>
+__device__ __forceinline__ void unpack8_pairs<F32>(const Raw8<F32>& r, f32x2* v) {
+    v[0] = f2_pack(__uint_as_float(r.a.x), __uint_as_float(r.a.y)), v[1] = f2_pack(__uint_as_float(r.a.z), __uint_as_float(r.a.w));
+    v[2] = f2_pack(__uint_as_float(r.b.x), __uint_as_float(r.b.y)), v[3] = f2_pack(__uint_as_float(r.b.z), __uint_as_float(r.b.w));
+}
+
+// A strip none of whose rows has a tap before its sequence start (all but the strips that hold a sequence start or
+// the first K - 1 rows) runs without per-tap tests, two channels per packed multiply-add, the silu in its short
+// exact form (silu_ieee_fast_f32_x2); the other strips take the literal element path.
 // Two CTAs per SM (128 registers) measured best: one CTA (145 registers) or three and four (spills) are 20 to 60 %
 // slower, and so was keeping the next strip's loads in flight during the arithmetic (159 registers).
 template <typename T, int K, int R>
@@ -86,27 +184,7 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
         const uint32_t strip = fast_div(idx, cvecs_div);
         const int c0 = (int)(idx - strip * cvecs) * 8;
         const int t0 = (int)strip * R;
-        float wt[8][K];
-        if (K == 4) {   // a channel's four taps are one 16-byte load
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 t4 = __ldg(reinterpret_cast<const float4*>(w) + (c0 + j));
-                wt[j][0] = t4.x, wt[j][1] = t4.y, wt[j][2 % K] = t4.z, wt[j][3 % K] = t4.w;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-#pragma unroll
-                for (int tap = 0; tap < K; ++tap) {
-                    wt[j][tap] = __ldg(w + (size_t)(c0 + j) * K + tap);
-                }
-            }
-        }
-        int lo_of[R];   // the sequence start of every row of the strip, requested up front as well
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            lo_of[r] = (seq_start && t0 + r < rows) ? __ldg(seq_start + t0 + r) : 0;
-        }
+        const int t1 = min(t0 + R, rows);
         // All R + K - 1 rows of the strip are requested before any is used, so a thread has that many loads in flight.
         Raw8<T> raw[R + K - 1];
 #pragma unroll
@@ -118,10 +196,39 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
                 raw[i] = Raw8<T>{};
             }
         }
-        float win[K][8];   // win[i] = x[t - (K-1) + i] for the current row t; win[K-1] is the row itself
+        bool plain = t0 >= K - 1;
+        if (seq_start) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                if (t0 + r < rows) plain &= __ldg(seq_start + t0 + r) <= t0 + r - (K - 1);
+            }
+        }
+        f32x2 wt[4][K];   // wt[p][tap] = the tap weights of channels c0 + 2p and c0 + 2p + 1
+        if (K == 4) {     // a channel's four taps are one 16-byte load
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float4 ta = __ldg(reinterpret_cast<const float4*>(w) + (c0 + 2 * p));
+                const float4 tb = __ldg(reinterpret_cast<const float4*>(w) + (c0 + 2 * p + 1));
+                wt[p][0] = f2_pack(ta.x, tb.x), wt[p][1] = f2_pack(ta.y, tb.y);
+                wt[p][2 % K] = f2_pack(ta.z, tb.z), wt[p][3 % K] = f2_pack(ta.w, tb.w);
+            }
+        } else {
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+#pragma unroll
+                for (int tap = 0; tap < K; ++tap) {
+                    wt[p][tap] = f2_pack(__ldg(w + (size_t)(c0 + 2 * p) * K + tap), __ldg(w + (size_t)(c0 + 2 * p + 1) * K + tap));
+                }
+            }
+        }
+        if (!plain) {
+            causal_conv_silu_strip_literal<T, K>(out, x, w, t0, t1, c0, channels, seq_start, history, slot_map);
+            continue;
+        }
+        f32x2 win[K][4];   // win[i] = x[t - (K-1) + i] for the current row t; win[K-1] is the row itself
 #pragma unroll
         for (int i = 0; i < K - 1; ++i) {
-            unpack8<T>(raw[i], win[i + 1]);
+            unpack8_pairs<T>(raw[i], win[i + 1]);
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -132,28 +239,28 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
 #pragma unroll
             for (int i = 0; i < K - 1; ++i) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) win[i][j] = win[i + 1][j];
+                for (int p = 0; p < 4; ++p) win[i][p] = win[i + 1][p];
             }
-            unpack8<T>(raw[r + K - 1], win[K - 1]);
-            const int lo = lo_of[r];
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            unpack8_pairs<T>(raw[r + K - 1], win[K - 1]);
+            f32x2 acc[4];
 #pragma unroll
-            for (int tap = 0; tap < K; ++tap) {
-                const int src = t - (K - 1) + tap;
-                if (src >= lo) {
+            for (int p = 0; p < 4; ++p) {
+                acc[p] = f2_fma(wt[p][0], win[0][p], f2_splat(0.0f));
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(wt[j][tap], win[tap][j], acc[j]);
-                } else if (history && src >= lo - (K - 1)) {
-                    const int slot = slot_map ? slot_map[t] : 0;
-                    float h[8];
-                    load8<T>(history + ((size_t)slot * (K - 1) + (size_t)(src - lo + (K - 1))) * channels + c0, h);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(wt[j][tap], h[j], acc[j]);
-                }
+                for (int tap = 1; tap < K; ++tap) acc[p] = f2_fma(wt[p][tap], win[tap][p], acc[p]);
             }
             float o[8];
+            if (silu_f32_fast_domain_x2<4>(acc)) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = silu_ieee_div(acc[j]);
+                for (int p = 0; p < 4; ++p) {
+                    const f32x2 q = silu_ieee_fast_f32_x2(acc[p]);
+                    o[2 * p] = q.x, o[2 * p + 1] = q.y;
+                }
+            } else {
+                const Float8 lit = silu8_literal(acc[0].x, acc[0].y, acc[1].x, acc[1].y, acc[2].x, acc[2].y, acc[3].x, acc[3].y);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = lit.v[j];
+            }
             store8<T>(out + (size_t)t * channels + c0, o);
         }
     }
@@ -171,22 +278,7 @@ causal_conv_silu_generic_kernel(typename T::storage* __restrict__ out, const typ
     for (size_t idx = (size_t)blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
         const int t = (int)(idx / channels);
         const int ch = (int)(idx - (size_t)t * channels);
-        const int lo = seq_start ? seq_start[t] : 0;
-        float acc = 0.0f;
-        for (int tap = 0; tap < k; ++tap) {
-            const int src = t - (k - 1) + tap;
-            float v;
-            if (src >= lo) {
-                v = load_scalar<T>(x + (size_t)src * channels + ch);
-            } else if (history && src >= lo - (k - 1)) {
-                const int slot = slot_map ? slot_map[t] : 0;
-                v = load_scalar<T>(history + ((size_t)slot * (k - 1) + (size_t)(src - lo + (k - 1))) * channels + ch);
-            } else {
-                continue;
-            }
-            acc = __fmaf_rn(w[(size_t)ch * k + tap], v, acc);
-        }
-        store_scalar<T>(out + idx, silu_ieee_div(acc));
+        store_scalar<T>(out + idx, causal_conv_silu_element<T>(x, w, t, ch, channels, k, seq_start, history, slot_map));
     }
 }
 

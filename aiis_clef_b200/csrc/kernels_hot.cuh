@@ -366,6 +366,43 @@ __device__ __forceinline__ f32x2 silu_ieee_fast_x2(f32x2 g2) {
     return f2_fma(rem, r2, q0);
 }
 
+// The same short form for ANY f32 g with |g| <= 44 (accumulators, not bf16 values), the sign of g copied onto
+// the quotient (d > 0, so the exact quotient has the sign of g; the short form loses the sign of a zero). Every
+// f32 pattern of that range is compared on the device by the tests: the short form differs from div.rn for
+// exactly two of them, kSiluF32Miss0 and kSiluF32Miss1, which silu_f32_fast_domain sends to the literal form.
+constexpr uint32_t kSiluF32Miss0 = 0x3E609AF2u;   // 0.21934107
+constexpr uint32_t kSiluF32Miss1 = 0x3E24A9BFu;   // 0.16080378
+__device__ __forceinline__ f32x2 silu_ieee_fast_f32_x2(f32x2 g2) {
+    const f32x2 q = silu_ieee_fast_x2(g2);
+    return make_float2(__uint_as_float((__float_as_uint(q.x) & 0x7fffffffu) | (__float_as_uint(g2.x) & 0x80000000u)),
+                       __uint_as_float((__float_as_uint(q.y) & 0x7fffffffu) | (__float_as_uint(g2.y) & 0x80000000u)));
+}
+// True when all n values may take silu_ieee_fast_f32_x2: |g| <= 44 (a NaN fails) and none of the two exceptions.
+template <int N>
+__device__ __forceinline__ bool silu_f32_fast_domain(const float* g) {
+    float m = 0.0f;
+    bool miss = false;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        m = fmaxf_nan(m, fabsf(g[i]));
+        miss |= __float_as_uint(g[i]) == kSiluF32Miss0 || __float_as_uint(g[i]) == kSiluF32Miss1;
+    }
+    return m <= kSiluFastMaxAbs && !miss;
+}
+
+template <int NP>
+__device__ __forceinline__ bool silu_f32_fast_domain_x2(const f32x2* g) {
+    float m = 0.0f;
+    bool miss = false;
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        m = max3_abs_nan(m, g[i].x, g[i].y);
+        miss |= __float_as_uint(g[i].x) == kSiluF32Miss0 || __float_as_uint(g[i].x) == kSiluF32Miss1 ||
+                __float_as_uint(g[i].y) == kSiluF32Miss0 || __float_as_uint(g[i].y) == kSiluF32Miss1;
+    }
+    return m <= kSiluFastMaxAbs && !miss;
+}
+
 // (g0, g1) -> __fdividef(g, 1 + __expf(-g)) per lane, short form for |g| <= 44: g * rcp.approx(d).
 __device__ __forceinline__ f32x2 silu_approx_fast_x2(f32x2 g2) {
     const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));

@@ -57,6 +57,8 @@ BYTES_PER_ROW = {
     "swiglu": 3 * 2 * INTER,                                                                  # 36,864
     "rms_norm_gated": 3 * 2 * HIDDEN,                                                         # 12,288
     "qk_norm_rope_q": 2 * Q_HEADS * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,                 # 8,452
+    # the head shape the reference's fused kernel serves: 16 heads x 256 with the gate half split off ([q | gate] in)
+    "qk_norm_rope_q_hd256_gate": 2 * Q_HEADS * 512 * 2 + 4 + 2 * (ROTARY // 2) * 4,           # 33,028
     # the steps either side of the fused quantisers (attention width = Q_HEADS * HEAD_DIM = HIDDEN here)
     "rope_kv_write": 4 * KV_HEADS * HEAD_DIM * 2 + 8 + 2 * (ROTARY // 2) * 4,                 # 2,312 (k, v in; both caches out)
     "qk_norm_rope_kv_write": 4 * KV_HEADS * HEAD_DIM * 2 + 8 + 2 * (ROTARY // 2) * 4,         # 2,312
@@ -226,7 +228,7 @@ def workload_config():
                     "+NVFP4; partial RoPE 16 q / 2 kv heads x 128, rotary 64, theta 1e7, cpos = 0..8191",
         "rows_per_gpu": ROWS, "hidden": HIDDEN, "intermediate": INTER, "activation_storage": "bf16",
         "l2": f"inputs larger than L2: {NSETS} rotating buffer sets of about 0.37 GB each",
-        "launch": "one CUDA graph replay per step (4 kernels)", "parallelism": "row-range replicas, no collective",
+        "launch": "one CUDA graph replay per step (3 kernels)", "parallelism": "row-range replicas, no collective",
     }
 
 
@@ -300,11 +302,14 @@ def run_gpu_arm(args):
             "q8_i": torch.empty(ROWS, INTER, dtype=torch.uint8, device="cuda"),
             "s8": torch.empty(ROWS, dtype=torch.int16, device="cuda"),
             "mixed": randn_bf16(ROWS, CONV_DIM), "conv_out": torch.empty(ROWS, CONV_DIM, dtype=torch.bfloat16, device="cuda"),
+            "qg256": randn_bf16(ROWS, Q_HEADS, 512), "q256": torch.empty(ROWS, Q_HEADS, 256, dtype=torch.bfloat16, device="cuda"),
+            "gate256": torch.empty(ROWS, Q_HEADS, 256, dtype=torch.bfloat16, device="cuda"),
         })
     w_conv = (torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5).contiguous()
     seq_start = torch.zeros(ROWS, dtype=torch.int32, device="cuda")
     cache_map = torch.randperm(ROWS, device="cuda", generator=gen).to(torch.int32)   # the engine's cpos: a slot per token
     w_head = (torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
+    w_head256 = (torch.randn(256, device="cuda", generator=gen) * 0.1).contiguous()
 
     launchers = {
         "rms_norm_quantise_nvfp4": lambda d: lib.clef_rms_norm_quantise_nvfp4(
@@ -331,6 +336,9 @@ def run_gpu_arm(args):
         "qk_norm_rope_q": lambda d: lib.clef_qk_norm_rope(stream(), p(d["q"]), p(w_head), p(cos), p(sin), p(d["h"]),
                                                           None, ROWS * Q_HEADS, Q_HEADS, HEAD_DIM, ROTARY, EPS, None,
                                                           None, p(cpos), 0),
+        "qk_norm_rope_q_hd256_gate": lambda d: lib.clef_qk_norm_rope(
+            stream(), p(d["qg256"]), p(w_head256), p(cos), p(sin), p(d["q256"]), p(d["gate256"]), ROWS * Q_HEADS, Q_HEADS, 256,
+            ROTARY, EPS, None, None, p(cpos), 0),
         "rope_kv_write": lambda d: lib.clef_rope_kv_write(
             stream(), p(d["cache_k"]), p(d["cache_v"]), p(d["k"]), p(d["v"]), p(cos), p(sin), ROWS, KV_HEADS, HEAD_DIM,
             ROTARY, None, None, p(cpos), p(cache_map), None, 0),
@@ -627,8 +635,18 @@ def run_profile_case(args):
         assert lib.clef_swiglu_quantise_fp8(st(), p(gate), p(up), p(q8_i), p(s8), ROWS, INTER, 0) == 0
         assert lib.clef_rms_norm_gated_quantise_fp8(st(), p(o), p(z), p(wg), p(q8_h), p(s8), ROWS * VH, HEAD_DIM, EPS, VH,
                                                     ROWS * VH, 0) == 0
+        # the fused RoPE launch of the step, the head_dim-256 norm + RoPE, and the causal convolution (15 per round)
+        k_out, qg, q256, g256 = torch.empty_like(k), rnd(ROWS, Q_HEADS, 512), u8(ROWS * Q_HEADS * 512), u8(ROWS * Q_HEADS * 512)
+        w256 = torch.randn(256, device="cuda", generator=gen) * 0.1
+        mixed, w_conv = rnd(ROWS, CONV_DIM), torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5
+        conv_out = torch.empty_like(mixed)
+        assert lib.clef_rope_qk(st(), p(outs[6]), p(q), Q_HEADS, p(k_out), p(k), KV_HEADS, p(cos), p(sin), ROWS, HEAD_DIM, ROTARY,
+                                None, None, p(pos), 0) == 0
+        assert lib.clef_qk_norm_rope(st(), p(qg), p(w256), p(cos), p(sin), p(q256), p(g256), ROWS * Q_HEADS, Q_HEADS, 256, ROTARY,
+                                     EPS, None, None, p(pos), 0) == 0
+        assert lib.clef_causal_conv_silu(st(), p(conv_out), p(mixed), p(w_conv), ROWS, CONV_DIM, CONV_K, None, None, None, 0) == 0
         torch.cuda.synchronize()
-    print(json.dumps({"profile_case": "ok", "rows": ROWS, "tuned_kernels_per_round": 12}))
+    print(json.dumps({"profile_case": "ok", "rows": ROWS, "tuned_kernels_per_round": 15}))
 
 
 def main():

@@ -388,6 +388,13 @@ def probe_silu_bf16():
     return _read_results(buf, 2)
 
 
+def probe_silu_f32(base: int, count: int):
+    buf = _result_buffer(2)
+    launch("ref_probe", "probe_silu_f32", (148 * 8,), (256,), [(base, ctypes.c_ulonglong), (count, ctypes.c_ulonglong), buf])
+    torch.cuda.synchronize()
+    return _read_results(buf, 2)
+
+
 def probe_sigmoid_mul_bf16():
     buf = _result_buffer(2)
     launch("ref_probe", "probe_sigmoid_mul_bf16", (256,), (256,), [buf])

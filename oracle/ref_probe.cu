@@ -216,6 +216,40 @@ extern "C" __global__ void probe_silu_bf16(ProbeResult* result) {
     }
 }
 
+// The short silu form for f32 accumulators (the causal convolution) against g / (1 + __expf(-g)) for `count` f32
+// patterns from `base`, those with |g| <= 44 only, bit for bit including the sign of zero.
+// result[0]: the short form on every such pattern (two known exceptions); result[1]: on the patterns its domain
+// check admits (the exceptions excluded): no mismatch allowed.
+extern "C" __global__ void probe_silu_f32(unsigned long long base, unsigned long long count, ProbeResult* result) {
+    unsigned long long checked = 0, admitted = 0;
+    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < count;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+        const uint32_t bits = (uint32_t)(base + i);
+        const float g = __uint_as_float(bits);
+        if (!(fabsf(g) <= clef::kSiluFastMaxAbs)) {
+            continue;
+        }
+        const float other = __uint_as_float((mix(bits) & 0x3FFFFFFFu) | (bits & 0x80000000u)) ;   // some |value| < 2
+        const float want = g / (1.0f + __expf(-g));
+        const clef::f32x2 a = clef::silu_ieee_fast_f32_x2(clef::f2_pack(g, other));
+        const clef::f32x2 b = clef::silu_ieee_fast_f32_x2(clef::f2_pack(other, g));
+        const bool ok = __float_as_uint(a.x) == __float_as_uint(want) && __float_as_uint(b.y) == __float_as_uint(want);
+        ++checked;
+        if (!ok) {
+            report(&result[0], bits);
+        }
+        const float one[1] = {g};
+        if (clef::silu_f32_fast_domain<1>(one)) {
+            ++admitted;
+            if (!ok) {
+                report(&result[1], bits);
+            }
+        }
+    }
+    atomicAdd(&result[0].checked, checked);
+    atomicAdd(&result[1].checked, admitted);
+}
+
 // The short form of x * 1.0f / (1.0f + __expf(-g)) (kernels/elementwise.cu:350-353) for every pair of a
 // bf16 g with |g| <= 44 and a finite bf16 x: 2^16 threads (one per g) each walk all x. Zero results may
 // differ in sign. result[0]: all pairs; result[1]: the pairs of the tuned kernels' domain, x == 0 or |x| >= 2^-60.

@@ -79,6 +79,30 @@ def test_causal_conv_silu(rows, channels, k, mode, choice):
     np.testing.assert_allclose(out_f.cpu().numpy(), f32, rtol=2e-6, atol=1e-30)
 
 
+def test_causal_conv_silu_accumulators_outside_the_short_silu_domain():
+    """One tap with weight 1 makes the accumulator the input itself: the two f32 values the short silu form misses,
+    values beyond |44|, infinities, NaN, zeros of both signs and subnormals must all come out as the reference
+    kernel's literal expression gives them (f32 storage, bit for bit)."""
+    rows, channels, k = 64, 64, 4
+    special = np.array([0x3E609AF2, 0x3E24A9BF, 0xBE609AF2, 0x42300000, 0x42300001, 0xC2300001, 0x42B00000, 0xC2B00000,
+                        0x7F800000, 0xFF800000, 0x7FC00000, 0x00000000, 0x80000000, 0x00000001, 0x80000001, 0x007FFFFF,
+                        0x00800000, 0x3F800000, 0xC1200000, 0x41A00000], np.uint32)
+    rng = np.random.default_rng(44)
+    xb = rng.standard_normal((rows, channels)).astype(np.float32)
+    flat = xb.reshape(-1)
+    flat[rng.choice(flat.size, special.size * 8, replace=False)] = np.tile(special, 8).view(np.float32)
+    w = np.zeros((channels, k), np.float32)
+    w[:, k - 1] = 1.0
+    dx, dw = torch.from_numpy(xb).cuda(), torch.from_numpy(w).cuda()
+    seq_start = i32(np.arange(rows))                 # every row starts a sequence: only the last tap is live
+    ref = ref_gpu.causal_conv_silu(dx, dw, rows, channels, k, seq_start, None, None)
+    for choice in (0, 1):
+        clef.set_kernel_choice(choice)
+        got = clef.Device(0).causal_conv_silu_dev(dx, dw, rows, channels, k, seq_start, None, None)
+        torch.cuda.synchronize()
+        assert torch.equal(got.view(torch.int32), ref.view(torch.int32)), choice
+
+
 def test_causal_conv_silu_with_pass_maps_and_history_round_trip():
     """Two passes over the same requests: the first pass saves each request's last k - 1 rows as its history
     (hist_save of the pass maps), the second continues the requests; a request continued this way must equal the
