@@ -18,6 +18,16 @@ namespace {
 template <typename T>
 void launch_conv(cudaStream_t s, const DeviceInfo& dev, void* out, const void* x, const float* w, int rows, int channels,
                  int k, const int32_t* seq_start, const void* history, const int32_t* slot_map) {
+    if (k == 4 && channels % 8 == 0 && use_hot() && T::kBytes == 2) {   // bf16: 4 channels per thread, three CTAs per SM (measured)
+        static std::atomic<int> occ{0};
+        auto kernel = causal_conv_silu_c4_kernel<4, 8, 3>;
+        const int per_sm = ctas_per_sm(kernel, 0, occ);
+        const size_t items = (size_t)((rows + 7) / 8) * (channels / 4);
+        launch_hot(kernel, clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0, s, (uint16_t*)out,
+                   (const uint16_t*)x, w, rows, channels, (const int*)seq_start, (const uint16_t*)history,
+                   (const int*)slot_map, make_fast_div((uint32_t)(channels / 4)));
+        return;
+    }
     if (k == 4 && channels % 8 == 0 && use_hot()) {
         constexpr int kRows = T::kBytes == 2 ? 8 : 4;   // rows per thread: 11 (bf16) or 7 (f32) 16/32-byte loads in flight
         static std::atomic<int> occ{0};

@@ -165,7 +165,8 @@ __device__ __forceinline__ void unpack8_pairs<F32>(const Raw8<F32>& r, f32x2* v)
 
 // A strip none of whose rows has a tap before its sequence start (all but the strips that hold a sequence start or
 // the first K - 1 rows) runs without per-tap tests, two channels per packed multiply-add, the silu in its short
-// exact form (silu_ieee_fast_f32_x2); the other strips take the literal element path.
+// exact form (silu_ieee_refined_f32_x2); the other strips take the literal path. Used for f32 storage; bf16 storage takes
+// the 4-channel kernel below.
 // Two CTAs per SM (128 registers) measured best: one CTA (145 registers) or three and four (spills) are 20 to 60 %
 // slower, and so was keeping the next strip's loads in flight during the arithmetic (159 registers).
 template <typename T, int K, int R>
@@ -250,10 +251,10 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
                 for (int tap = 1; tap < K; ++tap) acc[p] = f2_fma(wt[p][tap], win[tap][p], acc[p]);
             }
             float o[8];
-            if (silu_f32_fast_domain_x2<4>(acc)) {
+            if (silu_f32_magnitude_domain_x2<4>(acc)) {
 #pragma unroll
                 for (int p = 0; p < 4; ++p) {
-                    const f32x2 q = silu_ieee_fast_f32_x2(acc[p]);
+                    const f32x2 q = silu_ieee_refined_f32_x2(acc[p]);
                     o[2 * p] = q.x, o[2 * p + 1] = q.y;
                 }
             } else {
@@ -262,6 +263,96 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
                 for (int j = 0; j < 8; ++j) o[j] = lit.v[j];
             }
             store8<T>(out + (size_t)t * channels + c0, o);
+        }
+    }
+}
+
+// bf16 storage, 4 channels per thread (8-byte loads and stores): half the registers of the 8-channel form, so more
+// warps are resident to overlap one thread's load phase with another's arithmetic. A strip that lies inside the
+// matrix with its halo and has no tap before a sequence start runs without any per-row or per-tap test; every
+// other strip (the first, a ragged last one, one holding a sequence start) takes the literal path. The arithmetic
+// is scalar on purpose: packed multiply-adds cost more register-pair moves here than they save (measured: 105
+// against 99 instructions per row of 4 values).
+template <int K, int R, int MIN_CTAS>
+__global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
+causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, const float* __restrict__ w, int rows,
+                           int channels, const int* __restrict__ seq_start, const uint16_t* __restrict__ history,
+                           const int* __restrict__ slot_map, FastDiv cvecs_div) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const uint32_t cvecs = cvecs_div.d;   // channels / 4
+    const uint32_t strips = ((uint32_t)rows + R - 1) / R;
+    const uint32_t total = strips * cvecs;
+    const uint32_t step = gridDim.x * kCtaThreads;
+    const bool starts_vector = R == 8 && (reinterpret_cast<uintptr_t>(seq_start) & 15) == 0;
+    for (uint32_t idx = blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
+        const uint32_t strip = fast_div(idx, cvecs_div);
+        const int c0 = (int)(idx - strip * cvecs) * 4;
+        const int t0 = (int)strip * R;
+        bool plain = t0 >= K - 1 && t0 + R <= rows;   // every row of the strip and of its halo exists
+        uint2 raw[R + K - 1];
+        float wt[4][K];
+        if (plain) {
+            const uint16_t* base = x + (size_t)(t0 - (K - 1)) * channels + c0;
+#pragma unroll
+            for (int i = 0; i < R + K - 1; ++i) raw[i] = ldg_stream_v2(base + (size_t)i * channels);
+            if (K == 4) {   // a channel's four taps are one 16-byte load
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 t4 = __ldg(reinterpret_cast<const float4*>(w) + (c0 + j));
+                    wt[j][0] = t4.x, wt[j][1] = t4.y, wt[j][2 % K] = t4.z, wt[j][3 % K] = t4.w;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                    for (int tap = 0; tap < K; ++tap) wt[j][tap] = __ldg(w + (size_t)(c0 + j) * K + tap);
+                }
+            }
+            if (seq_start) {
+                const int lim = t0 - (K - 1);
+                if (starts_vector) {   // the 8 sequence starts as two 16-byte loads
+                    const int4 a = __ldg(reinterpret_cast<const int4*>(seq_start + t0));
+                    const int4 b = __ldg(reinterpret_cast<const int4*>(seq_start + t0) + 1);
+                    plain = a.x <= lim && a.y <= lim + 1 && a.z <= lim + 2 && a.w <= lim + 3 && b.x <= lim + 4 &&
+                            b.y <= lim + 5 && b.z <= lim + 6 && b.w <= lim + 7;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < R; ++r) plain &= __ldg(seq_start + t0 + r) <= lim + r;
+                }
+            }
+        }
+        if (!plain) {
+            if ((c0 & 4) == 0) {   // the literal path works on 8 channels: the even thread of a pair does both halves
+                causal_conv_silu_strip_literal<Bf16, K>(out, x, w, t0, min(t0 + R, rows), c0, channels, seq_start, history, slot_map);
+            }
+            continue;
+        }
+        float xs[R + K - 1][4];   // every row of the strip widened once; row r reads xs[r .. r + K - 1]
+#pragma unroll
+        for (int i = 0; i < R + K - 1; ++i) {
+            xs[i][0] = bf16_lo(raw[i].x), xs[i][1] = bf16_hi(raw[i].x), xs[i][2] = bf16_lo(raw[i].y), xs[i][3] = bf16_hi(raw[i].y);
+        }
+        uint16_t* orow = out + (size_t)t0 * channels + c0;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float a4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                a4[j] = 0.0f;
+#pragma unroll
+                for (int tap = 0; tap < K; ++tap) a4[j] = __fmaf_rn(wt[j][tap], xs[r + tap][j], a4[j]);
+            }
+            const float m = fmaxf_nan(max3_abs_nan(fabsf(a4[0]), a4[1], a4[2]), fabsf(a4[3]));
+            float o4[4];
+            if (m <= kSiluFastMaxAbs) {   // false for a NaN too
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o4[j] = silu_ieee_refined_f32(a4[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o4[j] = silu_ieee_div(a4[j]);
+            }
+            stg_v2(orow + (size_t)r * channels, make_uint2(pack_bf16x2(o4[0], o4[1]), pack_bf16x2(o4[2], o4[3])));
         }
     }
 }

@@ -366,43 +366,40 @@ __device__ __forceinline__ f32x2 silu_ieee_fast_x2(f32x2 g2) {
     return f2_fma(rem, r2, q0);
 }
 
-// The same short form for ANY f32 g with |g| <= 44 (accumulators, not bf16 values), the sign of g copied onto
-// the quotient (d > 0, so the exact quotient has the sign of g; the short form loses the sign of a zero). Every
-// f32 pattern of that range is compared on the device by the tests: the short form differs from div.rn for
-// exactly two of them, kSiluF32Miss0 and kSiluF32Miss1, which silu_f32_fast_domain sends to the literal form.
-constexpr uint32_t kSiluF32Miss0 = 0x3E609AF2u;   // 0.21934107
-constexpr uint32_t kSiluF32Miss1 = 0x3E24A9BFu;   // 0.16080378
-__device__ __forceinline__ f32x2 silu_ieee_fast_f32_x2(f32x2 g2) {
-    const f32x2 q = silu_ieee_fast_x2(g2);
+// silu for ANY f32 g with |g| <= 44 (accumulators, not bf16 values): the short form above misses div.rn by one ulp
+// for two f32 patterns (0x3E609AF2, 0x3E24A9BF), so the reciprocal takes one Newton step first; after it the
+// quotient equals div.rn for EVERY f32 g of the range (all patterns are compared on the device by the tests).
+// The sign of g is copied onto the result: d > 0, so the exact quotient has the sign of g, and the short form
+// loses the sign of a zero.
+__device__ __forceinline__ f32x2 silu_ieee_refined_f32_x2(f32x2 g2) {
+    // Steps with a constant or a negated operand stay scalar (immediates and operand negation are free there; a
+    // packed operation would need the constant moved into a register pair); the others are packed.
+    const float dx = __fadd_rn(1.0f, ex2_approx(__fmul_rn(g2.x, kNegLog2e)));
+    const float dy = __fadd_rn(1.0f, ex2_approx(__fmul_rn(g2.y, kNegLog2e)));
+    const float rx = rcp_approx(dx), ry = rcp_approx(dy);
+    const f32x2 r0 = make_float2(rx, ry);
+    const f32x2 r2 = f2_fma(make_float2(__fmaf_rn(-dx, rx, 1.0f), __fmaf_rn(-dy, ry, 1.0f)), r0, r0);
+    const f32x2 q0 = f2_mul(g2, r2);
+    const f32x2 q = f2_fma(make_float2(__fmaf_rn(-dx, q0.x, g2.x), __fmaf_rn(-dy, q0.y, g2.y)), r2, q0);
     return make_float2(__uint_as_float((__float_as_uint(q.x) & 0x7fffffffu) | (__float_as_uint(g2.x) & 0x80000000u)),
                        __uint_as_float((__float_as_uint(q.y) & 0x7fffffffu) | (__float_as_uint(g2.y) & 0x80000000u)));
 }
-// True when all n values may take silu_ieee_fast_f32_x2: |g| <= 44 (a NaN fails) and none of the two exceptions.
-template <int N>
-__device__ __forceinline__ bool silu_f32_fast_domain(const float* g) {
-    float m = 0.0f;
-    bool miss = false;
-#pragma unroll
-    for (int i = 0; i < N; ++i) {
-        m = fmaxf_nan(m, fabsf(g[i]));
-        miss |= __float_as_uint(g[i]) == kSiluF32Miss0 || __float_as_uint(g[i]) == kSiluF32Miss1;
-    }
-    return m <= kSiluFastMaxAbs && !miss;
+// The same quotient, one value, all scalar (no register pairs to form).
+__device__ __forceinline__ float silu_ieee_refined_f32(float g) {
+    const float d = __fadd_rn(1.0f, ex2_approx(__fmul_rn(g, kNegLog2e)));
+    float r = rcp_approx(d);
+    r = __fmaf_rn(__fmaf_rn(-d, r, 1.0f), r, r);
+    const float q0 = __fmul_rn(g, r);
+    const float q = __fmaf_rn(__fmaf_rn(-d, q0, g), r, q0);
+    return __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(g) & 0x80000000u));
 }
-
 template <int NP>
-__device__ __forceinline__ bool silu_f32_fast_domain_x2(const f32x2* g) {
+__device__ __forceinline__ bool silu_f32_magnitude_domain_x2(const f32x2* g) {
     float m = 0.0f;
-    bool miss = false;
 #pragma unroll
-    for (int i = 0; i < NP; ++i) {
-        m = max3_abs_nan(m, g[i].x, g[i].y);
-        miss |= __float_as_uint(g[i].x) == kSiluF32Miss0 || __float_as_uint(g[i].x) == kSiluF32Miss1 ||
-                __float_as_uint(g[i].y) == kSiluF32Miss0 || __float_as_uint(g[i].y) == kSiluF32Miss1;
-    }
-    return m <= kSiluFastMaxAbs && !miss;
+    for (int i = 0; i < NP; ++i) m = max3_abs_nan(m, g[i].x, g[i].y);
+    return m <= kSiluFastMaxAbs;   // false for a NaN
 }
-
 // (g0, g1) -> __fdividef(g, 1 + __expf(-g)) per lane, short form for |g| <= 44: g * rcp.approx(d).
 __device__ __forceinline__ f32x2 silu_approx_fast_x2(f32x2 g2) {
     const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));

@@ -389,6 +389,7 @@ def probe_silu_bf16():
 
 
 def probe_silu_f32(base: int, count: int):
+    """[packed, scalar] short silu of f32 accumulators against the literal expression."""
     buf = _result_buffer(2)
     launch("ref_probe", "probe_silu_f32", (148 * 8,), (256,), [(base, ctypes.c_ulonglong), (count, ctypes.c_ulonglong), buf])
     torch.cuda.synchronize()

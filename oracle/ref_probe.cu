@@ -216,12 +216,11 @@ extern "C" __global__ void probe_silu_bf16(ProbeResult* result) {
     }
 }
 
-// The short silu form for f32 accumulators (the causal convolution) against g / (1 + __expf(-g)) for `count` f32
+// The short silu forms for f32 accumulators (the causal convolution) against g / (1 + __expf(-g)) for `count` f32
 // patterns from `base`, those with |g| <= 44 only, bit for bit including the sign of zero.
-// result[0]: the short form on every such pattern (two known exceptions); result[1]: on the patterns its domain
-// check admits (the exceptions excluded): no mismatch allowed.
+// result[0]: silu_ieee_refined_f32_x2 in both lanes; result[1]: silu_ieee_refined_f32. No mismatch allowed.
 extern "C" __global__ void probe_silu_f32(unsigned long long base, unsigned long long count, ProbeResult* result) {
-    unsigned long long checked = 0, admitted = 0;
+    unsigned long long checked = 0;
     for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < count;
          i += (unsigned long long)gridDim.x * blockDim.x) {
         const uint32_t bits = (uint32_t)(base + i);
@@ -229,25 +228,20 @@ extern "C" __global__ void probe_silu_f32(unsigned long long base, unsigned long
         if (!(fabsf(g) <= clef::kSiluFastMaxAbs)) {
             continue;
         }
-        const float other = __uint_as_float((mix(bits) & 0x3FFFFFFFu) | (bits & 0x80000000u)) ;   // some |value| < 2
+        const float other = __uint_as_float((mix(bits) & 0x3FFFFFFFu) | (bits & 0x80000000u));   // some |value| < 2
         const float want = g / (1.0f + __expf(-g));
-        const clef::f32x2 a = clef::silu_ieee_fast_f32_x2(clef::f2_pack(g, other));
-        const clef::f32x2 b = clef::silu_ieee_fast_f32_x2(clef::f2_pack(other, g));
-        const bool ok = __float_as_uint(a.x) == __float_as_uint(want) && __float_as_uint(b.y) == __float_as_uint(want);
+        const clef::f32x2 a = clef::silu_ieee_refined_f32_x2(clef::f2_pack(g, other));
+        const clef::f32x2 b = clef::silu_ieee_refined_f32_x2(clef::f2_pack(other, g));
         ++checked;
-        if (!ok) {
+        if (__float_as_uint(a.x) != __float_as_uint(want) || __float_as_uint(b.y) != __float_as_uint(want)) {
             report(&result[0], bits);
         }
-        const float one[1] = {g};
-        if (clef::silu_f32_fast_domain<1>(one)) {
-            ++admitted;
-            if (!ok) {
-                report(&result[1], bits);
-            }
+        if (__float_as_uint(clef::silu_ieee_refined_f32(g)) != __float_as_uint(want)) {
+            report(&result[1], bits);
         }
     }
     atomicAdd(&result[0].checked, checked);
-    atomicAdd(&result[1].checked, admitted);
+    atomicAdd(&result[1].checked, checked);
 }
 
 // The short form of x * 1.0f / (1.0f + __expf(-g)) (kernels/elementwise.cu:350-353) for every pair of a

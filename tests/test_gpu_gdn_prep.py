@@ -103,6 +103,26 @@ def test_causal_conv_silu_accumulators_outside_the_short_silu_domain():
         assert torch.equal(got.view(torch.int32), ref.view(torch.int32)), choice
 
 
+@pytest.mark.parametrize("offset", [0, 1, 2])
+def test_causal_conv_silu_sequence_starts_at_any_alignment(offset):
+    """The tuned kernel reads the 8 sequence starts of a strip as two 16-byte loads when the array allows it: the
+    same map at a 16-byte aligned address and 4 and 8 bytes off it, many short sequences, ragged row count."""
+    rows, channels, k = 1003, 256, 4
+    rng = np.random.default_rng(9 + offset)
+    xb = normal_bf16(rng, (rows, channels))
+    w = (rng.standard_normal((channels, k)) * 0.5).astype(np.float32)
+    seq_start, slot_map = packed_sequences(rng, rows, 37)
+    hist = normal_bf16(rng, (37, k - 1, channels))
+    holder = torch.zeros(rows + 8, dtype=torch.int32, device="cuda")
+    d_ss = holder[offset:offset + rows]
+    d_ss.copy_(i32(seq_start))
+    dw, d_sm = torch.from_numpy(w).cuda(), i32(slot_map)
+    ref = ref_gpu.causal_conv_silu(dev_f32_from_bits(xb), dw, rows, channels, k, d_ss.clone(), dev_f32_from_bits(hist), d_sm)
+    got = clef.Device(0).causal_conv_silu_dev(dev_bf16(xb), dw, rows, channels, k, d_ss, dev_bf16(hist), d_sm)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(got), bits(ref.to(torch.bfloat16)))
+
+
 def test_causal_conv_silu_with_pass_maps_and_history_round_trip():
     """Two passes over the same requests: the first pass saves each request's last k - 1 rows as its history
     (hist_save of the pass maps), the second continues the requests; a request continued this way must equal the
