@@ -155,6 +155,41 @@ int clef_gdn_gates(clef_stream_t stream, const void* a, const void* b, const flo
     return check_launch(what);
 }
 
+int clef_gdn_prep(clef_stream_t stream, const void* mixed, float* v_out, void* q_hi, void* q_lo, void* k_hi, void* k_lo,
+                  float* kn, int seq_len, int heads, int kh, int kd, int conv_dim, float q_scale, int dtype) {
+    const char* what = "clef_gdn_prep";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!mixed || !v_out || !q_hi || !q_lo || !k_hi || !k_lo || !kn) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (seq_len < 0 || heads <= 0 || kh <= 0 || heads % kh != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: seq_len %d heads %d kh %d (heads must be a multiple of kh)", what, seq_len, heads, kh);
+    }
+    if (kd != kGdnKd) return fail(CLEF_ERR_INVALID, "%s: kd %d (the scan's operand layout is built for 128)", what, kd);
+    if ((long long)conv_dim < 2LL * kh * kd + (long long)heads * kd || conv_dim % 8 != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: conv_dim %d must hold q, k (kh x kd each) and v (heads x kd) and be a multiple of 8",
+                    what, conv_dim);
+    }
+    if (!aligned(mixed, 16) || !aligned(v_out, 16) || !aligned(q_hi, 16) || !aligned(q_lo, 16) || !aligned(k_hi, 16) ||
+        !aligned(k_lo, 16) || !aligned(kn, 16)) {
+        return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
+    }
+    if (seq_len == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    const int nchunks = (seq_len + kGdnChunk - 1) / kGdnChunk;
+    const size_t warps = (size_t)nchunks * kGdnChunk * kh + (size_t)seq_len * heads;
+    const unsigned grid = clamp_grid((warps + kCtaThreads / 32 - 1) / (kCtaThreads / 32), (size_t)dev.sms * 8);
+    if (dtype == CLEF_BF16) {
+        gdn_prep_kernel<Bf16><<<grid, kCtaThreads, 0, as_stream(stream)>>>(
+            (const uint16_t*)mixed, v_out, (uint8_t*)q_hi, (uint8_t*)q_lo, (uint8_t*)k_hi, (uint8_t*)k_lo, kn, seq_len, heads, kh,
+            nchunks, conv_dim, q_scale);
+    } else {
+        gdn_prep_kernel<F32><<<grid, kCtaThreads, 0, as_stream(stream)>>>(
+            (const float*)mixed, v_out, (uint8_t*)q_hi, (uint8_t*)q_lo, (uint8_t*)k_hi, (uint8_t*)k_lo, kn, seq_len, heads, kh,
+            nchunks, conv_dim, q_scale);
+    }
+    return check_launch(what);
+}
+
 int clef_split_q_gate(clef_stream_t stream, const void* qg, void* q, void* gate, int tokens, int heads, int head_dim,
                       int dtype) {
     const char* what = "clef_split_q_gate";

@@ -398,6 +398,109 @@ conv_hist_save_kernel(const typename T::storage* __restrict__ src, typename T::s
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// gdn_prep (kernels/gdn_chunk.cu:1176-1239): the convolved row [q | k | v] of a token becomes the operands of the
+// chunked GDN scan. Every q and k head (kd = 128) is L2-normalised, rsqrtf(sum of squares + 1e-6), q additionally
+// scaled by q_scale; the sum is the reference's: lane l adds p = l, l + 32, l + 64, l + 96 in order by fused
+// multiply-add, then the xor tree 16 .. 1. Each value v is stored as the bf16 pair hi = rn(v), lo = rn(v - hi) in
+// the scan's layout: per (expanded head, 64-token chunk) two 64-column tiles of 64 rows x 128 bytes, the 16-byte
+// segment index xor-ed with row % 8 (kernels/gdn_chunk.cu:35-40); k heads are repeated heads / kh times
+// (repeat_interleave), normalised k also goes out as f32 (kn), v is copied as f32. One warp per (token, k head).
+// Rows of the last chunk past seq_len are written as zeros, so the caller need not clear the hi / lo buffers
+// (the reference allocates them zeroed, src/cuda/mod.rs:3615-3618).
+// ---------------------------------------------------------------------------------------------
+constexpr int kGdnChunk = 64, kGdnKd = 128, kGdnTileCols = 64, kGdnRowBytes = 128;
+
+__device__ __forceinline__ size_t gdn_operand_offset(size_t chunk_index, int row_in_chunk, int p) {
+    const int tile = p / kGdnTileCols, c = p - tile * kGdnTileCols;
+    const int seg = c >> 3, e = c & 7;
+    return (chunk_index * (kGdnKd / kGdnTileCols) + tile) * (size_t)(kGdnChunk * kGdnRowBytes) +
+           (size_t)row_in_chunk * kGdnRowBytes + (size_t)((seg ^ (row_in_chunk & 7)) * 16 + e * 2);
+}
+
+__device__ __forceinline__ void store_bf16_hi_lo(float v, uint8_t* hi, uint8_t* lo, size_t off) {
+    const uint32_t h = pack_bf16x2(v, 0.0f) & 0xffffu;
+    *reinterpret_cast<uint16_t*>(hi + off) = (uint16_t)h;
+    *reinterpret_cast<uint16_t*>(lo + off) = (uint16_t)(pack_bf16x2(__fsub_rn(v, __uint_as_float(h << 16)), 0.0f) & 0xffffu);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads)
+gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict__ v_out, uint8_t* __restrict__ q_hi,
+                uint8_t* __restrict__ q_lo, uint8_t* __restrict__ k_hi, uint8_t* __restrict__ k_lo, float* __restrict__ kn,
+                int seq_len, int heads, int kh, int nchunks, int conv_dim, float q_scale) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp0 = ((size_t)blockIdx.x * kCtaThreads + threadIdx.x) >> 5;
+    const size_t warps = (size_t)gridDim.x * (kCtaThreads / 32);
+    const int ratio = heads / kh;
+    const size_t head_items = (size_t)nchunks * kGdnChunk * kh;   // pad rows of the last chunk included
+    const size_t v_items = (size_t)seq_len * heads;               // 128 values each
+    for (size_t item = warp0; item < head_items + v_items; item += warps) {
+        if (item >= head_items) {   // a 128-value piece of v: 4 values per lane, f32 out
+            const size_t j = item - head_items;
+            const size_t t = j / heads;
+            const int hh = (int)(j - t * heads);
+            const typename T::storage* src = mixed + t * conv_dim + (size_t)2 * kh * kGdnKd + (size_t)hh * kGdnKd + lane * 4;
+            float4 v;
+            if (T::kBytes == 2) {
+                const uint2 raw = ldg_stream_v2(src);
+                v = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+            } else {
+                const uint4 raw = ldg_stream_v4(src);
+                v = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+            }
+            *reinterpret_cast<float4*>(v_out + (t * heads + hh) * kGdnKd + lane * 4) = v;
+            continue;
+        }
+        const size_t t = item / kh;
+        const int h = (int)(item - t * kh);
+        const bool live = t < (size_t)seq_len;
+        float q[4] = {0.f, 0.f, 0.f, 0.f}, k[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            const typename T::storage* qr = mixed + t * conv_dim + (size_t)h * kGdnKd;
+            const typename T::storage* kr = qr + (size_t)kh * kGdnKd;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                q[i] = load_scalar<T>(qr + lane + 32 * i);
+                k[i] = load_scalar<T>(kr + lane + 32 * i);
+            }
+        }
+        float sq = 0.0f, sk = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            sq = __fmaf_rn(q[i], q[i], sq);
+            sk = __fmaf_rn(k[i], k[i], sk);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            sq = __fadd_rn(sq, __shfl_xor_sync(kFullMask, sq, off));
+            sk = __fadd_rn(sk, __shfl_xor_sync(kFullMask, sk, off));
+        }
+        const float rq = __fmul_rn(rsqrtf(__fadd_rn(sq, 1e-6f)), q_scale);
+        const float rk = rsqrtf(__fadd_rn(sk, 1e-6f));
+        const size_t chunk = t / kGdnChunk;
+        const int r = (int)(t - chunk * kGdnChunk);
+        for (int rep = 0; rep < ratio; ++rep) {
+            const int he = h * ratio + rep;
+            const size_t idx = (size_t)he * nchunks + chunk;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int p = lane + 32 * i;
+                const size_t off = gdn_operand_offset(idx, r, p);
+                if (live) {
+                    const float kv = __fmul_rn(k[i], rk);
+                    store_bf16_hi_lo(__fmul_rn(q[i], rq), q_hi, q_lo, off);
+                    store_bf16_hi_lo(kv, k_hi, k_lo, off);
+                    kn[(t * heads + he) * kGdnKd + p] = kv;
+                } else {
+                    *reinterpret_cast<uint16_t*>(q_hi + off) = 0, *reinterpret_cast<uint16_t*>(q_lo + off) = 0;
+                    *reinterpret_cast<uint16_t*>(k_hi + off) = 0, *reinterpret_cast<uint16_t*>(k_lo + off) = 0;
+                }
+            }
+        }
+    }
+}
+
 // gdn_gates (kernels/elementwise.cu:361-377): beta = 1 / (1 + __expf(-b)); decay = -__expf(a_log[h]) * softplus(a + dt_bias[h])
 // with softplus(x) = x above 20 and log1pf(__expf(x)) otherwise. Outputs are f32.
 template <typename T>

@@ -64,6 +64,7 @@ SYMBOLS = {
     "clef_causal_conv_silu": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I]),
     "clef_conv_hist_save": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I]),
     "clef_gdn_gates": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I]),
+    "clef_gdn_prep": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I]),
     "clef_split_q_gate": (_I, [_P, _P, _P, _P, _I, _I, _I, _I]),
     "clef_split_qkv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "clef_repeat_interleave": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
@@ -479,6 +480,23 @@ class Device:
         with torch.cuda.device(self.device):
             _check(self.lib.clef_conv_hist_save(_stream(), _ptr(hist), _ptr(src), _ptr(saves), n_saves, rows, k, channels,
                                                 _dtype_code(src)), "clef_conv_hist_save")
+
+    # -- src/cuda/mod.rs:3606-3647 ------------------------------------------------------------
+    def gdn_prep_dev(self, mixed, seq_len: int, kh: int, kd: int, heads: int, conv_dim: int):
+        """-> dict(v, q_hi, q_lo, k_hi, k_lo, kn): the chunked scan's operands of the convolved rows; q_scale is
+        1 / sqrt(kd) as in the reference launcher."""
+        _dev_tensor(mixed, "mixed")
+        nchunks = (seq_len + 63) // 64
+        nbytes = heads * nchunks * 2 * 64 * 128
+        out = {"v": self._empty((seq_len, heads * kd), torch.float32), "kn": self._empty((seq_len, heads, kd), torch.float32)}
+        for name in ("q_hi", "q_lo", "k_hi", "k_lo"):
+            out[name] = self._empty((nbytes,), torch.uint8)
+        q_scale = float(_np.float32(1.0) / _np.sqrt(_np.float32(kd)))
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_gdn_prep(_stream(), _ptr(mixed), _ptr(out["v"]), _ptr(out["q_hi"]), _ptr(out["q_lo"]),
+                                          _ptr(out["k_hi"]), _ptr(out["k_lo"]), _ptr(out["kn"]), seq_len, heads, kh, kd, conv_dim,
+                                          q_scale, _dtype_code(mixed)), "clef_gdn_prep")
+        return out
 
     # -- src/cuda/mod.rs:2858-2882 ------------------------------------------------------------
     def gdn_gates_dev(self, a, b, a_log, dt_bias, tokens: int, heads: int):

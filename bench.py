@@ -73,6 +73,9 @@ BYTES_PER_ROW = {
     "rms_norm_gated_quantise_fp8": 2 * 2 * HIDDEN + HIDDEN + 2,                               # 10,242
     # in front of the GDN scan: causal convolution (4 taps) + silu over the 8,192 mixed q/k/v channels
     "causal_conv_silu": 2 * 2 * CONV_DIM + 4,                                                 # 32,772
+    # the scan's operands from the convolved row (16 q/k heads, 32 v heads of 128): bf16 row in; q and k as bf16
+    # hi + lo pairs for 32 expanded heads, normalised k and v as f32 out
+    "gdn_prep": 2 * CONV_DIM + 4 * 32 * 128 * 2 + 2 * 32 * 128 * 4,                           # 81,920
 }
 # The step: RMSNorm+NVFP4, SwiGLU+NVFP4, and the partial RoPE of the q and the k heads, which share their positions
 # and go out as one launch (clef_rope_qk); rope_q / rope_k alone are reported under "kernels".
@@ -306,6 +309,10 @@ def run_gpu_arm(args):
             "gate256": torch.empty(ROWS, Q_HEADS, 256, dtype=torch.bfloat16, device="cuda"),
         })
     w_conv = (torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5).contiguous()
+    gdn_bytes = 32 * ((ROWS + 63) // 64) * 2 * 64 * 128     # one set of operand buffers (0.5 GB of outputs, far above L2)
+    gdn_ops = [torch.empty(gdn_bytes, dtype=torch.uint8, device="cuda") for _ in range(4)]
+    gdn_kn = torch.empty(ROWS, 32 * 128, dtype=torch.float32, device="cuda")
+    gdn_v = torch.empty(ROWS, 32 * 128, dtype=torch.float32, device="cuda")
     seq_start = torch.zeros(ROWS, dtype=torch.int32, device="cuda")
     cache_map = torch.randperm(ROWS, device="cuda", generator=gen).to(torch.int32)   # the engine's cpos: a slot per token
     w_head = (torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
@@ -360,6 +367,8 @@ def run_gpu_arm(args):
                                                                       p(d["s8"]), ROWS, INTER, 0),
         "rms_norm_gated_quantise_fp8": lambda d: lib.clef_rms_norm_gated_quantise_fp8(
             stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["q8_h"]), p(d["s8"]), ROWS * VH, HEAD_DIM, EPS, VH, ROWS * VH, 0),
+        "gdn_prep": lambda d: lib.clef_gdn_prep(stream(), p(d["mixed"]), p(gdn_v), p(gdn_ops[0]), p(gdn_ops[1]), p(gdn_ops[2]),
+                                                p(gdn_ops[3]), p(gdn_kn), ROWS, 32, 16, 128, CONV_DIM, 128 ** -0.5, 0),
         "causal_conv_silu": lambda d: lib.clef_causal_conv_silu(stream(), p(d["conv_out"]), p(d["mixed"]), p(w_conv), ROWS,
                                                                 CONV_DIM, CONV_K, p(seq_start), None, None, 0),
     }

@@ -273,6 +273,15 @@ int clef_causal_conv_silu(clef_stream_t stream, void* out, const void* x, const 
 int clef_conv_hist_save(clef_stream_t stream, void* hist, const void* src, const int32_t* saves, int n_saves, int rows,
                         int k, int channels, int dtype);
 
+/* gdn_prep_kernel (kernels/gdn_chunk.cu:1176-1239), Device::gdn_prep_dev (src/cuda/mod.rs:3606-3647): the convolved
+ * row [q (kh x kd) | k (kh x kd) | v (heads x kd)] of each of seq_len tokens (row stride conv_dim) becomes the chunked
+ * scan's operands: q and k heads L2-normalised (q times q_scale), each value split into a bf16 pair hi + lo and stored
+ * in the scan's swizzled layout, heads * ceil(seq_len / 64) * 2 * 64 * 128 bytes per buffer, k heads repeated
+ * heads / kh times; kn = normalised k as f32 [seq_len, heads, kd]; v_out = v as f32 [seq_len, heads * kd]. kd must be
+ * 128. Rows of the last chunk past seq_len are written as zeros (the reference allocates the buffers zeroed). */
+int clef_gdn_prep(clef_stream_t stream, const void* mixed, float* v_out, void* q_hi, void* q_lo, void* k_hi, void* k_lo,
+                  float* kn, int seq_len, int heads, int kh, int kd, int conv_dim, float q_scale, int dtype);
+
 /* gdn_gates_kernel (kernels/elementwise.cu:361-377), Device::gdn_gates_dev (src/cuda/mod.rs:2858-2882):
  * beta = sigmoid(b), decay = -exp(a_log[h]) * softplus(a + dt_bias[h]) for a, b [tokens, heads]; outputs are f32. */
 int clef_gdn_gates(clef_stream_t stream, const void* a, const void* b, const float* a_log, const float* dt_bias,

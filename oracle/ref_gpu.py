@@ -20,7 +20,7 @@ _functions: dict[tuple[str, str], object] = {}
 
 
 def available() -> bool:
-    return all((_DIR / f"{n}.cubin").exists() for n in ("elementwise", "quantise", "ref_probe", "head", "to_bf16"))
+    return all((_DIR / f"{n}.cubin").exists() for n in ("elementwise", "quantise", "ref_probe", "head", "to_bf16", "gdn_prep"))
 
 
 def _cu():
@@ -144,6 +144,24 @@ def gdn_gates(a, b, a_log, dt_bias, tokens, heads):
     beta = torch.empty(tokens * heads, dtype=torch.float32, device=a.device)
     launch("elementwise", "gdn_gates_kernel", ((tokens * heads + 255) // 256,), (256,), [a, b, a_log, dt_bias, decay, beta, tokens, heads])
     return decay.view(tokens, heads), beta.view(tokens, heads)
+
+
+def gdn_prep(mixed, seq_len, kh, kd, heads, conv_dim):
+    """src/cuda/mod.rs:3606-3647: gdn_prep_kernel of kernels/gdn_chunk.cu, one block per token, zeroed operand buffers."""
+    nchunks = (seq_len + 63) // 64
+    nbytes = heads * nchunks * 2 * 64 * 128
+    dev = mixed.device
+    out = {"v": torch.empty(seq_len * heads * kd, dtype=torch.float32, device=dev),
+           "kn": torch.zeros(seq_len * heads * kd, dtype=torch.float32, device=dev)}
+    for name in ("q_hi", "q_lo", "k_hi", "k_lo"):
+        out[name] = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    import numpy as np
+
+    q_scale = float(np.float32(1.0) / np.sqrt(np.float32(kd)))
+    launch("gdn_prep", "gdn_prep_kernel", (seq_len,), (256,),
+           [mixed, out["v"], out["q_hi"], out["q_lo"], out["k_hi"], out["k_lo"], out["kn"], seq_len, heads, kh, kd, nchunks,
+            conv_dim, q_scale])
+    return out
 
 
 def split_q_gate(qg, tokens, heads, head_dim):

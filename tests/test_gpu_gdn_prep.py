@@ -179,6 +179,61 @@ def test_gdn_gates(tokens, heads):
     np.testing.assert_allclose(beta.cpu().numpy(), cb, rtol=3e-6, atol=1e-30)
 
 
+@pytest.mark.parametrize("seq_len,kh,heads,extra", [(1, 16, 32, 0), (64, 16, 32, 0), (130, 4, 8, 8), (778, 16, 32, 0), (65, 4, 4, 24),
+                                                   (2048, 16, 32, 0)])
+def test_gdn_prep_operands_of_the_chunked_scan(seq_len, kh, heads, extra):
+    """clef_gdn_prep against the reference's gdn_prep_kernel on the same GPU: the four hi / lo operand buffers (the
+    whole buffers, pad rows of the last chunk included), the f32 normalised k and the f32 v, byte for byte, from f32
+    and from bf16 rows; and against a plain numpy restatement of the normalisation and of the operand layout.
+    (The reference kernel gives each of its four row warps kh / 4 heads, so it serves kh % 4 == 0 only.)"""
+    kd = 128
+    conv_dim = 2 * kh * kd + heads * kd + extra
+    rng = np.random.default_rng(seq_len + kh)
+    xb = normal_bf16(rng, (seq_len, conv_dim))
+    xb[rng.integers(0, seq_len, 2), : kd] = 0                      # an all-zero q head: rsqrt(1e-6) * 0
+    dev = clef.Device(0)
+    ref = ref_gpu.gdn_prep(dev_f32_from_bits(xb), seq_len, kh, kd, heads, conv_dim)
+    for mixed in (dev_f32_from_bits(xb), dev_bf16(xb)):
+        got = dev.gdn_prep_dev(mixed, seq_len, kh, kd, heads, conv_dim)
+        torch.cuda.synchronize()
+        for name in ("q_hi", "q_lo", "k_hi", "k_lo"):
+            assert torch.equal(got[name], ref[name]), name
+        assert torch.equal(got["kn"].view(-1).view(torch.int32), ref["kn"].view(torch.int32))
+        assert torch.equal(got["v"].view(-1).view(torch.int32), ref["v"].view(torch.int32))
+    # numpy restatement: value(t, he, p) = x / sqrt(sum x^2 + 1e-6) (* kd^-0.5 for q) = hi + lo up to bf16^2 precision,
+    # stored at ((he * nchunks + t // 64) * 2 + p // 64) * 8192 + (t % 64) * 128 + (((p % 64) // 8) ^ (t % 8)) * 16 + (p % 8) * 2
+    x = orc.bf16_to_f32(xb).astype(np.float64)
+    nchunks = (seq_len + 63) // 64
+    ratio = heads // kh
+    t = np.arange(seq_len)[:, None, None]
+    he = np.arange(heads)[None, :, None]
+    p = np.arange(kd)[None, None, :]
+    off = (((he * nchunks + t // 64) * 2 + p // 64) * 8192 + (t % 64) * 128 + (((p % 64) // 8) ^ (t % 8)) * 16 + (p % 8) * 2) // 2
+    for name, base, scale in (("q", 0, kd ** -0.5), ("k", kh * kd, 1.0)):
+        heads_x = x[:, base: base + kh * kd].reshape(seq_len, kh, kd)
+        want = heads_x / np.sqrt((heads_x ** 2).sum(-1, keepdims=True) + 1e-6) * scale
+        want = np.repeat(want, ratio, axis=1)
+        hi = orc.bf16_to_f32(got[name + "_hi"].cpu().numpy().view(np.uint16))[off].astype(np.float64)
+        lo = orc.bf16_to_f32(got[name + "_lo"].cpu().numpy().view(np.uint16))[off].astype(np.float64)
+        assert np.abs(hi + lo - want).max() <= 2e-6                  # rsqrtf is good to 2 ulp; |value| <= 1
+        assert (np.abs(lo) <= np.abs(hi) * 2.0 ** -8 + 1e-30).all()  # lo is the rounding remainder of hi
+        if name == "k":
+            assert np.abs(got["kn"].cpu().numpy() - want).max() <= 2e-6
+    assert np.array_equal(got["v"].cpu().numpy(), orc.bf16_to_f32(xb)[:, 2 * kh * kd: 2 * kh * kd + heads * kd])
+
+
+def test_gdn_prep_argument_errors():
+    lib = clef.load()
+    from gpu_util import ptr, stream
+    b = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    args = lambda **kw: [kw.get(k, d) for k, d in (("seq_len", 4), ("heads", 4), ("kh", 2), ("kd", 128), ("conv_dim", 1024))]
+    call = lambda **kw: lib.clef_gdn_prep(stream(), ptr(b), ptr(b), ptr(b), ptr(b), ptr(b), ptr(b), ptr(b), *args(**kw), 0.1, 0)
+    assert call(kd=64) == -1              # the operand layout is built for 128
+    assert call(heads=3) == -1            # not a multiple of kh
+    assert call(conv_dim=1016) == -1      # too narrow for q, k and v
+    assert call(seq_len=0) == 0
+
+
 @pytest.mark.parametrize("tokens", [1, 778, 4099])
 def test_splitting_copies(tokens):
     rng = np.random.default_rng(tokens)
