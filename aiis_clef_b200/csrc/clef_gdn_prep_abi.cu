@@ -190,6 +190,46 @@ int clef_gdn_prep(clef_stream_t stream, const void* mixed, float* v_out, void* q
     return check_launch(what);
 }
 
+int clef_gdn_conv_prep(clef_stream_t stream, const void* x, const float* w, float* v_out, void* q_hi, void* q_lo, void* k_hi,
+                       void* k_lo, float* kn, int rows, int channels, int k, const int32_t* seq_start, const void* history,
+                       const int32_t* slot_map, int heads, int kh, int kd, float q_scale, int dtype) {
+    const char* what = "clef_gdn_conv_prep";
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!x || !w || !v_out || !q_hi || !q_lo || !k_hi || !k_lo || !kn) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (rows < 0 || channels <= 0 || k <= 0 || heads <= 0 || kh <= 0 || heads % kh != 0) {
+        return fail(CLEF_ERR_INVALID, "%s: rows %d channels %d k %d heads %d kh %d", what, rows, channels, k, heads, kh);
+    }
+    if (kd != kGdnKd) return fail(CLEF_ERR_INVALID, "%s: kd %d (the scan's operand layout is built for 128)", what, kd);
+    if ((long long)channels != 2LL * kh * kd + (long long)heads * kd) {
+        return fail(CLEF_ERR_INVALID, "%s: channels %d must be q, k (kh x kd each) and v (heads x kd)", what, channels);
+    }
+    if (!aligned(x, 16) || !aligned(w, 16) || !aligned(v_out, 16) || !aligned(q_hi, 16) || !aligned(q_lo, 16) ||
+        !aligned(k_hi, 16) || !aligned(k_lo, 16) || !aligned(kn, 16) || (history && !aligned(history, 16))) {
+        return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
+    }
+    if (k != 4) return CLEF_DECLINED;   // the caller runs clef_causal_conv_silu and clef_gdn_prep
+    if (rows == 0) return CLEF_OK;
+    if ((size_t)rows * channels >= ((size_t)1 << 34)) return fail(CLEF_ERR_TOO_LARGE, "%s: %d x %d values", what, rows, channels);
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    const int nchunks = (rows + kGdnChunk - 1) / kGdnChunk;
+    const size_t items = (size_t)nchunks * (kGdnChunk / 8) * (channels / kGdnKd);
+    const FastDiv groups_div = make_fast_div((uint32_t)(channels / kGdnKd));
+    auto launch = [&](auto kernel, std::atomic<int>& occ, auto* xp, auto* hp) {
+        const int per_sm = ctas_per_sm(kernel, 0, occ);
+        launch_hot(kernel, clamp_grid((items + kCtaThreads / 32 - 1) / (kCtaThreads / 32), (size_t)dev.sms * per_sm), 0,
+                   as_stream(stream), xp, w, v_out, (uint8_t*)q_hi, (uint8_t*)q_lo, (uint8_t*)k_hi, (uint8_t*)k_lo, kn, rows,
+                   channels, (const int*)seq_start, hp, (const int*)slot_map, heads, kh, nchunks, q_scale, groups_div);
+    };
+    static std::atomic<int> occ[2];
+    if (dtype == CLEF_BF16) {
+        launch(gdn_conv_prep_kernel<Bf16, 4, 8, 2>, occ[0], (const uint16_t*)x, (const uint16_t*)history);
+    } else {
+        launch(gdn_conv_prep_kernel<F32, 4, 8, 2>, occ[1], (const float*)x, (const float*)history);
+    }
+    return check_launch(what);
+}
+
 int clef_split_q_gate(clef_stream_t stream, const void* qg, void* q, void* gate, int tokens, int heads, int head_dim,
                       int dtype) {
     const char* what = "clef_split_q_gate";

@@ -65,6 +65,7 @@ SYMBOLS = {
     "clef_conv_hist_save": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I]),
     "clef_gdn_gates": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I]),
     "clef_gdn_prep": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I]),
+    "clef_gdn_conv_prep": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _F, _I]),
     "clef_split_q_gate": (_I, [_P, _P, _P, _P, _I, _I, _I, _I]),
     "clef_split_qkv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "clef_repeat_interleave": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
@@ -496,6 +497,27 @@ class Device:
             _check(self.lib.clef_gdn_prep(_stream(), _ptr(mixed), _ptr(out["v"]), _ptr(out["q_hi"]), _ptr(out["q_lo"]),
                                           _ptr(out["k_hi"]), _ptr(out["k_lo"]), _ptr(out["kn"]), seq_len, heads, kh, kd, conv_dim,
                                           q_scale, _dtype_code(mixed)), "clef_gdn_prep")
+        return out
+
+    # -- src/cuda/mod.rs:3649-3707 ------------------------------------------------------------
+    def gdn_conv_prep_dev(self, x, w, seq_len: int, kh: int, kd: int, heads: int, conv_dim: int, k: int, seq_start=None,
+                          history=None, slot_map=None):
+        """Causal convolution + silu + gdn_prep in one launch -> dict(v, q_hi, q_lo, k_hi, k_lo, kn)."""
+        _dev_tensor(x, "x")
+        nchunks = (seq_len + 63) // 64
+        nbytes = heads * nchunks * 2 * 64 * 128
+        out = {"v": self._empty((seq_len, heads * kd), torch.float32), "kn": self._empty((seq_len, heads, kd), torch.float32)}
+        for name in ("q_hi", "q_lo", "k_hi", "k_lo"):
+            out[name] = self._empty((nbytes,), torch.uint8)
+        q_scale = float(_np.float32(1.0) / _np.sqrt(_np.float32(kd)))
+        with torch.cuda.device(self.device):
+            status = _check(self.lib.clef_gdn_conv_prep(_stream(), _ptr(x), _ptr(w), _ptr(out["v"]), _ptr(out["q_hi"]),
+                                                        _ptr(out["q_lo"]), _ptr(out["k_hi"]), _ptr(out["k_lo"]), _ptr(out["kn"]),
+                                                        seq_len, conv_dim, k, _ptr(seq_start), _ptr(history), _ptr(slot_map),
+                                                        heads, kh, kd, q_scale, _dtype_code(x)), "clef_gdn_conv_prep")
+        if status == CLEF_DECLINED:   # a tap count other than 4: the two calls
+            mixed = self.causal_conv_silu_dev(x, w, seq_len, conv_dim, k, seq_start, history, slot_map)
+            return self.gdn_prep_dev(mixed, seq_len, kh, kd, heads, conv_dim)
         return out
 
     # -- src/cuda/mod.rs:2858-2882 ------------------------------------------------------------

@@ -282,6 +282,14 @@ int clef_conv_hist_save(clef_stream_t stream, void* hist, const void* src, const
 int clef_gdn_prep(clef_stream_t stream, const void* mixed, float* v_out, void* q_hi, void* q_lo, void* k_hi, void* k_lo,
                   float* kn, int seq_len, int heads, int kh, int kd, int conv_dim, float q_scale, int dtype);
 
+/* gdn_conv_prep_kernel (kernels/gdn_chunk.cu:1008-1172), Device::gdn_conv_prep_dev (src/cuda/mod.rs:3649-3707):
+ * clef_causal_conv_silu followed by clef_gdn_prep in one launch, the convolved rows staying in f32 in between (as
+ * in the reference). x [rows, channels] with channels = 2 kh kd + heads kd, w [channels, k] f32; the maps as for
+ * clef_causal_conv_silu; outputs as for clef_gdn_prep. k must be 4 (CLEF_DECLINED otherwise: run the two calls). */
+int clef_gdn_conv_prep(clef_stream_t stream, const void* x, const float* w, float* v_out, void* q_hi, void* q_lo, void* k_hi,
+                       void* k_lo, float* kn, int rows, int channels, int k, const int32_t* seq_start, const void* history,
+                       const int32_t* slot_map, int heads, int kh, int kd, float q_scale, int dtype);
+
 /* gdn_gates_kernel (kernels/elementwise.cu:361-377), Device::gdn_gates_dev (src/cuda/mod.rs:2858-2882):
  * beta = sigmoid(b), decay = -exp(a_log[h]) * softplus(a + dt_bias[h]) for a, b [tokens, heads]; outputs are f32. */
 int clef_gdn_gates(clef_stream_t stream, const void* a, const void* b, const float* a_log, const float* dt_bias,

@@ -234,6 +234,45 @@ def test_gdn_prep_argument_errors():
     assert call(seq_len=0) == 0
 
 
+@pytest.mark.parametrize("mode", ["plain", "sequences", "history"])
+@pytest.mark.parametrize("seq_len,kh,heads", [(1, 4, 4), (64, 4, 8), (203, 4, 8), (778, 16, 32), (2048, 16, 32)])
+def test_gdn_conv_prep_equals_the_reference_chain(seq_len, kh, heads, mode):
+    """clef_gdn_conv_prep (one launch) against the reference kernels causal_conv_silu_kernel -> gdn_prep_kernel on the
+    same GPU, the convolved rows in f32 in between: all six outputs byte for byte, from f32 and from bf16 rows."""
+    kd, k = 128, 4
+    conv_dim = 2 * kh * kd + heads * kd
+    rng = np.random.default_rng(seq_len * 7 + kh)
+    xb = normal_bf16(rng, (seq_len, conv_dim))
+    w = (rng.standard_normal((conv_dim, k)) * 0.5).astype(np.float32)
+    n_seq = min(5, seq_len)
+    seq_start = slot_map = hist = None
+    if mode != "plain":
+        seq_start, slot_map = packed_sequences(rng, seq_len, n_seq)
+    if mode == "history":
+        hist = normal_bf16(rng, (n_seq, k - 1, conv_dim))
+    dw = torch.from_numpy(w).cuda()
+    d_ss = None if seq_start is None else i32(seq_start)
+    d_sm = None if hist is None else i32(slot_map)
+    conv = ref_gpu.causal_conv_silu(dev_f32_from_bits(xb), dw, seq_len, conv_dim, k, d_ss,
+                                    None if hist is None else dev_f32_from_bits(hist), d_sm)
+    ref = ref_gpu.gdn_prep(conv.contiguous().view(-1), seq_len, kh, kd, heads, conv_dim)
+    dev = clef.Device(0)
+    for x_in, h_in in ((dev_f32_from_bits(xb), None if hist is None else dev_f32_from_bits(hist)),
+                       (dev_bf16(xb), None if hist is None else dev_bf16(hist))):
+        got = dev.gdn_conv_prep_dev(x_in, dw, seq_len, kh, kd, heads, conv_dim, k, d_ss, h_in, d_sm)
+        torch.cuda.synchronize()
+        for name in ("q_hi", "q_lo", "k_hi", "k_lo"):
+            assert torch.equal(got[name], ref[name]), name
+        assert torch.equal(got["kn"].view(-1).view(torch.int32), ref["kn"].view(torch.int32))
+        assert torch.equal(got["v"].view(-1).view(torch.int32), ref["v"].view(torch.int32))
+    # and the two-call composition of this library with an f32 intermediate gives the same bytes
+    mid = dev.causal_conv_silu_dev(dev_f32_from_bits(xb), dw, seq_len, conv_dim, k, d_ss,
+                                   None if hist is None else dev_f32_from_bits(hist), d_sm)
+    two = dev.gdn_prep_dev(mid, seq_len, kh, kd, heads, conv_dim)
+    for name in ("q_hi", "q_lo", "k_hi", "k_lo"):
+        assert torch.equal(two[name], got[name]), name
+
+
 @pytest.mark.parametrize("tokens", [1, 778, 4099])
 def test_splitting_copies(tokens):
     rng = np.random.default_rng(tokens)
