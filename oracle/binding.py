@@ -417,3 +417,17 @@ def gdn_gates(a, b, a_log, dt_bias, tokens, heads):
     load().oracle_gdn_gates(_p(a), _p(b), _p(_c(a_log, np.float32)), _p(_c(dt_bias, np.float32)), _p(decay), _p(beta),
                             tokens, heads, _dtype_code(a))
     return decay, beta
+
+
+def gdn_prep(mixed, seq_len, kh, kd, heads, conv_dim):
+    """kernels/gdn_chunk.cu:1176-1239 restated on the CPU -> dict(v, q_hi, q_lo, k_hi, k_lo (uint16 bf16 words), kn)."""
+    mixed = _c(mixed)
+    nchunks = (seq_len + 63) // 64
+    words = heads * nchunks * 2 * 64 * 64
+    out = {"v": np.empty((seq_len, heads * kd), np.float32), "kn": np.empty((seq_len, heads, kd), np.float32)}
+    for name in ("q_hi", "q_lo", "k_hi", "k_lo"):
+        out[name] = np.zeros(words, np.uint16)
+    q_scale = np.float32(1.0) / np.sqrt(np.float32(kd))
+    load().oracle_gdn_prep(_p(mixed), _p(out["v"]), _p(out["q_hi"]), _p(out["q_lo"]), _p(out["k_hi"]), _p(out["k_lo"]),
+                           _p(out["kn"]), seq_len, heads, kh, kd, conv_dim, ctypes.c_float(float(q_scale)), _dtype_code(mixed))
+    return out

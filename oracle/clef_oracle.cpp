@@ -970,6 +970,58 @@ ORACLE_API void oracle_gdn_gates(const void* a, const void* b, const float* a_lo
     }
 }
 
+// kernels/gdn_chunk.cu:1176-1239 gdn_prep_kernel (and the second half of gdn_conv_prep_kernel, :1109-1172): the
+// convolved row [q | k | v] of each token becomes the chunked scan's operands. Per head: lane l of 32 adds the
+// squares of p = l, l + 32, ... by fused multiply-add, the 32 partial sums go through the xor tree 16 .. 1;
+// value = x * rsqrt(sum + 1e-6) (q also times q_scale), split as hi = rn_bf16(value), lo = rn_bf16(value - hi)
+// (split_bf16, :13-17) and stored at the swizzled offset of :1211-1216; k heads repeat heads / kh times; kn is the
+// normalised k in f32, v_out the v part of the row. 1 / sqrtf stands in for the device's rsqrtf (within 2 ulp).
+ORACLE_API void oracle_gdn_prep(const void* mixed, float* v_out, uint16_t* q_hi, uint16_t* q_lo, uint16_t* k_hi,
+                                uint16_t* k_lo, float* kn, int seq_len, int heads, int kh, int kd, int conv_dim,
+                                float q_scale, int dtype) {
+    const int nchunks = (seq_len + 63) / 64;
+    const int ratio = heads / kh;
+    std::vector<float> row((size_t)conv_dim);
+    for (int t = 0; t < seq_len; ++t) {
+        widen_row(mixed, (size_t)t * conv_dim, conv_dim, dtype, row.data());
+        for (int h = 0; h < kh; ++h) {
+            for (int which = 0; which < 2; ++which) {   // 0: q, 1: k
+                const float* x = row.data() + (size_t)which * kh * kd + (size_t)h * kd;
+                float lane[32];
+                for (int l = 0; l < 32; ++l) {
+                    float s = 0.0f;
+                    for (int p = l; p < kd; p += 32) s = std::fmaf(x[p], x[p], s);
+                    lane[l] = s;
+                }
+                for (int off = 16; off > 0; off >>= 1) {
+                    float next[32];
+                    for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ off];
+                    std::memcpy(lane, next, sizeof(lane));
+                }
+                float r = 1.0f / std::sqrt(lane[0] + 1e-6f);
+                if (which == 0) r = r * q_scale;
+                for (int rep = 0; rep < ratio; ++rep) {
+                    const int he = h * ratio + rep;
+                    const size_t idx = (size_t)he * nchunks + (size_t)(t / 64);
+                    const int rr = t % 64;
+                    for (int p = 0; p < kd; ++p) {
+                        const int tile = p / 64, c = p % 64, seg = c / 8, e = c % 8;
+                        const size_t off = ((idx * (size_t)(kd / 64) + tile) * (64 * 128) + (size_t)rr * 128 +
+                                            (size_t)((seg ^ (rr % 8)) * 16 + e * 2)) / 2;   // in bf16 units
+                        const float val = x[p] * r;
+                        const uint16_t hi = f32_to_bf16_bits(val);
+                        const uint16_t lo = f32_to_bf16_bits(val - bf16_bits_to_f32(hi));
+                        (which == 0 ? q_hi : k_hi)[off] = hi;
+                        (which == 0 ? q_lo : k_lo)[off] = lo;
+                        if (which == 1) kn[((size_t)t * heads + he) * kd + p] = val;
+                    }
+                }
+            }
+        }
+        std::memcpy(v_out + (size_t)t * heads * kd, row.data() + (size_t)2 * kh * kd, sizeof(float) * (size_t)heads * kd);
+    }
+}
+
 // Quantise rows of f32 values that were produced elsewhere (for instance a GPU f32 result), so a
 // test can separate "same pre-quantisation values" from "same quantiser".
 ORACLE_API void oracle_quantise_rows_f32(const float* v, uint8_t* packed, uint8_t* scales, int rows, int cols,

@@ -220,6 +220,15 @@ def test_gdn_prep_operands_of_the_chunked_scan(seq_len, kh, heads, extra):
         if name == "k":
             assert np.abs(got["kn"].cpu().numpy() - want).max() <= 2e-6
     assert np.array_equal(got["v"].cpu().numpy(), orc.bf16_to_f32(xb)[:, 2 * kh * kd: 2 * kh * kd + heads * kd])
+    # the CPU oracle (1 / sqrtf for rsqrtf): same layout, the f32 values within the 2 ulp of rsqrtf plus one rounding,
+    # the hi words equal except where that difference crosses a bf16 rounding boundary
+    if seq_len <= 778:
+        cpu = orc.gdn_prep(xb, seq_len, kh, kd, heads, conv_dim)
+        np.testing.assert_allclose(got["kn"].cpu().numpy(), cpu["kn"], rtol=4e-7, atol=1e-30)
+        for name in ("q_hi", "k_hi"):
+            g = got[name].cpu().numpy().view(np.uint16)
+            assert bf16_ulp_distance(g, cpu[name]).max() <= 1 and (g != cpu[name]).mean() < 1e-3
+            assert np.array_equal(g == 0, cpu[name] == 0)            # the same words are written
 
 
 def test_gdn_prep_argument_errors():

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from oracle import binding as orc
-from util import lcg_stream
+from util import lcg_stream, to_bf16_bits
 
 E2M1 = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
 
@@ -401,3 +401,46 @@ def test_gdn_gates_known_answers():
     assert beta[0, 0] == 0.5 and beta[0, 1] < 1e-12
     np.testing.assert_allclose(decay[0, 0], -np.log(2.0), rtol=1e-6)       # -exp(0) * log1p(exp(0))
     np.testing.assert_allclose(decay[0, 1], -np.e * 25.0, rtol=1e-6)      # softplus(x) = x above 20
+
+
+def test_gdn_prep_operand_layout_and_split():
+    """kernels/gdn_chunk.cu:1176-1239 restated: unit-vector heads give 1 / sqrt(1 + 1e-6) at one position (hi = 1.0,
+    lo = the remainder), the stored position follows the swizzled operand layout, k heads repeat heads / kh times,
+    hi + lo reproduces the normalised value to bf16^2 precision, pad rows of the last chunk stay zero."""
+    seq_len, kh, heads, kd = 70, 4, 8, 128
+    conv_dim = 2 * kh * kd + heads * kd
+    rng = np.random.default_rng(70)
+    x = rng.standard_normal((seq_len, conv_dim)).astype(np.float32)
+    x[3, :] = 0.0
+    x[3, 5] = 2.0                                   # q head 0 of token 3: the unit vector e_5 times 2
+    x[3, kh * kd + 2 * kd + 77] = -3.0              # k head 2 of token 3: -e_77 times 3
+    out = orc.gdn_prep(x, seq_len, kh, kd, heads, conv_dim)
+    nchunks, ratio = 2, heads // kh
+
+    def word(he, t, p):
+        return (((he * nchunks + t // 64) * 2 + p // 64) * 8192 + (t % 64) * 128 + ((((p % 64) // 8) ^ (t % 8)) * 16) + (p % 8) * 2) // 2
+
+    q_scale = np.float32(1.0) / np.sqrt(np.float32(kd))
+    unit = np.float32(2.0) * (np.float32(1.0) / np.sqrt(np.float32(4.0) + np.float32(1e-6)))
+    want_q = np.float32(unit * q_scale)
+    hi = orc.bf16_to_f32(out["q_hi"])
+    lo = orc.bf16_to_f32(out["q_lo"])
+    for he in (0, 1):                               # q head 0 -> expanded heads 0 and 1
+        assert hi[word(he, 3, 5)] == orc.bf16_to_f32(to_bf16_bits(np.array([want_q])))[0]
+        assert np.float32(hi[word(he, 3, 5)] + lo[word(he, 3, 5)]) == pytest.approx(want_q, rel=2.0 ** -15)
+        assert hi[word(he, 3, 6)] == 0.0
+    khi = orc.bf16_to_f32(out["k_hi"])
+    assert khi[word(4, 3, 77)] == -1.0 and khi[word(5, 3, 77)] == -1.0 and khi[word(6, 3, 77)] == 0.0
+    assert out["kn"][3, 4, 77] == pytest.approx(-1.0, rel=1e-6) and out["kn"][3, 5, 77] == out["kn"][3, 4, 77]
+    # every value: hi + lo against float64, the whole layout at once
+    t = np.arange(seq_len)[:, None, None]
+    he = np.arange(heads)[None, :, None]
+    p = np.arange(kd)[None, None, :]
+    off = word(he, t, p)
+    heads_x = x[:, kh * kd: 2 * kh * kd].reshape(seq_len, kh, kd).astype(np.float64)
+    want = np.repeat(heads_x / np.sqrt((heads_x ** 2).sum(-1, keepdims=True) + 1e-6), ratio, axis=1)
+    err = np.abs(khi[off].astype(np.float64) + orc.bf16_to_f32(out["k_lo"])[off] - want)
+    assert (err <= np.abs(want) * 2.0 ** -16 + 1e-7).all()       # two bf16 roundings deep, plus the f32 arithmetic
+    assert np.array_equal(out["v"], x[:, 2 * kh * kd:])
+    pad = word(np.arange(heads)[:, None, None], np.arange(seq_len, 128)[None, :, None], np.arange(kd)[None, None, :])
+    assert not out["q_hi"][pad].any() and not out["k_lo"][pad].any()
