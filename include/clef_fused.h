@@ -2,14 +2,16 @@
  *
  * Drop-in boundary: each entry point replaces one launcher of aiis-clef's CUDA launch layer
  * (`impl Device` in src/cuda/mod.rs) together with the kernel it launches (kernels/elementwise.cu,
- * kernels/quantise.cu, and the conversion / add kernels of attention_mma.cu and head.cu). The argument
+ * kernels/quantise.cu, the conversion / add kernels of attention_mma.cu and head.cu, and the prep kernels
+ * of gdn_chunk.cu). The argument
  * order after `stream` is the reference KERNEL's positional parameter list, so a binding only has to pass
  * what it already passes to `launch_builder().arg(..)`.
  *
  * Groups, in the order of this file: layout helpers; the fused path (embedding gather, RMSNorm, gated
  * RMSNorm, SwiGLU, RoPE, each with its NVFP4 quantiser); the steps either side of it in a layer
  * (KV-cache write, sigmoid_mul, residual add, alone and fused); the FP8 (E4M3) quantisers; the
- * elementwise kernels in front of the Gated-DeltaNet scan; process-wide settings. A few entry points
+ * elementwise kernels in front of the Gated-DeltaNet scan (kernels/elementwise.cu, and the two prep
+ * kernels of kernels/gdn_chunk.cu); process-wide settings. A few entry points
  * fuse several reference launches into one and say so ("one launch", "one pass"); their results equal
  * the reference's chain of kernels byte for byte.
  *
