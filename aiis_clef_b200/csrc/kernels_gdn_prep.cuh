@@ -425,6 +425,19 @@ __device__ __forceinline__ void store_bf16_hi_lo(float v, uint8_t* hi, uint8_t* 
 }
 
 template <typename T>
+__device__ __forceinline__ void load4_as_f32(const typename T::storage* p, float* v);
+template <>
+__device__ __forceinline__ void load4_as_f32<Bf16>(const uint16_t* p, float* v) {
+    const uint2 raw = ldg_stream_v2(p);
+    v[0] = bf16_lo(raw.x), v[1] = bf16_hi(raw.x), v[2] = bf16_lo(raw.y), v[3] = bf16_hi(raw.y);
+}
+template <>
+__device__ __forceinline__ void load4_as_f32<F32>(const float* p, float* v) {
+    const uint4 raw = ldg_stream_v4(p);
+    v[0] = __uint_as_float(raw.x), v[1] = __uint_as_float(raw.y), v[2] = __uint_as_float(raw.z), v[3] = __uint_as_float(raw.w);
+}
+
+template <typename T>
 __global__ void __launch_bounds__(kCtaThreads)
 gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict__ v_out, uint8_t* __restrict__ q_hi,
                 uint8_t* __restrict__ q_lo, uint8_t* __restrict__ k_hi, uint8_t* __restrict__ k_lo, float* __restrict__ kn,
@@ -455,7 +468,11 @@ gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict
         const size_t t = item / kh;
         const int h = (int)(item - t * kh);
         const bool live = t < (size_t)seq_len;
+        // Each lane reads its head rows twice: strided (p = lane + 32 i) for the sum in the reference's order, and
+        // its 4 adjacent values (p = 4 lane ..) for the outputs, so that every store is 8 or 16 bytes wide. The
+        // second read hits L1.
         float q[4] = {0.f, 0.f, 0.f, 0.f}, k[4] = {0.f, 0.f, 0.f, 0.f};
+        float qa[4] = {0.f, 0.f, 0.f, 0.f}, ka[4] = {0.f, 0.f, 0.f, 0.f};
         if (live) {
             const typename T::storage* qr = mixed + t * conv_dim + (size_t)h * kGdnKd;
             const typename T::storage* kr = qr + (size_t)kh * kGdnKd;
@@ -464,6 +481,8 @@ gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict
                 q[i] = load_scalar<T>(qr + lane + 32 * i);
                 k[i] = load_scalar<T>(kr + lane + 32 * i);
             }
+            load4_as_f32<T>(qr + lane * 4, qa);
+            load4_as_f32<T>(kr + lane * 4, ka);
         }
         float sq = 0.0f, sk = 0.0f;
 #pragma unroll
@@ -478,24 +497,30 @@ gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict
         }
         const float rq = __fmul_rn(rsqrtf(__fadd_rn(sq, 1e-6f)), q_scale);
         const float rk = rsqrtf(__fadd_rn(sk, 1e-6f));
+        uint32_t qw[4], kw[4];   // hi words 0, 1 and lo words 0, 1
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            qa[j] = __fmul_rn(qa[j], rq);
+            ka[j] = __fmul_rn(ka[j], rk);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            qw[j] = pack_bf16x2(qa[2 * j], qa[2 * j + 1]);
+            qw[2 + j] = pack_bf16x2(__fsub_rn(qa[2 * j], bf16_lo(qw[j])), __fsub_rn(qa[2 * j + 1], bf16_hi(qw[j])));
+            kw[j] = pack_bf16x2(ka[2 * j], ka[2 * j + 1]);
+            kw[2 + j] = pack_bf16x2(__fsub_rn(ka[2 * j], bf16_lo(kw[j])), __fsub_rn(ka[2 * j + 1], bf16_hi(kw[j])));
+        }
         const size_t chunk = t / kGdnChunk;
         const int r = (int)(t - chunk * kGdnChunk);
         for (int rep = 0; rep < ratio; ++rep) {
             const int he = h * ratio + rep;
-            const size_t idx = (size_t)he * nchunks + chunk;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int p = lane + 32 * i;
-                const size_t off = gdn_operand_offset(idx, r, p);
-                if (live) {
-                    const float kv = __fmul_rn(k[i], rk);
-                    store_bf16_hi_lo(__fmul_rn(q[i], rq), q_hi, q_lo, off);
-                    store_bf16_hi_lo(kv, k_hi, k_lo, off);
-                    kn[(t * heads + he) * kGdnKd + p] = kv;
-                } else {
-                    *reinterpret_cast<uint16_t*>(q_hi + off) = 0, *reinterpret_cast<uint16_t*>(q_lo + off) = 0;
-                    *reinterpret_cast<uint16_t*>(k_hi + off) = 0, *reinterpret_cast<uint16_t*>(k_lo + off) = 0;
-                }
+            const size_t off = gdn_operand_offset((size_t)he * nchunks + chunk, r, lane * 4);
+            stg_v2(q_hi + off, make_uint2(qw[0], qw[1]));
+            stg_v2(q_lo + off, make_uint2(qw[2], qw[3]));
+            stg_v2(k_hi + off, make_uint2(kw[0], kw[1]));
+            stg_v2(k_lo + off, make_uint2(kw[2], kw[3]));
+            if (live) {
+                *reinterpret_cast<float4*>(kn + (t * heads + he) * kGdnKd + lane * 4) = make_float4(ka[0], ka[1], ka[2], ka[3]);
             }
         }
     }
@@ -514,19 +539,6 @@ gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict
 // per SM at 8 cycles per issued instruction leave both the issue slots and the memory system half idle. What the
 // fusion saves is the intermediate buffer and a launch, not time.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__device__ __forceinline__ void load4_as_f32(const typename T::storage* p, float* v);
-template <>
-__device__ __forceinline__ void load4_as_f32<Bf16>(const uint16_t* p, float* v) {
-    const uint2 raw = ldg_stream_v2(p);
-    v[0] = bf16_lo(raw.x), v[1] = bf16_hi(raw.x), v[2] = bf16_lo(raw.y), v[3] = bf16_hi(raw.y);
-}
-template <>
-__device__ __forceinline__ void load4_as_f32<F32>(const float* p, float* v) {
-    const uint4 raw = ldg_stream_v4(p);
-    v[0] = __uint_as_float(raw.x), v[1] = __uint_as_float(raw.y), v[2] = __uint_as_float(raw.z), v[3] = __uint_as_float(raw.w);
-}
-
 template <typename T, int K, int R, int MIN_CTAS>
 __global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
 gdn_conv_prep_kernel(const typename T::storage* __restrict__ x, const float* __restrict__ w, float* __restrict__ v_out,
