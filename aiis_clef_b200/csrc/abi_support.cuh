@@ -134,6 +134,11 @@ inline int check_scale_layout(const char* what, int rows, int cols, int blk_mn, 
 
 inline bool use_hot() { return kernel_choice() == 0; }
 
+// The tuned quantising kernels cover the global scales real checkpoints carry; see kHotGlobalScaleMin.
+inline bool hot_scale_ok(float global_scale) {
+    return global_scale >= kHotGlobalScaleMin && global_scale <= kHotGlobalScaleMax;
+}
+
 // chunk as the kernels take it: negated when the interleaved tile order is selected (nvfp4_codec.cuh, SfLayout).
 inline int fold_scale_layout(int chunk) { return scale_layout() == CLEF_SF_INTERLEAVED ? -chunk : chunk; }
 

@@ -220,7 +220,7 @@ static int rms_norm_quantise_impl(const char* what, clef_stream_t stream, const 
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
-    if (dtype == CLEF_BF16 && use_hot() && (cols == 2048 || cols == 4096) && aligned(x, 32) &&
+    if (dtype == CLEF_BF16 && use_hot() && hot_scale_ok(global_scale) && (cols == 2048 || cols == 4096) && aligned(x, 32) &&
         (!addend || (aligned(addend, 32) && aligned(sum_out, 32)))) {
         const size_t groups = ((size_t)rows_total + 7) / 8;
         const size_t smem = (size_t)cols * sizeof(float);
@@ -353,7 +353,7 @@ int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, cons
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
-    if (dtype == CLEF_BF16 && use_hot() && cols == 128 && aligned(x, 32) && aligned(gate, 32)) {
+    if (dtype == CLEF_BF16 && use_hot() && hot_scale_ok(global_scale) && cols == 128 && aligned(x, 32) && aligned(gate, 32)) {
         static std::atomic<int> occ{0};
         const int per_sm = ctas_per_sm(gated_norm_quant_hot_kernel, 0, occ);
         const size_t groups = ((size_t)rows + 63) / 64;   // 64 head rows per CTA step
@@ -431,7 +431,7 @@ int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, ui
     if (rows_total == 0) return CLEF_OK;
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
-    if (dtype == CLEF_BF16 && use_hot() && cols % 512 == 0 && (size_t)rows_total * (cols / 512) < 0x7fffffffull &&
+    if (dtype == CLEF_BF16 && use_hot() && hot_scale_ok(global_scale) && cols % 512 == 0 && (size_t)rows_total * (cols / 512) < 0x7fffffffull &&
         aligned(x, 32)) {
         constexpr int kUnits = 2;
         static std::atomic<int> occ{0};
@@ -472,7 +472,7 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
     const size_t total_blocks = (size_t)rows_total * (cols / 16);
-    if (dtype == CLEF_BF16 && use_hot() && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(gate, 32) &&
+    if (dtype == CLEF_BF16 && use_hot() && hot_scale_ok(global_scale) && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(gate, 32) &&
         aligned(up, 32)) {
         const uint32_t segs = (uint32_t)(cols / 512);
         const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;

@@ -328,7 +328,7 @@ int clef_sigmoid_mul_quantise_nvfp4(clef_stream_t stream, const void* x, const v
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
     const size_t total_blocks = (size_t)rows_total * (cols / 16);
-    if (dtype == CLEF_BF16 && use_hot() && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(x, 32) &&
+    if (dtype == CLEF_BF16 && use_hot() && hot_scale_ok(global_scale) && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(x, 32) &&
         aligned(gate, 32)) {
         const uint32_t segs = (uint32_t)(cols / 512);
         const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;

@@ -83,6 +83,13 @@ __device__ __forceinline__ void stg_v2(void* p, uint2 v) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// L2 prefetch hint for the 128-byte line holding p. The row-structured kernels issue it for their FIRST round of
+// activations before pdl_wait_prior_grids(): the hint moves the line from DRAM towards L2 and returns nothing
+// to the SM, so it cannot observe a value (L2 is the point of coherence; a line the previous kernel is still
+// writing is updated in place). Its only effect is that the first round's DRAM latency runs under the previous
+// kernel's tail instead of after it. p must lie inside the tensor the kernel is going to read.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // Load 4 consecutive activations (one "quad" = the reference's float4) as f32.
 template <typename T>
 __device__ __forceinline__ float4 load_quad(const typename T::storage* base, size_t quad_index);

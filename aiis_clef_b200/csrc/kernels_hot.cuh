@@ -87,11 +87,18 @@ __device__ __forceinline__ uint32_t e2m1_pack8(float e0, float e1, float e2, flo
     return r;
 }
 
-// Block quantiser on the quad-pair layout, fast path only. Returns false, writing nothing, when the
-// block needs the literal path (a NaN or infinity, a scale argument that overflows, a scaled value of
-// 2^24 or more, or 0 < amax < 2^-100 where the short division by six is not exact); the caller then
-// runs its cold routine, which recomputes the block from global memory. Keeping the literal path out
-// of this function keeps address-taken arrays and call set-up out of the hot loop.
+// Block quantiser on the quad-pair layout, fast path only. Always writes stored/lo/hi; returns false when
+// they are not the block's answer and the caller must run its cold routine (which recomputes the block from
+// global memory, literally, and overwrites what was stored). Keeping the literal path out of this function
+// keeps address-taken arrays and call set-up out of the hot loop.
+//
+// Fast domain: the block's scale is a normal, unclamped E4M3 code (8 <= code <= 0x7E), or the block is all
+// zeros. With 2^-64 <= global_scale <= 2^64 (the launchers send other scales to the shape-general kernels)
+// a normal code implies amax >= 2^-68, where the short division by six is exact, and a scaled maximum
+// amax * inv_scale within a rounding step of 6, far inside the FP4 converter's domain; a NaN or an infinity
+// in the block makes the scale argument NaN or infinite, whose code is out of range. What falls outside is
+// rare in activations: scale arguments below 2^-6 (subnormal codes), above 448 (clamped), non-finite values.
+// For an all-zero block the codes come out as zeros whatever table entry is read, and the scale byte is 0.
 // NEG: the pairs hold the NEGATED values (the SwiGLU fast path produces -v); magnitudes are unaffected
 // and the sign is restored by scaling with -inv_scale.
 template <bool NEG>
@@ -103,14 +110,10 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
         amax = max3_abs_nan(amax, v[i].x, v[i].y);
     }
     const float sv = __fmul_rn(div_six_fast(amax), global_scale);
-    const uint32_t stored = e4m3_encode_finite(sv);
-    const float inv = inv_table[stored];
-    const float pmax = __fmul_rn(amax, inv);
-    // 0 < amax < 2^-100 as one unsigned compare on the bit pattern (+0 wraps to the top)
-    const bool tiny = (__float_as_uint(amax) - 1u) < (__float_as_uint(kDivSixExactFrom) - 1u);
-    // No early exit: the codes are computed unconditionally (on values the fast path does not cover the
-    // result is simply not used), which leaves the compiler free to interleave several blocks.
-    const bool ok = (fabsf(sv) <= 3.0e38f) && (pmax < kE2m1FastLimit) && !tiny;
+    // e4m3_encode_finite's normal branch: round the 3-bit mantissa half up by an integer add, rebase the exponent
+    const uint32_t code = ((__float_as_uint(sv) + 0x00080000u) >> 20) - (120u << 3);
+    const bool normal = (code - 8u) <= 0x76u;
+    const float inv = inv_table[code & (uint32_t)(kInvScaleTableSize - 1)];
     constexpr float kNudge = -4.33488326e-08f;   // see e2m1x2_fast
     const f32x2 inv2 = f2_splat(NEG ? -inv : inv);
     const f32x2 nudge2 = f2_splat(kNudge);
@@ -121,10 +124,10 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
         p[i] = f2_fma(t, nudge2, t);
     }
     // quad q: p[2q] = (x, z), p[2q+1] = (y, w); element order x, y, z, w
-    stored_out = stored;
+    stored_out = normal ? code : 0u;
     lo_out = e2m1_pack8(p[0].x, p[1].x, p[0].y, p[1].y, p[2].x, p[3].x, p[2].y, p[3].y);
     hi_out = e2m1_pack8(p[4].x, p[5].x, p[4].y, p[5].y, p[6].x, p[7].x, p[6].y, p[7].y);
-    return ok;
+    return normal || amax == 0.0f;
 }
 
 // Cold path shared by the kernels: the caller has the block's 16 f32 values recomputed in natural
@@ -227,8 +230,15 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
         const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
         s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
     }
-    pdl_wait_prior_grids();
     int row = blockIdx.x * 8 + warp;
+    if (row < rows) {   // this warp's first row towards L2 (a lane covers 128 bytes); see prefetch_l2
+#pragma unroll
+        for (int h = 0; h < NB / 4; ++h) {
+            prefetch_l2(x + (size_t)row * COLS + (size_t)(lane + 32 * h) * 64);
+            if (ADD) prefetch_l2(addend + (size_t)row * COLS + (size_t)(lane + 32 * h) * 64);
+        }
+    }
+    pdl_wait_prior_grids();
     U8x32 d[NB];
     if (!ADD && row < rows) {
 #pragma unroll
@@ -300,8 +310,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
         const float inv = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
                                                    : inv_rms(row_tree_256(p, lane), COLS, eps);
         const f32x2 inv2 = f2_splat(inv);
-        uint32_t stored[NB], lo[NB], hi[NB];
-        bool fast[NB];
+        uint32_t bad = 0u;   // bit j: block j is outside the fast domain
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
 #pragma unroll
@@ -310,20 +319,23 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
                 v[j][2 * q] = f2_mul(f2_mul(v[j][2 * q], inv2), make_float2(w.x, w.y));
                 v[j][2 * q + 1] = f2_mul(f2_mul(v[j][2 * q + 1], inv2), make_float2(w.z, w.w));
             }
-            fast[j] = quantise16_qp<false>(v[j], global_scale, s_inv, stored[j], lo[j], hi[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < NB; ++j) {
+            uint32_t stored, lo, hi;
+            const bool ok = quantise16_qp<false>(v[j], global_scale, s_inv, stored, lo, hi);
             const int b = lane + 32 * j;
-            uint2* pdst = reinterpret_cast<uint2*>(prow + b * 8);
-            uint8_t* sdst = srow + (size_t)(b >> 2) * chunk + (b & 3);
-            if (fast[j]) {
-                *pdst = make_uint2(lo[j], hi[j]);
-                *sdst = (uint8_t)stored[j];
-            } else {
-                // ADD: this lane stored the block's sum above, so it reads its own bytes back.
-                rms_block_cold((ADD ? (const uint16_t*)sum_out : x) + (size_t)row * COLS + b * 16, weight + b * 16, inv,
-                               global_scale, pdst, sdst);
+            *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(lo, hi);
+            srow[(size_t)(b >> 2) * chunk + (b & 3)] = (uint8_t)stored;
+            bad |= ok ? 0u : (1u << j);
+        }
+        if (bad) {   // rare: the literal path overwrites what the fast path stored
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                if (bad & (1u << j)) {
+                    const int b = lane + 32 * j;
+                    // ADD: this lane stored the block's sum above, so it reads its own bytes back.
+                    rms_block_cold((ADD ? (const uint16_t*)sum_out : x) + (size_t)row * COLS + b * 16, weight + b * 16, inv,
+                                   global_scale, reinterpret_cast<uint2*>(prow + b * 8),
+                                   srow + (size_t)(b >> 2) * chunk + (b & 3));
+                }
             }
         }
     }
@@ -544,13 +556,14 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
                 g[k] = ldg_stream_v8(gate + (size_t)next * 512 + lane * 16);
                 u[k] = ldg_stream_v8(up + (size_t)next * 512 + lane * 16);
             }
+            // The short forms sit behind the domain test: measured faster here than running them unconditionally.
             uint32_t stored, lo, hi;
-            bool done = false;
+            bool ok = false;
             if (gated_fast_domain<ACT, false>(gv, uv, up + (size_t)unit * 512 + lane * 16)) {
                 gated_fast<ACT>(gv, uv);
-                done = quantise16_qp<false>(gv, global_scale, s_inv, stored, lo, hi);
+                ok = quantise16_qp<false>(gv, global_scale, s_inv, stored, lo, hi);
             }
-            if (done) {
+            if (ok) {
                 *pdst = make_uint2(lo, hi);
                 *sdst = (uint8_t)stored;
             } else {
@@ -627,6 +640,13 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
         s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
     }
     fill_inv_scale_table(s_inv, global_scale);
+    {   // the CTA's first 64 head rows towards L2: 128 lines of x, 128 of gate; see prefetch_l2
+        const uint32_t first = blockIdx.x * (kCtaThreads / 4);
+        const uint32_t line = threadIdx.x & 127;   // 2 lines per head row
+        if (first + (line >> 1) < (uint32_t)rows_live) {
+            prefetch_l2((threadIdx.x < 128 ? x : gate) + (size_t)first * COLS + (size_t)line * 64);
+        }
+    }
     pdl_wait_prior_grids();
     U8x32 dx[2], dg[2];
     if (hrow < (uint32_t)rows_live) {
@@ -764,10 +784,10 @@ quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed
                 d[k] = ldg_stream_v8(x + (size_t)next * 512 + lane * 16);
             }
             uint32_t stored, lo, hi;
-            if (quantise16_qp<false>(v, global_scale, s_inv, stored, lo, hi)) {
-                *pdst = make_uint2(lo, hi);
-                *sdst = (uint8_t)stored;
-            } else {
+            const bool ok = quantise16_qp<false>(v, global_scale, s_inv, stored, lo, hi);
+            *pdst = make_uint2(lo, hi);
+            *sdst = (uint8_t)stored;
+            if (!ok) {   // rare: the literal path overwrites what the fast path stored
                 quantise_block_cold(x + (size_t)unit * 512 + lane * 16, global_scale, pdst, sdst);
             }
         }
@@ -796,8 +816,14 @@ rms_norm_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
         }
         s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
     }
-    pdl_wait_prior_grids();
     int row = blockIdx.x * 8 + warp;
+    if (row < rows) {   // this warp's first row towards L2; see prefetch_l2
+#pragma unroll
+        for (int h = 0; h < NB / 4; ++h) {
+            prefetch_l2(x + (size_t)row * COLS + (size_t)(lane + 32 * h) * 64);
+        }
+    }
+    pdl_wait_prior_grids();
     U8x32 d[NB];
     if (row < rows) {
 #pragma unroll
@@ -910,6 +936,13 @@ gated_norm_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict
         const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
         s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
     }
+    {   // the CTA's first 64 head rows towards L2: 128 lines of x, 128 of gate; see prefetch_l2
+        const uint32_t first = blockIdx.x * (kCtaThreads / 4);
+        const uint32_t line = threadIdx.x & 127;   // 2 lines per head row
+        if (first + (line >> 1) < (uint32_t)rows) {
+            prefetch_l2((threadIdx.x < 128 ? x : gate) + (size_t)first * COLS + (size_t)line * 64);
+        }
+    }
     pdl_wait_prior_grids();
     U8x32 dx[2], dg[2];
     if (hrow < (uint32_t)rows) {
@@ -987,7 +1020,7 @@ __device__ __forceinline__ size_t kv_cache_row(int token, const int* cache_map, 
 // With KV: `out` is the key cache; total_items counts the items of the key rows followed by as many items of
 // the value rows kv.v (every item of a value row is a copy item), and both land at the token's cache row.
 template <bool KV>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, 6)
 rope_hot_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, const float* __restrict__ cos_t,
                 const float* __restrict__ sin_t, uint32_t total_items, int heads, int head_dim, int rotary_dim,
                 const int* __restrict__ seq_start, const int* __restrict__ pos_base,
@@ -1113,16 +1146,19 @@ __device__ __forceinline__ void rope_segment_item(const RopeSegment& sg, uint32_
     }
 }
 
+#ifndef CLEF_ROPE_MIN_CTAS
+#define CLEF_ROPE_MIN_CTAS 6
+#endif
 template <int NSEG>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, CLEF_ROPE_MIN_CTAS)
 rope_multi_hot_kernel(RopeSegments segs, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int head_dim,
                       int rotary_dim, const int* __restrict__ seq_start, const int* __restrict__ pos_base,
                       const int* __restrict__ pos_map, const int* __restrict__ cache_map,
                       const int* __restrict__ cache_len, FastDiv items_div) {
     pdl_launch_dependents();
-    pdl_wait_prior_grids();
     const uint32_t total_items = segs.seg[NSEG - 1].end_item;
     const uint32_t stride = gridDim.x * blockDim.x;
+    pdl_wait_prior_grids();
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_items; idx += stride) {
         // (the segments are addressed with constant indices: kernel parameters cannot be indexed dynamically)
         if (idx < segs.seg[0].end_item) {

@@ -197,6 +197,11 @@ __device__ __forceinline__ void quantise16(const float* v, float global_scale, c
     hi_out = e2m1x8_fast(p + 8);
 }
 
+// Range of global_scale the tuned kernels' block quantiser is built for (quantise16_qp in kernels_hot.cuh);
+// launchers send any other scale (zero, negative, NaN, or beyond these) to the shape-general kernels.
+constexpr float kHotGlobalScaleMin = 5.42101086e-20f;   // 2^-64
+constexpr float kHotGlobalScaleMax = 1.84467441e+19f;   // 2^64
+
 // amax / 6 without the IEEE-division sequence: q0 = x * RN(1/6), one exact-remainder correction.
 // Checked against div.rn.f32 for every non-negative finite f32: equal for x = 0 and for every
 // x >= 2^-100; smaller non-zero x go to the literal path.
