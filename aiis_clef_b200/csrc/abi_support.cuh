@@ -117,7 +117,10 @@ inline int check_dtype(int dtype, const char* what) {
     return CLEF_OK;
 }
 
-inline int check_scale_layout(const char* what, int rows, int cols, int blk_mn, int chunk) {
+// Checks the shape and the scale-tile arguments of an NVFP4 entry point and folds the tile order into `chunk` the way
+// the kernels take it (negated for the interleaved order; nvfp4_codec.cuh, SfLayout). `sf_layout` is the call's own
+// choice or CLEF_SF_DEFAULT for the process default (clef_set_scale_layout).
+inline int check_scale_layout(const char* what, int rows, int cols, int blk_mn, int* chunk, int sf_layout) {
     if (rows < 0 || cols <= 0) {
         return fail(CLEF_ERR_INVALID, "%s: rows %d / cols %d", what, rows, cols);
     }
@@ -125,9 +128,20 @@ inline int check_scale_layout(const char* what, int rows, int cols, int blk_mn, 
         return fail(CLEF_ERR_INVALID,
                     "%s: cols %d is not a multiple of 64 (four 16-value blocks fill one scale group)", what, cols);
     }
-    if (blk_mn <= 0 || chunk != blk_mn * 4) {
+    if (blk_mn <= 0 || *chunk != blk_mn * 4) {
         return fail(CLEF_ERR_INVALID, "%s: scale atom blk_mn %d / chunk %d (chunk must be blk_mn * 4)", what, blk_mn,
-                    chunk);
+                    *chunk);
+    }
+    if (sf_layout == CLEF_SF_DEFAULT) sf_layout = scale_layout();
+    if (sf_layout != CLEF_SF_ACTIVATION && sf_layout != CLEF_SF_INTERLEAVED) {
+        return fail(CLEF_ERR_INVALID, "%s: scale-tile order %d", what, sf_layout);
+    }
+    if (sf_layout == CLEF_SF_INTERLEAVED) {
+        if (blk_mn % 32 != 0) {   // the order interleaves 32-row groups: row r sits at (r % 32) * (blk_mn / 32) + r / 32
+            return fail(CLEF_ERR_INVALID, "%s: the interleaved scale-tile order needs blk_mn %% 32 == 0 (blk_mn %d)", what,
+                        blk_mn);
+        }
+        *chunk = -*chunk;
     }
     return CLEF_OK;
 }
@@ -138,9 +152,6 @@ inline bool use_hot() { return kernel_choice() == 0; }
 inline bool hot_scale_ok(float global_scale) {
     return global_scale >= kHotGlobalScaleMin && global_scale <= kHotGlobalScaleMax;
 }
-
-// chunk as the kernels take it: negated when the interleaved tile order is selected (nvfp4_codec.cuh, SfLayout).
-inline int fold_scale_layout(int chunk) { return scale_layout() == CLEF_SF_INTERLEAVED ? -chunk : chunk; }
 
 inline cudaStream_t as_stream(clef_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 

@@ -205,12 +205,12 @@ int clef_rms_norm(clef_stream_t stream, const void* x, const float* weight, void
 // RMSNorm + NVFP4 of x, or (addend != NULL) of the stored sum x + addend, which is also written to sum_out.
 static int rms_norm_quantise_impl(const char* what, clef_stream_t stream, const void* x, const void* addend,
                                   void* sum_out, const float* weight, uint8_t* packed, uint8_t* scales, int rows,
-                                  int cols, float eps, float global_scale, int blk_mn, int chunk, int dtype) {
+                                  int cols, float eps, float global_scale, int blk_mn, int chunk, int dtype,
+                                  int sf_layout) {
     if (int r = check_dtype(dtype, what)) return r;
     if (!x || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (addend && !sum_out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
-    if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
-    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
+    if (int r = check_scale_layout(what, rows, cols, blk_mn, &chunk, sf_layout)) return r;   // folds the tile order into chunk
     if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(packed, 8) || (addend && (!aligned(addend, 16) || !aligned(sum_out, 16)))) {
         return fail(CLEF_ERR_INVALID, "%s: activations and weight must be 16-byte aligned, packed 8-byte aligned", what);
     }
@@ -261,7 +261,14 @@ int clef_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* x, const floa
                                  uint8_t* scales, int rows, int cols, float eps, float global_scale, int blk_mn,
                                  int chunk, int dtype) {
     return rms_norm_quantise_impl("clef_rms_norm_quantise_nvfp4", stream, x, nullptr, nullptr, weight, packed, scales,
-                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype);
+                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype, CLEF_SF_DEFAULT);
+}
+
+int clef_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, const void* x, const float* weight, uint8_t* packed,
+                                    uint8_t* scales, int rows, int cols, float eps, float global_scale, int blk_mn,
+                                    int chunk, int dtype, int sf_layout) {
+    return rms_norm_quantise_impl("clef_rms_norm_quantise_nvfp4_ex", stream, x, nullptr, nullptr, weight, packed, scales,
+                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype, sf_layout);
 }
 
 int clef_add_rms_norm_quantise_nvfp4(clef_stream_t stream, void* sum_out, const void* a, const void* b,
@@ -269,7 +276,15 @@ int clef_add_rms_norm_quantise_nvfp4(clef_stream_t stream, void* sum_out, const 
                                      float eps, float global_scale, int blk_mn, int chunk, int dtype) {
     if (!b || !sum_out) return fail(CLEF_ERR_INVALID, "clef_add_rms_norm_quantise_nvfp4: null pointer");
     return rms_norm_quantise_impl("clef_add_rms_norm_quantise_nvfp4", stream, a, b, sum_out, weight, packed, scales,
-                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype);
+                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype, CLEF_SF_DEFAULT);
+}
+
+int clef_add_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, void* sum_out, const void* a, const void* b,
+                                        const float* weight, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                                        float eps, float global_scale, int blk_mn, int chunk, int dtype, int sf_layout) {
+    if (!b || !sum_out) return fail(CLEF_ERR_INVALID, "clef_add_rms_norm_quantise_nvfp4_ex: null pointer");
+    return rms_norm_quantise_impl("clef_add_rms_norm_quantise_nvfp4_ex", stream, a, b, sum_out, weight, packed, scales,
+                                  rows, cols, eps, global_scale, blk_mn, chunk, dtype, sf_layout);
 }
 
 // ---- gated rms_norm family -------------------------------------------------------------------------
@@ -326,9 +341,9 @@ int clef_rms_norm_gated(clef_stream_t stream, const void* x, const void* gate, c
     return check_launch(what);
 }
 
-int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, const void* gate, const float* weight,
+static int clef_rms_norm_gated_quantise_nvfp4_impl(clef_stream_t stream, const void* x, const void* gate, const float* weight,
                                        uint8_t* packed, uint8_t* scales, int rows, int cols, float eps,
-                                       float global_scale, int blk_mn, int chunk, int vh, int rows_live, int dtype) {
+                                       float global_scale, int blk_mn, int chunk, int vh, int rows_live, int dtype, int sf_layout) {
     const char* what = "clef_rms_norm_gated_quantise_nvfp4";
     if (int r = check_dtype(dtype, what)) return r;
     if (!x || !gate || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
@@ -340,8 +355,7 @@ int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, cons
         return fail(CLEF_ERR_INVALID, "%s: rows %d must be a multiple of vh %d and rows_live %d <= rows", what, rows, vh,
                     rows_live);
     }
-    if (int r = check_scale_layout(what, rows / vh, vh * cols, blk_mn, chunk)) return r;
-    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
+    if (int r = check_scale_layout(what, rows / vh, vh * cols, blk_mn, &chunk, sf_layout)) return r;   // folds the tile order into chunk
     if ((rows / vh) % blk_mn != 0) {
         return fail(CLEF_ERR_INVALID, "%s: rows/vh = %d tokens is not a multiple of blk_mn %d (rows counts padding)", what,
                     rows / vh, blk_mn);
@@ -370,6 +384,18 @@ int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, cons
                                         global_scale, blk_mn, chunk, vh);
     }
     return check_launch(what);
+}
+
+int clef_rms_norm_gated_quantise_nvfp4(clef_stream_t stream, const void* x, const void* gate, const float* weight,
+                                       uint8_t* packed, uint8_t* scales, int rows, int cols, float eps,
+                                       float global_scale, int blk_mn, int chunk, int vh, int rows_live, int dtype) {
+    return clef_rms_norm_gated_quantise_nvfp4_impl(stream, x, gate, weight, packed, scales, rows, cols, eps, global_scale, blk_mn, chunk, vh, rows_live, dtype, CLEF_SF_DEFAULT);
+}
+
+int clef_rms_norm_gated_quantise_nvfp4_ex(clef_stream_t stream, const void* x, const void* gate, const float* weight,
+                                       uint8_t* packed, uint8_t* scales, int rows, int cols, float eps,
+                                       float global_scale, int blk_mn, int chunk, int vh, int rows_live, int dtype, int sf_layout) {
+    return clef_rms_norm_gated_quantise_nvfp4_impl(stream, x, gate, weight, packed, scales, rows, cols, eps, global_scale, blk_mn, chunk, vh, rows_live, dtype, sf_layout);
 }
 
 // ---- swiglu / quantise -------------------------------------------------------------------------------
@@ -416,13 +442,12 @@ int clef_swiglu(clef_stream_t stream, const void* gate, const void* up, void* ou
     return check_launch(what);
 }
 
-int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
-                        float global_scale, int blk_mn, int chunk, int dtype) {
+static int clef_quantise_nvfp4_impl(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                        float global_scale, int blk_mn, int chunk, int dtype, int sf_layout) {
     const char* what = "clef_quantise_nvfp4";
     if (int r = check_dtype(dtype, what)) return r;
     if (!x || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
-    if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
-    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
+    if (int r = check_scale_layout(what, rows, cols, blk_mn, &chunk, sf_layout)) return r;   // folds the tile order into chunk
     if (!aligned(x, 16) || !aligned(packed, 8)) {
         return fail(CLEF_ERR_INVALID, "%s: x must be 16-byte aligned, packed 8-byte aligned", what);
     }
@@ -454,14 +479,23 @@ int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, ui
     return check_launch(what);
 }
 
-int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const void* up, uint8_t* packed,
+int clef_quantise_nvfp4(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                        float global_scale, int blk_mn, int chunk, int dtype) {
+    return clef_quantise_nvfp4_impl(stream, x, packed, scales, rows, cols, global_scale, blk_mn, chunk, dtype, CLEF_SF_DEFAULT);
+}
+
+int clef_quantise_nvfp4_ex(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                        float global_scale, int blk_mn, int chunk, int dtype, int sf_layout) {
+    return clef_quantise_nvfp4_impl(stream, x, packed, scales, rows, cols, global_scale, blk_mn, chunk, dtype, sf_layout);
+}
+
+static int clef_swiglu_quantise_nvfp4_impl(clef_stream_t stream, const void* gate, const void* up, uint8_t* packed,
                                uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
-                               int dtype) {
+                               int dtype, int sf_layout) {
     const char* what = "clef_swiglu_quantise_nvfp4";
     if (int r = check_dtype(dtype, what)) return r;
     if (!gate || !up || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
-    if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
-    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
+    if (int r = check_scale_layout(what, rows, cols, blk_mn, &chunk, sf_layout)) return r;   // folds the tile order into chunk
     if (!aligned(gate, 16) || !aligned(up, 16) || !aligned(packed, 8)) {
         return fail(CLEF_ERR_INVALID, "%s: gate and up must be 16-byte aligned, packed 8-byte aligned", what);
     }
@@ -495,6 +529,18 @@ int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const voi
                                            blk_mn, chunk);
     }
     return check_launch(what);
+}
+
+int clef_swiglu_quantise_nvfp4(clef_stream_t stream, const void* gate, const void* up, uint8_t* packed,
+                               uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                               int dtype) {
+    return clef_swiglu_quantise_nvfp4_impl(stream, gate, up, packed, scales, rows, cols, global_scale, blk_mn, chunk, dtype, CLEF_SF_DEFAULT);
+}
+
+int clef_swiglu_quantise_nvfp4_ex(clef_stream_t stream, const void* gate, const void* up, uint8_t* packed,
+                               uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                               int dtype, int sf_layout) {
+    return clef_swiglu_quantise_nvfp4_impl(stream, gate, up, packed, scales, rows, cols, global_scale, blk_mn, chunk, dtype, sf_layout);
 }
 
 // ---- rope ----------------------------------------------------------------------------------------------

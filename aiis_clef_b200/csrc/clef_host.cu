@@ -38,6 +38,7 @@ struct clef_device {
     int ordinal = 0;
     cudaStream_t streams[kStreams] = {nullptr, nullptr};
     cudaEvent_t slot_free[kStreams] = {nullptr, nullptr};
+    cudaEvent_t fence[kStreams] = {nullptr, nullptr};   // orders the two streams at the start and the end of a call
     void* arena[kStreams] = {nullptr, nullptr};
     size_t arena_bytes[kStreams] = {0, 0};
     void* consts = nullptr;       // small operands (weights, tables): two halves, used by alternate calls
@@ -65,6 +66,12 @@ struct DeviceScope {
         }
     }
 };
+
+// Declares the scope and refuses the call when the handle's device cannot be made current (the launches and
+// copies would otherwise go to whatever device the caller had selected, on this handle's streams).
+#define CLEF_DEVICE_SCOPE(dev, what)                                                                   \
+    DeviceScope scope(dev);                                                                            \
+    if (!scope.ok) return fail(CLEF_ERR_CUDA, "%s: cannot select device %d", what, (dev)->ordinal)
 
 int ensure_arena(clef_device* dev, int slot, size_t bytes) {
     if (dev->arena_bytes[slot] >= bytes) {
@@ -125,6 +132,10 @@ int run_tiled(clef_device* dev, int rows, int atom, int tile_rows, std::vector<R
     for (int s = 0; s < kStreams; ++s) {
         if (int rc = ensure_arena(dev, s, slot_bytes)) return rc;
     }
+    // Device pointers a caller passes (clef_device_alloc / clef_device_upload) are ordered on stream 0 only:
+    // stream 1 starts this call behind everything stream 0 holds so far.
+    CLEF_CUDA(cudaEventRecord(dev->fence[0], dev->streams[0]));
+    CLEF_CUDA(cudaStreamWaitEvent(dev->streams[1], dev->fence[0], 0));
     const int rows_padded = (int)round_up((size_t)rows, (size_t)atom);
     int tile = 0;
     for (int r0 = 0; r0 < rows_padded; r0 += tile_rows, ++tile) {
@@ -157,6 +168,10 @@ int run_tiled(clef_device* dev, int rows, int atom, int tile_rows, std::vector<R
         // the half of the constants arena this call read may be rewritten once this point is reached
         CLEF_CUDA(cudaEventRecord(dev->gen_done[dev->consts_gen][s], dev->streams[s]));
     }
+    // ... and what the caller enqueues on stream 0 next (an upload over an operand, clef_device_free) comes
+    // behind the tiles that ran on stream 1.
+    CLEF_CUDA(cudaEventRecord(dev->fence[1], dev->streams[1]));
+    CLEF_CUDA(cudaStreamWaitEvent(dev->streams[0], dev->fence[1], 0));
     if (!dev->pipelined) {
         for (int s = 0; s < kStreams; ++s) {
             CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
@@ -229,19 +244,23 @@ int clef_device_open(int ordinal, clef_device** out) {
     }
     clef_device* dev = new clef_device();
     dev->ordinal = ordinal;
-    DeviceScope scope(dev);
-    if (!scope.ok) {
-        delete dev;
-        return fail(CLEF_ERR_CUDA, "clef_device_open: cannot select device %d", ordinal);
-    }
-    // The reference runs its one stream at the highest priority (src/cuda/mod.rs:610-628).
-    int least = 0, greatest = 0;
-    CLEF_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
-    for (int s = 0; s < kStreams; ++s) {
-        CLEF_CUDA(cudaStreamCreateWithPriority(&dev->streams[s], cudaStreamNonBlocking, greatest));
-        CLEF_CUDA(cudaEventCreateWithFlags(&dev->slot_free[s], cudaEventDisableTiming));
-        CLEF_CUDA(cudaEventCreateWithFlags(&dev->gen_done[0][s], cudaEventDisableTiming));
-        CLEF_CUDA(cudaEventCreateWithFlags(&dev->gen_done[1][s], cudaEventDisableTiming));
+    const int rc = [&]() -> int {
+        CLEF_DEVICE_SCOPE(dev, "clef_device_open");
+        // The reference runs its one stream at the highest priority (src/cuda/mod.rs:610-628).
+        int least = 0, greatest = 0;
+        CLEF_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+        for (int s = 0; s < kStreams; ++s) {
+            CLEF_CUDA(cudaStreamCreateWithPriority(&dev->streams[s], cudaStreamNonBlocking, greatest));
+            CLEF_CUDA(cudaEventCreateWithFlags(&dev->slot_free[s], cudaEventDisableTiming));
+            CLEF_CUDA(cudaEventCreateWithFlags(&dev->fence[s], cudaEventDisableTiming));
+            CLEF_CUDA(cudaEventCreateWithFlags(&dev->gen_done[0][s], cudaEventDisableTiming));
+            CLEF_CUDA(cudaEventCreateWithFlags(&dev->gen_done[1][s], cudaEventDisableTiming));
+        }
+        return CLEF_OK;
+    }();
+    if (rc != CLEF_OK) {
+        clef_device_close(dev);   // destroys whatever was created before the failing step (the message stays)
+        return rc;
     }
     *out = dev;
     return CLEF_OK;
@@ -257,6 +276,7 @@ int clef_device_close(clef_device* dev) {
                 cudaStreamDestroy(dev->streams[s]);
             }
             if (dev->slot_free[s]) cudaEventDestroy(dev->slot_free[s]);
+            if (dev->fence[s]) cudaEventDestroy(dev->fence[s]);
             if (dev->gen_done[0][s]) cudaEventDestroy(dev->gen_done[0][s]);
             if (dev->gen_done[1][s]) cudaEventDestroy(dev->gen_done[1][s]);
             if (dev->arena[s]) cudaFree(dev->arena[s]);
@@ -273,7 +293,7 @@ clef_stream_t clef_device_stream(clef_device* dev) { return dev ? (clef_stream_t
 
 int clef_device_synchronize(clef_device* dev) {
     if (int rc = check_handle(dev, "clef_device_synchronize")) return rc;
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_device_synchronize");
     for (int s = 0; s < kStreams; ++s) {
         CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
     }
@@ -285,7 +305,7 @@ int clef_device_set_pipelined(clef_device* dev, int on) {
     std::lock_guard<std::mutex> guard(dev->lock);
     dev->pipelined = on != 0;
     if (!dev->pipelined) {
-        DeviceScope scope(dev);
+        CLEF_DEVICE_SCOPE(dev, "clef_device_set_pipelined");
         for (int s = 0; s < kStreams; ++s) {
             CLEF_CUDA(cudaStreamSynchronize(dev->streams[s]));
         }
@@ -296,7 +316,7 @@ int clef_device_set_pipelined(clef_device* dev, int on) {
 int clef_device_alloc(clef_device* dev, size_t bytes, void** out) {
     if (int rc = check_handle(dev, "clef_device_alloc")) return rc;
     if (!out) return fail(CLEF_ERR_INVALID, "clef_device_alloc: null out pointer");
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_device_alloc");
     CLEF_CUDA(cudaMallocAsync(out, bytes ? bytes : 1, dev->streams[0]));
     return CLEF_OK;
 }
@@ -304,7 +324,7 @@ int clef_device_alloc(clef_device* dev, size_t bytes, void** out) {
 int clef_device_free(clef_device* dev, void* ptr) {
     if (int rc = check_handle(dev, "clef_device_free")) return rc;
     if (!ptr) return CLEF_OK;
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_device_free");
     CLEF_CUDA(cudaFreeAsync(ptr, dev->streams[0]));
     return CLEF_OK;
 }
@@ -312,7 +332,7 @@ int clef_device_free(clef_device* dev, void* ptr) {
 int clef_device_upload(clef_device* dev, void* dst_device, const void* src_host, size_t bytes) {
     if (int rc = check_handle(dev, "clef_device_upload")) return rc;
     if ((!dst_device || !src_host) && bytes) return fail(CLEF_ERR_INVALID, "clef_device_upload: null pointer");
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_device_upload");
     CLEF_CUDA(cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, dev->streams[0]));
     return CLEF_OK;
 }
@@ -320,7 +340,7 @@ int clef_device_upload(clef_device* dev, void* dst_device, const void* src_host,
 int clef_device_download(clef_device* dev, void* dst_host, const void* src_device, size_t bytes) {
     if (int rc = check_handle(dev, "clef_device_download")) return rc;
     if ((!dst_host || !src_device) && bytes) return fail(CLEF_ERR_INVALID, "clef_device_download: null pointer");
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_device_download");
     CLEF_CUDA(cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, dev->streams[0]));
     CLEF_CUDA(cudaStreamSynchronize(dev->streams[0]));
     return CLEF_OK;
@@ -348,7 +368,7 @@ int clef_host_embed_gather(clef_device* dev, const void* table_device, const int
     }
     if (tokens == 0) return CLEF_OK;
     std::lock_guard<std::mutex> guard(dev->lock);
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_embed_gather");
     const size_t row = (size_t)hidden * elem_bytes(dtype);
     std::vector<RowStream> in{{ids, nullptr, sizeof(int32_t), 0}};
     std::vector<RowStream> outs{{nullptr, out, row, 0}};
@@ -378,7 +398,7 @@ int clef_host_quantise_nvfp4(clef_device* dev, const void* x, uint8_t* packed, u
     if (!x || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (rows == 0) return CLEF_OK;
     std::lock_guard<std::mutex> guard(dev->lock);
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_quantise_nvfp4");
     const size_t row_in = (size_t)cols * elem_bytes(dtype);
     std::vector<RowStream> in{{x, nullptr, row_in, 0}};
     std::vector<RowStream> outs{{nullptr, packed, (size_t)cols / 2, 0}, {nullptr, scales, (size_t)cols / 16, 0}};
@@ -403,7 +423,7 @@ int clef_host_quantise_fp8(clef_device* dev, const void* x, uint8_t* out, uint16
     if (!x || !out || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (rows == 0) return CLEF_OK;
     std::lock_guard<std::mutex> guard(dev->lock);
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_quantise_fp8");
     const size_t row_in = (size_t)cols * elem_bytes(dtype);
     std::vector<RowStream> in{{x, nullptr, row_in, 0}};
     std::vector<RowStream> outs{{nullptr, out, (size_t)cols, 0}, {nullptr, scales, sizeof(uint16_t), 0}};
@@ -424,7 +444,7 @@ int clef_host_rms_norm_quantise_nvfp4(clef_device* dev, const void* x, const flo
     if (!x || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (rows == 0) return CLEF_OK;
     std::lock_guard<std::mutex> guard(dev->lock);
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_rms_norm_quantise_nvfp4");
     std::vector<void*> consts;
     if (int rc = upload_consts(dev, {{weight, (size_t)cols * sizeof(float)}}, consts)) return rc;
     const size_t row_in = (size_t)cols * elem_bytes(dtype);
@@ -455,7 +475,7 @@ int clef_host_swiglu_quantise_nvfp4(clef_device* dev, const void* gate, const vo
     if (!gate || !up || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (rows == 0) return CLEF_OK;
     std::lock_guard<std::mutex> guard(dev->lock);
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_swiglu_quantise_nvfp4");
     const size_t row_in = (size_t)cols * elem_bytes(dtype);
     std::vector<RowStream> in{{gate, nullptr, row_in, 0}, {up, nullptr, row_in, 0}};
     std::vector<RowStream> outs{{nullptr, packed, (size_t)cols / 2, 0}, {nullptr, scales, (size_t)cols / 16, 0}};
@@ -482,7 +502,7 @@ int clef_host_rms_norm_gated_quantise_nvfp4(clef_device* dev, const void* x, con
     if (!x || !gate || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
     if (rows == 0) return CLEF_OK;
     std::lock_guard<std::mutex> guard(dev->lock);
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_rms_norm_gated_quantise_nvfp4");
     std::vector<void*> consts;
     if (int rc = upload_consts(dev, {{weight, (size_t)cols * sizeof(float)}}, consts)) return rc;
     // Tiles are cut in TOKENS; a token row carries vh head rows.
@@ -526,7 +546,7 @@ int clef_host_rope(clef_device* dev, void* out, const void* x, const float* cos_
         }
     }
     std::lock_guard<std::mutex> guard(dev->lock);
-    DeviceScope scope(dev);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_rope");
     const size_t table_bytes = (size_t)table_rows * rotary_dim * sizeof(float);
     std::vector<void*> consts;
     if (int rc = upload_consts(dev, {{cos_table, table_bytes}, {sin_table, table_bytes}}, consts)) return rc;
@@ -550,12 +570,12 @@ int clef_host_rope(clef_device* dev, void* out, const void* x, const float* cos_
 }
 
 // ---- per-token maps -----------------------------------------------------------------------------------------
-int clef_pass_geometries(size_t slots, size_t max_chunk, size_t* out, size_t cap) {
-    // src/gpu.rs:689 (HEAD_RUNGS), :711-733 (Rungs::body_at), :779-795 (pass_geometries).
-    static const size_t head[8] = {64, 128, 256, 512, 1024, 2048, 4096, 8192};
-    if (slots == 0) slots = 1;
-    const size_t granule = CLEF_CHUNK_GRANULE;
-    size_t top = std::max(granule, (max_chunk + granule - 1) / granule * granule);
+namespace {
+// Rungs::body_at (src/gpu.rs:711-733): the head rungs up to `top`, their multiples by 2..slots up to `top`, and
+// `top` itself when no rung reaches it; `top` is max(max_chunk, granule), NOT rounded to the granule.
+std::vector<size_t> body_rungs(size_t slots, size_t max_chunk, size_t* top_out) {
+    static const size_t head[8] = {64, 128, 256, 512, 1024, 2048, 4096, 8192};   // src/gpu.rs:689
+    const size_t top = std::max<size_t>(max_chunk, CLEF_CHUNK_GRANULE);
     std::vector<size_t> rungs;
     for (size_t r : head) {
         if (r <= top) rungs.push_back(r);
@@ -568,6 +588,16 @@ int clef_pass_geometries(size_t slots, size_t max_chunk, size_t* out, size_t cap
     if (rungs.empty() || *std::max_element(rungs.begin(), rungs.end()) < top) rungs.push_back(top);
     std::sort(rungs.begin(), rungs.end());
     rungs.erase(std::unique(rungs.begin(), rungs.end()), rungs.end());
+    if (top_out) *top_out = top;
+    return rungs;
+}
+}  // namespace
+
+int clef_pass_geometries(size_t slots, size_t max_chunk, size_t* out, size_t cap) {
+    // src/gpu.rs:779-795 (pass_geometries) on Rungs::body_at(max_chunk).
+    if (slots == 0) slots = 1;
+    size_t top = 0;
+    const std::vector<size_t> rungs = body_rungs(slots, max_chunk, &top);
     std::vector<size_t> geoms = rungs;
     // The reference also caps totals at the engine's admission limit (max_batch_tokens), which in the
     // shipped configuration is not below slots * top; that product is the cap used here.
@@ -588,21 +618,8 @@ int clef_pass_geometries(size_t slots, size_t max_chunk, size_t* out, size_t cap
 
 int clef_rungs_decompose(size_t tokens, size_t slots, size_t max_chunk, size_t* bases, size_t* rows, size_t cap) {
     // Rungs::decompose, src/gpu.rs:762-775, on Rungs::body_at(max_chunk).
-    static const size_t head[8] = {64, 128, 256, 512, 1024, 2048, 4096, 8192};
     if (slots == 0) slots = 1;
-    const size_t granule = CLEF_CHUNK_GRANULE;
-    const size_t top = std::max(granule, (max_chunk + granule - 1) / granule * granule);
-    std::vector<size_t> rungs;
-    for (size_t r : head) {
-        if (r <= top) rungs.push_back(r);
-    }
-    for (size_t k = 2; k <= slots; ++k) {
-        for (size_t r : head) {
-            if (k * r <= top) rungs.push_back(k * r);
-        }
-    }
-    if (rungs.empty() || *std::max_element(rungs.begin(), rungs.end()) < top) rungs.push_back(top);
-    std::sort(rungs.begin(), rungs.end());
+    const std::vector<size_t> rungs = body_rungs(slots, max_chunk, nullptr);
     const size_t smallest = rungs.front();
     size_t n = 0, base = 0;
     while (base < tokens) {

@@ -310,14 +310,13 @@ int clef_sigmoid_mul(clef_stream_t stream, void* out, const void* x, const void*
     return check_launch(what);
 }
 
-int clef_sigmoid_mul_quantise_nvfp4(clef_stream_t stream, const void* x, const void* gate, uint8_t* packed,
+static int clef_sigmoid_mul_quantise_nvfp4_impl(clef_stream_t stream, const void* x, const void* gate, uint8_t* packed,
                                     uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
-                                    int dtype) {
+                                    int dtype, int sf_layout) {
     const char* what = "clef_sigmoid_mul_quantise_nvfp4";
     if (int r = check_dtype(dtype, what)) return r;
     if (!x || !gate || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
-    if (int r = check_scale_layout(what, rows, cols, blk_mn, chunk)) return r;
-    chunk = fold_scale_layout(chunk);   // kernels take the tile order folded into the sign of chunk
+    if (int r = check_scale_layout(what, rows, cols, blk_mn, &chunk, sf_layout)) return r;   // folds the tile order into chunk
     if (!aligned(x, 16) || !aligned(gate, 16) || !aligned(packed, 8)) {
         return fail(CLEF_ERR_INVALID, "%s: x and gate must be 16-byte aligned, packed 8-byte aligned", what);
     }
@@ -349,6 +348,18 @@ int clef_sigmoid_mul_quantise_nvfp4(clef_stream_t stream, const void* x, const v
                                                      blk_mn, chunk);
     }
     return check_launch(what);
+}
+
+int clef_sigmoid_mul_quantise_nvfp4(clef_stream_t stream, const void* x, const void* gate, uint8_t* packed,
+                                    uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                                    int dtype) {
+    return clef_sigmoid_mul_quantise_nvfp4_impl(stream, x, gate, packed, scales, rows, cols, global_scale, blk_mn, chunk, dtype, CLEF_SF_DEFAULT);
+}
+
+int clef_sigmoid_mul_quantise_nvfp4_ex(clef_stream_t stream, const void* x, const void* gate, uint8_t* packed,
+                                    uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                                    int dtype, int sf_layout) {
+    return clef_sigmoid_mul_quantise_nvfp4_impl(stream, x, gate, packed, scales, rows, cols, global_scale, blk_mn, chunk, dtype, sf_layout);
 }
 
 int clef_add(clef_stream_t stream, void* out, const void* a, const void* b, size_t total, int dtype) {

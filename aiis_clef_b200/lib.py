@@ -70,6 +70,12 @@ SYMBOLS = {
     "clef_split_qkv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "clef_repeat_interleave": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
     "clef_set_scale_layout": (_I, [_I]),
+    "clef_quantise_nvfp4_ex": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _I]),
+    "clef_rms_norm_quantise_nvfp4_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I, _I]),
+    "clef_rms_norm_gated_quantise_nvfp4_ex": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I, _I, _I, _I]),
+    "clef_swiglu_quantise_nvfp4_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _I]),
+    "clef_sigmoid_mul_quantise_nvfp4_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _I]),
+    "clef_add_rms_norm_quantise_nvfp4_ex": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I, _I]),
     "clef_set_kernel_choice": (None, [_I]),
 }
 
@@ -707,6 +713,29 @@ class HostDevice:
 
     def synchronize(self):
         _check(self.lib.clef_device_synchronize(self.handle), "clef_device_synchronize")
+
+    # stream-ordered device memory of the handle (raw device addresses; clef_device_alloc / _upload / _download / _free)
+    def alloc(self, nbytes: int) -> int:
+        out = _P()
+        _check(self.lib.clef_device_alloc(self.handle, ctypes.c_size_t(nbytes), ctypes.byref(out)), "clef_device_alloc")
+        return out.value
+
+    def free(self, address: int):
+        _check(self.lib.clef_device_free(self.handle, ctypes.c_void_p(address)), "clef_device_free")
+
+    def upload(self, address: int, src, nbytes: int):
+        """Enqueue a host-to-device copy (returns at once: `src` must stay alive until the handle is synchronised)."""
+        _check(self.lib.clef_device_upload(self.handle, ctypes.c_void_p(address), self._hp(src), ctypes.c_size_t(nbytes)),
+               "clef_device_upload")
+
+    def download(self, dst, address: int, nbytes: int):
+        _check(self.lib.clef_device_download(self.handle, self._hp(dst), ctypes.c_void_p(address), ctypes.c_size_t(nbytes)),
+               "clef_device_download")
+
+    def embed_gather_from(self, table_address: int, ids, out, tokens: int, hidden: int, dtype_code: int = CLEF_BF16):
+        """clef_host_embed_gather with the table given as a raw device address (one obtained from `alloc`)."""
+        _check(self.lib.clef_host_embed_gather(self.handle, ctypes.c_void_p(table_address), self._hp(ids), self._hp(out), tokens,
+                                               hidden, dtype_code), "clef_host_embed_gather")
 
     def __del__(self):
         try:

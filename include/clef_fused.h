@@ -312,15 +312,40 @@ int clef_split_qkv(clef_stream_t stream, const void* mixed, void* q, void* k, vo
 int clef_repeat_interleave(clef_stream_t stream, const void* src, void* out, int tokens, int kh, int ratio, int dim,
                            int dtype);
 
-/* Order of the rows inside a [blk_mn rows x 4 blocks] scale tile, for every NVFP4 entry point of the process:
+/* Order of the rows inside a [blk_mn rows x 4 blocks] scale tile:
  *   CLEF_SF_ACTIVATION   row r at byte 4 r: the reference's activation-side ("conflict-free") order,
  *                        kernels/quantise.cu:34-41, src/swizzle.rs:64-65. Default.
  *   CLEF_SF_INTERLEAVED  row r at byte 4 ((r % 32) * (blk_mn / 32) + r / 32): the 32 x 4 x 4 order of
  *                        src/swizzle.rs:66-68 that block-scaled tensor-core GEMMs (tcgen05) read directly.
- * It is a property of the GEMM that consumes the operands, so it is set once, not per call. */
+ *                        Needs blk_mn % 32 == 0 (refused otherwise).
+ * The order is a property of the GEMM that consumes the operands. clef_set_scale_layout sets the PROCESS-WIDE
+ * default that the NVFP4 entry points above use; it is read when a call is made, so it is baked into a CUDA graph
+ * at capture time, and it is shared by every thread. A caller with two consumers (a mixed checkpoint, two
+ * threads) passes the order per call instead: every NVFP4 entry point has an `_ex` form with one more argument,
+ * `sf_layout` = CLEF_SF_ACTIVATION, CLEF_SF_INTERLEAVED or CLEF_SF_DEFAULT (the process default), as the
+ * reference passes `conflict_free` per call (src/swizzle.rs:64-69). */
+#define CLEF_SF_DEFAULT (-1)
 #define CLEF_SF_ACTIVATION 0
 #define CLEF_SF_INTERLEAVED 1
 int clef_set_scale_layout(int layout);
+int clef_quantise_nvfp4_ex(clef_stream_t stream, const void* x, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                           float global_scale, int blk_mn, int chunk, int dtype, int sf_layout);
+int clef_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, const void* x, const float* weight, uint8_t* packed,
+                                    uint8_t* scales, int rows, int cols, float eps, float global_scale, int blk_mn,
+                                    int chunk, int dtype, int sf_layout);
+int clef_rms_norm_gated_quantise_nvfp4_ex(clef_stream_t stream, const void* x, const void* gate, const float* weight,
+                                          uint8_t* packed, uint8_t* scales, int rows, int cols, float eps,
+                                          float global_scale, int blk_mn, int chunk, int vh, int rows_live, int dtype,
+                                          int sf_layout);
+int clef_swiglu_quantise_nvfp4_ex(clef_stream_t stream, const void* gate, const void* up, uint8_t* packed,
+                                  uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                                  int dtype, int sf_layout);
+int clef_sigmoid_mul_quantise_nvfp4_ex(clef_stream_t stream, const void* x, const void* gate, uint8_t* packed,
+                                       uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
+                                       int dtype, int sf_layout);
+int clef_add_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, void* sum_out, const void* a, const void* b,
+                                        const float* weight, uint8_t* packed, uint8_t* scales, int rows, int cols,
+                                        float eps, float global_scale, int blk_mn, int chunk, int dtype, int sf_layout);
 
 /* Kernel selection for tests and measurements: 0 = automatic (tuned kernel when the shape has one),
  * 1 = always the shape-general kernel. Process-wide; not part of the reference interface. */

@@ -44,7 +44,10 @@ int clef_device_synchronize(clef_device* dev);
  * one); outputs are complete in host memory after clef_device_synchronize. The caller keeps every host buffer of a
  * call, inputs and weights included, alive and unchanged until then. Switching it off synchronises. */
 int clef_device_set_pipelined(clef_device* dev, int on);
-/* Stream-ordered device memory (src/cuda/mod.rs:3971-4051); not for use inside a stream capture. */
+/* Stream-ordered device memory (src/cuda/mod.rs:3971-4051); not for use inside a stream capture. alloc, upload
+ * and free are enqueued on the handle's stream (clef_device_stream) and return at once; download waits for its
+ * copy. A host-slice call that is given such a pointer (clef_host_embed_gather's table) starts behind them on
+ * both of the handle's streams, and a free or an upload issued after the call comes behind all of its tiles. */
 int clef_device_alloc(clef_device* dev, size_t bytes, void** out);
 int clef_device_free(clef_device* dev, void* ptr);
 int clef_device_upload(clef_device* dev, void* dst_device, const void* src_host, size_t bytes);

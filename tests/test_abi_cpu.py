@@ -71,6 +71,18 @@ def test_bad_arguments_are_refused_before_cuda(clef_lib):
     assert lib.clef_sigmoid_mul_quantise_nvfp4(None, p, p, p, p, 4, 100, 1.0, 128, 512, 0) == -1
     assert lib.clef_add_rms_norm_quantise_nvfp4(None, None, p, p, p, p, p, 4, 2048, 1e-6, 1.0, 128, 512, 0) == -1
     assert lib.clef_add(None, p, p, ctypes.c_void_p(0x1004), 64, 0) == -1
+    # the interleaved scale-tile order interleaves 32-row groups: an atom that is not a multiple of 32 is refused
+    assert lib.clef_quantise_nvfp4_ex(None, p, p, p, 4, 128, 1.0, 48, 192, 0, 1) == -1
+    assert b"blk_mn % 32" in lib.clef_last_error()
+    assert lib.clef_quantise_nvfp4_ex(None, p, p, p, 4, 128, 1.0, 16, 64, 0, 1) == -1
+    assert lib.clef_quantise_nvfp4_ex(None, p, p, p, 4, 128, 1.0, 128, 512, 0, 7) == -1          # no such order
+    assert lib.clef_quantise_nvfp4_ex(None, p, p, p, 0, 128, 1.0, 96, 384, 0, 1) == 0            # 96 = 3 x 32 is fine
+    assert lib.clef_set_scale_layout(1) == 0
+    try:
+        assert lib.clef_quantise_nvfp4(None, p, p, p, 4, 128, 1.0, 48, 192, 0) == -1             # the process default applies
+        assert lib.clef_quantise_nvfp4_ex(None, p, p, p, 0, 128, 1.0, 48, 192, 0, 0) == 0        # a per-call order overrides it
+    finally:
+        assert lib.clef_set_scale_layout(0) == 0
     # zero-sized work is accepted without a device
     assert lib.clef_sigmoid_mul(None, p, p, p, 0, 0) == 0
     assert lib.clef_add(None, p, p, p, 0, 1) == 0

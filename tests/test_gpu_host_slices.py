@@ -151,3 +151,31 @@ def test_host_quantise_fp8(host_dev, rows):
     want_q, want_s = orc.quantise_fp8(x, rows, cols)
     assert_bytes_equal(out.numpy(), want_q.reshape(-1), "host fp8 codes")
     assert_bytes_equal(scales.numpy(), want_s, "host fp8 scales")
+
+
+def test_table_uploaded_through_the_handle_then_gathered_over_several_tiles(host_dev):
+    """clef_device_alloc, clef_device_upload from pinned memory (asynchronous, stream 0), then at once
+    clef_host_embed_gather over more than three row tiles (odd tiles run on the handle's second stream), then
+    download and free: the gather must see the whole uploaded table, the download the same bytes."""
+    vocab, hidden, tokens = 60000, 2048, 20000            # a 245 MB upload; 20,000 rows = 4 tiles of about 6,000
+    rng = np.random.default_rng(47)
+    table = orc.bits_to_torch_bf16(normal_bf16(rng, (vocab, hidden), scale=0.02)).pin_memory()
+    ids = rng.integers(0, vocab, tokens).astype(np.int32)
+    ids[-5:] = vocab - 1                                  # the end of the table: the last bytes the upload writes
+    nbytes = vocab * hidden * 2
+    for mode in (False, True):
+        host_dev.set_pipelined(mode)
+        try:
+            address = host_dev.alloc(nbytes)
+            host_dev.upload(address, table, nbytes)
+            got = pinned(np.zeros((tokens, hidden), np.uint16))
+            host_dev.embed_gather_from(address, ids, got, tokens, hidden)
+            back = pinned(np.zeros(vocab * hidden, np.uint16))
+            host_dev.download(back, address, nbytes)      # waits for its copy (and, behind the fence, for the gather)
+            host_dev.free(address)
+            host_dev.synchronize()
+            want = orc.bf16_bits(table)
+            assert_bytes_equal(got.numpy(), want[ids], f"gather from an uploaded table (pipelined={mode})")
+            assert_bytes_equal(back.numpy(), want.reshape(-1), "download of the uploaded table")
+        finally:
+            host_dev.set_pipelined(False)

@@ -80,6 +80,11 @@ def test_rung_ladder():
     assert clef.rungs_decompose(16717) == [(0, 8192), (8192, 8192), (16384, 256), (16640, 64), (16704, 64)]
     assert [r for _, r in clef.rungs_decompose(6144, slots=1)] == [4096, 2048]
     assert [r for _, r in clef.rungs_decompose(6144, slots=3)] == [6144]
+    # a chunk limit that is not a multiple of the 64-row granule is kept as it is (Rungs::body_at clamps to
+    # max(top, 64) only, src/gpu.rs:715): the ladder ends in the limit itself
+    assert clef.pass_geometries(1, 1000) == [64, 128, 256, 512, 1000]
+    assert clef.pass_geometries(1, 10) == [64]
+    assert [r for _, r in clef.rungs_decompose(2100, slots=1, max_chunk=1000)] == [1000, 1000, 64, 64]
     cut = clef.rungs_decompose(130712)
     assert sum(r for _, r in cut) >= 130712 and sum(r for _, r in cut) - 130712 < 64
     assert all(a[0] + a[1] == b[0] for a, b in zip(cut, cut[1:]))
