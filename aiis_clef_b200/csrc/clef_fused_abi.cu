@@ -231,7 +231,7 @@ static int rms_norm_quantise_impl(const char* what, clef_stream_t stream, const 
         const int per_sm = ctas_per_sm(rms_norm_quant_hot_kernel<NB, ADD>, smem, occ);                             \
         launch_hot(rms_norm_quant_hot_kernel<NB, ADD>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,      \
                    (const uint16_t*)x, (const uint16_t*)addend, (uint16_t*)sum_out, weight, packed, scales, rows,  \
-                   rows_total, eps, global_scale, blk_mn, chunk, atom_div);                                        \
+                   rows_total, eps, global_scale, blk_mn, chunk, atom_div, (const int*)nullptr);                   \
     }
         if (cols == 2048) {
             if (addend) CLEF_RMSQ_HOT(4, true) else CLEF_RMSQ_HOT(4, false)
@@ -285,6 +285,57 @@ int clef_add_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, void* sum_out, con
     if (!b || !sum_out) return fail(CLEF_ERR_INVALID, "clef_add_rms_norm_quantise_nvfp4_ex: null pointer");
     return rms_norm_quantise_impl("clef_add_rms_norm_quantise_nvfp4_ex", stream, a, b, sum_out, weight, packed, scales,
                                   rows, cols, eps, global_scale, blk_mn, chunk, dtype, sf_layout);
+}
+
+// Embedding gather + RMSNorm + NVFP4 in one pass over the gathered row (bf16, hidden 2048 or 4096); other shapes
+// and f32 run the two entry points it stands for.
+static int embed_rms_norm_quantise_impl(const char* what, clef_stream_t stream, const void* table, const int32_t* ids,
+                                        void* h_out, const float* weight, uint8_t* packed, uint8_t* scales, int tokens,
+                                        int hidden, float eps, float global_scale, int blk_mn, int chunk, int dtype,
+                                        int sf_layout) {
+    if (int r = check_dtype(dtype, what)) return r;
+    if (!table || !ids || !h_out || !weight || !packed || !scales) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (tokens < 0 || hidden <= 0) return fail(CLEF_ERR_INVALID, "%s: tokens %d hidden %d", what, tokens, hidden);
+    int folded = chunk;
+    if (int r = check_scale_layout(what, tokens, hidden, blk_mn, &folded, sf_layout)) return r;
+    int rows_total = 0;
+    if (int r = clef_nvfp4_sizes(tokens, hidden, blk_mn, &rows_total, nullptr, nullptr)) return r;
+    if (rows_total == 0) return CLEF_OK;
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    if (dtype == CLEF_BF16 && use_hot() && hot_scale_ok(global_scale) && (hidden == 2048 || hidden == 4096) && aligned(table, 32) &&
+        aligned(h_out, 32) && aligned(weight, 16) && aligned(packed, 8)) {
+        const size_t groups = ((size_t)rows_total + 7) / 8;
+        const size_t smem = (size_t)hidden * sizeof(float);
+        const FastDiv atom_div = make_fast_div((uint32_t)blk_mn);
+        auto launch = [&](auto kernel, std::atomic<int>& occ) {
+            const int per_sm = ctas_per_sm(kernel, smem, occ);
+            launch_hot(kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, as_stream(stream), (const uint16_t*)table,
+                       (const uint16_t*)nullptr, (uint16_t*)h_out, weight, packed, scales, tokens, rows_total, eps, global_scale,
+                       blk_mn, folded, atom_div, (const int*)ids);
+        };
+        static std::atomic<int> occ[2];
+        if (hidden == 2048) launch(rms_norm_quant_hot_kernel<4, false, true>, occ[0]);
+        else launch(rms_norm_quant_hot_kernel<8, false, true>, occ[1]);
+        return check_launch(what);
+    }
+    if (int r = clef_embed_gather(stream, table, ids, h_out, tokens, hidden, dtype)) return r;
+    return rms_norm_quantise_impl(what, stream, h_out, nullptr, nullptr, weight, packed, scales, tokens, hidden, eps, global_scale,
+                                  blk_mn, chunk, dtype, sf_layout);
+}
+
+int clef_embed_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* table, const int32_t* ids, void* h_out,
+                                       const float* weight, uint8_t* packed, uint8_t* scales, int tokens, int hidden,
+                                       float eps, float global_scale, int blk_mn, int chunk, int dtype) {
+    return embed_rms_norm_quantise_impl("clef_embed_rms_norm_quantise_nvfp4", stream, table, ids, h_out, weight, packed, scales,
+                                        tokens, hidden, eps, global_scale, blk_mn, chunk, dtype, CLEF_SF_DEFAULT);
+}
+
+int clef_embed_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, const void* table, const int32_t* ids, void* h_out,
+                                          const float* weight, uint8_t* packed, uint8_t* scales, int tokens, int hidden,
+                                          float eps, float global_scale, int blk_mn, int chunk, int dtype, int sf_layout) {
+    return embed_rms_norm_quantise_impl("clef_embed_rms_norm_quantise_nvfp4_ex", stream, table, ids, h_out, weight, packed,
+                                        scales, tokens, hidden, eps, global_scale, blk_mn, chunk, dtype, sf_layout);
 }
 
 // ---- gated rms_norm family -------------------------------------------------------------------------

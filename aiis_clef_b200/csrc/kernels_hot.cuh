@@ -206,12 +206,16 @@ static __device__ __noinline__ void rms_block_cold(const uint16_t* xblk, const f
 // in front); that sum is also written to sum_out, which may be x itself. The sum is rounded to bf16 before
 // the norm, so the result equals the add followed by the plain kernel on the stored residual. This variant
 // loads at the top of each row instead of one row ahead (two inputs would not fit the register budget).
-template <int NB, bool ADD>
+// With EMBED the row is row ids[row] of the table `x` (the embedding gather of kernels/elementwise.cu:396-407
+// fused in front) and is also copied to sum_out (the residual stream the layer goes on with): the first layer's
+// gather and norm + quantiser in one pass over the row.
+template <int NB, bool ADD, bool EMBED = false>
 __global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? CLEF_RMS_MIN_CTAS : 1))
 rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ addend, uint16_t* sum_out,
                           const float* __restrict__ weight, uint8_t* __restrict__ packed,
                           uint8_t* __restrict__ scales, int rows, int rows_total, float eps, float global_scale,
-                          int blk_mn, int chunk, FastDiv atom_div) {
+                          int blk_mn, int chunk, FastDiv atom_div, const int* __restrict__ ids) {
+    static_assert(!(ADD && EMBED), "one fused producer at a time");
     constexpr int COLS = NB * 512;
     constexpr int BLOCKS = COLS / 16;
     __shared__ float s_inv[kInvScaleTableSize];
@@ -231,7 +235,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
         s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
     }
     int row = blockIdx.x * 8 + warp;
-    if (row < rows) {   // this warp's first row towards L2 (a lane covers 128 bytes); see prefetch_l2
+    if (!EMBED && row < rows) {   // this warp's first row towards L2 (a lane covers 128 bytes); see prefetch_l2
 #pragma unroll
         for (int h = 0; h < NB / 4; ++h) {
             prefetch_l2(x + (size_t)row * COLS + (size_t)(lane + 32 * h) * 64);
@@ -239,11 +243,14 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
         }
     }
     pdl_wait_prior_grids();
+    // (the token ids are an activation of the pass: they are read after the wait, so there is no early hint for EMBED)
+    auto source_row = [&](int r) { return x + (size_t)(EMBED ? __ldg(ids + r) : r) * COLS; };
     U8x32 d[NB];
     if (!ADD && row < rows) {
+        const uint16_t* src = source_row(row);
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
+            d[j] = ldg_stream_v8(src + (size_t)(lane + 32 * j) * 16);
         }
     }
     __syncthreads();
@@ -262,6 +269,9 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
             }
             continue;
         }
+        // EMBED: the next row's table row is known one row ahead, so that its loads can go out below.
+        const int next = row + gridDim.x * 8;
+        const uint16_t* next_src = (!ADD && next < rows) ? source_row(next) : nullptr;
         // Unpack once; partial sums P[j & 1][k] in-lane over j (stride 2, ascending), as the reference thread does.
         f32x2 v[NB][8];
         float p[2][4];
@@ -281,6 +291,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
             float quad[4];
+            if (EMBED) stg_v8(sum_out + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16, d[j]);   // the gathered row
             unpack16_quadpairs(d[j], v[j]);
             if (ADD) {
                 f32x2 t[8];
@@ -300,11 +311,10 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
             }
         }
         // The raw registers are free now: fetch this warp's next row while the current one is processed.
-        const int next = row + gridDim.x * 8;
         if (!ADD && next < rows) {
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
-                d[j] = ldg_stream_v8(x + (size_t)next * COLS + (size_t)(lane + 32 * j) * 16);
+                d[j] = ldg_stream_v8(next_src + (size_t)(lane + 32 * j) * 16);
             }
         }
         const float inv = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
@@ -331,8 +341,8 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
             for (int j = 0; j < NB; ++j) {
                 if (bad & (1u << j)) {
                     const int b = lane + 32 * j;
-                    // ADD: this lane stored the block's sum above, so it reads its own bytes back.
-                    rms_block_cold((ADD ? (const uint16_t*)sum_out : x) + (size_t)row * COLS + b * 16, weight + b * 16, inv,
+                    // ADD, EMBED: this lane stored the block's row above, so it reads its own bytes back.
+                    rms_block_cold(((ADD || EMBED) ? (const uint16_t*)sum_out : x) + (size_t)row * COLS + b * 16, weight + b * 16, inv,
                                    global_scale, reinterpret_cast<uint2*>(prow + b * 8),
                                    srow + (size_t)(b >> 2) * chunk + (b & 3));
                 }

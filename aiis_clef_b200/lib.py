@@ -57,6 +57,8 @@ SYMBOLS = {
     "clef_sigmoid_mul_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
     "clef_add": (_I, [_P, _P, _P, _P, _SZ, _I]),
     "clef_add_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
+    "clef_embed_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
+    "clef_embed_rms_norm_quantise_nvfp4_ex": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I, _I]),
     "clef_quantise_fp8": (_I, [_P, _P, _P, _P, _I, _I, _I]),
     "clef_swiglu_quantise_fp8": (_I, [_P, _P, _P, _P, _P, _I, _I, _I]),
     "clef_rms_norm_fp8_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I]),
@@ -428,6 +430,21 @@ class Device:
                                                              blk_mn, chunk, _dtype_code(a)),
                    "clef_add_rms_norm_quantise_nvfp4")
         return sum_out, packed, scales
+
+    def embed_rms_norm_quantise_nvfp4_dev(self, table, ids, weight, tokens: int, hidden: int, eps: float, global_scale: float,
+                                          tile_m: int, h_out=None):
+        """embed_gather_dev followed by rms_norm_quantise_nvfp4_dev on the gathered rows, one pass; returns
+        (h, packed, scales)."""
+        _dev_tensor(table, "table"), _dev_tensor(ids, "ids")
+        if h_out is None:
+            h_out = self._empty((tokens, hidden), table.dtype)
+        blk_mn, chunk, _, packed, scales = self._quant_outputs(tokens, hidden, tile_m)
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_embed_rms_norm_quantise_nvfp4(_stream(), _ptr(table), _ptr(ids), _ptr(h_out), _ptr(weight),
+                                                               _ptr(packed), _ptr(scales), tokens, hidden, eps, global_scale,
+                                                               blk_mn, chunk, _dtype_code(table)),
+                   "clef_embed_rms_norm_quantise_nvfp4")
+        return h_out, packed, scales
 
     # ==== FP8 (E4M3) activation quantisers ======================================================
 

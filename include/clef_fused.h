@@ -223,6 +223,16 @@ int clef_add_rms_norm_quantise_nvfp4(clef_stream_t stream, void* sum_out, const 
                                      const float* weight, uint8_t* packed, uint8_t* scales, int rows, int cols,
                                      float eps, float global_scale, int blk_mn, int chunk, int dtype);
 
+/* The first layer's token-embedding gather and its norm + quantiser in one pass over the gathered row
+ * (embed_dev followed by fused_norm_quantise_nvfp4, src/gpu.rs:1792-1798 and :461-474): row t of the table row
+ * ids[t] is copied to h_out[t] (the residual stream) and rms_norm_quantise_nvfp4 of it goes to packed/scales.
+ * Bytes equal clef_embed_gather followed by clef_rms_norm_quantise_nvfp4 on h_out. One kernel for bf16 and
+ * hidden 2048 or 4096 (9H/2 + 9H/16 + 4 bytes per row instead of 13H/2 + 9H/16 + 4); other shapes run the two
+ * entry points. No counterpart as ONE kernel in the reference. */
+int clef_embed_rms_norm_quantise_nvfp4(clef_stream_t stream, const void* table, const int32_t* ids, void* h_out,
+                                       const float* weight, uint8_t* packed, uint8_t* scales, int tokens, int hidden,
+                                       float eps, float global_scale, int blk_mn, int chunk, int dtype);
+
 /* ------------------------------------------------------------------------------------------------
  * FP8 (E4M3) activation quantisers, for the FP8 projections of a mixed NVFP4 + FP8 checkpoint.
  * Per quantised row: scale = amax / 448, stored as the upper 16 bits of that f32 (one uint16 per row);
@@ -346,6 +356,9 @@ int clef_sigmoid_mul_quantise_nvfp4_ex(clef_stream_t stream, const void* x, cons
 int clef_add_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, void* sum_out, const void* a, const void* b,
                                         const float* weight, uint8_t* packed, uint8_t* scales, int rows, int cols,
                                         float eps, float global_scale, int blk_mn, int chunk, int dtype, int sf_layout);
+int clef_embed_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, const void* table, const int32_t* ids, void* h_out,
+                                          const float* weight, uint8_t* packed, uint8_t* scales, int tokens, int hidden,
+                                          float eps, float global_scale, int blk_mn, int chunk, int dtype, int sf_layout);
 
 /* Kernel selection for tests and measurements: 0 = automatic (tuned kernel when the shape has one),
  * 1 = always the shape-general kernel. Process-wide; not part of the reference interface. */

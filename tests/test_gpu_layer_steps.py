@@ -399,3 +399,45 @@ def test_rope_qk_and_rope_qkv_write_equal_the_separate_calls(rows, q_heads, kv_h
     n = min(rows, 4)
     assert torch.equal(c2[0][7:7 + n], want_k[:n].to(torch.bfloat16)) and torch.equal(c2[1][7:7 + n], v[:n].to(torch.bfloat16))
     assert (c2[0][:7].float() == -1.0).all() and (c2[0][7 + n:].float() == -1.0).all()
+
+
+# ---- the first layer's gather and norm + quantiser in one pass ------------------------------------------------------------
+@pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
+@pytest.mark.parametrize("dtype", [BF16, F32], ids=["bf16", "f32"])
+@pytest.mark.parametrize("tokens,hidden,vocab", [(1, 2048, 50), (778, 2048, 32768), (129, 4096, 1000), (8192, 2048, 32768), (65, 1024, 300)])
+def test_embed_rms_norm_quantise_equals_the_two_calls(tokens, hidden, vocab, dtype, choice):
+    """clef_embed_rms_norm_quantise_nvfp4 == clef_embed_gather, then clef_rms_norm_quantise_nvfp4 on the gathered rows
+    (each compared with the reference kernels in test_gpu_parity_*.py), byte for byte, h included; and against the CPU
+    oracle of the 778-row configuration's chain."""
+    clef.set_kernel_choice(choice)
+    rng = np.random.default_rng(tokens + hidden)
+    tbits = normal_bf16(rng, (vocab, hidden), scale=0.02, outlier_channels=8)
+    table = dev_bf16(tbits) if dtype == BF16 else dev_f32_from_bits(tbits)
+    ids_np = rng.integers(0, vocab, tokens).astype(np.int32)
+    ids_np[-1] = vocab - 1
+    ids = i32(ids_np)
+    w_np = (rng.standard_normal(hidden) * 0.1).astype(np.float32)
+    w = torch.from_numpy(w_np).cuda()
+    dev = clef.Device(0)
+    gs = 448.0 * 6.0 / 30.0
+    want_h = dev.embed_gather_dev(table, ids, tokens, hidden)
+    want_p, want_s = dev.rms_norm_quantise_nvfp4_dev(want_h, w, tokens, hidden, 1e-6, gs, 128)
+    got_h, got_p, got_s = dev.embed_rms_norm_quantise_nvfp4_dev(table, ids, w, tokens, hidden, 1e-6, gs, 128)
+    torch.cuda.synchronize()
+    assert got_h.dtype == want_h.dtype and torch.equal(got_h, want_h)
+    assert torch.equal(got_p, want_p) and torch.equal(got_s, want_s)
+    cpu_p, cpu_s = orc.rms_norm_quantise_nvfp4(tbits[ids_np], w_np, tokens, hidden, 1e-6, gs)
+    assert_bytes_equal(got_s.cpu().numpy(), cpu_s, "scales vs CPU oracle")
+    assert_bytes_equal(got_p.cpu().numpy().reshape(-1), cpu_p, "packed vs CPU oracle")
+    # interleaved scale-tile order per call
+    rp = (tokens + 127) // 128 * 128
+    pk, sc, h2 = Guarded(rp * hidden // 2), Guarded(rp * hidden // 16), torch.empty_like(want_h)
+    assert call("clef_embed_rms_norm_quantise_nvfp4_ex", stream(), ptr(table), ptr(ids), ptr(h2), ptr(w), pk.ptr, sc.ptr, tokens,
+                hidden, 1e-6, gs, 128, 512, dtype, 1) == 0
+    pk2, sc2 = Guarded(rp * hidden // 2), Guarded(rp * hidden // 16)
+    assert call("clef_rms_norm_quantise_nvfp4_ex", stream(), ptr(want_h), ptr(w), pk2.ptr, sc2.ptr, tokens, hidden, 1e-6, gs, 128,
+                512, dtype, 1) == 0
+    torch.cuda.synchronize()
+    pk.check_guards("packed")
+    sc.check_guards("scales")
+    assert np.array_equal(pk.bytes(), pk2.bytes()) and np.array_equal(sc.bytes(), sc2.bytes()) and torch.equal(h2, want_h)
