@@ -92,12 +92,13 @@ __device__ __forceinline__ uint32_t e2m1_pack8(float e0, float e1, float e2, flo
 // global memory, literally, and overwrites what was stored). Keeping the literal path out of this function
 // keeps address-taken arrays and call set-up out of the hot loop.
 //
-// Fast domain: the block's scale is a normal, unclamped E4M3 code (8 <= code <= 0x7E), or the block is all
-// zeros. With 2^-64 <= global_scale <= 2^64 (the launchers send other scales to the shape-general kernels)
-// a normal code implies amax >= 2^-68, where the short division by six is exact, and a scaled maximum
-// amax * inv_scale within a rounding step of 6, far inside the FP4 converter's domain; a NaN or an infinity
-// in the block makes the scale argument NaN or infinite, whose code is out of range. What falls outside is
-// rare in activations: scale arguments below 2^-6 (subnormal codes), above 448 (clamped), non-finite values.
+// Fast domain: the block's scale argument sv = (amax / 6) * global_scale lies in [2^-6, 2^30) (a normal E4M3
+// code, clamped to 0x7E from 448 up as the reference clamps it), or the block is all zeros. With
+// 2^-64 <= global_scale <= 2^64 (the launchers send other scales to the shape-general kernels) sv >= 2^-6
+// implies amax >= 2^-68, where the short division by six is exact; sv < 2^30 keeps the scaled maximum
+// amax * inv_scale below 6 * 2^30 / 448 < 2^24, inside the FP4 converter's domain (which saturates at 6 as the
+// reference does); a NaN or an infinity in the block makes sv NaN or infinite, whose code is out of range. What
+// falls outside is rare in activations: scale arguments below 2^-6 (subnormal codes) and non-finite values.
 // For an all-zero block the codes come out as zeros whatever table entry is read, and the scale byte is 0.
 // NEG: the pairs hold the NEGATED values (the SwiGLU fast path produces -v); magnitudes are unaffected
 // and the sign is restored by scaling with -inv_scale.
@@ -112,8 +113,9 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
     const float sv = __fmul_rn(div_six_fast(amax), global_scale);
     // e4m3_encode_finite's normal branch: round the 3-bit mantissa half up by an integer add, rebase the exponent
     const uint32_t code = ((__float_as_uint(sv) + 0x00080000u) >> 20) - (120u << 3);
-    const bool normal = (code - 8u) <= 0x76u;
-    const float inv = inv_table[code & (uint32_t)(kInvScaleTableSize - 1)];
+    const bool normal = (code - 8u) < 288u;          // 2^-6 <= sv < 2^30 (code 296 is the first with exponent 30)
+    const uint32_t stored = min(code, 0x7Eu);        // the reference's clamp; also a safe table index for any code
+    const float inv = inv_table[stored];
     constexpr float kNudge = -4.33488326e-08f;   // see e2m1x2_fast
     const f32x2 inv2 = f2_splat(NEG ? -inv : inv);
     const f32x2 nudge2 = f2_splat(kNudge);
@@ -124,7 +126,7 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
         p[i] = f2_fma(t, nudge2, t);
     }
     // quad q: p[2q] = (x, z), p[2q+1] = (y, w); element order x, y, z, w
-    stored_out = normal ? code : 0u;
+    stored_out = normal ? stored : 0u;
     lo_out = e2m1_pack8(p[0].x, p[1].x, p[0].y, p[1].y, p[2].x, p[3].x, p[2].y, p[3].y);
     hi_out = e2m1_pack8(p[4].x, p[5].x, p[4].y, p[5].y, p[6].x, p[7].x, p[6].y, p[7].y);
     return normal || amax == 0.0f;

@@ -3,20 +3,28 @@
 
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torchrun, one rank per GPU)
     python bench.py --impl reference ...                     (the reference arithmetic on the host cores)
+    python bench.py --profile-case KERNEL[,KERNEL...]        (three launches of the named entry points, for ncu)
 
 A step is one pass of the hot path over one 8,192-row chunk (hidden 2048, bf16 activations, fp32
 math): RMSNorm+NVFP4, SwiGLU(2x6144)+NVFP4, partial RoPE on 16 q and 2 kv heads x 128 (rotary 64,
 theta 1e7, cpos = 0..8191). Inputs are seeded synthetic tensors already resident in HBM; buffer
 sets rotate so no step can be served from L2. Rank 0 prints ONE JSON line: rows/s over all ranks
-(`value`, device-timed, max over ranks), the end-to-end figure through the host-slice C-ABI with
-host<->device copies inside the timed region (`e2e`), the HBM roofline of the dominant kernel
-(`roofline`), the CPU restatement timed on the host cores (`cpu_baseline`), clocks and per-kernel
-details. Every rank works on its own chunk (weak scaling); the path has no collective.
+(`value`: K graph replays per batch, the median of five batches, device-timed, max over ranks), the
+end-to-end figure through the host-slice C-ABI with host<->device copies inside the timed region
+(`e2e`), the HBM roofline of the dominant kernel (`roofline`), the CPU restatement timed on the host
+cores (`cpu_baseline`), clocks, per-kernel figures (each kernel rotating over at least three L2
+sizes of its own buffers), the 130,712-row pass sharded by row range over the ranks as one CUDA graph
+(strong scaling, with a check that the shards' bytes equal a single-GPU run's), and on one GPU the
+benchmark definition's other configurations (the gated chain in four chunks, the 130,712-row pass as
+rung-sized passes, the rung sweep with four coalesced requests). Every rank works on its own chunk
+in the headline (weak scaling); the path has no collective.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
+import math
 import os
 import subprocess
 import sys
@@ -39,8 +47,10 @@ CONV_DIM, CONV_K = 8192, 4   # GDN convolution: 2 x 16 x 128 (q, k) + 32 x 128 (
 VOCAB = 32768
 EPS = 1e-6
 GS_NORM, GS_SWIGLU, GS_GATED = 64.0, 48.0, 96.0     # per-projection input_global_scale stand-ins
-NSETS = 4                    # rotating buffer sets (each far larger than L2)
+NSETS = 4                    # rotating buffer sets of the step (each far larger than L2)
 FULL_ROWS = 130712
+BATCHES = 5                  # timed batches per figure; the median is reported
+ROTATE_BYTES = 400e6         # a kernel timed alone rotates over at least this much of its own buffers (3 x the 126 MB L2)
 
 # Algorithmic bytes per row (inputs read once + outputs written once; shared vectors excluded).
 BYTES_PER_ROW = {
@@ -51,6 +61,8 @@ BYTES_PER_ROW = {
     "rope_qk": 2 * (Q_HEADS + KV_HEADS) * HEAD_DIM * 2 + 4 + 2 * (ROTARY // 2) * 4,           # 9,476 (q and k, one launch)
     "embed_gather": 4 + 2 * HIDDEN + 2 * HIDDEN,                                              # 8,196
     "rms_norm_gated_quantise_nvfp4": 2 * 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,             # 9,344
+    # the first layer's gather and norm + quantiser in one pass (writes h too)
+    "embed_rms_norm_quantise_nvfp4": 4 + 2 * HIDDEN + 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,   # 9,348
     # the unfused entry points (what the engine runs when a fusion is switched off), bf16 in and out
     "quantise_nvfp4": 2 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,                                # 5,248
     "rms_norm": 2 * HIDDEN + 2 * HIDDEN,                                                      # 8,192
@@ -76,18 +88,17 @@ BYTES_PER_ROW = {
     # the scan's operands from the convolved row (16 q/k heads, 32 v heads of 128): bf16 row in; q and k as bf16
     # hi + lo pairs for 32 expanded heads, normalised k and v as f32 out
     "gdn_prep": 2 * CONV_DIM + 4 * 32 * 128 * 2 + 2 * 32 * 128 * 4,                           # 81,920
-    "gdn_conv_prep": 2 * CONV_DIM + 4 + 4 * 32 * 128 * 2 + 2 * 32 * 128 * 4,                  # 81,924 (conv + prep, one launch)
 }
 # The step: RMSNorm+NVFP4, SwiGLU+NVFP4, and the partial RoPE of the q and the k heads, which share their positions
 # and go out as one launch (clef_rope_qk); rope_q / rope_k alone are reported under "kernels".
 STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk"]
 FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk",
-                "rms_norm_gated_quantise_nvfp4"]     # config 4: the full fused chain over 130,712 rows
+                "rms_norm_gated_quantise_nvfp4"]     # the full fused chain over 130,712 rows
 DOMINANT = "swiglu_quantise_nvfp4"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel at 8,192 rows, from
-# the ncu capture summarised in profiles/. Reads equal the input bytes; part of the output is still in
-# L2 when the kernel ends, which is why the total is below the algorithmic 229.6 MB.
-DOMINANT_TRAFFIC_BYTES = 220_115_456   # 201.36 MB read + 18.75 MB written (profiles/hot_kernels_8192rows_ncu_full.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel at 8,192 rows: read from a small
+# text file under profiles/ that also records a hash of the kernel sources it was measured on.
+TRAFFIC_FILE = ROOT / "profiles" / "swiglu_quantise_nvfp4_8192rows_dram_traffic.txt"
+KERNEL_SOURCES = ["kernels_hot.cuh", "nvfp4_codec.cuh", "common.cuh", "f32x2.cuh"]
 
 
 def measured_peak_gbs():
@@ -98,6 +109,31 @@ def measured_peak_gbs():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def kernel_sources_hash() -> str:
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        h.update((ROOT / "aiis_clef_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def dominant_traffic():
+    """(bytes per launch or None, note). The file holds `key: value` lines written from an ncu capture."""
+    if not TRAFFIC_FILE.exists():
+        return None, "no ncu capture recorded"
+    fields = {}
+    for line in TRAFFIC_FILE.read_text().splitlines():
+        if ":" in line and not line.lstrip().startswith("#"):
+            k, v = line.split(":", 1)
+            fields[k.strip()] = v.strip()
+    try:
+        total = int(fields["dram_bytes_read"]) + int(fields["dram_bytes_write"])
+    except (KeyError, ValueError):
+        return None, "capture file unreadable"
+    same = fields.get("kernel_sources_sha256_16") == kernel_sources_hash()
+    note = f"ncu capture of {fields.get('captured', '?')}" + ("" if same else "; the kernel sources have changed since that capture")
+    return total, note
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -231,95 +267,164 @@ def workload_config():
         "workload": "configs[1]: one 8,192-row chunk per GPU, hidden 2048 bf16: RMSNorm+NVFP4; SwiGLU 2x6144 "
                     "+NVFP4; partial RoPE 16 q / 2 kv heads x 128, rotary 64, theta 1e7, cpos = 0..8191",
         "rows_per_gpu": ROWS, "hidden": HIDDEN, "intermediate": INTER, "activation_storage": "bf16",
-        "l2": f"inputs larger than L2: {NSETS} rotating buffer sets of about 0.37 GB each",
+        "l2": f"inputs larger than L2: {NSETS} rotating buffer sets of about 0.37 GB each; a kernel timed alone rotates over "
+              f"at least {ROTATE_BYTES / 1e6:.0f} MB of its own buffers",
         "launch": "one CUDA graph replay per step (3 kernels)", "parallelism": "row-range replicas, no collective",
+        "timing": f"median of {BATCHES} batches of `steps` replays, CUDA events, max over ranks",
     }
 
 
 # ---------------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------------
-def run_gpu_arm(args):
-    import ctypes
+class Recorder(dict):
+    """A buffer set that remembers which of its tensors a launcher touched."""
 
-    import torch
-    import torch.distributed as dist
+    def __init__(self, base):
+        super().__init__(base)
+        self.used = []
 
-    import aiis_clef_b200 as clef
+    def __getitem__(self, key):
+        if key not in self.used:
+            self.used.append(key)
+        return super().__getitem__(key)
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus > 1 and world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    lib = clef.load()
-    dev = clef.Device(local_rank)
 
-    def p(t):
-        return ctypes.c_void_p(t.data_ptr())
+class Harness:
+    """Device buffers, C-ABI launch closures and graph-replayed timing shared by the sections of the GPU arm."""
 
-    def stream():
-        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    def __init__(self, args):
+        import ctypes
 
-    def ok(status):
+        import torch
+        import torch.distributed as dist
+
+        import aiis_clef_b200 as clef
+
+        self.torch, self.dist, self.clef, self.ctypes = torch, dist, clef, ctypes
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if args.gpus > 1 and self.world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={self.world})")
+        torch.cuda.set_device(self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+        self.lib = clef.load()
+        self.dev = clef.Device(self.local_rank)
+        self.gen = torch.Generator(device="cuda")
+        self.gen.manual_seed(1000 + self.rank)
+        self.launches = 0
+
+    # -- small helpers ----------------------------------------------------------------------------------
+    def p(self, t):
+        return None if t is None else self.ctypes.c_void_p(t.data_ptr())
+
+    def stream(self):
+        return self.ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def ok(self, status):
         if status != 0:
-            raise RuntimeError(f"C-ABI call failed ({status}): {clef.lib.last_error()}")
+            raise RuntimeError(f"C-ABI call failed ({status}): {self.clef.lib.last_error()}")
 
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(1000 + rank)
+    def randn_bf16(self, *shape, gen=None):
+        t = self.torch
+        return t.randn(*shape, device="cuda", generator=gen or self.gen, dtype=t.float32).to(t.bfloat16)
 
-    def randn_bf16(*shape):
-        return torch.randn(*shape, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    def u8(self, n):
+        return self.torch.empty(n, dtype=self.torch.uint8, device="cuda")
 
-    rows_padded, pk_h, sc_h = clef.nvfp4_sizes(ROWS, HIDDEN, 128)
-    _, pk_i, sc_i = clef.nvfp4_sizes(ROWS, INTER, 128)
-    w_norm = (torch.randn(HIDDEN, device="cuda", generator=gen) * 0.1).contiguous()
-    w_gated = (1.0 + torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
-    cpos = torch.arange(ROWS, dtype=torch.int32, device="cuda")
-    cos, sin = dev.rope_tables_dev(cpos, ROWS, ROTARY, THETA)
-    table = randn_bf16(VOCAB, HIDDEN) * 0.02
-    sets = []
-    for _ in range(NSETS):
-        x = randn_bf16(ROWS, HIDDEN)
-        x[:, torch.randperm(HIDDEN, device="cuda", generator=gen)[:8]] *= 20.0
-        sets.append({
-            "x": x, "gate": randn_bf16(ROWS, INTER), "up": randn_bf16(ROWS, INTER),
-            "q": randn_bf16(ROWS, Q_HEADS, HEAD_DIM), "k": randn_bf16(ROWS, KV_HEADS, HEAD_DIM),
-            "o": randn_bf16(ROWS * VH, HEAD_DIM), "z": randn_bf16(ROWS * VH, HEAD_DIM),
-            "ids": torch.randint(0, VOCAB, (ROWS,), device="cuda", generator=gen, dtype=torch.int32),
-            "pk_h": torch.empty(pk_h, dtype=torch.uint8, device="cuda"), "sc_h": torch.empty(sc_h, dtype=torch.uint8, device="cuda"),
-            "pk_i": torch.empty(pk_i, dtype=torch.uint8, device="cuda"), "sc_i": torch.empty(sc_i, dtype=torch.uint8, device="cuda"),
-            "pk_g": torch.empty(pk_h, dtype=torch.uint8, device="cuda"), "sc_g": torch.empty(sc_h, dtype=torch.uint8, device="cuda"),
-            "q_out": torch.empty(ROWS, Q_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
-            "k_out": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
-            "h": torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16, device="cuda"),
-            "act_i": torch.empty(ROWS, INTER, dtype=torch.bfloat16, device="cuda"),
-            "g_out": torch.empty(ROWS * VH, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
-            "v": randn_bf16(ROWS, KV_HEADS, HEAD_DIM), "res": randn_bf16(ROWS, HIDDEN),
-            "cache_k": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
-            "cache_v": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda"),
-            "sum": torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16, device="cuda"),
-            "q8_h": torch.empty(ROWS, HIDDEN, dtype=torch.uint8, device="cuda"),
-            "q8_i": torch.empty(ROWS, INTER, dtype=torch.uint8, device="cuda"),
-            "s8": torch.empty(ROWS, dtype=torch.int16, device="cuda"),
-            "mixed": randn_bf16(ROWS, CONV_DIM), "conv_out": torch.empty(ROWS, CONV_DIM, dtype=torch.bfloat16, device="cuda"),
-            "qg256": randn_bf16(ROWS, Q_HEADS, 512), "q256": torch.empty(ROWS, Q_HEADS, 256, dtype=torch.bfloat16, device="cuda"),
-            "gate256": torch.empty(ROWS, Q_HEADS, 256, dtype=torch.bfloat16, device="cuda"),
-        })
-    w_conv = (torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5).contiguous()
-    gdn_bytes = 32 * ((ROWS + 63) // 64) * 2 * 64 * 128     # one set of operand buffers (0.5 GB of outputs, far above L2)
-    gdn_ops = [torch.empty(gdn_bytes, dtype=torch.uint8, device="cuda") for _ in range(4)]
-    gdn_kn = torch.empty(ROWS, 32 * 128, dtype=torch.float32, device="cuda")
-    gdn_v = torch.empty(ROWS, 32 * 128, dtype=torch.float32, device="cuda")
-    seq_start = torch.zeros(ROWS, dtype=torch.int32, device="cuda")
-    cache_map = torch.randperm(ROWS, device="cuda", generator=gen).to(torch.int32)   # the engine's cpos: a slot per token
-    w_head = (torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1).contiguous()
-    w_head256 = (torch.randn(256, device="cuda", generator=gen) * 0.1).contiguous()
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
 
-    launchers = {
+    def max_over_ranks(self, values: list[float]) -> list[float]:
+        if self.world == 1:
+            return list(values)
+        t = self.torch.tensor(values, device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.cpu().tolist()
+
+    # -- timing -----------------------------------------------------------------------------------------
+    def capture(self, launches):
+        """One CUDA graph holding `launches` (closures that return a C-ABI status) in order."""
+        torch = self.torch
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for fn in launches:
+                self.ok(fn())
+        return g
+
+    def time_graphs(self, graphs, replays: int, batches: int = BATCHES, sync_ranks: bool = False):
+        """Milliseconds per batch of `replays` replays (graphs taken round-robin), one entry per batch."""
+        torch = self.torch
+        for g in graphs[: max(1, min(len(graphs), 3))]:
+            g.replay()
+        torch.cuda.synchronize()
+        out = []
+        for _ in range(batches):
+            if sync_ranks:
+                self.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for i in range(replays):
+                graphs[i % len(graphs)].replay()
+            e.record()
+            if sync_ranks:
+                self.barrier()
+            else:
+                torch.cuda.synchronize()
+            out.append(s.elapsed_time(e))
+        return out
+
+
+def make_step_set(h: Harness):
+    """One buffer set holding every tensor the timed entry points use at 8,192 rows."""
+    torch = h.torch
+    rows_padded, pk_h, sc_h = h.clef.nvfp4_sizes(ROWS, HIDDEN, 128)
+    _, pk_i, sc_i = h.clef.nvfp4_sizes(ROWS, INTER, 128)
+    x = h.randn_bf16(ROWS, HIDDEN)
+    x[:, torch.randperm(HIDDEN, device="cuda", generator=h.gen)[:8]] *= 20.0
+    bf = torch.bfloat16
+    return {
+        "x": x, "gate": h.randn_bf16(ROWS, INTER), "up": h.randn_bf16(ROWS, INTER),
+        "q": h.randn_bf16(ROWS, Q_HEADS, HEAD_DIM), "k": h.randn_bf16(ROWS, KV_HEADS, HEAD_DIM),
+        "o": h.randn_bf16(ROWS * VH, HEAD_DIM), "z": h.randn_bf16(ROWS * VH, HEAD_DIM),
+        "ids": torch.randint(0, VOCAB, (ROWS,), device="cuda", generator=h.gen, dtype=torch.int32),
+        "pk_h": h.u8(pk_h), "sc_h": h.u8(sc_h), "pk_i": h.u8(pk_i), "sc_i": h.u8(sc_i), "pk_g": h.u8(pk_h), "sc_g": h.u8(sc_h),
+        "q_out": torch.empty(ROWS, Q_HEADS, HEAD_DIM, dtype=bf, device="cuda"),
+        "k_out": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=bf, device="cuda"),
+        "h": torch.empty(ROWS, HIDDEN, dtype=bf, device="cuda"),
+        "act_i": torch.empty(ROWS, INTER, dtype=bf, device="cuda"),
+        "g_out": torch.empty(ROWS * VH, HEAD_DIM, dtype=bf, device="cuda"),
+        "v": h.randn_bf16(ROWS, KV_HEADS, HEAD_DIM), "res": h.randn_bf16(ROWS, HIDDEN),
+        "cache_k": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=bf, device="cuda"),
+        "cache_v": torch.empty(ROWS, KV_HEADS, HEAD_DIM, dtype=bf, device="cuda"),
+        "sum": torch.empty(ROWS, HIDDEN, dtype=bf, device="cuda"),
+        "q8_h": h.u8(ROWS * HIDDEN), "q8_i": h.u8(ROWS * INTER),
+        "s8": torch.empty(ROWS, dtype=torch.int16, device="cuda"),
+        "mixed": h.randn_bf16(ROWS, CONV_DIM), "conv_out": torch.empty(ROWS, CONV_DIM, dtype=bf, device="cuda"),
+        "qg256": h.randn_bf16(ROWS, Q_HEADS, 512), "q256": torch.empty(ROWS, Q_HEADS, 256, dtype=bf, device="cuda"),
+        "gate256": torch.empty(ROWS, Q_HEADS, 256, dtype=bf, device="cuda"),
+        "gdn_ops": h.u8(4 * 32 * ((ROWS + 63) // 64) * 2 * 64 * 128),     # the scan's four operand tensors, back to back
+        "gdn_kn": torch.empty(ROWS, 32 * 128, dtype=torch.float32, device="cuda"),
+        "gdn_v": torch.empty(ROWS, 32 * 128, dtype=torch.float32, device="cuda"),
+    }
+
+
+def make_launchers(h: Harness, shared: dict):
+    """name -> closure(buffer set) -> C-ABI status, at 8,192 rows."""
+    lib, p, stream = h.lib, h.p, h.stream
+    rows_padded = (ROWS + 127) // 128 * 128
+    w_norm, w_gated, cos, sin, cpos, table = (shared[k] for k in ("w_norm", "w_gated", "cos", "sin", "cpos", "table"))
+    w_conv, seq_start, cache_map, w_head, w_head256 = (shared[k] for k in ("w_conv", "seq_start", "cache_map", "w_head", "w_head256"))
+    op_bytes = 32 * ((ROWS + 63) // 64) * 2 * 64 * 128
+
+    def ops(d, i):
+        return h.ctypes.c_void_p(d["gdn_ops"].data_ptr() + i * op_bytes)
+
+    return {
         "rms_norm_quantise_nvfp4": lambda d: lib.clef_rms_norm_quantise_nvfp4(
             stream(), p(d["x"]), p(w_norm), p(d["pk_h"]), p(d["sc_h"]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, 0),
         "swiglu_quantise_nvfp4": lambda d: lib.clef_swiglu_quantise_nvfp4(
@@ -331,6 +436,8 @@ def run_gpu_arm(args):
         "rope_k": lambda d: lib.clef_rope(stream(), p(d["k_out"]), p(d["k"]), p(cos), p(sin), ROWS, KV_HEADS, HEAD_DIM,
                                           ROTARY, None, None, p(cpos), 0),
         "embed_gather": lambda d: lib.clef_embed_gather(stream(), p(table), p(d["ids"]), p(d["h"]), ROWS, HIDDEN, 0),
+        "embed_rms_norm_quantise_nvfp4": lambda d: lib.clef_embed_rms_norm_quantise_nvfp4(
+            stream(), p(table), p(d["ids"]), p(d["h"]), p(w_norm), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, 0),
         "rms_norm_gated_quantise_nvfp4": lambda d: lib.clef_rms_norm_gated_quantise_nvfp4(
             stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["pk_g"]), p(d["sc_g"]), rows_padded * VH, HEAD_DIM, EPS,
             GS_GATED, 128, 512, VH, ROWS * VH, 0),
@@ -338,7 +445,6 @@ def run_gpu_arm(args):
                                                             GS_NORM, 128, 512, 0),
         "rms_norm": lambda d: lib.clef_rms_norm(stream(), p(d["x"]), p(w_norm), p(d["h"]), ROWS, HIDDEN, EPS, 0),
         "swiglu": lambda d: lib.clef_swiglu(stream(), p(d["gate"]), p(d["up"]), p(d["act_i"]), ROWS * INTER, 0),
-        # (shares its output buffers with the gated quantiser above: neither is part of the checked step)
         "rms_norm_gated": lambda d: lib.clef_rms_norm_gated(stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["g_out"]),
                                                             ROWS * VH, HEAD_DIM, EPS, 0),
         "qk_norm_rope_q": lambda d: lib.clef_qk_norm_rope(stream(), p(d["q"]), p(w_head), p(cos), p(sin), p(d["h"]),
@@ -368,82 +474,169 @@ def run_gpu_arm(args):
                                                                       p(d["s8"]), ROWS, INTER, 0),
         "rms_norm_gated_quantise_fp8": lambda d: lib.clef_rms_norm_gated_quantise_fp8(
             stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["q8_h"]), p(d["s8"]), ROWS * VH, HEAD_DIM, EPS, VH, ROWS * VH, 0),
-        "gdn_prep": lambda d: lib.clef_gdn_prep(stream(), p(d["mixed"]), p(gdn_v), p(gdn_ops[0]), p(gdn_ops[1]), p(gdn_ops[2]),
-                                                p(gdn_ops[3]), p(gdn_kn), ROWS, 32, 16, 128, CONV_DIM, 128 ** -0.5, 0),
-        "gdn_conv_prep": lambda d: lib.clef_gdn_conv_prep(
-            stream(), p(d["mixed"]), p(w_conv), p(gdn_v), p(gdn_ops[0]), p(gdn_ops[1]), p(gdn_ops[2]), p(gdn_ops[3]), p(gdn_kn),
-            ROWS, CONV_DIM, CONV_K, p(seq_start), None, None, 32, 16, 128, 128 ** -0.5, 0),
+        "gdn_prep": lambda d: lib.clef_gdn_prep(stream(), p(d["mixed"]), p(d["gdn_v"]), ops(d, 0), ops(d, 1), ops(d, 2),
+                                                ops(d, 3), p(d["gdn_kn"]), ROWS, 32, 16, 128, CONV_DIM, 128 ** -0.5, 0),
         "causal_conv_silu": lambda d: lib.clef_causal_conv_silu(stream(), p(d["conv_out"]), p(d["mixed"]), p(w_conv), ROWS,
                                                                 CONV_DIM, CONV_K, p(seq_start), None, None, 0),
     }
 
-    def step_eager(d):
+
+def make_shared(h: Harness):
+    torch = h.torch
+    cpos = torch.arange(ROWS, dtype=torch.int32, device="cuda")
+    cos, sin = h.dev.rope_tables_dev(cpos, ROWS, ROTARY, THETA)
+    return {
+        "w_norm": (torch.randn(HIDDEN, device="cuda", generator=h.gen) * 0.1).contiguous(),
+        "w_gated": (1.0 + torch.randn(HEAD_DIM, device="cuda", generator=h.gen) * 0.1).contiguous(),
+        "cpos": cpos, "cos": cos, "sin": sin,
+        "table": h.randn_bf16(VOCAB, HIDDEN) * 0.02,
+        "w_conv": (torch.randn(CONV_DIM, CONV_K, device="cuda", generator=h.gen) * 0.5).contiguous(),
+        "seq_start": torch.zeros(ROWS, dtype=torch.int32, device="cuda"),
+        "cache_map": torch.randperm(ROWS, device="cuda", generator=h.gen).to(torch.int32),   # the engine's cpos: a slot per token
+        "w_head": (torch.randn(HEAD_DIM, device="cuda", generator=h.gen) * 0.1).contiguous(),
+        "w_head256": (torch.randn(256, device="cuda", generator=h.gen) * 0.1).contiguous(),
+    }
+
+
+def time_each_kernel(h: Harness, launchers, proto, steps: int):
+    """ms per launch of every entry point alone: a graph of launches that rotates over `sets` private copies of the
+    tensors the entry point touches (at least ROTATE_BYTES of them, so neither reads nor writes are served by L2)."""
+    torch = h.torch
+    out, sets_used = {}, {}
+    for name, fn in launchers.items():
+        rec = Recorder(proto)
+        h.ok(fn(rec))
+        torch.cuda.synchronize()
+        per_set = BYTES_PER_ROW[name] * ROWS
+        nsets = int(min(160, max(4, math.ceil(ROTATE_BYTES / per_set))))
+        sets = [proto]
+        for i in range(1, nsets):
+            d = dict(proto)
+            for key in rec.used:
+                t = proto[key]
+                if key == "ids":      # other token ids per set, so that the gathered table rows differ from launch to launch
+                    d[key] = torch.randint(0, VOCAB, t.shape, device="cuda", generator=h.gen, dtype=torch.int32)
+                else:
+                    d[key] = t.roll(i * 131, 0) if t.dim() > 1 else torch.empty_like(t)
+            sets.append(d)
+        per_graph = nsets * max(1, -(-12 // nsets))
+        graph = h.capture([(lambda d=sets[i % nsets]: fn(d)) for i in range(per_graph)])
+        replays = max(2, -(-max(steps, 24) // per_graph))
+        ms = h.time_graphs([graph], replays)
+        out[name] = float(np.median(ms)) / (replays * per_graph)
+        sets_used[name] = nsets
+        del graph, sets
+    return out, sets_used
+
+
+def run_gpu_arm(args):
+    h = Harness(args)
+    torch, clef, lib, p = h.torch, h.clef, h.lib, h.p
+    shared = make_shared(h)
+    launchers = make_launchers(h, shared)
+    sets = [make_step_set(h) for _ in range(NSETS)]
+
+    def step(d):
         for name in STEP_KERNELS:
-            ok(launchers[name](d))
+            h.ok(launchers[name](d))
 
     # One CUDA graph per buffer set: the reference replays one graph per pass geometry.
     for d in sets:
-        step_eager(d)
+        step(d)
     torch.cuda.synchronize()
     graphs = []
     for d in sets:
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            step_eager(d)
+            step(d)
         graphs.append(g)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(h.local_rank) if h.rank == 0 else None
     if sampler:
         sampler.start()
         time.sleep(0.5)          # let nvidia-smi come up: the timed region is only tens of milliseconds long
     for i in range(args.warmup):
         graphs[i % NSETS].replay()
-    barrier()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(args.steps):
-        graphs[i % NSETS].replay()
-    end.record()
-    barrier()
-    elapsed_ms = start.elapsed_time(end)
+    batch_ms = h.time_graphs(graphs, args.steps, BATCHES, sync_ranks=True)
+    batch_ms = h.max_over_ranks(batch_ms)
+    elapsed_ms = float(np.median(batch_ms))
 
-    # Per-kernel launch durations: the same buffers, each kernel alone, launched back to back from a CUDA
-    # graph (so the host launch rate does not limit kernels of a few microseconds), CUDA events on the
-    # launching stream around the replays.
-    kernel_ms = {}
-    per_graph = 3 * NSETS
-    for name, fn in launchers.items():
-        for i in range(NSETS):
-            ok(fn(sets[i]))
-        torch.cuda.synchronize()
-        kg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(kg):
-            for i in range(per_graph):
-                fn(sets[i % NSETS])
-        kg.replay()
-        torch.cuda.synchronize()
-        replays = max(2, -(-max(args.steps, 24) // per_graph))
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(replays):
-            kg.replay()
-        e.record()
-        torch.cuda.synchronize()
-        kernel_ms[name] = s.elapsed_time(e) / (replays * per_graph)
+    kernel_ms, kernel_sets = time_each_kernel(h, launchers, sets[0], args.steps)
     clocks = sampler.stop() if sampler else None
 
-    # ---- end to end: host buffers in, host buffers out, through the host-slice C-ABI ----------------------
-    hd = clef.HostDevice(local_rank)
-    d0 = sets[0]
+    e2e = end_to_end(h, args, sets[0], shared)
+    full = full_pass(h, shared)
+    extras = other_configurations(h, shared, launchers, sets) if h.world == 1 else None
+
+    names = list(launchers)
+    flat = [e2e["ms_total"]] + [kernel_ms[k] for k in names] + [full["chain_ms"]] + [full["kernel_ms"][k] for k in FULL_KERNELS] \
+        + [full["alt_chain_ms"]]
+    flat = h.max_over_ranks(flat)
+    e2e_ms = flat[0]
+    kernel_ms = dict(zip(names, flat[1:1 + len(names)]))
+    rest = flat[1 + len(names):]
+    full["chain_ms"], full["alt_chain_ms"] = rest[0], rest[-1]
+    full["kernel_ms"] = dict(zip(FULL_KERNELS, rest[1:1 + len(FULL_KERNELS)]))
+
+    if h.rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        ms_per_step = elapsed_ms / args.steps
+        value = h.world * ROWS * args.steps / (elapsed_ms * 1e-3)
+        kernels = {}
+        for name, ms in kernel_ms.items():
+            gbs = BYTES_PER_ROW[name] * ROWS / (ms * 1e-3) / 1e9
+            kernels[name] = {"us": round(ms * 1e3, 2), "rows_per_s": ROWS / (ms * 1e-3), "GBs": round(gbs, 1),
+                             "frac_of_measured_peak": round(gbs / peak, 4), "frac_of_8TBs": round(gbs / 8000.0, 4),
+                             "bytes_per_row": BYTES_PER_ROW[name], "sets": kernel_sets[name],
+                             "l2_defeated": bool(kernel_sets[name] * BYTES_PER_ROW[name] * ROWS >= 3 * 126e6)}
+        dom = kernels[DOMINANT]
+        traffic, traffic_note = dominant_traffic()
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": h.world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(),
+            "batches_ms_per_step": {"median": ms_per_step, "min": min(batch_ms) / args.steps, "max": max(batch_ms) / args.steps,
+                                    "n": len(batch_ms)},
+            "roofline": {"bound": "hbm", "kernel": DOMINANT, "achieved": dom["GBs"], "peak": peak, "unit": "GB/s",
+                         "frac": round(dom["GBs"] / peak, 4), "peak_kind": f"of {peak_kind}",
+                         "traffic": traffic, "traffic_source": traffic_note,
+                         "algorithmic_bytes_per_launch": BYTES_PER_ROW[DOMINANT] * ROWS},
+            "e2e": {"value": h.world * ROWS * e2e["steps"] / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
+                    "d2h_bytes_per_step": e2e["d2h"], "steps": e2e["steps"], "outputs_equal_device_path": e2e["equal"],
+                    "outputs_compared": e2e["compared"],
+                    "api": "clef_host_* (host-slice C-ABI, pinned host buffers, two-stream row tiles, pipelined mode: "
+                           "one clef_device_synchronize per step)"},
+            "gpu_launches": len(STEP_KERNELS) * args.steps * BATCHES,
+            "gpu_launches_note": f"{len(STEP_KERNELS)} kernels x {args.steps} steps x {BATCHES} timed batches",
+            "clocks": clocks,
+            "kernels": kernels,
+            "step_GBs": round(sum(BYTES_PER_ROW[k] for k in STEP_KERNELS) * ROWS / (ms_per_step * 1e-3) / 1e9, 1),
+            "step_frac_of_measured_peak": round(sum(BYTES_PER_ROW[k] for k in STEP_KERNELS) * ROWS / (ms_per_step * 1e-3) / 1e9 / peak, 4),
+            "full_pass_130712_rows": summarise_full(full, h.world, peak),
+        }
+        if extras is not None:
+            line["other_configurations"] = summarise_extras(extras, peak)
+        if h.world == 1:
+            cpu, _, _ = time_cpu(3, 1, budget_s=20.0)
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if h.world > 1:
+        h.dist.barrier()
+        h.dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# end to end: host buffers in, host buffers out, through the host-slice C-ABI
+# ---------------------------------------------------------------------------------------------------------
+def end_to_end(h: Harness, args, d0, shared):
+    torch, clef = h.torch, h.clef
+    _, pk_h, sc_h = clef.nvfp4_sizes(ROWS, HIDDEN, 128)
+    _, pk_i, sc_i = clef.nvfp4_sizes(ROWS, INTER, 128)
+    hd = clef.HostDevice(h.local_rank)
     host = {k: d0[k].cpu().pin_memory() for k in ("x", "gate", "up", "q", "k")}
-    host["cpos"] = cpos.cpu().pin_memory()
-    host_w = w_norm.cpu().numpy()
-    host_cos, host_sin = cos.cpu().pin_memory(), sin.cpu().pin_memory()
+    host["cpos"] = shared["cpos"].cpu().pin_memory()
+    host_w = shared["w_norm"].cpu().numpy()
+    host_cos, host_sin = shared["cos"].cpu().pin_memory(), shared["sin"].cpu().pin_memory()
     out = {
         "pk_h": torch.empty(pk_h, dtype=torch.uint8).pin_memory(), "sc_h": torch.empty(sc_h, dtype=torch.uint8).pin_memory(),
         "pk_i": torch.empty(pk_i, dtype=torch.uint8).pin_memory(), "sc_i": torch.empty(sc_i, dtype=torch.uint8).pin_memory(),
@@ -463,210 +656,325 @@ def run_gpu_arm(args):
     h2d = sum(host[k].numel() * host[k].element_size() for k in ("x", "gate", "up", "q", "k")) + 2 * host["cpos"].numel() * 4 \
         + host_w.nbytes + 2 * 2 * host_cos.numel() * 4
     d2h = sum(t.numel() * t.element_size() for t in out.values())
-    e2e_steps = max(3, min(args.steps, 10))
+    steps = max(3, min(args.steps, 10))
     for _ in range(2):
         e2e_step()
-    barrier()
+    h.barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    for _ in range(steps):
         e2e_step()
     torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    # the end-to-end outputs are the device path's outputs
-    e2e_ok = bool(torch.equal(out["pk_i"], d0["pk_i"].cpu()) and torch.equal(out["sc_h"], d0["sc_h"].cpu())
-                  and torch.equal(out["q"], d0["q_out"].cpu()))
+    seconds = time.perf_counter() - t0
+    # every output of the end-to-end step is the device path's output
+    pairs = [("pk_h", "pk_h"), ("sc_h", "sc_h"), ("pk_i", "pk_i"), ("sc_i", "sc_i"), ("q", "q_out"), ("k", "k_out")]
+    equal = all(bool(torch.equal(out[a], d0[b].cpu())) for a, b in pairs)
     hd.close()
-
-    # ---- the 130,712-row pass, row-range sharded over the ranks (strong scaling, reported as an extra) -----
-    full = full_pass(clef, lib, dev, world, rank, gen, p, stream, ok, w_norm, table)
-
-    times = torch.tensor([elapsed_ms, e2e_s * 1e3] + [kernel_ms[k] for k in launchers] + [full[k] for k in sorted(full)],
-                         device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    times = times.cpu().tolist()
-    elapsed_ms, e2e_ms = times[0], times[1]
-    kernel_ms = dict(zip(launchers, times[2:2 + len(launchers)]))
-    full = dict(zip(sorted(full), times[2 + len(launchers):]))
-
-    if rank == 0:
-        peak, peak_kind = measured_peak_gbs()
-        ms_per_step = elapsed_ms / args.steps
-        value = world * ROWS * args.steps / (elapsed_ms * 1e-3)
-        kernels = {}
-        for name, ms in kernel_ms.items():
-            gbs = BYTES_PER_ROW[name] * ROWS / (ms * 1e-3) / 1e9
-            kernels[name] = {"us": round(ms * 1e3, 2), "rows_per_s": ROWS / (ms * 1e-3), "GBs": round(gbs, 1),
-                             "frac_of_measured_peak": round(gbs / peak, 4), "frac_of_8TBs": round(gbs / 8000.0, 4),
-                             "bytes_per_row": BYTES_PER_ROW[name]}
-        dom = kernels[DOMINANT]
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": workload_config(),
-            "roofline": {"bound": "hbm", "kernel": DOMINANT, "achieved": dom["GBs"], "peak": peak, "unit": "GB/s",
-                         "frac": round(dom["GBs"] / peak, 4), "peak_kind": f"of {peak_kind}",
-                         "traffic": DOMINANT_TRAFFIC_BYTES,
-                         "algorithmic_bytes_per_launch": BYTES_PER_ROW[DOMINANT] * ROWS},
-            "e2e": {"value": world * ROWS * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(d2h), "steps": e2e_steps, "outputs_equal_device_path": e2e_ok,
-                    "api": "clef_host_* (host-slice C-ABI, pinned host buffers, two-stream row tiles, pipelined mode: "
-                           "one clef_device_synchronize per step)"},
-            "gpu_launches": len(STEP_KERNELS) * args.steps,
-            "clocks": clocks,
-            "kernels": kernels,
-            "step_GBs": round(sum(BYTES_PER_ROW[k] for k in STEP_KERNELS) * ROWS / (ms_per_step * 1e-3) / 1e9, 1),
-            "full_pass_130712_rows": summarise_full(full, world, peak),
-        }
-        if world == 1:
-            cpu, _, _ = time_cpu(3, 1, budget_s=20.0)
-            line["cpu_baseline"] = cpu
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    return {"ms_total": seconds * 1e3, "steps": steps, "h2d": int(h2d), "d2h": int(d2h), "equal": equal, "compared": len(pairs)}
 
 
-def full_pass(clef, lib, dev, world, rank, gen, p, stream, ok, w_norm, table):
-    """Every fused kernel over this rank's row range of the 130,712-row pass; ms per launch, by kernel."""
-    import torch
+# ---------------------------------------------------------------------------------------------------------
+# the 130,712-row pass, row-range sharded over the ranks (strong scaling)
+# ---------------------------------------------------------------------------------------------------------
+def checksum(torch, t):
+    """Two 64-bit wrap-around sums over the bytes of a tensor (length a multiple of 8): plain and position-weighted."""
+    w = t.reshape(-1).view(torch.uint8).view(torch.int64)
+    idx = torch.arange(1, w.numel() + 1, device=w.device, dtype=torch.int64)
+    return [int(w.sum().item()), int((w * (2 * idx + 1)).sum().item())]
 
-    first, n = clef.shard_rows(FULL_ROWS, 128, world, rank)
-    if n == 0:
-        return {k: 0.0 for k in FULL_KERNELS}
 
-    def randn_bf16(*shape):
-        return torch.randn(*shape, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
+def full_pass_inputs(h: Harness, first: int, n: int):
+    """This rank's row range of the identically seeded 130,712-row inputs (every rank draws the same full tensors)."""
+    torch = h.torch
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(424242)
 
-    rp, pk_h, sc_h = clef.nvfp4_sizes(n, HIDDEN, 128)
+    def rows_of(*shape):
+        full = h.randn_bf16(FULL_ROWS, *shape, gen=gen)
+        part = full[first:first + n].contiguous()
+        del full
+        return part
+
+    x = rows_of(HIDDEN)
+    gate, up = rows_of(INTER), rows_of(INTER)
+    q, k = rows_of(Q_HEADS, HEAD_DIM), rows_of(KV_HEADS, HEAD_DIM)
+    o, z = rows_of(VH, HEAD_DIM), rows_of(VH, HEAD_DIM)
+    ids = torch.randint(0, VOCAB, (FULL_ROWS,), device="cuda", generator=gen, dtype=torch.int32)[first:first + n].contiguous()
+    return {"x": x, "gate": gate, "up": up, "q": q, "k": k, "o": o.view(n * VH, HEAD_DIM), "z": z.view(n * VH, HEAD_DIM), "ids": ids}
+
+
+def full_pass_outputs(h: Harness, n: int):
+    torch, clef = h.torch, h.clef
+    _, pk_h, sc_h = clef.nvfp4_sizes(n, HIDDEN, 128)
     _, pk_i, sc_i = clef.nvfp4_sizes(n, INTER, 128)
-    positions = torch.arange(FULL_ROWS, dtype=torch.int32, device="cuda")
-    cos, sin = dev.rope_tables_dev(positions, FULL_ROWS, ROTARY, THETA)
-    cpos = positions[first:first + n].contiguous()        # one request of 130,712 tokens at slot 0
-    w_gated = torch.ones(HEAD_DIM, device="cuda")
-    x, gate, up = randn_bf16(n, HIDDEN), randn_bf16(n, INTER), randn_bf16(n, INTER)
-    q, k = randn_bf16(n, Q_HEADS, HEAD_DIM), randn_bf16(n, KV_HEADS, HEAD_DIM)
-    o, z = randn_bf16(n * VH, HEAD_DIM), randn_bf16(n * VH, HEAD_DIM)
-    ids = torch.randint(0, VOCAB, (n,), device="cuda", generator=gen, dtype=torch.int32)
-    u8 = lambda nbytes: torch.empty(nbytes, dtype=torch.uint8, device="cuda")   # noqa: E731
-    pkh, sch, pki, sci, pkg, scg = u8(pk_h), u8(sc_h), u8(pk_i), u8(sc_i), u8(pk_h), u8(sc_h)
-    qo, ko, h = torch.empty_like(q), torch.empty_like(k), torch.empty_like(x)
-    calls = {
-        "rms_norm_quantise_nvfp4": lambda: lib.clef_rms_norm_quantise_nvfp4(stream(), p(x), p(w_norm), p(pkh), p(sch), n, HIDDEN, EPS, GS_NORM, 128, 512, 0),
-        "swiglu_quantise_nvfp4": lambda: lib.clef_swiglu_quantise_nvfp4(stream(), p(gate), p(up), p(pki), p(sci), n, INTER, GS_SWIGLU, 128, 512, 0),
-        "rope_qk": lambda: lib.clef_rope_qk(stream(), p(qo), p(q), Q_HEADS, p(ko), p(k), KV_HEADS, p(cos), p(sin), n, HEAD_DIM,
-                                            ROTARY, None, None, p(cpos), 0),
-        "embed_gather": lambda: lib.clef_embed_gather(stream(), p(table), p(ids), p(h), n, HIDDEN, 0),
+    bf = torch.bfloat16
+    return {"pkh": h.u8(pk_h), "sch": h.u8(sc_h), "pki": h.u8(pk_i), "sci": h.u8(sc_i), "pkg": h.u8(pk_h), "scg": h.u8(sc_h),
+            "pke": h.u8(pk_h), "sce": h.u8(sc_h),
+            "qo": torch.empty(n, Q_HEADS, HEAD_DIM, dtype=bf, device="cuda"), "ko": torch.empty(n, KV_HEADS, HEAD_DIM, dtype=bf, device="cuda"),
+            "h": torch.empty(n, HIDDEN, dtype=bf, device="cuda")}
+
+
+def full_pass_calls(h: Harness, shared, tables, inp, out, n: int, first: int):
+    lib, p, stream = h.lib, h.p, h.stream
+    rp = (n + 127) // 128 * 128
+    cos, sin, positions = tables
+    cpos = positions[first:first + n]
+    w_norm, table = shared["w_norm"], shared["table"]
+    w_gated = shared["w_gated"]
+    return {
+        "embed_gather": lambda: lib.clef_embed_gather(stream(), p(table), p(inp["ids"]), p(out["h"]), n, HIDDEN, 0),
+        "rms_norm_quantise_nvfp4": lambda: lib.clef_rms_norm_quantise_nvfp4(stream(), p(inp["x"]), p(w_norm), p(out["pkh"]), p(out["sch"]), n,
+                                                                             HIDDEN, EPS, GS_NORM, 128, 512, 0),
+        "swiglu_quantise_nvfp4": lambda: lib.clef_swiglu_quantise_nvfp4(stream(), p(inp["gate"]), p(inp["up"]), p(out["pki"]), p(out["sci"]), n,
+                                                                         INTER, GS_SWIGLU, 128, 512, 0),
+        "rope_qk": lambda: lib.clef_rope_qk(stream(), p(out["qo"]), p(inp["q"]), Q_HEADS, p(out["ko"]), p(inp["k"]), KV_HEADS, p(cos), p(sin), n,
+                                            HEAD_DIM, ROTARY, None, None, p(cpos), 0),
         "rms_norm_gated_quantise_nvfp4": lambda: lib.clef_rms_norm_gated_quantise_nvfp4(
-            stream(), p(o), p(z), p(w_gated), p(pkg), p(scg), rp * VH, HEAD_DIM, EPS, GS_GATED, 128, 512, VH, n * VH, 0),
+            stream(), p(inp["o"]), p(inp["z"]), p(w_gated), p(out["pkg"]), p(out["scg"]), rp * VH, HEAD_DIM, EPS, GS_GATED, 128, 512, VH,
+            n * VH, 0),
+        # alternative head of the chain: gather + norm + quantiser of the gathered rows in one pass (its own outputs)
+        "embed_rms_norm_quantise_nvfp4": lambda: lib.clef_embed_rms_norm_quantise_nvfp4(
+            stream(), p(table), p(inp["ids"]), p(out["h"]), p(w_norm), p(out["pke"]), p(out["sce"]), n, HIDDEN, EPS, GS_NORM, 128, 512, 0),
     }
+
+
+def shard_checksums(h: Harness, out, first_row: int, n: int, base_row: int):
+    """Checksums of the rows [first_row, first_row + n) of a pass whose buffers start at row `base_row` (both multiples
+    of the 128-row scale atom, except the ragged end): packed and scale slices are contiguous per atom-aligned range."""
+    torch = h.torch
+    lo = first_row - base_row
+    rp = (n + 127) // 128 * 128
+    sums = []
+    for pk, sc, cols in (("pkh", "sch", HIDDEN), ("pki", "sci", INTER), ("pkg", "scg", HIDDEN)):
+        sums += checksum(torch, out[pk][lo * cols // 2:(lo + rp) * cols // 2])
+        sums += checksum(torch, out[sc][lo * cols // 16:(lo + rp) * cols // 16])
+    for name in ("qo", "ko", "h"):
+        sums += checksum(torch, out[name][lo:lo + n])
+    return sums
+
+
+def full_pass(h: Harness, shared):
+    """The five fused kernels over this rank's row range of the 130,712-row pass as ONE CUDA graph (programmatic
+    dependent launch between its kernels), replayed over rotating buffer sets; plus each kernel alone, and the
+    comparison of every shard's bytes with a single-GPU run of the same seeded inputs."""
+    torch, clef = h.torch, h.clef
+    first, n = clef.shard_rows(FULL_ROWS, 128, h.world, h.rank)
+    positions = torch.arange(FULL_ROWS, dtype=torch.int32, device="cuda")
+    cos, sin = h.dev.rope_tables_dev(positions, FULL_ROWS, ROTARY, THETA)   # one request of 130,712 tokens at slot 0
+    tables = (cos, sin, positions)
+    inp = full_pass_inputs(h, first, n)
+    per_set = sum(BYTES_PER_ROW[k] for k in FULL_KERNELS) * n
+    nsets = int(max(1, min(4, math.ceil(2e9 / per_set))))      # 1 set of 7.9 GB on one GPU, 3 sets of 1 GB each on eight
+    in_sets = [inp] + [{k: (v.roll(7 * i, 0) if v.dtype != torch.int32 else v.clone()) for k, v in inp.items()} for i in range(1, nsets)]
+    out_sets = [full_pass_outputs(h, n) for _ in range(nsets)]
+    calls = [full_pass_calls(h, shared, tables, in_sets[i], out_sets[i], n, first) for i in range(nsets)]
+    for c in calls:
+        for name in FULL_KERNELS:
+            h.ok(c[name]())
+    torch.cuda.synchronize()
+    sums = shard_checksums(h, out_sets[0], first, n, first)     # before anything overwrites set 0's outputs
+
+    chain = [h.capture([c[name] for name in FULL_KERNELS]) for c in calls]
+    replays = max(20, 4 * nsets)
+    chain_ms = float(np.median(h.time_graphs(chain, replays, BATCHES, sync_ranks=True))) / replays
+    alt_names = ["embed_rms_norm_quantise_nvfp4"] + [k for k in FULL_KERNELS if k not in ("embed_gather", "rms_norm_quantise_nvfp4")]
+    alt = [h.capture([c[name] for name in alt_names]) for c in calls]
+    alt_chain_ms = float(np.median(h.time_graphs(alt, replays, BATCHES, sync_ranks=True))) / replays
+    kernel_ms = {}
+    for name in FULL_KERNELS:
+        per = max(1, min(6, int(ROTATE_BYTES // max(1, BYTES_PER_ROW[name] * n)) + 1))
+        g = [h.capture([c[name]]) for c in calls]
+        reps = max(10, 2 * per * nsets)
+        kernel_ms[name] = float(np.median(h.time_graphs(g, reps))) / reps
+        del g
+    del chain, alt
+
+    # every shard's bytes against a single-GPU run of the same inputs (rank 0 runs the whole pass once more)
+    equal = None
+    if h.world > 1:
+        mine = torch.tensor(sums, device="cuda", dtype=torch.int64)
+        gathered = [torch.empty_like(mine) for _ in range(h.world)]
+        h.dist.all_gather(gathered, mine)
+        if h.rank == 0:
+            del in_sets, out_sets, calls
+            torch.cuda.empty_cache()
+            whole_in = full_pass_inputs(h, 0, FULL_ROWS)
+            whole_out = full_pass_outputs(h, FULL_ROWS)
+            whole = full_pass_calls(h, shared, tables, whole_in, whole_out, FULL_ROWS, 0)
+            for name in FULL_KERNELS:
+                h.ok(whole[name]())
+            torch.cuda.synchronize()
+            equal = True
+            for r in range(h.world):
+                f, m = clef.shard_rows(FULL_ROWS, 128, h.world, r)
+                equal = equal and (shard_checksums(h, whole_out, f, m, 0) == gathered[r].cpu().tolist())
+            del whole_in, whole_out
+    return {"chain_ms": chain_ms, "alt_chain_ms": alt_chain_ms, "kernel_ms": kernel_ms, "rows_this_rank": n, "sets": nsets,
+            "replays": replays, "shards_equal_single_gpu": equal}
+
+
+def summarise_full(full, world, peak):
+    chain_ms = full["chain_ms"]
+    total_bytes = sum(BYTES_PER_ROW[k] for k in FULL_KERNELS) * FULL_ROWS
+    alt_bytes = total_bytes - (BYTES_PER_ROW["embed_gather"] + BYTES_PER_ROW["rms_norm_quantise_nvfp4"] -
+                               BYTES_PER_ROW["embed_rms_norm_quantise_nvfp4"]) * FULL_ROWS
+    per_kernel = {k: {"ms": round(v, 4), "GBs_per_gpu": round(BYTES_PER_ROW[k] * FULL_ROWS / world / (v * 1e-3) / 1e9, 1)}
+                  for k, v in full["kernel_ms"].items()}
+    return {"n_gpus": world, "scaling": "strong (row-range shards aligned to the 128-row scale atom, max over ranks)",
+            "chain_ms": round(chain_ms, 4), "chain": "the five kernels of a rank's shard as one CUDA graph, timed as a whole "
+            f"({full['replays']} replays per batch over {full['sets']} rotating buffer set(s), median of {BATCHES} batches)",
+            "rows_per_s": FULL_ROWS / (chain_ms * 1e-3),
+            "GBs_aggregate": round(total_bytes / (chain_ms * 1e-3) / 1e9, 1),
+            "frac_of_measured_peak_per_gpu": round(total_bytes / (chain_ms * 1e-3) / 1e9 / world / peak, 4),
+            "sum_of_kernels_timed_alone_ms": round(sum(full["kernel_ms"].values()), 4),
+            "kernels_timed_alone": per_kernel,
+            "chain_with_fused_embed_norm_ms": round(full["alt_chain_ms"], 4),
+            "chain_with_fused_embed_norm_GBs_aggregate": round(alt_bytes / (full["alt_chain_ms"] * 1e-3) / 1e9, 1),
+            "shards_equal_single_gpu": full["shards_equal_single_gpu"],
+            "l2": "every rank's chain touches far more than L2 per replay (60,296 B per row) and rotates over buffer sets"}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the benchmark definition's other configurations (one GPU)
+# ---------------------------------------------------------------------------------------------------------
+def other_configurations(h: Harness, shared, launchers, sets):
+    torch, clef, lib, p, stream = h.torch, h.clef, h.lib, h.p, h.stream
     out = {}
-    for name, fn in calls.items():
-        for _ in range(3):
-            ok(fn())
+    # -- the gated chain: 32,768 tokens in four 8,192-token chunks (one graph replay per chunk), two requests rotating
+    gated_sets = [dict(sets[i % NSETS]) for i in range(8)]
+    for i in range(NSETS, 8):
+        for key in ("o", "z", "pk_g", "sc_g"):
+            gated_sets[i][key] = sets[i % NSETS][key].roll(17 * i, 0) if key in ("o", "z") else torch.empty_like(sets[0][key])
+    graphs = [h.capture([lambda d=d: launchers["rms_norm_gated_quantise_nvfp4"](d)]) for d in gated_sets]
+    ms = float(np.median(h.time_graphs(graphs, 40))) / 40
+    out["gated_chain_4x8192"] = {"ms_per_chunk": ms, "bytes_per_chunk": BYTES_PER_ROW["rms_norm_gated_quantise_nvfp4"] * ROWS}
+    del graphs, gated_sets
+
+    # -- the 130,712-row pass the way the reference cuts it: rung-sized passes, one graph per pass
+    cuts = clef.rungs_decompose(FULL_ROWS)
+    padded = cuts[-1][0] + cuts[-1][1]
+    positions = torch.arange(padded, dtype=torch.int32, device="cuda")
+    cos, sin = h.dev.rope_tables_dev(positions, padded, ROTARY, THETA)
+    inp = full_pass_inputs(h, 0, FULL_ROWS)
+    pad = padded - FULL_ROWS
+    if pad:   # the last pass is padded to its rung (64-row granule), as the engine pads it
+        inp = {k: torch.cat([v, v[:pad * (VH if k in ("o", "z") else 1)]]) for k, v in inp.items()}
+    passes = []
+    for base, rows in cuts:
+        sl = {k: v[base * (VH if k in ("o", "z") else 1):(base + rows) * (VH if k in ("o", "z") else 1)] for k, v in inp.items()}
+        # output slices of a pass: rows are multiples of 64; scale tiles are 128-row atoms, so each pass owns buffers of its own
+        o = full_pass_outputs(h, rows)
+        calls = full_pass_calls(h, shared, (cos, sin, positions), sl, o, rows, base)
+        passes.append((h.capture([calls[name] for name in FULL_KERNELS]), o))
+    graphs = [g for g, _ in passes]
+    ms = float(np.median(h.time_graphs(graphs, len(graphs) * 3))) / 3
+    out["full_pass_as_rung_passes"] = {"ms": ms, "passes": len(cuts), "rungs": sorted({r for _, r in cuts}, reverse=True), "rows": padded}
+    del passes, graphs, inp
+
+    # -- rung sweep: four coalesced requests per pass, per-token maps uploaded before every replay
+    rng = np.random.default_rng(0xED)
+    table_rows = 16384
+    positions = torch.arange(table_rows, dtype=torch.int32, device="cuda")
+    cos, sin = h.dev.rope_tables_dev(positions, table_rows, ROTARY, THETA)
+    sweep = {}
+    pool_rows = NSETS * ROWS
+    for rung in (64, 128, 256, 512, 1024, 2048, 4096, 8192):
+        gran = rung // 64
+        nreq = min(4, gran)
+        cuts_g = np.sort(rng.choice(np.arange(1, gran), nreq - 1, replace=False)) if nreq > 1 else np.zeros(0, np.int64)
+        sizes = np.diff(np.concatenate([[0], cuts_g, [gran]])) * 64
+        chunks = []
+        for slot, s in enumerate(sizes):       # a request that already holds `start` tokens in its cache slot continues by s rows
+            start = int(rng.integers(0, (8192 - int(s)) // 64 + 1)) * 64
+            chunks.append((rng.integers(0, VOCAB, start + int(s)).astype(np.uint32), start, slot, int(s)))
+        maps = clef.pass_maps(chunks, 8192)
+        # the pass's seven per-token maps travel as one pinned block, as the engine uploads them before a replay
+        names7 = ("ids", "seq_start", "seq_end", "cpos", "cbase", "slot_map", "rope_pos")
+        host_maps = torch.from_numpy(np.stack([maps[k].astype(np.int32) for k in names7])).pin_memory()
+        dev_maps = torch.empty(7, rung, dtype=torch.int32, device="cuda")
+        dev_pos = dev_maps[6]
+        rp = (rung + 127) // 128 * 128
+        slices = min(pool_rows // rp, 256)
+        launches = []
+        for i in range(slices):
+            d = sets[(i * rp // ROWS) % NSETS]
+            r0 = (i * rp) % ROWS
+            if r0 + rp > ROWS:
+                continue
+            view = {k: d[k][r0:r0 + rung] for k in ("x", "gate", "up", "q", "k")}
+            o = {"pk_h": d["pk_h"][r0 * HIDDEN // 2:], "sc_h": d["sc_h"][r0 * HIDDEN // 16:], "pk_i": d["pk_i"][r0 * INTER // 2:],
+                 "sc_i": d["sc_i"][r0 * INTER // 16:], "q_out": d["q_out"][r0:], "k_out": d["k_out"][r0:]}
+            launches.append(lambda v=view, o=o: lib.clef_rms_norm_quantise_nvfp4(
+                stream(), p(v["x"]), p(shared["w_norm"]), p(o["pk_h"]), p(o["sc_h"]), rung, HIDDEN, EPS, GS_NORM, 128, 512, 0))
+            launches.append(lambda v=view, o=o: lib.clef_swiglu_quantise_nvfp4(
+                stream(), p(v["gate"]), p(v["up"]), p(o["pk_i"]), p(o["sc_i"]), rung, INTER, GS_SWIGLU, 128, 512, 0))
+            launches.append(lambda v=view, o=o: lib.clef_rope_qk(
+                stream(), p(o["q_out"]), p(v["q"]), Q_HEADS, p(o["k_out"]), p(v["k"]), KV_HEADS, p(cos), p(sin), rung, HEAD_DIM, ROTARY,
+                None, None, p(dev_pos), 0))
+        per_pass = [h.capture(launches[3 * i:3 * i + 3]) for i in range(len(launches) // 3)]
+        dev_maps.copy_(host_maps, non_blocking=True)
+        for g in per_pass[:3]:
+            g.replay()
         torch.cuda.synchronize()
-        reps = 10
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(reps):
-            fn()
-        e.record()
-        torch.cuda.synchronize()
-        out[name] = s.elapsed_time(e) / reps
+        times = []
+        n_pass = max(len(per_pass), 24)
+        for _ in range(BATCHES):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for i in range(n_pass):
+                dev_maps.copy_(host_maps, non_blocking=True)    # the pass's maps go up before its graph is replayed
+                per_pass[i % len(per_pass)].replay()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) / n_pass)
+        sweep[rung] = {"us_per_pass": float(np.median(times)) * 1e3, "requests": nreq, "slices": len(per_pass)}
+        del per_pass, launches
+    out["rung_sweep"] = sweep
     return out
 
 
-def summarise_full(full_ms, world, peak):
-    chain_ms = sum(full_ms.values())
-    per_kernel = {k: {"ms": round(v, 4), "GBs_aggregate": round(BYTES_PER_ROW[k] * FULL_ROWS / (v * 1e-3) / 1e9, 1) if v else None}
-                  for k, v in full_ms.items()}
-    total_bytes = sum(BYTES_PER_ROW[k] for k in FULL_KERNELS) * FULL_ROWS
-    return {"n_gpus": world, "scaling": "strong (row-range shards aligned to the 128-row scale atom, max over ranks)",
-            "chain_ms": round(chain_ms, 4), "rows_per_s": FULL_ROWS / (chain_ms * 1e-3) if chain_ms else None,
-            "GBs_aggregate": round(total_bytes / (chain_ms * 1e-3) / 1e9, 1) if chain_ms else None,
-            "frac_of_measured_peak_per_gpu": round(total_bytes / (chain_ms * 1e-3) / 1e9 / world / peak, 4) if chain_ms else None,
-            "kernels": per_kernel, "l2": "each rank's slice of every operand is larger than L2 at 1-4 GPUs"}
+def summarise_extras(extras, peak):
+    step_bytes = sum(BYTES_PER_ROW[k] for k in STEP_KERNELS)
+    g = extras["gated_chain_4x8192"]
+    gbs = g["bytes_per_chunk"] / (g["ms_per_chunk"] * 1e-3) / 1e9
+    r = extras["full_pass_as_rung_passes"]
+    total = sum(BYTES_PER_ROW[k] for k in FULL_KERNELS) * r["rows"]
+    sweep = {}
+    for rung, v in extras["rung_sweep"].items():
+        gb = step_bytes * rung / (v["us_per_pass"] * 1e-6) / 1e9
+        sweep[str(rung)] = {"us_per_pass": round(v["us_per_pass"], 2), "rows_per_s": rung / (v["us_per_pass"] * 1e-6), "GBs": round(gb, 1),
+                            "frac_of_measured_peak": round(gb / peak, 4), "requests": v["requests"]}
+    return {
+        "gated_chain_32768_rows_in_four_chunks": {
+            "us_per_8192_row_chunk": round(g["ms_per_chunk"] * 1e3, 2), "ms_per_32768_rows": round(4 * g["ms_per_chunk"], 4),
+            "rows_per_s": ROWS / (g["ms_per_chunk"] * 1e-3), "GBs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4)},
+        "full_pass_130712_rows_as_rung_passes": {
+            "ms": round(r["ms"], 4), "passes": r["passes"], "rungs": r["rungs"], "rows_incl_padding": r["rows"],
+            "rows_per_s": FULL_ROWS / (r["ms"] * 1e-3), "GBs": round(total / (r["ms"] * 1e-3) / 1e9, 1),
+            "frac_of_measured_peak": round(total / (r["ms"] * 1e-3) / 1e9 / peak, 4),
+            "note": "one CUDA graph of the five kernels per pass (src/gpu.rs:762-775 cuts the request into rungs)"},
+        "rung_sweep_step_with_four_coalesced_requests": sweep,
+    }
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --profile-case: a small, self-ending run for ncu
+# ---------------------------------------------------------------------------------------------------------
 def run_profile_case(args):
-    """`--profile`: launch every tuned kernel twice at 8,192 rows on fresh buffers and exit; the small,
-    self-ending case that ncu captures are taken on (see profiles/)."""
-    import ctypes
-
-    import torch
-
-    import aiis_clef_b200 as clef
-
-    torch.cuda.set_device(0)
-    lib = clef.load()
-    dev = clef.Device(0)
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(7)
-
-    def p(t):
-        return ctypes.c_void_p(t.data_ptr())
-
-    def st():
-        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-
-    def rnd(*shape):
-        return torch.randn(*shape, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
-
-    def u8(n):
-        return torch.empty(n, dtype=torch.uint8, device="cuda")
-
-    rp, pk_h, sc_h = clef.nvfp4_sizes(ROWS, HIDDEN, 128)
-    _, pk_i, sc_i = clef.nvfp4_sizes(ROWS, INTER, 128)
-    w = torch.randn(HIDDEN, device="cuda", generator=gen) * 0.1
-    wg = 1.0 + torch.randn(HEAD_DIM, device="cuda", generator=gen) * 0.1
-    pos = torch.arange(ROWS, dtype=torch.int32, device="cuda")
-    cos, sin = dev.rope_tables_dev(pos, ROWS, ROTARY, THETA)
-    table = rnd(VOCAB, HIDDEN)
-    for _ in range(2):
-        x, gate, up = rnd(ROWS, HIDDEN), rnd(ROWS, INTER), rnd(ROWS, INTER)
-        q, o, z = rnd(ROWS, Q_HEADS, HEAD_DIM), rnd(ROWS * VH, HEAD_DIM), rnd(ROWS * VH, HEAD_DIM)
-        ids = torch.randint(0, VOCAB, (ROWS,), device="cuda", generator=gen, dtype=torch.int32)
-        outs = [u8(pk_h), u8(sc_h), u8(pk_i), u8(sc_i), u8(pk_h), u8(sc_h), torch.empty_like(q), torch.empty_like(x)]
-        assert lib.clef_rms_norm_quantise_nvfp4(st(), p(x), p(w), p(outs[0]), p(outs[1]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, 0) == 0
-        assert lib.clef_swiglu_quantise_nvfp4(st(), p(gate), p(up), p(outs[2]), p(outs[3]), ROWS, INTER, GS_SWIGLU, 128, 512, 0) == 0
-        assert lib.clef_rms_norm_gated_quantise_nvfp4(st(), p(o), p(z), p(wg), p(outs[4]), p(outs[5]), rp * VH, HEAD_DIM, EPS,
-                                                      GS_GATED, 128, 512, VH, ROWS * VH, 0) == 0
-        assert lib.clef_rope(st(), p(outs[6]), p(q), p(cos), p(sin), ROWS, Q_HEADS, HEAD_DIM, ROTARY, None, None, p(pos), 0) == 0
-        assert lib.clef_embed_gather(st(), p(table), p(ids), p(outs[7]), ROWS, HIDDEN, 0) == 0
-        # the steps either side of the path and the FP8 quantisers (7 more tuned kernels, 12 per round)
-        k, v, res = rnd(ROWS, KV_HEADS, HEAD_DIM), rnd(ROWS, KV_HEADS, HEAD_DIM), rnd(ROWS, HIDDEN)
-        cache_k, cache_v = torch.empty_like(k), torch.empty_like(v)
-        cmap = torch.randperm(ROWS, device="cuda", generator=gen).to(torch.int32)
-        q8_h, q8_i, s8, total = u8(ROWS * HIDDEN), u8(ROWS * INTER), u8(ROWS * 2), torch.empty_like(x)
-        assert lib.clef_rope_kv_write(st(), p(cache_k), p(cache_v), p(k), p(v), p(cos), p(sin), ROWS, KV_HEADS, HEAD_DIM, ROTARY,
-                                      None, None, p(pos), p(cmap), None, 0) == 0
-        assert lib.clef_sigmoid_mul_quantise_nvfp4(st(), p(q), p(res), p(outs[4]), p(outs[5]), ROWS, HIDDEN, GS_NORM, 128, 512, 0) == 0
-        assert lib.clef_add_rms_norm_quantise_nvfp4(st(), p(total), p(x), p(res), p(w), p(outs[0]), p(outs[1]), ROWS, HIDDEN, EPS,
-                                                    GS_NORM, 128, 512, 0) == 0
-        assert lib.clef_quantise_fp8(st(), p(x), p(q8_h), p(s8), ROWS, HIDDEN, 0) == 0
-        assert lib.clef_rms_norm_fp8_bf16(st(), p(x), p(w), p(q8_h), p(s8), p(total), ROWS, HIDDEN, EPS, 0) == 0
-        assert lib.clef_swiglu_quantise_fp8(st(), p(gate), p(up), p(q8_i), p(s8), ROWS, INTER, 0) == 0
-        assert lib.clef_rms_norm_gated_quantise_fp8(st(), p(o), p(z), p(wg), p(q8_h), p(s8), ROWS * VH, HEAD_DIM, EPS, VH,
-                                                    ROWS * VH, 0) == 0
-        # the fused RoPE launch of the step, the head_dim-256 norm + RoPE, and the causal convolution
-        k_out, qg, q256, g256 = torch.empty_like(k), rnd(ROWS, Q_HEADS, 512), u8(ROWS * Q_HEADS * 512), u8(ROWS * Q_HEADS * 512)
-        w256 = torch.randn(256, device="cuda", generator=gen) * 0.1
-        mixed, w_conv = rnd(ROWS, CONV_DIM), torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5
-        conv_out = torch.empty_like(mixed)
-        assert lib.clef_rope_qk(st(), p(outs[6]), p(q), Q_HEADS, p(k_out), p(k), KV_HEADS, p(cos), p(sin), ROWS, HEAD_DIM, ROTARY,
-                                None, None, p(pos), 0) == 0
-        assert lib.clef_qk_norm_rope(st(), p(qg), p(w256), p(cos), p(sin), p(q256), p(g256), ROWS * Q_HEADS, Q_HEADS, 256, ROTARY,
-                                     EPS, None, None, p(pos), 0) == 0
-        assert lib.clef_causal_conv_silu(st(), p(conv_out), p(mixed), p(w_conv), ROWS, CONV_DIM, CONV_K, None, None, None, 0) == 0
-        # the scan's operands from the convolved rows, and convolution + operands in one launch (17 per round)
-        ops = [u8(32 * ((ROWS + 63) // 64) * 2 * 64 * 128) for _ in range(4)]
-        kn, vv = torch.empty(ROWS, 4096, device="cuda"), torch.empty(ROWS, 4096, device="cuda")
-        assert lib.clef_gdn_prep(st(), p(conv_out), p(vv), p(ops[0]), p(ops[1]), p(ops[2]), p(ops[3]), p(kn), ROWS, 32, 16, 128,
-                                 CONV_DIM, 128 ** -0.5, 0) == 0
-        assert lib.clef_gdn_conv_prep(st(), p(mixed), p(w_conv), p(vv), p(ops[0]), p(ops[1]), p(ops[2]), p(ops[3]), p(kn), ROWS,
-                                      CONV_DIM, CONV_K, None, None, None, 32, 16, 128, 128 ** -0.5, 0) == 0
-        torch.cuda.synchronize()
-    print(json.dumps({"profile_case": "ok", "rows": ROWS, "tuned_kernels_per_round": 17}))
+    """Launch each named entry point three times at 8,192 rows on fresh buffers and exit: the case ncu captures are
+    taken on, one kernel per ncu call (`-k regex:<kernel> -s 1 -c 1`; see profiles/)."""
+    h = Harness(args)
+    shared = make_shared(h)
+    launchers = make_launchers(h, shared)
+    names = [n for n in args.profile_case.split(",") if n]
+    unknown = [n for n in names if n not in launchers]
+    if unknown:
+        raise SystemExit(f"unknown entry point(s) {unknown}; known: {sorted(launchers)}")
+    for _ in range(3):
+        d = make_step_set(h)          # fresh inputs: nothing of them is in L2 when the kernel starts
+        for n in names:
+            h.ok(launchers[n](d))
+        h.torch.cuda.synchronize()
+    print(json.dumps({"profile_case": "ok", "rows": ROWS, "entry_points": names, "launches_each": 3}))
 
 
 def main():
@@ -675,11 +983,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--profile", action="store_true",
-                    help="launch each tuned kernel twice at 8,192 rows and exit (the case ncu captures are taken on)")
+    ap.add_argument("--profile-case", default="",
+                    help="comma-separated entry points: launch each three times at 8,192 rows and exit (for ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.profile:
+    if args.profile_case:
         run_profile_case(args)
     elif args.impl == "reference":
         run_reference_arm(args)

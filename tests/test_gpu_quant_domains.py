@@ -1,10 +1,11 @@
 """The tuned quantising kernels at the edges of their block quantiser's fast domain, and at the exact shapes of
 the benchmark step, against the reference's own kernels (oracle/_ref cubins) on the same GPU.
 
-The tuned kernels quantise a block on a short path when its scale is a normal, unclamped E4M3 code (or the block is
-all zeros) and recompute it literally otherwise. These tests drive whole launches into the literal path
-(subnormal scale codes, clamped codes, zero and non-finite blocks, global scales outside the tuned range) and
-compare bytes with the reference kernels, padding included.
+The tuned kernels quantise a block on a short path when its scale argument lies in [2^-6, 2^30) (a normal E4M3 code,
+clamped from 448 up) or the block is all zeros, and recompute it literally otherwise. These tests drive whole
+launches to both sides of those edges (subnormal scale codes, clamped codes, scale arguments beyond 2^30, zero and
+non-finite blocks, global scales outside the tuned range) and compare bytes with the reference kernels, padding
+included.
 """
 import numpy as np
 import pytest
@@ -85,11 +86,12 @@ def _with_zero_rows(bits, rng, every=7):
     return bits
 
 
-@pytest.mark.parametrize("global_scale", [2e-3, 0.02, 3e4, 1e7, 1e-25])
+@pytest.mark.parametrize("global_scale", [2e-3, 0.02, 3e4, 1e7, 3e9, 1e10, 1e-25])
 @pytest.mark.parametrize("cols", [2048, 4096])
 def test_rms_norm_quantise_outside_the_fast_domain(cols, global_scale):
     """Normalised values are O(1), so the global scale alone decides the code range: 2e-3 gives subnormal scale codes,
-    0.02 a mix of subnormal and normal ones, 3e4 and 1e7 clamped ones, 1e-25 the shape-general kernel."""
+    0.02 a mix of subnormal and normal ones, 3e4 and 1e7 clamped ones, 3e9 scale arguments around 2^30 (the end of the
+    short path), 1e10 beyond it, 1e-25 the shape-general kernel."""
     rows = 300
     rng = np.random.default_rng(cols + 5)
     x = _with_zero_rows(normal_bf16(rng, (rows, cols), outlier_channels=8), rng)
@@ -104,7 +106,7 @@ def test_rms_norm_quantise_outside_the_fast_domain(cols, global_scale):
     assert_bytes_equal(got_p, ref_p.cpu().numpy(), "packed vs reference chain")
 
 
-@pytest.mark.parametrize("global_scale", [2e-3, 0.05, 3e4, 1e-25])
+@pytest.mark.parametrize("global_scale", [2e-3, 0.05, 3e4, 4e9, 1e11, 1e-25])
 def test_swiglu_quantise_outside_the_fast_domain(global_scale):
     rows, cols = 129, 6144
     rng = np.random.default_rng(77)
@@ -119,7 +121,7 @@ def test_swiglu_quantise_outside_the_fast_domain(global_scale):
     assert_bytes_equal(got_p, ref_p.cpu().numpy(), "packed vs reference fused kernel")
 
 
-@pytest.mark.parametrize("global_scale", [2e-3, 0.05, 3e4, 1e-25])
+@pytest.mark.parametrize("global_scale", [2e-3, 0.05, 3e4, 4e9, 1e11, 1e-25])
 def test_gated_norm_quantise_outside_the_fast_domain(global_scale):
     tokens, vh, cols = 130, 16, 128
     rows = tokens * vh
