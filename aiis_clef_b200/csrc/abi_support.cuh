@@ -95,6 +95,10 @@ void launch_hot(void (*kernel)(KArgs...), unsigned grid, size_t smem, cudaStream
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch
 }
 
+// Whether a grid-stride launch of `ctas_wanted` CTA-sized pieces on `cap` resident CTAs is short enough (at most
+// six rounds per thread) for the RoPE kernels' hoisted-load form; see rope_hot_kernel.
+inline bool rope_launch_is_short(size_t ctas_wanted, size_t cap) { return ctas_wanted <= 6 * cap; }
+
 inline unsigned clamp_grid(size_t wanted, size_t cap) {
     size_t g = wanted < cap ? wanted : cap;
     return (unsigned)(g < 1 ? 1 : g);

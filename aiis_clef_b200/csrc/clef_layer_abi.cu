@@ -169,6 +169,12 @@ static int rope_qkv_impl(const char* what, clef_stream_t stream, void* q_out, co
             launch_hot(rope_multi_hot_kernel<3>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, as_stream(stream), segs, cos_table,
                        sin_table, head_dim, rotary_dim, (const int*)seq_start, (const int*)pos_base, (const int*)pos_map,
                        (const int*)cache_map, (const int*)cache_len, make_fast_div((uint32_t)per_row));
+        } else if (pos_map && !seq_start && !pos_base &&
+                   rope_launch_is_short(ctas, (size_t)dev.sms * 6)) {   // the engine's case: a pass of at most 8,192 rows, positions from its map
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rope_qk_map_hot_kernel, 0, occ);
+            launch_hot(rope_qk_map_hot_kernel, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, as_stream(stream), segs, cos_table,
+                       sin_table, head_dim, rotary_dim, (const int*)pos_map, make_fast_div((uint32_t)per_row));
         } else {
             static std::atomic<int> occ{0};
             const int per_sm = ctas_per_sm(rope_multi_hot_kernel<2>, 0, occ);

@@ -109,6 +109,17 @@ def test_rope_and_embed_full_size():
         out2 = dev.rope_apply_dev(x, cos, sin, rows, heads, 128, 64, seq_start=seq_start,
                                   pos_base=torch.zeros(1, dtype=torch.int32, device="cuda"))
         assert torch.equal(out, out2)
+    # q and k in one launch: long launches take the streaming kernel, short ones the kernel with hoisted loads; both
+    # must give the bytes of the separate calls (sizes either side of the switch, and the ragged full size)
+    for n in (130712, 40000, 8192, 20000):
+        q, k = randn_bf16(gen, n, 16, 128), randn_bf16(gen, n, 2, 128)
+        want_q = dev.rope_apply_dev(q, cos, sin, n, 16, 128, 64, pos_map=positions)
+        want_k = dev.rope_apply_dev(k, cos, sin, n, 2, 128, 64, pos_map=positions)
+        got_q, got_k = dev.rope_qk_dev(q, k, cos, sin, n, 16, 2, 128, 64, pos_map=positions)
+        assert torch.equal(got_q, want_q) and torch.equal(got_k, want_k)
+        ref = ref_gpu.rope(q.float(), cos, sin, n, 16, 128, 64, None, None, positions)
+        assert max_bf16_ulp(got_q, ref.to(torch.bfloat16)) <= 2
+        del q, k, want_q, want_k, got_q, got_k, ref
     vocab = 32768
     table = randn_bf16(gen, vocab, HIDDEN)
     ids = torch.randint(0, vocab, (rows,), device="cuda", generator=gen, dtype=torch.int32)
