@@ -15,6 +15,7 @@
 #include "common.cuh"
 #include "f32x2.cuh"
 #include "nvfp4_codec.cuh"
+#include "silu_forms.cuh"
 
 namespace clef {
 
@@ -366,20 +367,6 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
 // by the tests; -0.0 gives +0.0, which the quantiser cannot tell apart). Blocks holding a larger |g|,
 // an infinity or a NaN take the literal expression.
 // ---------------------------------------------------------------------------------------------
-constexpr float kSiluFastMaxAbs = 44.0f;
-constexpr float kNegLog2e = -1.4426950408889634f;
-
-__device__ __forceinline__ float ex2_approx(float t) {
-    float r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
-    return r;
-}
-__device__ __forceinline__ float rcp_approx(float d) {
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
-    return r;
-}
-
 // (g0, g1) -> (silu(g0), silu(g1)) with the IEEE quotient, short form; domain above.
 __device__ __forceinline__ f32x2 silu_ieee_fast_x2(f32x2 g2) {
     const f32x2 t2 = f2_mul(g2, f2_splat(kNegLog2e));
@@ -407,15 +394,6 @@ __device__ __forceinline__ f32x2 silu_ieee_refined_f32_x2(f32x2 g2) {
     const f32x2 q = f2_fma(make_float2(__fmaf_rn(-dx, q0.x, g2.x), __fmaf_rn(-dy, q0.y, g2.y)), r2, q0);
     return make_float2(__uint_as_float((__float_as_uint(q.x) & 0x7fffffffu) | (__float_as_uint(g2.x) & 0x80000000u)),
                        __uint_as_float((__float_as_uint(q.y) & 0x7fffffffu) | (__float_as_uint(g2.y) & 0x80000000u)));
-}
-// The same quotient, one value, all scalar (no register pairs to form).
-__device__ __forceinline__ float silu_ieee_refined_f32(float g) {
-    const float d = __fadd_rn(1.0f, ex2_approx(__fmul_rn(g, kNegLog2e)));
-    float r = rcp_approx(d);
-    r = __fmaf_rn(__fmaf_rn(-d, r, 1.0f), r, r);
-    const float q0 = __fmul_rn(g, r);
-    const float q = __fmaf_rn(__fmaf_rn(-d, q0, g), r, q0);
-    return __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(g) & 0x80000000u));
 }
 template <int NP>
 __device__ __forceinline__ bool silu_f32_magnitude_domain_x2(const f32x2* g) {

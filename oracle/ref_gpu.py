@@ -441,3 +441,18 @@ def probe_blocks(values, global_scale: float, use_pairs: bool = False):
            [values, (n, ctypes.c_ulonglong), float(global_scale), ws, wp, gs, gp, buf, int(use_pairs)])
     torch.cuda.synchronize()
     return _read_results(buf, 2), ws, wp, gs, gp
+
+
+def probe_epilogue(accg, accu, a_rows: int, rows_padded: int, cols: int, gscale_g: float, gscale_u: float, out_global: float,
+                   mode: int, blk_mn: int = 128, interleaved: bool = False):
+    """The GEMM-epilogue quantiser of aiis_clef_b200/csrc/nvfp4_epilogue.cuh (mode 0: a thread holds a block; 1: the
+    mma.sync fragment layout) or the reference header's arithmetic in that fragment layout (mode 2) on f32
+    "accumulators" [rows_padded, cols]; returns (packed, scales) in clef_swiglu_quantise_nvfp4's layout."""
+    assert rows_padded % blk_mn == 0 and rows_padded % 16 == 0 and cols % 64 == 0
+    packed = torch.zeros(rows_padded * (cols // 2), dtype=torch.uint8, device=accg.device)
+    scales = torch.zeros(rows_padded * (cols // 16), dtype=torch.uint8, device=accg.device)
+    chunk = 4 * blk_mn
+    launch("ref_probe", "probe_epilogue", (148 * 4,), (256,),
+           [accg, accu, a_rows, rows_padded, cols, float(gscale_g), float(gscale_u), float(out_global), blk_mn,
+            -chunk if interleaved else chunk, packed, scales, mode])
+    return packed, scales

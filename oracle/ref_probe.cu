@@ -15,6 +15,7 @@
 #include "kernels_generic.cuh"
 #include "kernels_hot.cuh"   // packed-pair quantiser and the short silu forms of the tuned kernels
 #include "kernels_fp8.cuh"   // e4m3_encode_any, the FP8 quantisers' element encoder
+#include "nvfp4_epilogue.cuh"   // the GEMM-epilogue quantiser as device functions
 
 struct ProbeResult {
     unsigned long long checked;
@@ -302,4 +303,83 @@ extern "C" __global__ void probe_div_six(ProbeResult* result) {
         }
     }
     atomicAdd(&result[0].checked, checked);
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// The GEMM-epilogue quantiser (nvfp4_epilogue.cuh) fed with "accumulators" from global memory.
+// accg / accu: [rows_padded, cols] f32 (rows >= a_rows are padding of the M tile). Outputs use the layout of
+// clef_swiglu_quantise_nvfp4: packed [rows_padded, cols / 2], scales tiled (chunk_arg < 0: interleaved order).
+// mode 0: one thread per (row, block) holding the block (the tcgen05.ld 32x32b layout);
+// mode 1: the mma.sync m16n8 fragment layout of kernels/gemm.cu through nvfp4_swiglu_epilogue_quad4;
+// mode 2: the same fragment walk spelled with the REFERENCE's header (to_e4m3 / to_e2m1 / from_e4m3) and the
+//         literal SwiGLU expression, as kernels/gemm.cu:895-958 writes it.
+// ---------------------------------------------------------------------------------------------------------
+extern "C" __global__ void probe_epilogue(const float* accg, const float* accu, int a_rows, int rows_padded, int cols,
+                                          float gscale_g, float gscale_u, float out_global, int blk_mn, int chunk_arg,
+                                          uint8_t* packed, uint8_t* scales, int mode) {
+    const int blocks = cols / 16;
+    const int order = chunk_arg < 0 ? clef::kSfInterleaved : clef::kSfActivation;
+    if (mode == 0) {
+        const long long total = (long long)rows_padded * blocks;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+            const int row = (int)(i / blocks), b = (int)(i % blocks);
+            const clef::Nvfp4Block q = clef::nvfp4_swiglu_epilogue_block16(accg + (size_t)row * cols + b * 16, accu + (size_t)row * cols + b * 16,
+                                                                            gscale_g, gscale_u, out_global, nullptr, row < a_rows);
+            scales[clef::nvfp4_scale_offset(row, b, blocks, blk_mn, order)] = (uint8_t)q.stored;
+            *reinterpret_cast<uint2*>(packed + (size_t)row * (cols / 2) + b * 8) = make_uint2(q.lo, q.hi);
+        }
+        return;
+    }
+    // fragment walk: a warp per 16-row x 16-column tile; lane holds rows c_row and c_row + 8, columns 8 s + 2 (lane & 3) + e
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int c_row = lane >> 2, quad = lane & 3;
+    const long long tiles = (long long)(rows_padded / 16) * blocks;
+    for (long long t = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tiles; t += warps) {
+        const int r0 = (int)(t / blocks) * 16, b = (int)(t % blocks);
+        for (int r = 0; r < 2; ++r) {
+            const int row = r0 + c_row + 8 * r;
+            float g[4], u[4];
+            for (int s = 0; s < 2; ++s) {
+                for (int e = 0; e < 2; ++e) {
+                    const size_t at = (size_t)row * cols + b * 16 + 8 * s + 2 * quad + e;
+                    g[2 * s + e] = accg[at];
+                    u[2 * s + e] = accu[at];
+                }
+            }
+            uint32_t stored, byte0, byte1;
+            if (mode == 1) {
+                const clef::Nvfp4Quad q = clef::nvfp4_swiglu_epilogue_quad4(g, u, gscale_g, gscale_u, out_global, row < a_rows);
+                stored = q.stored;
+                byte0 = q.byte[0];
+                byte1 = q.byte[1];
+            } else {
+                float vv[4];
+                float m0 = 0.0f;
+                for (int i = 0; i < 4; ++i) {
+                    const float gg = g[i] * gscale_g;
+                    const float gu = u[i] * gscale_u;
+                    vv[i] = (gg / (1.0f + __expf(-gg))) * gu;
+                }
+                m0 = fmaxf(fmaxf(fabsf(vv[0]), fabsf(vv[1])), fmaxf(fabsf(vv[2]), fabsf(vv[3])));
+                m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+                m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+                const uint8_t st = (row < a_rows) ? to_e4m3((m0 / 6.0f) * out_global) : (uint8_t)0;
+                const float stored_f = from_e4m3(st);
+                const float inv_scale = (stored_f > 0.0f) ? out_global / stored_f : 0.0f;
+                stored = st;
+                byte0 = byte1 = 0;
+                if (row < a_rows) {
+                    byte0 = to_e2m1(vv[0] * inv_scale) | (to_e2m1(vv[1] * inv_scale) << 4);
+                    byte1 = to_e2m1(vv[2] * inv_scale) | (to_e2m1(vv[3] * inv_scale) << 4);
+                }
+            }
+            if (quad == 0) {
+                scales[clef::nvfp4_scale_offset(row, b, blocks, blk_mn, order)] = (uint8_t)stored;
+            }
+            packed[(size_t)row * (cols / 2) + b * 8 + quad] = (uint8_t)byte0;
+            packed[(size_t)row * (cols / 2) + b * 8 + 4 + quad] = (uint8_t)byte1;
+        }
+    }
 }
