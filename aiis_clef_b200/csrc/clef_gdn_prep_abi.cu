@@ -207,7 +207,10 @@ int clef_gdn_conv_prep(clef_stream_t stream, const void* x, const float* w, floa
         !aligned(k_hi, 16) || !aligned(k_lo, 16) || !aligned(kn, 16) || (history && !aligned(history, 16))) {
         return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
     }
-    if (k != 4) return CLEF_DECLINED;   // the caller runs clef_causal_conv_silu and clef_gdn_prep
+    // The fused kernel is no faster than clef_causal_conv_silu + clef_gdn_prep (220 against 72 + 142 us at 8,192 tokens x
+    // 8,192 channels: it is held at two CTAs per SM); what it saves is the intermediate buffer. So it declines, and
+    // the caller runs the faster pair, unless the process asked for memory-saving fusions (clef_set_kernel_choice(2)).
+    if (k != 4 || !use_memory_saving_fusions()) return CLEF_DECLINED;
     if (rows == 0) return CLEF_OK;
     if ((size_t)rows * channels >= ((size_t)1 << 34)) return fail(CLEF_ERR_TOO_LARGE, "%s: %d x %d values", what, rows, channels);
     DeviceInfo dev;

@@ -9,7 +9,7 @@ import torch
 import aiis_clef_b200 as clef
 from oracle import binding as orc
 from oracle import ref_gpu
-from gpu_util import dev_bf16, dev_f32_from_bits
+from gpu_util import dev_bf16, dev_f32_from_bits, ptr, stream
 from util import bf16_ulp_distance, normal_bf16, to_bf16_bits
 
 pytestmark = pytest.mark.gpu
@@ -266,6 +266,16 @@ def test_gdn_conv_prep_equals_the_reference_chain(seq_len, kh, heads, mode):
                                     None if hist is None else dev_f32_from_bits(hist), d_sm)
     ref = ref_gpu.gdn_prep(conv.contiguous().view(-1), seq_len, kh, kd, heads, conv_dim)
     dev = clef.Device(0)
+    # by default the entry point declines (the two calls are the faster form) ...
+    lib = clef.load()
+    dx, dh = dev_bf16(xb), (None if hist is None else dev_bf16(hist))
+    bufs = [torch.empty(heads * ((seq_len + 63) // 64) * 2 * 64 * 128, dtype=torch.uint8, device="cuda") for _ in range(4)]
+    kn_, v_ = torch.empty(seq_len, heads, kd, device="cuda"), torch.empty(seq_len, heads * kd, device="cuda")
+    assert lib.clef_gdn_conv_prep(stream(), ptr(dx), ptr(dw), ptr(v_), ptr(bufs[0]), ptr(bufs[1]), ptr(bufs[2]), ptr(bufs[3]), ptr(kn_),
+                                  seq_len, conv_dim, k, ptr(d_ss), ptr(dh), ptr(d_sm), heads, kh, kd,
+                                  float(np.float32(1.0) / np.sqrt(np.float32(kd))), 0) == 1
+    # ... and runs as one launch once memory-saving fusions are asked for
+    clef.set_kernel_choice(2)
     for x_in, h_in in ((dev_f32_from_bits(xb), None if hist is None else dev_f32_from_bits(hist)),
                        (dev_bf16(xb), None if hist is None else dev_bf16(hist))):
         got = dev.gdn_conv_prep_dev(x_in, dw, seq_len, kh, kd, heads, conv_dim, k, d_ss, h_in, d_sm)
