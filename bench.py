@@ -761,6 +761,13 @@ def full_pass(h: Harness, shared):
     positions = torch.arange(FULL_ROWS, dtype=torch.int32, device="cuda")
     cos, sin = h.dev.rope_tables_dev(positions, FULL_ROWS, ROTARY, THETA)   # one request of 130,712 tokens at slot 0
     tables = (cos, sin, positions)
+    # the replicated operands of the pass (norm weights, embedding table) are the same on every rank
+    wgen = torch.Generator(device="cuda")
+    wgen.manual_seed(515151)
+    shared = dict(shared)
+    shared["w_norm"] = (torch.randn(HIDDEN, device="cuda", generator=wgen) * 0.1).contiguous()
+    shared["w_gated"] = (1.0 + torch.randn(HEAD_DIM, device="cuda", generator=wgen) * 0.1).contiguous()
+    shared["table"] = h.randn_bf16(VOCAB, HIDDEN, gen=wgen) * 0.02
     inp = full_pass_inputs(h, first, n)
     per_set = sum(BYTES_PER_ROW[k] for k in FULL_KERNELS) * n
     nsets = int(max(1, min(4, math.ceil(2e9 / per_set))))      # 1 set of 7.9 GB on one GPU, 3 sets of 1 GB each on eight
