@@ -89,9 +89,11 @@ BYTES_PER_ROW = {
     # hi + lo pairs for 32 expanded heads, normalised k and v as f32 out
     "gdn_prep": 2 * CONV_DIM + 4 * 32 * 128 * 2 + 2 * 32 * 128 * 4,                           # 81,920
 }
-# The step: RMSNorm+NVFP4, SwiGLU+NVFP4, and the partial RoPE of the q and the k heads, which share their positions
-# and go out as one launch (clef_rope_qk); rope_q / rope_k alone are reported under "kernels".
-STEP_KERNELS = ["rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk"]
+# The step, in the order a layer runs its kernels: the partial RoPE of the q and the k heads (attention block; they
+# share their positions and go out as one launch, clef_rope_qk), RMSNorm+NVFP4 (the MLP block's input norm) and
+# SwiGLU+NVFP4. rope_q / rope_k alone are reported under "kernels". The order matters by up to 3 us per step: the
+# first kernel of a graph replay starts cold (no overlap with its predecessor), which costs the RoPE kernel least.
+STEP_KERNELS = ["rope_qk", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4"]
 FULL_KERNELS = ["embed_gather", "rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk",
                 "rms_norm_gated_quantise_nvfp4"]     # the full fused chain over 130,712 rows
 DOMINANT = "swiglu_quantise_nvfp4"
@@ -269,7 +271,8 @@ def workload_config():
         "rows_per_gpu": ROWS, "hidden": HIDDEN, "intermediate": INTER, "activation_storage": "bf16",
         "l2": f"inputs larger than L2: {NSETS} rotating buffer sets of about 0.37 GB each; a kernel timed alone rotates over "
               f"at least {ROTATE_BYTES / 1e6:.0f} MB of its own buffers",
-        "launch": "one CUDA graph replay per step (3 kernels)", "parallelism": "row-range replicas, no collective",
+        "launch": "one CUDA graph replay per step (3 kernels in layer order: RoPE q + k, RMSNorm+NVFP4, SwiGLU+NVFP4)",
+        "parallelism": "row-range replicas, no collective",
         "timing": f"median of {BATCHES} batches of `steps` replays, CUDA events, max over ranks",
     }
 
