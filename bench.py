@@ -913,13 +913,13 @@ def other_configurations(h: Harness, shared, launchers, sets):
             view = {k: d[k][r0:r0 + rung] for k in ("x", "gate", "up", "q", "k")}
             o = {"pk_h": d["pk_h"][r0 * HIDDEN // 2:], "sc_h": d["sc_h"][r0 * HIDDEN // 16:], "pk_i": d["pk_i"][r0 * INTER // 2:],
                  "sc_i": d["sc_i"][r0 * INTER // 16:], "q_out": d["q_out"][r0:], "k_out": d["k_out"][r0:]}
+            launches.append(lambda v=view, o=o: lib.clef_rope_qk(
+                stream(), p(o["q_out"]), p(v["q"]), Q_HEADS, p(o["k_out"]), p(v["k"]), KV_HEADS, p(cos), p(sin), rung, HEAD_DIM, ROTARY,
+                None, None, p(dev_pos), 0))
             launches.append(lambda v=view, o=o: lib.clef_rms_norm_quantise_nvfp4(
                 stream(), p(v["x"]), p(shared["w_norm"]), p(o["pk_h"]), p(o["sc_h"]), rung, HIDDEN, EPS, GS_NORM, 128, 512, 0))
             launches.append(lambda v=view, o=o: lib.clef_swiglu_quantise_nvfp4(
                 stream(), p(v["gate"]), p(v["up"]), p(o["pk_i"]), p(o["sc_i"]), rung, INTER, GS_SWIGLU, 128, 512, 0))
-            launches.append(lambda v=view, o=o: lib.clef_rope_qk(
-                stream(), p(o["q_out"]), p(v["q"]), Q_HEADS, p(o["k_out"]), p(v["k"]), KV_HEADS, p(cos), p(sin), rung, HEAD_DIM, ROTARY,
-                None, None, p(dev_pos), 0))
         per_pass = [h.capture(launches[3 * i:3 * i + 3]) for i in range(len(launches) // 3)]
         dev_maps.copy_(host_maps, non_blocking=True)
         for g in per_pass[:3]:
