@@ -321,8 +321,14 @@ fp8_rows_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
             s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
         }
     }
-    pdl_wait_prior_grids();
     int row = blockIdx.x * 8 + warp;
+    if (row < rows) {   // this warp's first row towards L2 (a lane covers 128 bytes); see prefetch_l2
+#pragma unroll
+        for (int h = 0; h < NB / 4; ++h) {
+            prefetch_l2(x + (size_t)row * COLS + (size_t)(lane + 32 * h) * 64);
+        }
+    }
+    pdl_wait_prior_grids();
     U8x32 d[NB];
     if (row < rows) {
 #pragma unroll
@@ -445,8 +451,13 @@ fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__
     const int team = warp / WPR, wt = warp % WPR;
     const int first_block = wt * 32 + lane;
     pdl_launch_dependents();
-    pdl_wait_prior_grids();
     int row = blockIdx.x * TEAMS + team;
+    if (row < rows && lane < 8 * BPL) {   // this warp's share of the team's first row towards L2; see prefetch_l2
+        const size_t off = (size_t)row * COLS + (size_t)(wt * 32 + 32 * WPR * (lane >> 3)) * 16 + (size_t)(lane & 7) * 64;
+        prefetch_l2(a + off);
+        if (MODE == kFp8SwiGLU) prefetch_l2(b + off);
+    }
+    pdl_wait_prior_grids();
     U8x32 da[BPL], db[MODE == kFp8SwiGLU ? BPL : 1];
     if (row < rows) {
 #pragma unroll
@@ -581,11 +592,15 @@ fp8_gated_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
         const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
         s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
     }
-    pdl_wait_prior_grids();
-    __syncthreads();
     // Head row of this lane group in step s of token t: t * VH + (wt * STEPS + s) * 8 + (lane >> 2).
     auto head_row = [&](int token, int step) { return (size_t)token * VH + (size_t)(wt * STEPS + step) * 8 + (lane >> 2); };
     int token = blockIdx.x * TEAMS + team;
+    if (token < tokens) {   // the warp's first 8 head rows towards L2: 16 lines of x, 16 of gate; see prefetch_l2
+        const size_t first = ((size_t)token * VH + (size_t)(wt * STEPS) * 8) * COLS;
+        prefetch_l2((lane < 16 ? x : gate) + first + (size_t)(lane & 15) * 64);
+    }
+    pdl_wait_prior_grids();
+    __syncthreads();
     U8x32 dx[2], dg[2];
     if (token < tokens) {
 #pragma unroll

@@ -1287,6 +1287,13 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
         const float4 t = *reinterpret_cast<const float4*>(weight + threadIdx.x * 4);
         s_w[threadIdx.x] = make_float4(1.0f + t.x, 1.0f + t.z, 1.0f + t.y, 1.0f + t.w);
     }
+    if (!KV) {   // the warp's first 8 head rows towards L2 (contiguous: 16 lines, 32 with the gate halves); see prefetch_l2
+        const uint32_t first = hrow - (uint32_t)(lane >> 2);
+        constexpr int LINES = 8 * STRIDE / 64;
+        if (lane < LINES && first + (uint32_t)(lane * 64 / STRIDE) < rows) {
+            prefetch_l2(x + (size_t)first * STRIDE + (size_t)lane * 64);
+        }
+    }
     pdl_wait_prior_grids();
     auto row_ptr = [&](uint32_t r) {
         return (KV && r >= key_rows) ? kv.v + (size_t)(r - key_rows) * HD : x + (size_t)r * STRIDE;
