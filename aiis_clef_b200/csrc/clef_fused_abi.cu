@@ -243,6 +243,21 @@ static int rms_norm_quantise_impl(const char* what, clef_stream_t stream, const 
 #undef CLEF_RMSQ_HOT
         return check_launch(what);
     }
+    if (dtype == CLEF_F32 && !addend && use_hot() && hot_scale_ok(global_scale) && (cols == 2048 || cols == 4096) && aligned(x, 32)) {
+        // f32 activations (the reference engine's residual stream): the tuned kernel's f32 form
+        const size_t groups = ((size_t)rows_total + 7) / 8;
+        const size_t smem = (size_t)cols * sizeof(float);
+        const FastDiv atom_div = make_fast_div((uint32_t)blk_mn);
+        auto launch = [&](auto kernel, std::atomic<int>& occ) {
+            const int per_sm = ctas_per_sm(kernel, smem, occ);
+            launch_hot(kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s, (const float*)x, weight, packed, scales, rows,
+                       rows_total, eps, global_scale, blk_mn, chunk, atom_div);
+        };
+        static std::atomic<int> occ[2];
+        if (cols == 2048) launch(rms_norm_quant_f32_hot_kernel<4>, occ[0]);
+        else launch(rms_norm_quant_f32_hot_kernel<8>, occ[1]);
+        return check_launch(what);
+    }
     if (addend) {   // shape-general path: the add, then the norm + quantiser on the stored sum
         if (int r = clef_add(stream, sum_out, x, addend, (size_t)rows * cols, dtype)) return r;
         x = sum_out;

@@ -103,7 +103,9 @@ __device__ __forceinline__ uint32_t e2m1_pack8(float e0, float e1, float e2, flo
 // For an all-zero block the codes come out as zeros whatever table entry is read, and the scale byte is 0.
 // NEG: the pairs hold the NEGATED values (the SwiGLU fast path produces -v); magnitudes are unaffected
 // and the sign is restored by scaling with -inv_scale.
-template <bool NEG>
+// NATURAL: the pairs hold consecutive values, pair i = (value 2i, value 2i + 1), instead of the quad-pair layout
+// (f32 activations arrive that way from a 32-byte load and need no widening).
+template <bool NEG, bool NATURAL = false>
 __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale, const float* inv_table,
                                               uint32_t& stored_out, uint32_t& lo_out, uint32_t& hi_out) {
     float amax = 0.0f;
@@ -128,8 +130,13 @@ __device__ __forceinline__ bool quantise16_qp(const f32x2* v, float global_scale
     }
     // quad q: p[2q] = (x, z), p[2q+1] = (y, w); element order x, y, z, w
     stored_out = normal ? stored : 0u;
-    lo_out = e2m1_pack8(p[0].x, p[1].x, p[0].y, p[1].y, p[2].x, p[3].x, p[2].y, p[3].y);
-    hi_out = e2m1_pack8(p[4].x, p[5].x, p[4].y, p[5].y, p[6].x, p[7].x, p[6].y, p[7].y);
+    if (NATURAL) {
+        lo_out = e2m1_pack8(p[0].x, p[0].y, p[1].x, p[1].y, p[2].x, p[2].y, p[3].x, p[3].y);
+        hi_out = e2m1_pack8(p[4].x, p[4].y, p[5].x, p[5].y, p[6].x, p[6].y, p[7].x, p[7].y);
+    } else {
+        lo_out = e2m1_pack8(p[0].x, p[1].x, p[0].y, p[1].y, p[2].x, p[3].x, p[2].y, p[3].y);
+        hi_out = e2m1_pack8(p[4].x, p[5].x, p[4].y, p[5].y, p[6].x, p[7].x, p[6].y, p[7].y);
+    }
     return normal || amax == 0.0f;
 }
 
@@ -348,6 +355,133 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
                     rms_block_cold(((ADD || EMBED) ? (const uint16_t*)sum_out : x) + (size_t)row * COLS + b * 16, weight + b * 16, inv,
                                    global_scale, reinterpret_cast<uint2*>(prow + b * 8),
                                    srow + (size_t)(b >> 2) * chunk + (b & 3));
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same kernel for f32 activations (the reference engine's own residual-stream type), cols = NB * 512.
+// A lane's 16-value block is 64 bytes (two 256-bit loads) and arrives as f32, so there is nothing to widen and the
+// loaded registers ARE the row: pairs hold consecutive values (NATURAL), the sum of squares is scalar
+// (fma(x, x, y * y) + fma(z, z, w * w), the reference's association; the quad-pair trick would cost the moves it saves),
+// the summation tree is row_tree_256. Without raw registers to prefetch into, a row is loaded at the top of its
+// iteration (as in the residual-add form) and the NEXT row is only named to L2 one row ahead.
+// ---------------------------------------------------------------------------------------------
+static __device__ __noinline__ void rms_block_cold_f32(const float* xblk, const float* wblk, float inv, float global_scale,
+                                                       uint2* packed_dst, uint8_t* scale_dst) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = xblk[i] * inv * (1.0f + wblk[i]);
+    }
+    quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? 2 : 1))
+rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restrict__ weight, uint8_t* __restrict__ packed,
+                              uint8_t* __restrict__ scales, int rows, int rows_total, float eps, float global_scale,
+                              int blk_mn, int chunk, FastDiv atom_div) {
+    constexpr int COLS = NB * 512;
+    constexpr int BLOCKS = COLS / 16;
+    __shared__ float s_inv[kInvScaleTableSize];
+    const SfLayout sf = sf_layout_of(blk_mn, chunk);   // a negated chunk selects the interleaved tile order
+    chunk = sf.chunk;
+    extern __shared__ float4 s_w[];   // (1 + w) of quad q of chunk L + 32 j at s_w[(4 j + q) * 32 + L], natural order
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+
+    pdl_launch_dependents();
+    fill_inv_scale_table(s_inv, global_scale);
+    for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
+        const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
+        const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
+        s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.y, 1.0f + w.z, 1.0f + w.w);
+    }
+    int row = blockIdx.x * 8 + warp;
+    // a row is COLS * 4 bytes = NB * 16 lines of 128 bytes: NB / 2 per lane
+    auto name_row_to_l2 = [&](int r) {
+#pragma unroll
+        for (int h = 0; h < NB / 2; ++h) {
+            prefetch_l2(x + (size_t)r * COLS + (size_t)(lane + 32 * h) * 32);
+        }
+    };
+    if (row < rows) name_row_to_l2(row);   // under the previous kernel's tail; see prefetch_l2
+    pdl_wait_prior_grids();
+    __syncthreads();
+
+    for (; row < rows_total; row += gridDim.x * 8) {
+        uint8_t* prow = packed + (size_t)row * (COLS / 2);
+        const uint32_t m_rest = fast_div((uint32_t)row, atom_div);
+        const uint32_t m_atom = sf_row_slot((uint32_t)row - m_rest * (uint32_t)blk_mn, sf);
+        uint8_t* srow = scales + (size_t)m_rest * (BLOCKS / 4) * (size_t)chunk + (size_t)m_atom * 4;
+        if (row >= rows) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int b = lane + 32 * j;
+                *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(0u, 0u);
+                srow[(size_t)(b >> 2) * chunk + (b & 3)] = 0;
+            }
+            continue;
+        }
+        const float* xrow = x + (size_t)row * COLS;
+        U8x32 d[NB][2];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            d[j][0] = ldg_stream_v8(xrow + (size_t)(lane + 32 * j) * 16);
+            d[j][1] = ldg_stream_v8(xrow + (size_t)(lane + 32 * j) * 16 + 8);
+        }
+        const int next = row + gridDim.x * 8;
+        if (next < rows) name_row_to_l2(next);
+        f32x2 v[NB][8];
+        float p[2][4];
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) p[a][k] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {   // quad q = words 4q .. 4q + 3 of the block
+                const U8x32& half = d[j][q >> 1];
+                const int o = (q & 1) * 4;
+                const float vx = __uint_as_float(half.w[o]), vy = __uint_as_float(half.w[o + 1]);
+                const float vz = __uint_as_float(half.w[o + 2]), vw = __uint_as_float(half.w[o + 3]);
+                v[j][2 * q] = f2_pack(vx, vy);
+                v[j][2 * q + 1] = f2_pack(vz, vw);
+                const float quad = __fadd_rn(__fmaf_rn(vx, vx, __fmul_rn(vy, vy)), __fmaf_rn(vz, vz, __fmul_rn(vw, vw)));
+                p[j & 1][q] = __fadd_rn(p[j & 1][q], quad);
+            }
+        }
+        const float inv = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
+                                                   : inv_rms(row_tree_256(p, lane), COLS, eps);
+        const f32x2 inv2 = f2_splat(inv);
+        uint32_t bad = 0u;   // bit j: block j is outside the fast domain
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 w = s_w[(4 * j + q) * 32 + lane];
+                v[j][2 * q] = f2_mul(f2_mul(v[j][2 * q], inv2), make_float2(w.x, w.y));
+                v[j][2 * q + 1] = f2_mul(f2_mul(v[j][2 * q + 1], inv2), make_float2(w.z, w.w));
+            }
+            uint32_t stored, lo, hi;
+            const bool ok = quantise16_qp<false, true>(v[j], global_scale, s_inv, stored, lo, hi);
+            const int b = lane + 32 * j;
+            *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(lo, hi);
+            srow[(size_t)(b >> 2) * chunk + (b & 3)] = (uint8_t)stored;
+            bad |= ok ? 0u : (1u << j);
+        }
+        if (bad) {   // rare: the literal path overwrites what the fast path stored
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                if (bad & (1u << j)) {
+                    const int b = lane + 32 * j;
+                    rms_block_cold_f32(xrow + b * 16, weight + b * 16, inv, global_scale, reinterpret_cast<uint2*>(prow + b * 8),
+                                       srow + (size_t)(b >> 2) * chunk + (b & 3));
                 }
             }
         }

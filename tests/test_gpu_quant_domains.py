@@ -99,11 +99,38 @@ def test_rms_norm_quantise_outside_the_fast_domain(cols, global_scale):
     dx, dw = dev_bf16(x), torch.from_numpy(w).cuda()
     got_p, got_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(dx), ptr(dw)],
                              [rows, cols, 1e-6, global_scale, 128, 512, BF16])
-    normed = ref_gpu.rms_norm(dev_f32_from_bits(x), dw, rows, cols, 1e-6)
+    xf = dev_f32_from_bits(x)
+    normed = ref_gpu.rms_norm(xf, dw, rows, cols, 1e-6)
     ref_p, ref_s = ref_gpu.quantise_nvfp4(normed, rows, cols, global_scale)
     torch.cuda.synchronize()
     assert_bytes_equal(got_s, ref_s.cpu().numpy(), "scales vs reference chain")
     assert_bytes_equal(got_p, ref_p.cpu().numpy(), "packed vs reference chain")
+    # the tuned f32 kernel (the engine's own dtype) on the same rows
+    f_p, f_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(xf), ptr(dw)], [rows, cols, 1e-6, global_scale, 128, 512, 1])
+    assert_bytes_equal(f_s, ref_s.cpu().numpy(), "f32 activations: scales vs reference chain")
+    assert_bytes_equal(f_p, ref_p.cpu().numpy(), "f32 activations: packed vs reference chain")
+
+
+def test_rms_norm_quantise_f32_on_arbitrary_f32_rows():
+    """f32 rows that are not bf16 values (the engine's residual stream), 4096 columns: the reference's own fused kernel
+    serves this shape, and the chain must agree with it too; 8,192 rows cover the tuned kernel's tail."""
+    for rows, cols in ((8192, 2048), (777, 4096)):
+        gen = torch.Generator(device="cuda").manual_seed(rows)
+        x = torch.randn(rows, cols, device="cuda", generator=gen) * 3.0
+        x[:, 5] *= 30.0
+        x[17] = 0.0
+        w = torch.randn(cols, device="cuda", generator=gen) * 0.1
+        got_p, got_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(x), ptr(w)], [rows, cols, 1e-6, 80.0, 128, 512, 1])
+        normed = ref_gpu.rms_norm(x, w, rows, cols, 1e-6)
+        ref_p, ref_s = ref_gpu.quantise_nvfp4(normed, rows, cols, 80.0)
+        torch.cuda.synchronize()
+        assert_bytes_equal(got_s, ref_s.cpu().numpy(), "scales vs reference chain")
+        assert_bytes_equal(got_p, ref_p.cpu().numpy(), "packed vs reference chain")
+        if cols == 4096:
+            fp, fs = ref_gpu.rms_norm_quantise_nvfp4(x, w, rows, cols, 1e-6, 80.0)
+            torch.cuda.synchronize()
+            assert_bytes_equal(got_s, fs.cpu().numpy(), "scales vs reference fused kernel")
+            assert_bytes_equal(got_p, fp.cpu().numpy(), "packed vs reference fused kernel")
 
 
 @pytest.mark.parametrize("global_scale", [2e-3, 0.05, 3e4, 4e9, 1e11, 1e-25])
