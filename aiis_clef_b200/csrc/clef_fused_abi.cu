@@ -444,6 +444,15 @@ static int clef_rms_norm_gated_quantise_nvfp4_impl(clef_stream_t stream, const v
                    make_fast_div((uint32_t)vh), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);
     }
+    if (dtype == CLEF_F32 && use_hot() && hot_scale_ok(global_scale) && cols == 128 && aligned(x, 32) && aligned(gate, 32)) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(gated_norm_quant_f32_hot_kernel, 0, occ);
+        const size_t groups = ((size_t)rows + 63) / 64;   // 64 head rows per CTA step
+        launch_hot(gated_norm_quant_f32_hot_kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, s, (const float*)x,
+                   (const float*)gate, weight, packed, scales, rows_live, rows, eps, global_scale, blk_mn, chunk, vh,
+                   make_fast_div((uint32_t)vh), make_fast_div((uint32_t)blk_mn));
+        return check_launch(what);
+    }
     if (dtype == CLEF_BF16) {
         launch_gated_generic<Bf16, true>(s, dev, x, gate, weight, nullptr, packed, scales, rows_live, rows, cols, eps,
                                          global_scale, blk_mn, chunk, vh);

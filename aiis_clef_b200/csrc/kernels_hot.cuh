@@ -846,6 +846,144 @@ gated_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __re
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same kernel for f32 activations (the reference engine's own type): a lane's two chunks of x and of the gate
+// are 64 bytes each and arrive as f32, pairs hold consecutive values (NATURAL), the sum of squares is scalar, the
+// tree is head_tree_32; rows are loaded at the top of a step and the next step's rows are only named to L2.
+// silu_approx_fast_x2 equals __fdividef(g, 1 + __expf(-g)) for every f32 |g| <= 44 (all patterns are compared on
+// the device by the tests), so the short form serves f32 gates as it serves bf16 ones.
+// ---------------------------------------------------------------------------------------------
+static __device__ __noinline__ void gated_block_cold_f32(const float* xblk, const float* gblk, const float* wblk, float inv,
+                                                         float global_scale, uint2* packed_dst, uint8_t* scale_dst) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = xblk[i] * inv * wblk[i] * silu_fast_div(gblk[i]);
+    }
+    quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
+}
+
+static __global__ void __launch_bounds__(kCtaThreads, 2)
+gated_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ weight,
+                                uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows_live, int rows_total,
+                                float eps, float global_scale, int blk_mn, int chunk, int vh, FastDiv vh_div, FastDiv atom_div) {
+    constexpr int COLS = 128;
+    __shared__ float s_inv[kInvScaleTableSize];
+    const SfLayout sf = sf_layout_of(blk_mn, chunk);   // a negated chunk selects the interleaved tile order
+    chunk = sf.chunk;
+    __shared__ float4 s_w[32];   // plain weight, natural order: s_w[(h * 4 + q) * 4 + m] = quad q of chunk m + 4h
+    const int lane = threadIdx.x & 31;
+    const int m = lane & 3;
+    const int k1_count = (vh * (COLS / 16)) >> 2;
+    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
+    uint32_t hrow = blockIdx.x * (kCtaThreads / 4) + (threadIdx.x >> 2);
+
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
+        s_w[threadIdx.x] = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
+    }
+    fill_inv_scale_table(s_inv, global_scale);
+    // a CTA step covers 64 head rows of 512 bytes: 256 lines of x and 256 of the gate, two of each per thread
+    auto name_step_to_l2 = [&](uint32_t first) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t line = threadIdx.x + 256 * h;   // 4 lines per head row
+            if (first + (line >> 2) < (uint32_t)rows_live) {
+                prefetch_l2(x + (size_t)first * COLS + (size_t)line * 32);
+                prefetch_l2(gate + (size_t)first * COLS + (size_t)line * 32);
+            }
+        }
+    };
+    name_step_to_l2(blockIdx.x * (kCtaThreads / 4));   // under the previous kernel's tail; see prefetch_l2
+    pdl_wait_prior_grids();
+    __syncthreads();
+
+    // Every lane of a warp runs the same number of steps (the shuffles need the full warp).
+    uint32_t cta_first = blockIdx.x * (kCtaThreads / 4);
+    for (uint32_t base = hrow - (uint32_t)(lane >> 2); base < (uint32_t)rows_total;
+         base += groups_in_grid, hrow += groups_in_grid, cta_first += groups_in_grid) {
+        const bool in_range = hrow < (uint32_t)rows_total;
+        const bool live = hrow < (uint32_t)rows_live;
+        U8x32 dx[2][2], dg[2][2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dx[h][half].w[i] = dg[h][half].w[i] = 0u;
+            }
+        }
+        if (live) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const size_t off = (size_t)hrow * COLS + (m + 4 * h) * 16;
+                dx[h][0] = ldg_stream_v8(x + off);
+                dx[h][1] = ldg_stream_v8(x + off + 8);
+                dg[h][0] = ldg_stream_v8(gate + off);
+                dg[h][1] = ldg_stream_v8(gate + off + 8);
+            }
+        }
+        if (cta_first + groups_in_grid < (uint32_t)rows_live) name_step_to_l2(cta_first + groups_in_grid);
+        f32x2 v[2][8], gv[2][8];
+        float quad[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U8x32& hx = dx[h][q >> 1];
+                const U8x32& hg = dg[h][q >> 1];
+                const int o = (q & 1) * 4;
+                const float vx = __uint_as_float(hx.w[o]), vy = __uint_as_float(hx.w[o + 1]);
+                const float vz = __uint_as_float(hx.w[o + 2]), vw = __uint_as_float(hx.w[o + 3]);
+                v[h][2 * q] = f2_pack(vx, vy);
+                v[h][2 * q + 1] = f2_pack(vz, vw);
+                gv[h][2 * q] = f2_pack(__uint_as_float(hg.w[o]), __uint_as_float(hg.w[o + 1]));
+                gv[h][2 * q + 1] = f2_pack(__uint_as_float(hg.w[o + 2]), __uint_as_float(hg.w[o + 3]));
+                quad[h][q] = __fadd_rn(__fmaf_rn(vx, vx, __fmul_rn(vy, vy)), __fmaf_rn(vz, vz, __fmul_rn(vw, vw)));
+            }
+        }
+        const float total = head_tree_32(quad[0], quad[1], lane);
+        if (!in_range) {
+            continue;
+        }
+        const uint32_t token = fast_div(hrow, vh_div);
+        const uint32_t head_block = (hrow - token * (uint32_t)vh) * (COLS / 16);
+        const uint32_t m_rest = fast_div(token, atom_div);
+        const uint32_t m_atom = sf_row_slot(token - m_rest * (uint32_t)blk_mn, sf);
+        const float inv = inv_rms_pow2<COLS>(total, eps);
+        const f32x2 inv2 = f2_splat(inv);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t block = head_block + m + 4 * h;
+            uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)hrow * (COLS / 2) + (m + 4 * h) * 8);
+            uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
+            if (!live) {
+                *pdst = make_uint2(0u, 0u);
+                *sdst = 0;
+                continue;
+            }
+            uint32_t stored, lo, hi;
+            const bool in_domain = block_abs_max(gv[h]) <= kSiluFastMaxAbs;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 w = s_w[(h * 4 + q) * 4 + m];
+                // ((x * inv) * w) * silu(g), left to right as the reference writes it
+                v[h][2 * q] = f2_mul(f2_mul(f2_mul(v[h][2 * q], inv2), make_float2(w.x, w.y)), silu_approx_fast_x2(gv[h][2 * q]));
+                v[h][2 * q + 1] = f2_mul(f2_mul(f2_mul(v[h][2 * q + 1], inv2), make_float2(w.z, w.w)), silu_approx_fast_x2(gv[h][2 * q + 1]));
+            }
+            const bool done = quantise16_qp<false, true>(v[h], global_scale, s_inv, stored, lo, hi) && in_domain;
+            if (done) {
+                *pdst = make_uint2(lo, hi);
+                *sdst = (uint8_t)stored;
+            } else {
+                const size_t off = (size_t)hrow * COLS + (m + 4 * h) * 16;
+                gated_block_cold_f32(x + off, gate + off, weight + (m + 4 * h) * 16, inv, global_scale, pdst, sdst);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Plain NVFP4 quantiser (kernels/quantise.cu:6-53) for cols % 512 == 0: the SwiGLU kernel's unit
 // structure with one input.
 // ---------------------------------------------------------------------------------------------

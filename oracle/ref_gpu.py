@@ -407,11 +407,12 @@ def probe_silu_bf16():
 
 
 def probe_silu_f32(base: int, count: int):
-    """[packed, scalar] short silu of f32 accumulators against the literal expression."""
-    buf = _result_buffer(2)
+    """[packed, scalar] short silu of f32 accumulators against the literal expression, and [2] the approximate-quotient
+    form of the gated norm against __fdividef(g, 1 + __expf(-g))."""
+    buf = _result_buffer(3)
     launch("ref_probe", "probe_silu_f32", (148 * 8,), (256,), [(base, ctypes.c_ulonglong), (count, ctypes.c_ulonglong), buf])
     torch.cuda.synchronize()
-    return _read_results(buf, 2)
+    return _read_results(buf, 3)
 
 
 def probe_sigmoid_mul_bf16():

@@ -240,9 +240,17 @@ extern "C" __global__ void probe_silu_f32(unsigned long long base, unsigned long
         if (__float_as_uint(clef::silu_ieee_refined_f32(g)) != __float_as_uint(want)) {
             report(&result[1], bits);
         }
+        // result[2]: the approximate-quotient form of the gated norm on f32 activations, __fdividef(g, 1 + __expf(-g))
+        const float want_fast = __fdividef(g, 1.0f + __expf(-g));
+        const clef::f32x2 c = clef::silu_approx_fast_x2(clef::f2_pack(g, other));
+        const clef::f32x2 e = clef::silu_approx_fast_x2(clef::f2_pack(other, g));
+        if (__float_as_uint(c.x) != __float_as_uint(want_fast) || __float_as_uint(e.y) != __float_as_uint(want_fast)) {
+            report(&result[2], bits);
+        }
     }
     atomicAdd(&result[0].checked, checked);
     atomicAdd(&result[1].checked, checked);
+    atomicAdd(&result[2].checked, checked);
 }
 
 // The short form of x * 1.0f / (1.0f + __expf(-g)) (kernels/elementwise.cu:350-353) for every pair of a

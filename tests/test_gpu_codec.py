@@ -106,16 +106,18 @@ def test_short_silu_forms_on_every_bf16_value():
 def test_short_silu_on_f32_accumulators():
     """The causal convolution applies silu to f32 accumulators: its short form (one Newton step on the approximate
     reciprocal, exact-remainder correction, the sign of g copied) must equal g / (1 + __expf(-g)) bit for bit on
-    every f32 pattern with |g| <= 44, in its packed and in its scalar spelling."""
-    res = [{"checked": 0, "mismatches": 0, "first_bad": []} for _ in range(2)]
+    every f32 pattern with |g| <= 44, in its packed and in its scalar spelling. The gated norm's approximate-quotient
+    form (third result) must equal __fdividef(g, 1 + __expf(-g)) on the same patterns: the tuned f32 gated kernel
+    relies on it."""
+    res = [{"checked": 0, "mismatches": 0, "first_bad": []} for _ in range(3)]
     for base in (0x00000000, 0x80000000):          # |g| <= 44 lies in the first 0x42300001 patterns of each sign
         part = ref_gpu.probe_silu_f32(base, 0x42300001)
         for r, q in zip(res, part):
             r["checked"] += q["checked"]
             r["mismatches"] += q["mismatches"]
             r["first_bad"] += q["first_bad"]
-    assert res[0]["checked"] == res[1]["checked"] == 2 * 0x42300001
-    assert res[0]["mismatches"] == 0 and res[1]["mismatches"] == 0, _fmt(res)
+    assert res[0]["checked"] == res[1]["checked"] == res[2]["checked"] == 2 * 0x42300001
+    assert res[0]["mismatches"] == 0 and res[1]["mismatches"] == 0 and res[2]["mismatches"] == 0, _fmt(res)
 
 
 def test_short_division_by_six():

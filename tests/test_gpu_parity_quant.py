@@ -274,10 +274,10 @@ def test_rms_norm_gated_quantise_nvfp4(tokens, vh, choice):
     want_p, want_s, pre = orc.rms_norm_gated_quantise_nvfp4(x, g, w, rows, cols, vh, eps, gs, want_pre=True)
     n_scale, n_code, bad = explain_mismatches(pre.reshape(tokens, vh * cols), gs, got_p, got_s, want_p, want_s, tokens, vh * cols, rel=8e-6)
     assert bad == 0, f"{bad} differences from the CPU oracle are not at a rounding boundary ({n_scale} scales, {n_code} codes)"
-    if choice == 1:
-        f_p, f_s = run_gated(xf, gf, dw, tokens, vh, cols, eps, gs, dtype=F32)
-        assert_bytes_equal(f_p, got_p, "f32 input packed")
-        assert_bytes_equal(f_s, got_s, "f32 input scales")
+    # f32 activations, the reference engine's own dtype (tuned f32 kernel or the shape-general one)
+    f_p, f_s = run_gated(xf, gf, dw, tokens, vh, cols, eps, gs, dtype=F32)
+    assert_bytes_equal(f_p, got_p, "f32 input packed")
+    assert_bytes_equal(f_s, got_s, "f32 input scales")
 
 
 def test_gated_recipe_of_the_reference():

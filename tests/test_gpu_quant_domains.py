@@ -171,6 +171,40 @@ def test_gated_norm_quantise_outside_the_fast_domain(global_scale):
     torch.cuda.synchronize()
     assert_bytes_equal(scales.bytes(), ref_s.cpu().numpy(), "scales vs reference fused kernel")
     assert_bytes_equal(packed.bytes(), ref_p.cpu().numpy(), "packed vs reference fused kernel")
+    # the tuned f32 kernel on the same rows
+    xf, gf = dev_f32_from_bits(x), dev_f32_from_bits(g)
+    p2, s2 = Guarded(tokens_padded * vh * cols // 2), Guarded(tokens_padded * vh * cols // 16)
+    assert call("clef_rms_norm_gated_quantise_nvfp4", stream(), ptr(xf), ptr(gf), ptr(dw), p2.ptr, s2.ptr, tokens_padded * vh, cols, 1e-6,
+                global_scale, 128, 512, vh, rows, 1) == 0
+    torch.cuda.synchronize()
+    p2.check_guards("gated packed, f32")
+    s2.check_guards("gated scales, f32")
+    assert_bytes_equal(s2.bytes(), ref_s.cpu().numpy(), "f32 activations: scales vs reference fused kernel")
+    assert_bytes_equal(p2.bytes(), ref_p.cpu().numpy(), "f32 activations: packed vs reference fused kernel")
+
+
+def test_gated_norm_quantise_f32_on_arbitrary_f32_rows():
+    """f32 head rows and gates that are not bf16 values (8,192 tokens x 16 heads: the tuned f32 kernel's tail; and a
+    ragged token count with 32 heads), with gates beyond the short silu form's range: the reference's fused kernel."""
+    for tokens, vh in ((8192, 16), (301, 32)):
+        rows, cols = tokens * vh, 128
+        gen = torch.Generator(device="cuda").manual_seed(tokens)
+        x = torch.randn(rows, cols, device="cuda", generator=gen) * 2.0
+        g = torch.randn(rows, cols, device="cuda", generator=gen) * 3.0
+        g[5, :16] = 50.0
+        g[6, 16:32] = -95.0
+        x[9] = 0.0
+        w = 1.0 + torch.randn(cols, device="cuda", generator=gen) * 0.1
+        tp = (tokens + 127) // 128 * 128
+        packed, scales = Guarded(tp * vh * cols // 2), Guarded(tp * vh * cols // 16)
+        assert call("clef_rms_norm_gated_quantise_nvfp4", stream(), ptr(x), ptr(g), ptr(w), packed.ptr, scales.ptr, tp * vh, cols, 1e-6,
+                    96.0, 128, 512, vh, rows, 1) == 0
+        ref_p, ref_s = ref_gpu.rms_norm_gated_quantise_nvfp4(x, g, w, rows, cols, vh, 1e-6, 96.0)
+        torch.cuda.synchronize()
+        packed.check_guards("gated packed")
+        scales.check_guards("gated scales")
+        assert_bytes_equal(scales.bytes(), ref_s.cpu().numpy(), "scales vs reference fused kernel")
+        assert_bytes_equal(packed.bytes(), ref_p.cpu().numpy(), "packed vs reference fused kernel")
 
 
 # ---------------------------------------------------------------------------------------------------------
