@@ -146,6 +146,22 @@ int clef_embed_gather(clef_stream_t stream, const void* table, const int32_t* id
 
 }  // extern "C"
 
+// The unit-structured f32 quantisers (MODE 0 plain, 1 SwiGLU first); one unit per warp per step.
+template <int MODE>
+static void launch_unit_quant_f32(cudaStream_t s, const DeviceInfo& dev, const float* gate, const float* up, uint8_t* packed,
+                                  uint8_t* scales, int rows, int rows_total, int cols, float global_scale, int blk_mn,
+                                  int chunk) {
+    constexpr int kMinCtas = MODE == 1 ? 3 : 4;
+    static std::atomic<int> occ{0};
+    const int per_sm = ctas_per_sm(unit_quant_f32_hot_kernel<MODE, kMinCtas>, 0, occ);
+    const uint32_t segs = (uint32_t)(cols / 512);
+    const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;
+    const size_t ctas = ((size_t)total_units + 7) / 8;
+    launch_hot(unit_quant_f32_hot_kernel<MODE, kMinCtas>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s, gate, up, packed,
+               scales, live_units, total_units, cols, global_scale, blk_mn, chunk, make_fast_div(segs),
+               make_fast_div((uint32_t)blk_mn));
+}
+
 template <typename T, bool QUANT>
 static int launch_rms_norm_generic(cudaStream_t stream, const DeviceInfo& dev, const void* x, const float* weight,
                                    void* out, uint8_t* packed, uint8_t* scales, int rows, int rows_total, int cols,
@@ -546,6 +562,12 @@ static int clef_quantise_nvfp4_impl(clef_stream_t stream, const void* x, uint8_t
                    make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
         return check_launch(what);
     }
+    if (dtype == CLEF_F32 && use_hot() && hot_scale_ok(global_scale) && cols % 512 == 0 && (size_t)rows_total * (cols / 512) < 0x7fffffffull &&
+        aligned(x, 32)) {
+        launch_unit_quant_f32<0>(as_stream(stream), dev, (const float*)x, nullptr, packed, scales, rows, rows_total, cols,
+                                 global_scale, blk_mn, chunk);
+        return check_launch(what);
+    }
     if (dtype == CLEF_BF16) {
         launch_quantise_generic<Bf16, kActNone>(as_stream(stream), dev, x, nullptr, packed, scales, rows, rows_total, cols,
                                              global_scale, blk_mn, chunk);
@@ -596,6 +618,12 @@ static int clef_swiglu_quantise_nvfp4_impl(clef_stream_t stream, const void* gat
         launch_hot(swiglu_quant_hot_kernel<kUnits, kMinCtas, kActSwiGLU>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,
                    (const uint16_t*)gate, (const uint16_t*)up, packed, scales, live_units, total_units, cols,
                    global_scale, blk_mn, chunk, make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
+        return check_launch(what);
+    }
+    if (dtype == CLEF_F32 && use_hot() && hot_scale_ok(global_scale) && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(gate, 32) &&
+        aligned(up, 32)) {
+        launch_unit_quant_f32<1>(s, dev, (const float*)gate, (const float*)up, packed, scales, rows, rows_total, cols,
+                                 global_scale, blk_mn, chunk);
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {

@@ -1057,6 +1057,98 @@ quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed
 }
 
 // ---------------------------------------------------------------------------------------------
+// The unit-structured quantisers for f32 activations: a lane owns one block of 16 f32 values (two
+// 32-byte loads), values stay in natural pair order, and the unit a warp handles next is named to L2
+// while the current one is processed (no raw registers are held across units: the values alone take
+// 32 registers per input).
+// MODE 0: plain quantiser (kernels/quantise.cu:6-53). MODE 1: SwiGLU first (kernels/quantise.cu:523-591),
+// silu through silu_ieee_refined_f32_x2, which equals the IEEE quotient for every f32 gate of |g| <= 44.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load16_f32_natural(const float* p, f32x2* v) {
+    const U8x32 a = ldg_stream_v8(p), b = ldg_stream_v8(p + 8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[i] = f2_pack(__uint_as_float(a.w[2 * i]), __uint_as_float(a.w[2 * i + 1]));
+        v[4 + i] = f2_pack(__uint_as_float(b.w[2 * i]), __uint_as_float(b.w[2 * i + 1]));
+    }
+}
+
+template <int MODE>
+static __device__ __noinline__ void unit_block_cold_f32(const float* gblk, const float* xblk, float global_scale,
+                                                        uint2* packed_dst, uint8_t* scale_dst) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = MODE == 1 ? gated_literal<kActSwiGLU>(gblk[i], xblk[i]) : gblk[i];
+    }
+    quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
+}
+
+template <int MODE, int MIN_CTAS>
+__global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
+unit_quant_f32_hot_kernel(const float* __restrict__ gate, const float* __restrict__ up, uint8_t* __restrict__ packed,
+                          uint8_t* __restrict__ scales, uint32_t live_units, uint32_t total_units, int cols,
+                          float global_scale, int blk_mn, int chunk, FastDiv seg_div, FastDiv atom_div) {
+    __shared__ float s_inv[kInvScaleTableSize];
+    const SfLayout sf = sf_layout_of(blk_mn, chunk);   // a negated chunk selects the interleaved tile order
+    chunk = sf.chunk;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warps = gridDim.x * (kCtaThreads / 32);
+    uint32_t unit = blockIdx.x * (kCtaThreads / 32) + (threadIdx.x >> 5);
+    const int k1_count = cols >> 6;
+    // a unit is 2 KiB per input = 16 lines of 128 bytes: lanes 0-15 name the gate's, lanes 16-31 the up's
+    auto name_unit_to_l2 = [&](uint32_t u) {
+        if (MODE == 1) {
+            prefetch_l2((lane < 16 ? gate : up) + (size_t)u * 512 + (size_t)(lane & 15) * 32);
+        } else if (lane < 16) {
+            prefetch_l2(gate + (size_t)u * 512 + (size_t)lane * 32);
+        }
+    };
+    pdl_launch_dependents();
+    fill_inv_scale_table(s_inv, global_scale);
+    if (unit < live_units) name_unit_to_l2(unit);   // under the previous kernel's tail; see prefetch_l2
+    pdl_wait_prior_grids();
+    __syncthreads();
+
+    for (; unit < total_units; unit += warps) {
+        const uint32_t row = fast_div(unit, seg_div);
+        const uint32_t block = (unit - row * seg_div.d) * 32 + lane;
+        const uint32_t m_rest = fast_div(row, atom_div);
+        const uint32_t m_atom = sf_row_slot(row - m_rest * (uint32_t)blk_mn, sf);
+        uint8_t* sdst = scales + ((size_t)m_rest * k1_count + (block >> 2)) * (size_t)chunk + m_atom * 4 + (block & 3);
+        uint2* pdst = reinterpret_cast<uint2*>(packed + (size_t)unit * 256 + lane * 8);
+        if (unit >= live_units) {
+            *pdst = make_uint2(0u, 0u);
+            *sdst = 0;
+            continue;
+        }
+        const float* gblk = gate + (size_t)unit * 512 + lane * 16;
+        const float* ublk = MODE == 1 ? up + (size_t)unit * 512 + lane * 16 : nullptr;
+        f32x2 gv[8], uv[8];
+        load16_f32_natural(gblk, gv);
+        if (MODE == 1) load16_f32_natural(ublk, uv);
+        const uint32_t next = unit + warps;
+        if (next < live_units) name_unit_to_l2(next);
+        uint32_t stored, lo, hi;
+        bool ok = true;
+        if (MODE == 1) {
+            ok = block_abs_max(gv) <= kSiluFastMaxAbs;   // false for a NaN
+            if (ok) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) gv[i] = f2_mul(silu_ieee_refined_f32_x2(gv[i]), uv[i]);
+            }
+        }
+        if (ok) ok = quantise16_qp<false, true>(gv, global_scale, s_inv, stored, lo, hi);
+        if (ok) {
+            *pdst = make_uint2(lo, hi);
+            *sdst = (uint8_t)stored;
+        } else {
+            unit_block_cold_f32<MODE>(gblk, ublk, global_scale, pdst, sdst);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // RMSNorm with bf16 output (kernels/elementwise.cu:4-68), cols = NB * 512: the quantising kernel's
 // row structure and summation tree, the normalised row rounded to bf16 instead of quantised, so the
 // result is the reference's f32 result rounded to nearest even.

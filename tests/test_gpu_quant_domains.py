@@ -77,6 +77,11 @@ def test_plain_quantiser_on_adversarial_blocks(global_scale):
     want_p, want_s = orc.quantise_nvfp4(x, rows, cols, global_scale)
     assert_bytes_equal(got_s, want_s, "scales vs CPU oracle")
     assert_bytes_equal(got_p, want_p, "packed vs CPU oracle")
+    # f32 activations (the engine's own dtype) through the tuned f32 kernel
+    xf = dev_f32_from_bits(x)
+    f_p, f_s = run_quant("clef_quantise_nvfp4", rows, cols, [ptr(xf)], [rows, cols, global_scale, 128, 512, 1])
+    assert_bytes_equal(f_s, ref_s.cpu().numpy(), f"f32 activations: scales vs reference kernel (global scale {global_scale})")
+    assert_bytes_equal(f_p, ref_p.cpu().numpy(), f"f32 activations: packed vs reference kernel (global scale {global_scale})")
 
 
 def _with_zero_rows(bits, rng, every=7):
@@ -146,6 +151,40 @@ def test_swiglu_quantise_outside_the_fast_domain(global_scale):
     torch.cuda.synchronize()
     assert_bytes_equal(got_s, ref_s.cpu().numpy(), "scales vs reference fused kernel")
     assert_bytes_equal(got_p, ref_p.cpu().numpy(), "packed vs reference fused kernel")
+    gf, uf = dev_f32_from_bits(gate), dev_f32_from_bits(up)
+    f_p, f_s = run_quant("clef_swiglu_quantise_nvfp4", rows, cols, [ptr(gf), ptr(uf)], [rows, cols, global_scale, 128, 512, 1])
+    assert_bytes_equal(f_s, ref_s.cpu().numpy(), "f32 activations: scales vs reference fused kernel")
+    assert_bytes_equal(f_p, ref_p.cpu().numpy(), "f32 activations: packed vs reference fused kernel")
+
+
+def test_unit_quantisers_f32_on_arbitrary_f32_values():
+    """f32 gate / up values that are not bf16 values (GEMM accumulators): the tuned f32 SwiGLU + NVFP4 and plain NVFP4
+    kernels against the reference's own kernels, bit for bit. Gates beyond +-44, infinities and NaN take the literal
+    path; 8,192 x 6144 covers the grid-stride tail and a padded last row tile."""
+    for rows, cols in ((8192, 6144), (333, 1024)):
+        gen = torch.Generator(device="cuda").manual_seed(rows + 1)
+        gate = torch.randn(rows, cols, device="cuda", generator=gen) * 4.0
+        up = torch.randn(rows, cols, device="cuda", generator=gen) * 2.0
+        gate[:, 7] *= 20.0                      # |g| beyond the short form's range in every row
+        gate[3, 40:56] = 0.0
+        gate[4, 64] = float("inf")
+        gate[5, 80] = float("-inf")
+        gate[6, 96] = float("nan")
+        up[7, 100] = float("inf")
+        up[8, 120] = float("nan")
+        up[9] = 0.0
+        gate[10] = -0.0
+        for gs in (48.0, 1e-3, 1e6):
+            got_p, got_s = run_quant("clef_swiglu_quantise_nvfp4", rows, cols, [ptr(gate), ptr(up)], [rows, cols, gs, 128, 512, 1])
+            ref_p, ref_s = ref_gpu.swiglu_quantise_nvfp4(gate, up, rows, cols, gs)
+            torch.cuda.synchronize()
+            assert_bytes_equal(got_s, ref_s.cpu().numpy(), f"SwiGLU scales vs reference fused kernel (global scale {gs})")
+            assert_bytes_equal(got_p, ref_p.cpu().numpy(), f"SwiGLU packed vs reference fused kernel (global scale {gs})")
+            got_p, got_s = run_quant("clef_quantise_nvfp4", rows, cols, [ptr(gate)], [rows, cols, gs, 128, 512, 1])
+            ref_p, ref_s = ref_gpu.quantise_nvfp4(gate, rows, cols, gs)
+            torch.cuda.synchronize()
+            assert_bytes_equal(got_s, ref_s.cpu().numpy(), f"plain scales vs reference kernel (global scale {gs})")
+            assert_bytes_equal(got_p, ref_p.cpu().numpy(), f"plain packed vs reference kernel (global scale {gs})")
 
 
 @pytest.mark.parametrize("global_scale", [2e-3, 0.05, 3e4, 4e9, 1e11, 1e-25])
