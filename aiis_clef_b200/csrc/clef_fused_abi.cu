@@ -208,6 +208,22 @@ int clef_rms_norm(clef_stream_t stream, const void* x, const float* weight, void
         }
         return check_launch("clef_rms_norm");
     }
+    if (dtype == CLEF_F32 && use_hot() && (cols == 2048 || cols == 4096) && aligned(x, 32) && aligned(out, 32)) {
+        const size_t groups = ((size_t)rows + 7) / 8;
+        const size_t smem = (size_t)cols * sizeof(float);
+        if (cols == 2048) {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rms_norm_f32_hot_kernel<4>, smem, occ);
+            launch_hot(rms_norm_f32_hot_kernel<4>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, as_stream(stream),
+                       (const float*)x, weight, (float*)out, rows, eps);
+        } else {
+            static std::atomic<int> occ{0};
+            const int per_sm = ctas_per_sm(rms_norm_f32_hot_kernel<8>, smem, occ);
+            launch_hot(rms_norm_f32_hot_kernel<8>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, as_stream(stream),
+                       (const float*)x, weight, (float*)out, rows, eps);
+        }
+        return check_launch("clef_rms_norm");
+    }
     if (dtype == CLEF_BF16) {
         launch_rms_norm_generic<Bf16, false>(as_stream(stream), dev, x, weight, out, nullptr, nullptr, rows, rows, cols,
                                              eps, 0.0f, 1, 4);
@@ -413,6 +429,15 @@ int clef_rms_norm_gated(clef_stream_t stream, const void* x, const void* gate, c
         const size_t groups = ((size_t)rows + 63) / 64;
         launch_hot(gated_norm_hot_kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, as_stream(stream),
                    (const uint16_t*)x, (const uint16_t*)gate, weight, (uint16_t*)out, rows, eps);
+        return check_launch(what);
+    }
+    if (dtype == CLEF_F32 && use_hot() && cols == 128 && gate && weight && aligned(x, 32) && aligned(gate, 32) &&
+        aligned(out, 32)) {
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(gated_norm_f32_hot_kernel, 0, occ);
+        const size_t groups = ((size_t)rows + 63) / 64;
+        launch_hot(gated_norm_f32_hot_kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, as_stream(stream),
+                   (const float*)x, (const float*)gate, weight, (float*)out, rows, eps);
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {

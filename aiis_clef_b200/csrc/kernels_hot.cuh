@@ -1231,6 +1231,91 @@ rms_norm_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
     }
 }
 
+// The same for f32 activations (the reference's own arithmetic type, so the result is the reference's bit for bit):
+// the f32 quantising kernel's row structure (natural pair order, loads at the top of a row, the next row named to
+// L2), the normalised row stored as f32.
+template <int NB>
+__global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? 2 : 1))
+rms_norm_f32_hot_kernel(const float* __restrict__ x, const float* __restrict__ weight, float* __restrict__ out, int rows,
+                        float eps) {
+    constexpr int COLS = NB * 512;
+    extern __shared__ float4 s_w[];   // (1 + w) of quad q of chunk L + 32 j at s_w[(4 j + q) * 32 + L], natural order
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    if (weight) {
+        for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
+            const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
+            const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
+            s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.y, 1.0f + w.z, 1.0f + w.w);
+        }
+    }
+    int row = blockIdx.x * 8 + warp;
+    auto name_row_to_l2 = [&](int r) {   // a row is NB * 16 lines of 128 bytes: NB / 2 per lane
+#pragma unroll
+        for (int h = 0; h < NB / 2; ++h) {
+            prefetch_l2(x + (size_t)r * COLS + (size_t)(lane + 32 * h) * 32);
+        }
+    };
+    if (row < rows) name_row_to_l2(row);   // under the previous kernel's tail; see prefetch_l2
+    pdl_wait_prior_grids();
+    __syncthreads();
+    for (; row < rows; row += gridDim.x * 8) {
+        const float* xrow = x + (size_t)row * COLS;
+        U8x32 d[NB][2];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            d[j][0] = ldg_stream_v8(xrow + (size_t)(lane + 32 * j) * 16);
+            d[j][1] = ldg_stream_v8(xrow + (size_t)(lane + 32 * j) * 16 + 8);
+        }
+        const int next = row + gridDim.x * 8;
+        if (next < rows) name_row_to_l2(next);
+        float p[2][4];
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) p[a][k] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U8x32& half = d[j][q >> 1];
+                const int o = (q & 1) * 4;
+                const float vx = __uint_as_float(half.w[o]), vy = __uint_as_float(half.w[o + 1]);
+                const float vz = __uint_as_float(half.w[o + 2]), vw = __uint_as_float(half.w[o + 3]);
+                const float quad = __fadd_rn(__fmaf_rn(vx, vx, __fmul_rn(vy, vy)), __fmaf_rn(vz, vz, __fmul_rn(vw, vw)));
+                p[j & 1][q] = __fadd_rn(p[j & 1][q], quad);
+            }
+        }
+        const f32x2 inv2 = f2_splat(inv_rms_pow2<COLS>(row_tree_256(p, lane), eps));
+        float* orow = out + (size_t)row * COLS;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                U8x32 o;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int q = 2 * half + e;
+                    f32x2 a = f2_mul(f2_pack(__uint_as_float(d[j][half].w[4 * e]), __uint_as_float(d[j][half].w[4 * e + 1])), inv2);
+                    f32x2 b = f2_mul(f2_pack(__uint_as_float(d[j][half].w[4 * e + 2]), __uint_as_float(d[j][half].w[4 * e + 3])), inv2);
+                    if (weight) {   // without a weight the reference computes x * inv only
+                        const float4 w = s_w[(4 * j + q) * 32 + lane];
+                        a = f2_mul(a, make_float2(w.x, w.y));
+                        b = f2_mul(b, make_float2(w.z, w.w));
+                    }
+                    o.w[4 * e] = __float_as_uint(a.x);
+                    o.w[4 * e + 1] = __float_as_uint(a.y);
+                    o.w[4 * e + 2] = __float_as_uint(b.x);
+                    o.w[4 * e + 3] = __float_as_uint(b.y);
+                }
+                stg_v8(orow + (size_t)(lane + 32 * j) * 16 + 8 * half, o);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // SwiGLU with bf16 output (kernels/elementwise.cu:225-241) over a flat array, 16 values per lane.
 // Blocks with max|g| <= 44 use the short exact quotient (see the quantising kernel); others the
@@ -1348,6 +1433,111 @@ gated_norm_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict
                 }
             }
             stg_v8(out + (size_t)hrow * COLS + (m + 4 * h) * 16, pack16_bf16(v[h]));
+        }
+    }
+}
+
+// The same for f32 activations: the f32 quantising kernel's step structure, the result stored as f32. Gates of
+// |g| <= 44 take the short form of __fdividef(g, 1 + __expf(-g)), equal to it for every f32 of that range.
+static __global__ void __launch_bounds__(kCtaThreads, 2)
+gated_norm_f32_hot_kernel(const float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ weight,
+                          float* __restrict__ out, int rows, float eps) {
+    constexpr int COLS = 128;
+    __shared__ float4 s_w[32];   // plain weight, natural order: s_w[(h * 4 + q) * 4 + m] = quad q of chunk m + 4h
+    const int lane = threadIdx.x & 31;
+    const int m = lane & 3;
+    const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
+    uint32_t hrow = blockIdx.x * (kCtaThreads / 4) + (threadIdx.x >> 2);
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
+        s_w[threadIdx.x] = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
+    }
+    // a CTA step covers 64 head rows of 512 bytes: 256 lines of x and 256 of the gate, two of each per thread
+    auto name_step_to_l2 = [&](uint32_t first) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t line = threadIdx.x + 256 * h;   // 4 lines per head row
+            if (first + (line >> 2) < (uint32_t)rows) {
+                prefetch_l2(x + (size_t)first * COLS + (size_t)line * 32);
+                prefetch_l2(gate + (size_t)first * COLS + (size_t)line * 32);
+            }
+        }
+    };
+    name_step_to_l2(blockIdx.x * (kCtaThreads / 4));   // under the previous kernel's tail; see prefetch_l2
+    pdl_wait_prior_grids();
+    __syncthreads();
+    // Every lane of a warp runs the same number of steps (the shuffles need the full warp).
+    uint32_t cta_first = blockIdx.x * (kCtaThreads / 4);
+    for (uint32_t base = hrow - (uint32_t)(lane >> 2); base < (uint32_t)rows;
+         base += groups_in_grid, hrow += groups_in_grid, cta_first += groups_in_grid) {
+        const bool live = hrow < (uint32_t)rows;
+        U8x32 dx[2][2], dg[2][2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dx[h][half].w[i] = dg[h][half].w[i] = 0u;
+            }
+        }
+        if (live) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const size_t off = (size_t)hrow * COLS + (m + 4 * h) * 16;
+                dx[h][0] = ldg_stream_v8(x + off);
+                dx[h][1] = ldg_stream_v8(x + off + 8);
+                dg[h][0] = ldg_stream_v8(gate + off);
+                dg[h][1] = ldg_stream_v8(gate + off + 8);
+            }
+        }
+        if (cta_first + groups_in_grid < (uint32_t)rows) name_step_to_l2(cta_first + groups_in_grid);
+        f32x2 v[2][8], gv[2][8];
+        float quad[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U8x32& hx = dx[h][q >> 1];
+                const U8x32& hg = dg[h][q >> 1];
+                const int o = (q & 1) * 4;
+                const float vx = __uint_as_float(hx.w[o]), vy = __uint_as_float(hx.w[o + 1]);
+                const float vz = __uint_as_float(hx.w[o + 2]), vw = __uint_as_float(hx.w[o + 3]);
+                v[h][2 * q] = f2_pack(vx, vy);
+                v[h][2 * q + 1] = f2_pack(vz, vw);
+                gv[h][2 * q] = f2_pack(__uint_as_float(hg.w[o]), __uint_as_float(hg.w[o + 1]));
+                gv[h][2 * q + 1] = f2_pack(__uint_as_float(hg.w[o + 2]), __uint_as_float(hg.w[o + 3]));
+                quad[h][q] = __fadd_rn(__fmaf_rn(vx, vx, __fmul_rn(vy, vy)), __fmaf_rn(vz, vz, __fmul_rn(vw, vw)));
+            }
+        }
+        const float total = head_tree_32(quad[0], quad[1], lane);
+        if (!live) {
+            continue;
+        }
+        const f32x2 inv2 = f2_splat(inv_rms_pow2<COLS>(total, eps));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const bool fast = block_abs_max(gv[h]) <= kSiluFastMaxAbs;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                U8x32 o;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float4 w = s_w[(h * 4 + 2 * half + e) * 4 + m];
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        const int i = 4 * half + 2 * e + t;
+                        const f32x2 wp = t == 0 ? make_float2(w.x, w.y) : make_float2(w.z, w.w);
+                        const f32x2 sl = fast ? silu_approx_fast_x2(gv[h][i])
+                                              : make_float2(silu_fast_div(gv[h][i].x), silu_fast_div(gv[h][i].y));
+                        // ((x * inv) * w) * silu(g), left to right as the reference writes it
+                        const f32x2 r = f2_mul(f2_mul(f2_mul(v[h][i], inv2), wp), sl);
+                        o.w[4 * e + 2 * t] = __float_as_uint(r.x);
+                        o.w[4 * e + 2 * t + 1] = __float_as_uint(r.y);
+                    }
+                }
+                stg_v8(out + (size_t)hrow * COLS + (m + 4 * h) * 16 + 8 * half, o);
+            }
         }
     }
 }

@@ -135,6 +135,45 @@ def test_rms_norm_gated(rows, cols, choice):
         assert_bytes_equal(o.as_f32().view(np.uint32), r.cpu().numpy().view(np.uint32), "f32 gated norm, optional operand absent")
 
 
+def test_norms_f32_on_arbitrary_f32_rows():
+    """f32 rows that are not bf16 values (the engine's residual stream and accumulators) through the tuned f32 kernels,
+    bit for bit against the reference kernels: 8,192 rows cover the grid-stride tails; gates beyond +-44, infinities
+    and NaN take the literal silu."""
+    clef.set_kernel_choice(0)
+    for rows, cols in ((8192, 2048), (1111, 4096)):
+        gen = torch.Generator(device="cuda").manual_seed(cols)
+        x = torch.randn(rows, cols, device="cuda", generator=gen) * 3.0
+        x[:, 9] *= 50.0
+        x[21] = 0.0
+        x[22, 5] = float("inf")
+        x[23, 6] = float("nan")
+        w = torch.randn(cols, device="cuda", generator=gen) * 0.1
+        for wt in (w, None):
+            out = out_buffer(rows * cols, F32)
+            assert call("clef_rms_norm", stream(), ptr(x), ptr(wt), out.ptr, rows, cols, 1e-6, F32) == 0
+            ref = ref_gpu.rms_norm(x, wt, rows, cols, 1e-6)
+            torch.cuda.synchronize()
+            out.check_guards("rms_norm f32")
+            assert_bytes_equal(out.as_f32().view(np.uint32), ref.cpu().numpy().view(np.uint32), "f32 rms_norm vs reference kernel")
+    rows, cols = 8192 * 16 + 37, 128
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(rows, cols, device="cuda", generator=gen) * 2.0
+    g = torch.randn(rows, cols, device="cuda", generator=gen) * 5.0
+    g[:, 3] *= 15.0
+    g[40, 8] = float("inf")
+    g[41, 9] = float("-inf")
+    g[42, 10] = float("nan")
+    x[43] = 0.0
+    g[44] = -0.0
+    w = 1.0 + torch.randn(cols, device="cuda", generator=gen) * 0.1
+    out = out_buffer(rows * cols, F32)
+    assert call("clef_rms_norm_gated", stream(), ptr(x), ptr(g), ptr(w), out.ptr, rows, cols, 1e-6, F32) == 0
+    ref = ref_gpu.rms_norm_gated(x, g, w, rows, cols, 1e-6)
+    torch.cuda.synchronize()
+    out.check_guards("rms_norm_gated f32")
+    assert_bytes_equal(out.as_f32().view(np.uint32), ref.cpu().numpy().view(np.uint32), "f32 gated norm vs reference kernel")
+
+
 # ---- swiglu --------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("total", [5 * 128, 5 * 128 - 1, 778 * 6144, 1, 3, 4099, 16, 17])
