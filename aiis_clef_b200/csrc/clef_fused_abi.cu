@@ -17,6 +17,7 @@
 #include "internal.hpp"
 #include "kernels_generic.cuh"
 #include "kernels_hot.cuh"
+#include "unit_quant_f32_launch.cuh"
 
 namespace {
 thread_local char g_error[512] = "";
@@ -146,22 +147,6 @@ int clef_embed_gather(clef_stream_t stream, const void* table, const int32_t* id
 
 }  // extern "C"
 
-// The unit-structured f32 quantisers (MODE 0 plain, 1 SwiGLU first); one unit per warp per step.
-template <int MODE>
-static void launch_unit_quant_f32(cudaStream_t s, const DeviceInfo& dev, const float* gate, const float* up, uint8_t* packed,
-                                  uint8_t* scales, int rows, int rows_total, int cols, float global_scale, int blk_mn,
-                                  int chunk) {
-    constexpr int kMinCtas = MODE == 1 ? 3 : 4;
-    static std::atomic<int> occ{0};
-    const int per_sm = ctas_per_sm(unit_quant_f32_hot_kernel<MODE, kMinCtas>, 0, occ);
-    const uint32_t segs = (uint32_t)(cols / 512);
-    const uint32_t live_units = (uint32_t)rows * segs, total_units = (uint32_t)rows_total * segs;
-    const size_t ctas = ((size_t)total_units + 7) / 8;
-    launch_hot(unit_quant_f32_hot_kernel<MODE, kMinCtas>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s, gate, up, packed,
-               scales, live_units, total_units, cols, global_scale, blk_mn, chunk, make_fast_div(segs),
-               make_fast_div((uint32_t)blk_mn));
-}
-
 template <typename T, bool QUANT>
 static int launch_rms_norm_generic(cudaStream_t stream, const DeviceInfo& dev, const void* x, const float* weight,
                                    void* out, uint8_t* packed, uint8_t* scales, int rows, int rows_total, int cols,
@@ -275,19 +260,26 @@ static int rms_norm_quantise_impl(const char* what, clef_stream_t stream, const 
 #undef CLEF_RMSQ_HOT
         return check_launch(what);
     }
-    if (dtype == CLEF_F32 && !addend && use_hot() && hot_scale_ok(global_scale) && (cols == 2048 || cols == 4096) && aligned(x, 32)) {
+    if (dtype == CLEF_F32 && use_hot() && hot_scale_ok(global_scale) && (cols == 2048 || cols == 4096) && aligned(x, 32) &&
+        (!addend || (aligned(addend, 32) && aligned(sum_out, 32)))) {
         // f32 activations (the reference engine's residual stream): the tuned kernel's f32 form
         const size_t groups = ((size_t)rows_total + 7) / 8;
         const size_t smem = (size_t)cols * sizeof(float);
         const FastDiv atom_div = make_fast_div((uint32_t)blk_mn);
         auto launch = [&](auto kernel, std::atomic<int>& occ) {
             const int per_sm = ctas_per_sm(kernel, smem, occ);
-            launch_hot(kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s, (const float*)x, weight, packed, scales, rows,
-                       rows_total, eps, global_scale, blk_mn, chunk, atom_div);
+            launch_hot(kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s, (const float*)x, (const float*)addend,
+                       (float*)sum_out, weight, packed, scales, rows, rows_total, eps, global_scale, blk_mn, chunk, atom_div,
+                       (const int*)nullptr);
         };
-        static std::atomic<int> occ[2];
-        if (cols == 2048) launch(rms_norm_quant_f32_hot_kernel<4>, occ[0]);
-        else launch(rms_norm_quant_f32_hot_kernel<8>, occ[1]);
+        static std::atomic<int> occ[4];
+        if (cols == 2048) {
+            if (addend) launch(rms_norm_quant_f32_hot_kernel<4, true>, occ[0]);
+            else launch(rms_norm_quant_f32_hot_kernel<4>, occ[1]);
+        } else {
+            if (addend) launch(rms_norm_quant_f32_hot_kernel<8, true>, occ[2]);
+            else launch(rms_norm_quant_f32_hot_kernel<8>, occ[3]);
+        }
         return check_launch(what);
     }
     if (addend) {   // shape-general path: the add, then the norm + quantiser on the stored sum
@@ -336,8 +328,8 @@ int clef_add_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, void* sum_out, con
                                   rows, cols, eps, global_scale, blk_mn, chunk, dtype, sf_layout);
 }
 
-// Embedding gather + RMSNorm + NVFP4 in one pass over the gathered row (bf16, hidden 2048 or 4096); other shapes
-// and f32 run the two entry points it stands for.
+// Embedding gather + RMSNorm + NVFP4 in one pass over the gathered row (hidden 2048 or 4096); other shapes run the
+// two entry points it stands for.
 static int embed_rms_norm_quantise_impl(const char* what, clef_stream_t stream, const void* table, const int32_t* ids,
                                         void* h_out, const float* weight, uint8_t* packed, uint8_t* scales, int tokens,
                                         int hidden, float eps, float global_scale, int blk_mn, int chunk, int dtype,
@@ -366,6 +358,22 @@ static int embed_rms_norm_quantise_impl(const char* what, clef_stream_t stream, 
         static std::atomic<int> occ[2];
         if (hidden == 2048) launch(rms_norm_quant_hot_kernel<4, false, true>, occ[0]);
         else launch(rms_norm_quant_hot_kernel<8, false, true>, occ[1]);
+        return check_launch(what);
+    }
+    if (dtype == CLEF_F32 && use_hot() && hot_scale_ok(global_scale) && (hidden == 2048 || hidden == 4096) && aligned(table, 32) &&
+        aligned(h_out, 32) && aligned(weight, 16) && aligned(packed, 8)) {
+        const size_t groups = ((size_t)rows_total + 7) / 8;
+        const size_t smem = (size_t)hidden * sizeof(float);
+        const FastDiv atom_div = make_fast_div((uint32_t)blk_mn);
+        auto launch = [&](auto kernel, std::atomic<int>& occ) {
+            const int per_sm = ctas_per_sm(kernel, smem, occ);
+            launch_hot(kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, as_stream(stream), (const float*)table,
+                       (const float*)nullptr, (float*)h_out, weight, packed, scales, tokens, rows_total, eps, global_scale, blk_mn,
+                       folded, atom_div, (const int*)ids);
+        };
+        static std::atomic<int> occ[2];
+        if (hidden == 2048) launch(rms_norm_quant_f32_hot_kernel<4, false, true>, occ[0]);
+        else launch(rms_norm_quant_f32_hot_kernel<8, false, true>, occ[1]);
         return check_launch(what);
     }
     if (int r = clef_embed_gather(stream, table, ids, h_out, tokens, hidden, dtype)) return r;

@@ -10,6 +10,7 @@
 
 #include "abi_support.cuh"
 #include "kernels_hot.cuh"
+#include "unit_quant_f32_launch.cuh"
 #include "kernels_layer.cuh"
 
 using namespace clef;
@@ -344,6 +345,12 @@ static int clef_sigmoid_mul_quantise_nvfp4_impl(clef_stream_t stream, const void
         launch_hot(swiglu_quant_hot_kernel<kUnits, kMinCtas, kActSigmoidMul>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0,
                    s, (const uint16_t*)gate, (const uint16_t*)x, packed, scales, live_units, total_units, cols,
                    global_scale, blk_mn, chunk, make_fast_div(segs), make_fast_div((uint32_t)blk_mn));
+        return check_launch(what);
+    }
+    if (dtype == CLEF_F32 && use_hot() && hot_scale_ok(global_scale) && cols % 512 == 0 && total_blocks / 32 < 0x7fffffffull && aligned(x, 32) &&
+        aligned(gate, 32)) {
+        launch_unit_quant_f32<2>(s, dev, (const float*)gate, (const float*)x, packed, scales, rows, rows_total, cols, global_scale,
+                                 blk_mn, chunk);
         return check_launch(what);
     }
     if (dtype == CLEF_BF16) {

@@ -379,11 +379,15 @@ static __device__ __noinline__ void rms_block_cold_f32(const float* xblk, const 
     quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
 }
 
-template <int NB>
+// ADD and EMBED as in the bf16 kernel: the row is x + addend (f32 sum, also stored to sum_out, which may be x), or
+// row ids[row] of the table x (also copied to sum_out).
+template <int NB, bool ADD = false, bool EMBED = false>
 __global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? 2 : 1))
-rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restrict__ weight, uint8_t* __restrict__ packed,
+rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restrict__ addend, float* sum_out,
+                              const float* __restrict__ weight, uint8_t* __restrict__ packed,
                               uint8_t* __restrict__ scales, int rows, int rows_total, float eps, float global_scale,
-                              int blk_mn, int chunk, FastDiv atom_div) {
+                              int blk_mn, int chunk, FastDiv atom_div, const int* __restrict__ ids) {
+    static_assert(!(ADD && EMBED), "one fused producer at a time");
     constexpr int COLS = NB * 512;
     constexpr int BLOCKS = COLS / 16;
     __shared__ float s_inv[kInvScaleTableSize];
@@ -402,14 +406,20 @@ rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restri
     }
     int row = blockIdx.x * 8 + warp;
     // a row is COLS * 4 bytes = NB * 16 lines of 128 bytes: NB / 2 per lane
-    auto name_row_to_l2 = [&](int r) {
+    auto name_row_to_l2 = [&](const float* src) {
 #pragma unroll
         for (int h = 0; h < NB / 2; ++h) {
-            prefetch_l2(x + (size_t)r * COLS + (size_t)(lane + 32 * h) * 32);
+            prefetch_l2(src + (size_t)(lane + 32 * h) * 32);
         }
     };
-    if (row < rows) name_row_to_l2(row);   // under the previous kernel's tail; see prefetch_l2
+    if (!EMBED && row < rows) {   // under the previous kernel's tail; see prefetch_l2
+        name_row_to_l2(x + (size_t)row * COLS);
+        if (ADD) name_row_to_l2(addend + (size_t)row * COLS);
+    }
     pdl_wait_prior_grids();
+    // (the token ids are an activation of the pass: they are read after the wait)
+    auto source_row = [&](int r) { return x + (size_t)(EMBED ? __ldg(ids + r) : r) * COLS; };
+    if (EMBED && row < rows) name_row_to_l2(source_row(row));
     __syncthreads();
 
     for (; row < rows_total; row += gridDim.x * 8) {
@@ -426,7 +436,7 @@ rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restri
             }
             continue;
         }
-        const float* xrow = x + (size_t)row * COLS;
+        const float* xrow = source_row(row);
         U8x32 d[NB][2];
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
@@ -434,7 +444,39 @@ rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restri
             d[j][1] = ldg_stream_v8(xrow + (size_t)(lane + 32 * j) * 16 + 8);
         }
         const int next = row + gridDim.x * 8;
-        if (next < rows) name_row_to_l2(next);
+        if (next < rows) {
+            name_row_to_l2(source_row(next));
+            if (ADD) name_row_to_l2(addend + (size_t)next * COLS);
+        }
+        if (ADD) {   // the addend arrives block by block, one block ahead of the sum
+            const float* arow = addend + (size_t)row * COLS;
+            float* srow_out = sum_out + (size_t)row * COLS;
+            U8x32 e[2][2];
+            e[0][0] = ldg_stream_v8(arow + (size_t)lane * 16);
+            e[0][1] = ldg_stream_v8(arow + (size_t)lane * 16 + 8);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                if (j + 1 < NB) {
+                    e[(j + 1) & 1][0] = ldg_stream_v8(arow + (size_t)(lane + 32 * (j + 1)) * 16);
+                    e[(j + 1) & 1][1] = ldg_stream_v8(arow + (size_t)(lane + 32 * (j + 1)) * 16 + 8);
+                }
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        d[j][half].w[i] = __float_as_uint(__fadd_rn(__uint_as_float(d[j][half].w[i]), __uint_as_float(e[j & 1][half].w[i])));
+                    }
+                    stg_v8(srow_out + (size_t)(lane + 32 * j) * 16 + 8 * half, d[j][half]);
+                }
+            }
+        }
+        if (EMBED) {   // the gathered row, for the residual stream
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                stg_v8(sum_out + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16, d[j][0]);
+                stg_v8(sum_out + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16 + 8, d[j][1]);
+            }
+        }
         f32x2 v[NB][8];
         float p[2][4];
 #pragma unroll
@@ -480,8 +522,9 @@ rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restri
             for (int j = 0; j < NB; ++j) {
                 if (bad & (1u << j)) {
                     const int b = lane + 32 * j;
-                    rms_block_cold_f32(xrow + b * 16, weight + b * 16, inv, global_scale, reinterpret_cast<uint2*>(prow + b * 8),
-                                       srow + (size_t)(b >> 2) * chunk + (b & 3));
+                    // ADD: this lane stored the block's sum above, so it reads its own values back.
+                    rms_block_cold_f32((ADD ? (const float*)sum_out + (size_t)row * COLS : xrow) + b * 16, weight + b * 16, inv, global_scale,
+                                       reinterpret_cast<uint2*>(prow + b * 8), srow + (size_t)(b >> 2) * chunk + (b & 3));
                 }
             }
         }
@@ -1063,6 +1106,8 @@ quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed
 // 32 registers per input).
 // MODE 0: plain quantiser (kernels/quantise.cu:6-53). MODE 1: SwiGLU first (kernels/quantise.cu:523-591),
 // silu through silu_ieee_refined_f32_x2, which equals the IEEE quotient for every f32 gate of |g| <= 44.
+// MODE 2: x * sigmoid(gate) first (kernels/elementwise.cu:344-353), `gate` the gate and `up` the x rows; the
+// quotient has two free f32 operands, so it is the literal IEEE division (the kernel stays memory-bound with it).
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void load16_f32_natural(const float* p, f32x2* v) {
     const U8x32 a = ldg_stream_v8(p), b = ldg_stream_v8(p + 8);
@@ -1079,7 +1124,8 @@ static __device__ __noinline__ void unit_block_cold_f32(const float* gblk, const
     float a[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        a[i] = MODE == 1 ? gated_literal<kActSwiGLU>(gblk[i], xblk[i]) : gblk[i];
+        a[i] = MODE == 1 ? gated_literal<kActSwiGLU>(gblk[i], xblk[i])
+                         : (MODE == 2 ? gated_literal<kActSigmoidMul>(gblk[i], xblk[i]) : gblk[i]);
     }
     quantise16_cold_store(a, global_scale, packed_dst, scale_dst);
 }
@@ -1098,7 +1144,7 @@ unit_quant_f32_hot_kernel(const float* __restrict__ gate, const float* __restric
     const int k1_count = cols >> 6;
     // a unit is 2 KiB per input = 16 lines of 128 bytes: lanes 0-15 name the gate's, lanes 16-31 the up's
     auto name_unit_to_l2 = [&](uint32_t u) {
-        if (MODE == 1) {
+        if (MODE != 0) {
             prefetch_l2((lane < 16 ? gate : up) + (size_t)u * 512 + (size_t)(lane & 15) * 32);
         } else if (lane < 16) {
             prefetch_l2(gate + (size_t)u * 512 + (size_t)lane * 32);
@@ -1123,10 +1169,10 @@ unit_quant_f32_hot_kernel(const float* __restrict__ gate, const float* __restric
             continue;
         }
         const float* gblk = gate + (size_t)unit * 512 + lane * 16;
-        const float* ublk = MODE == 1 ? up + (size_t)unit * 512 + lane * 16 : nullptr;
+        const float* ublk = MODE != 0 ? up + (size_t)unit * 512 + lane * 16 : nullptr;
         f32x2 gv[8], uv[8];
         load16_f32_natural(gblk, gv);
-        if (MODE == 1) load16_f32_natural(ublk, uv);
+        if (MODE != 0) load16_f32_natural(ublk, uv);
         const uint32_t next = unit + warps;
         if (next < live_units) name_unit_to_l2(next);
         uint32_t stored, lo, hi;
@@ -1136,6 +1182,12 @@ unit_quant_f32_hot_kernel(const float* __restrict__ gate, const float* __restric
             if (ok) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) gv[i] = f2_mul(silu_ieee_refined_f32_x2(gv[i]), uv[i]);
+            }
+        }
+        if (MODE == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                gv[i] = make_float2(gated_literal<kActSigmoidMul>(gv[i].x, uv[i].x), gated_literal<kActSigmoidMul>(gv[i].y, uv[i].y));
             }
         }
         if (ok) ok = quantise16_qp<false, true>(gv, global_scale, s_inv, stored, lo, hi);

@@ -360,6 +360,16 @@ def test_add_rms_norm_quantise_equals_the_chain(rows, cols, dtype, choice):
         torch.cuda.synchronize()
         assert_bytes_equal(orc.bf16_bits(da.cpu()).reshape(-1), cpu_sum.reshape(-1), "in-place residual")
         assert_bytes_equal(packed2.bytes(), want_p, "packed codes, in-place residual")
+    if dtype == F32:
+        # in place: sum_out aliases a
+        packed2, scales2 = Guarded(rp * cols // 2), Guarded(rp * cols // 16)
+        a2 = af.clone()
+        assert call("clef_add_rms_norm_quantise_nvfp4", stream(), ptr(a2), ptr(a2), ptr(bf), ptr(dw), packed2.ptr, scales2.ptr,
+                    rows, cols, 1e-6, gs, 128, 512, F32) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(a2.reshape(-1).view(torch.int32), total.reshape(-1).view(torch.int32)), "in-place f32 residual"
+        assert_bytes_equal(packed2.bytes(), ref_p.cpu().numpy(), "packed codes, in-place f32 residual")
+        assert_bytes_equal(scales2.bytes(), ref_s.cpu().numpy(), "scales, in-place f32 residual")
 
 
 # ---- q and k (and the KV-cache write) in one launch ---------------------------------------------------------------
