@@ -723,6 +723,21 @@ int clef_rope(clef_stream_t stream, void* out, const void* x, const float* cos_t
                    (const int*)pos_map, make_fast_div((uint32_t)(head_dim / 32)), make_fast_div((uint32_t)heads), KvCacheDest{});
         return check_launch(what);
     }
+    const size_t f32_items = (size_t)rows * heads * (head_dim / 16);
+    if (dtype == CLEF_F32 && use_hot() && head_dim % 16 == 0 && rotary_dim % 16 == 0 && f32_items < 0x7fffffffull &&
+        aligned(x, 32) && aligned(out, 32)) {
+        RopeSegmentsF32 segs{};
+        segs.x[0] = (const float*)x;
+        segs.out[0] = (float*)out;
+        segs.end_item[0] = (uint32_t)f32_items;
+        segs.heads_div[0] = make_fast_div((uint32_t)heads);
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(rope_f32_hot_kernel<1>, 0, occ);
+        launch_hot(rope_f32_hot_kernel<1>, clamp_grid((f32_items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0, s,
+                   segs, cos_table, sin_table, head_dim, rotary_dim, (const int*)seq_start, (const int*)pos_base,
+                   (const int*)pos_map, make_fast_div((uint32_t)(head_dim / 16)));
+        return check_launch(what);
+    }
     const size_t items = (size_t)rows * heads * ((rotary_dim / 8) + (head_dim - rotary_dim) / 4);
     if (dtype == CLEF_BF16) {
         static std::atomic<int> occ{0};
@@ -774,6 +789,26 @@ int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, 
         } else {
             if (gate_out) launch(qk_norm_rope_hd256_hot_kernel<true, false>, occ[2]);
             else launch(qk_norm_rope_hd256_hot_kernel<false, false>, occ[3]);
+        }
+        return check_launch(what);
+    }
+    if (dtype == CLEF_F32 && use_hot() && (head_dim == 128 || head_dim == 256) && rotary_dim == 64 && rows < 0x3fffffff) {
+        // f32 activations: one warp per head row, two rows in flight per warp
+        const size_t hot_groups = ((size_t)rows + 15) / 16;
+        const FastDiv heads_div = make_fast_div((uint32_t)heads);
+        auto launch = [&](auto kernel, std::atomic<int>& occ) {
+            const int per_sm = ctas_per_sm(kernel, 0, occ);
+            launch_hot(kernel, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0, as_stream(stream), (const float*)x, weight,
+                       cos_table, sin_table, (float*)out, (float*)gate_out, (uint32_t)rows, eps, (const int*)seq_start,
+                       (const int*)pos_base, (const int*)pos_map, heads_div);
+        };
+        static std::atomic<int> occ[4];
+        if (head_dim == 128) {
+            if (gate_out) launch(qk_norm_rope_f32_hot_kernel<128, true>, occ[0]);
+            else launch(qk_norm_rope_f32_hot_kernel<128, false>, occ[1]);
+        } else {
+            if (gate_out) launch(qk_norm_rope_f32_hot_kernel<256, true>, occ[2]);
+            else launch(qk_norm_rope_f32_hot_kernel<256, false>, occ[3]);
         }
         return check_launch(what);
     }

@@ -185,7 +185,26 @@ static int rope_qkv_impl(const char* what, clef_stream_t stream, void* q_out, co
         }
         return check_launch(what);
     }
-    // Other shapes and f32: the calls this entry point stands for.
+    const size_t q_items32 = (size_t)rows * q_heads * (head_dim / 16), k_items32 = (size_t)rows * kv_heads * (head_dim / 16);
+    if (dtype == CLEF_F32 && !to_cache && use_hot() && head_dim % 16 == 0 && rotary_dim % 16 == 0 &&
+        q_items32 + k_items32 < 0x7fffffffull && all32) {
+        RopeSegmentsF32 segs{};
+        segs.x[0] = (const float*)q;
+        segs.out[0] = (float*)q_out;
+        segs.end_item[0] = (uint32_t)q_items32;
+        segs.heads_div[0] = make_fast_div((uint32_t)q_heads);
+        segs.x[1] = (const float*)k;
+        segs.out[1] = (float*)k_dst;
+        segs.end_item[1] = (uint32_t)(q_items32 + k_items32);
+        segs.heads_div[1] = make_fast_div((uint32_t)kv_heads);
+        static std::atomic<int> occ{0};
+        const int per_sm = ctas_per_sm(rope_f32_hot_kernel<2>, 0, occ);
+        launch_hot(rope_f32_hot_kernel<2>, clamp_grid((q_items32 + k_items32 + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm),
+                   0, as_stream(stream), segs, cos_table, sin_table, head_dim, rotary_dim, (const int*)seq_start,
+                   (const int*)pos_base, (const int*)pos_map, make_fast_div((uint32_t)(head_dim / 16)));
+        return check_launch(what);
+    }
+    // Other shapes, and f32 with cache rows: the calls this entry point stands for.
     if (int r = clef_rope(stream, q_out, q, cos_table, sin_table, rows, q_heads, head_dim, rotary_dim, seq_start, pos_base,
                           pos_map, dtype)) return r;
     if (to_cache) {

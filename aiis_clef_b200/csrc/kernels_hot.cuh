@@ -1861,6 +1861,65 @@ rope_qk_map_hot_kernel(RopeSegments segs, const float* __restrict__ cos_t, const
     }
 }
 
+// The item structure for f32 activations (the reference's own type): a 32-byte chunk is 8 values, so a head row has
+// rotary_dim / 16 rotating items and (head_dim - rotary_dim) / 16 copy items; one or two tensors (q, or q and k)
+// per launch, plain output rows, loads hoisted above the split. head_dim % 16 == 0, rotary_dim % 16 == 0.
+struct RopeSegmentsF32 {
+    const float* x[2];
+    float* out[2];
+    uint32_t end_item[2];
+    FastDiv heads_div[2];
+};
+template <int NSEG>
+__global__ void __launch_bounds__(kCtaThreads, 6)
+rope_f32_hot_kernel(RopeSegmentsF32 segs, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int head_dim,
+                    int rotary_dim, const int* __restrict__ seq_start, const int* __restrict__ pos_base,
+                    const int* __restrict__ pos_map, FastDiv items_div) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const uint32_t q_items = segs.end_item[0], total_items = segs.end_item[NSEG - 1];
+    const uint32_t stride = gridDim.x * blockDim.x;
+    const uint32_t rot_items = (uint32_t)rotary_dim >> 4;
+    const int half = rotary_dim >> 1;
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_items; idx += stride) {
+        const bool is_q = NSEG == 1 || idx < q_items;
+        const uint32_t local = is_q ? idx : idx - q_items;
+        const uint32_t head_row = fast_div(local, items_div);
+        const uint32_t item = local - head_row * items_div.d;
+        const float* xr = (is_q ? segs.x[0] : segs.x[1]) + (size_t)head_row * head_dim;
+        float* orow = (is_q ? segs.out[0] : segs.out[1]) + (size_t)head_row * head_dim;
+        const bool rotates = item < rot_items;
+        const int c0 = rotates ? (int)item * 8 : rotary_dim + (int)(item - rot_items) * 16;
+        const int c1 = rotates ? half + (int)item * 8 : c0 + 8;
+        int pos = 0;
+        if (rotates) {
+            const int row = (int)(is_q ? fast_div(head_row, segs.heads_div[0]) : fast_div(head_row, segs.heads_div[1]));
+            pos = rope_position(row, seq_start, pos_base, pos_map);
+        }
+        U8x32 a = ldg_stream_v8(xr + c0);
+        U8x32 b = ldg_stream_v8(xr + c1);
+        if (rotates) {
+            const float* cp = cos_t + (size_t)pos * rotary_dim + item * 8;
+            const float* sp = sin_t + (size_t)pos * rotary_dim + item * 8;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {   // in place, quad by quad
+                const float4 c = __ldg(reinterpret_cast<const float4*>(cp) + q);
+                const float4 s = __ldg(reinterpret_cast<const float4*>(sp) + q);
+                const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float lo, hi;
+                    rope_pair(__uint_as_float(a.w[4 * q + e]), __uint_as_float(b.w[4 * q + e]), cv[e], sv[e], lo, hi);
+                    a.w[4 * q + e] = __float_as_uint(lo);
+                    b.w[4 * q + e] = __float_as_uint(hi);
+                }
+            }
+        }
+        stg_v8(orow + c0, a);
+        stg_v8(orow + c1, b);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Per-head RMSNorm + partial RoPE (kernels/elementwise.cu:70-142) for head_dim 128, rotary_dim 64.
 // Four lanes own one head row: lane m holds chunk m (dims 16m .. 16m+15, inside the rotary span)
@@ -2134,6 +2193,104 @@ qk_norm_rope_hd256_hot_kernel(const uint16_t* __restrict__ x, const float* __res
             }
         }
         stg_v8(orow + m * 16, pack16_bf16(v));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-head RMSNorm + partial RoPE for f32 activations (kernels/elementwise.cu:70-142), head_dim HD of 128 or 256,
+// rotary_dim 64. One warp per head row exactly as the reference's norm team (32 threads for up to 256 columns:
+// thread l adds quad l, then quad l + 32, then the 16..1 tree), two rows in flight per warp; the whole row stays in
+// registers. The rotation pairs dims j and j + 32, i.e. quad l of lanes l and l ^ 8 (l < 16): the partner's
+// normalised quad crosses by shuffle. With GATE the input row is [q | gate] and the gate half is copied.
+// ---------------------------------------------------------------------------------------------
+template <int HD, bool GATE>
+__global__ void __launch_bounds__(kCtaThreads, 4)
+qk_norm_rope_f32_hot_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, float* __restrict__ out, float* __restrict__ gate_out,
+                            uint32_t rows, float eps, const int* __restrict__ seq_start, const int* __restrict__ pos_base,
+                            const int* __restrict__ pos_map, FastDiv heads_div) {
+    constexpr int ROT = 64, NQ = HD / 128, STRIDE = GATE ? 2 * HD : HD, R = 2;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warps = gridDim.x * (kCtaThreads / 32);
+    pdl_launch_dependents();
+    float4 w1[NQ];   // (1 + w) of this lane's quads
+#pragma unroll
+    for (int k = 0; k < NQ; ++k) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(weight) + lane + 32 * k);
+        w1[k] = make_float4(1.0f + t.x, 1.0f + t.y, 1.0f + t.z, 1.0f + t.w);
+    }
+    pdl_wait_prior_grids();
+    const bool rotates = lane < 16, holds_lo = lane < 8;
+    for (uint32_t row0 = blockIdx.x * (kCtaThreads / 32) + (threadIdx.x >> 5); row0 < rows; row0 += R * warps) {
+        float4 v[R][NQ];
+        float4 c[R], sn[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint32_t row = row0 + r * warps;
+            c[r] = sn[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < NQ; ++k) v[r][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < rows) {
+#pragma unroll
+                for (int k = 0; k < NQ; ++k) {
+                    const uint4 t = ldg_stream_v4(x + (size_t)row * STRIDE + 4 * (lane + 32 * k));
+                    v[r][k] = make_float4(__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w));
+                }
+                if (rotates) {
+                    const int pos = rope_position((int)fast_div(row, heads_div), seq_start, pos_base, pos_map);
+                    c[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (size_t)pos * ROT) + (lane & 7));
+                    sn[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (size_t)pos * ROT) + (lane & 7));
+                }
+            }
+        }
+        if (GATE) {   // the gate halves ride along: loaded with the rows, stored straight away
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint32_t row = row0 + r * warps;
+                if (row < rows) {
+#pragma unroll
+                    for (int k = 0; k < NQ; ++k) {
+                        const uint4 t = ldg_stream_v4(x + (size_t)row * STRIDE + HD + 4 * (lane + 32 * k));
+                        stg_v4(gate_out + (size_t)row * HD + 4 * (lane + 32 * k), t);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint32_t row = row0 + r * warps;
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < NQ; ++k) acc = __fadd_rn(acc, quad_sq(v[r][k]));
+            const float inv = inv_rms(warp_tree_sum(acc), HD, eps);
+#pragma unroll
+            for (int k = 0; k < NQ; ++k) {
+                v[r][k] = make_float4(v[r][k].x * inv * w1[k].x, v[r][k].y * inv * w1[k].y, v[r][k].z * inv * w1[k].z,
+                                      v[r][k].w * inv * w1[k].w);
+            }
+            float4 p;   // the partner's normalised rotary quad
+            p.x = __shfl_xor_sync(kFullMask, v[r][0].x, 8);
+            p.y = __shfl_xor_sync(kFullMask, v[r][0].y, 8);
+            p.z = __shfl_xor_sync(kFullMask, v[r][0].z, 8);
+            p.w = __shfl_xor_sync(kFullMask, v[r][0].w, 8);
+            if (rotates) {
+                const float4 lo = holds_lo ? v[r][0] : p, hi = holds_lo ? p : v[r][0];
+                float4 olo, ohi;
+                rope_pair(lo.x, hi.x, c[r].x, sn[r].x, olo.x, ohi.x);
+                rope_pair(lo.y, hi.y, c[r].y, sn[r].y, olo.y, ohi.y);
+                rope_pair(lo.z, hi.z, c[r].z, sn[r].z, olo.z, ohi.z);
+                rope_pair(lo.w, hi.w, c[r].w, sn[r].w, olo.w, ohi.w);
+                v[r][0] = holds_lo ? olo : ohi;
+            }
+            if (row < rows) {
+#pragma unroll
+                for (int k = 0; k < NQ; ++k) {
+                    stg_v4(out + (size_t)row * HD + 4 * (lane + 32 * k),
+                           make_uint4(__float_as_uint(v[r][k].x), __float_as_uint(v[r][k].y), __float_as_uint(v[r][k].z),
+                                      __float_as_uint(v[r][k].w)));
+                }
+            }
+        }
     }
 }
 

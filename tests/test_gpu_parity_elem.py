@@ -303,6 +303,58 @@ def test_qk_norm_rope(tokens, heads, head_dim, rot, with_gate, choice):
 
 
 @pytest.mark.parametrize("with_gate", [False, True])
+@pytest.mark.parametrize("tokens,heads,head_dim", [(4099, 16, 256), (8192, 2, 256), (4099, 16, 128)])
+def test_qk_norm_rope_and_rope_f32_on_arbitrary_f32_rows(tokens, heads, head_dim, with_gate):
+    """f32 rows that are not bf16 values through the tuned f32 kernels at sizes with grid-stride tails, bit for bit
+    against the reference kernels (the fused one serves head_dim 256, the chain both)."""
+    clef.set_kernel_choice(0)
+    rot, rows = 64, tokens * heads
+    stride = 2 * head_dim if with_gate else head_dim
+    gen = torch.Generator(device="cuda").manual_seed(tokens + head_dim)
+    x = torch.randn(rows, stride, device="cuda", generator=gen) * 2.0
+    x[5] = 0.0
+    w = torch.randn(head_dim, device="cuda", generator=gen) * 0.1
+    table_len = 4096
+    cos, sin = clef.Device(0).rope_tables_dev(torch.arange(table_len, dtype=torch.int32, device="cuda"), table_len, rot, 1e7)
+    pos_map = torch.randint(0, table_len, (tokens,), device="cuda", generator=gen, dtype=torch.int32)
+    q_f = x[:, :head_dim].contiguous()
+    normed = ref_gpu.rms_norm(q_f, w, rows, head_dim, 1e-6)
+    chain = ref_gpu.rope(normed, cos, sin, tokens, heads, head_dim, rot, None, None, pos_map)
+    out = out_buffer(rows * head_dim, F32)
+    gate = out_buffer(rows * head_dim, F32) if with_gate else None
+    assert call("clef_qk_norm_rope", stream(), ptr(x), ptr(w), ptr(cos), ptr(sin), out.ptr, gate.ptr if gate else None, rows,
+                heads, head_dim, rot, 1e-6, None, None, ptr(pos_map), F32) == 0
+    torch.cuda.synchronize()
+    out.check_guards("qk_norm_rope f32")
+    assert_bytes_equal(out.as_f32().view(np.uint32), chain.cpu().numpy().view(np.uint32), "f32 qk_norm_rope vs reference chain")
+    if head_dim == 256:
+        fused, _ = ref_gpu.qk_norm_rope(x, w, cos, sin, rows, heads, head_dim, rot, 1e-6, None, None, pos_map, with_gate)
+        torch.cuda.synchronize()
+        assert_bytes_equal(out.as_f32().view(np.uint32), fused.cpu().numpy().view(np.uint32), "f32 qk_norm_rope vs reference fused kernel")
+    if with_gate:
+        gate.check_guards("gate f32")
+        assert_bytes_equal(gate.as_f32().view(np.uint32), x[:, head_dim:].contiguous().cpu().numpy().view(np.uint32), "gate half")
+    # the plain rotation of the same rows (q alone, then q and k in one launch)
+    ro = out_buffer(rows * head_dim, F32)
+    assert call("clef_rope", stream(), ro.ptr, ptr(q_f), ptr(cos), ptr(sin), tokens, heads, head_dim, rot, None, None, ptr(pos_map), F32) == 0
+    want = ref_gpu.rope(q_f, cos, sin, tokens, heads, head_dim, rot, None, None, pos_map)
+    torch.cuda.synchronize()
+    ro.check_guards("rope f32")
+    assert_bytes_equal(ro.as_f32().view(np.uint32), want.cpu().numpy().view(np.uint32), "f32 rope vs reference kernel")
+    kv_heads = 2
+    k_f = normed.view(tokens, heads, head_dim)[:, :kv_heads].contiguous()
+    qo, ko = out_buffer(rows * head_dim, F32), out_buffer(tokens * kv_heads * head_dim, F32)
+    assert call("clef_rope_qk", stream(), qo.ptr, ptr(q_f), heads, ko.ptr, ptr(k_f), kv_heads, ptr(cos), ptr(sin), tokens, head_dim, rot,
+                None, None, ptr(pos_map), F32) == 0
+    want_k = ref_gpu.rope(k_f, cos, sin, tokens, kv_heads, head_dim, rot, None, None, pos_map)
+    torch.cuda.synchronize()
+    qo.check_guards("rope_qk q f32")
+    ko.check_guards("rope_qk k f32")
+    assert_bytes_equal(qo.as_f32().view(np.uint32), want.cpu().numpy().view(np.uint32), "f32 rope_qk q vs reference kernel")
+    assert_bytes_equal(ko.as_f32().view(np.uint32), want_k.cpu().numpy().view(np.uint32), "f32 rope_qk k vs reference kernel")
+
+
+@pytest.mark.parametrize("with_gate", [False, True])
 @pytest.mark.parametrize("tokens,heads,head_dim", [(778, 16, 256), (4099, 16, 256), (129, 2, 256), (1, 1, 256), (4099, 16, 128), (65, 3, 128)])
 def test_qk_norm_rope_bf16_rounds_the_reference_f32_result(tokens, heads, head_dim, with_gate):
     """bf16 in and out: the tuned kernels (head_dim 128 and 256, rotary 64) and the general kernel must both give
