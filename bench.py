@@ -89,6 +89,21 @@ BYTES_PER_ROW = {
     # hi + lo pairs for 32 expanded heads, normalised k and v as f32 out
     "gdn_prep": 2 * CONV_DIM + 4 * 32 * 128 * 2 + 2 * 32 * 128 * 4,                           # 81,920
 }
+# The same entry points on f32 activations (the reference engine's own residual-stream type: the bit-exact drop-in),
+# reported under "other_configurations": 4-byte activations in and out, the quantised outputs unchanged.
+F32_BYTES_PER_ROW = {
+    "rms_norm_quantise_nvfp4": 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
+    "swiglu_quantise_nvfp4": 2 * 4 * INTER + INTER // 2 + INTER // 16,
+    "rope_qk": 2 * (Q_HEADS + KV_HEADS) * HEAD_DIM * 4 + 4 + 2 * (ROTARY // 2) * 4,
+    "rms_norm_gated_quantise_nvfp4": 2 * 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
+    "embed_rms_norm_quantise_nvfp4": 4 + 4 * HIDDEN + 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
+    "quantise_nvfp4": 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
+    "rms_norm": 2 * 4 * HIDDEN,
+    "rms_norm_gated": 3 * 4 * HIDDEN,
+    "qk_norm_rope_q_hd256_gate": 2 * Q_HEADS * 512 * 4 + 4 + 2 * (ROTARY // 2) * 4,
+    "sigmoid_mul_quantise_nvfp4": 2 * 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
+    "add_rms_norm_quantise_nvfp4": 3 * 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
+}
 # The step, in the order a layer runs its kernels: the partial RoPE of the q and the k heads (attention block; they
 # share their positions and go out as one launch, clef_rope_qk), RMSNorm+NVFP4 (the MLP block's input norm) and
 # SwiGLU+NVFP4. rope_q / rope_k alone are reported under "kernels". The order matters by up to 3 us per step: the
@@ -382,6 +397,19 @@ class Harness:
         return out
 
 
+def make_f32_set(h: Harness, proto: dict):
+    """The tensors the F32_BYTES_PER_ROW entry points touch, as f32 activations (the values of `proto` widened)."""
+    torch = h.torch
+    acts = ("x", "gate", "up", "q", "k", "o", "z", "res", "qg256")
+    outs = ("q_out", "k_out", "h", "g_out", "sum", "q256", "gate256")
+    d = dict(proto)
+    for key in acts:
+        d[key] = proto[key].float()
+    for key in outs:
+        d[key] = torch.empty(proto[key].shape, dtype=torch.float32, device="cuda")
+    return d
+
+
 def make_step_set(h: Harness):
     """One buffer set holding every tensor the timed entry points use at 8,192 rows."""
     torch = h.torch
@@ -416,11 +444,12 @@ def make_step_set(h: Harness):
     }
 
 
-def make_launchers(h: Harness, shared: dict):
-    """name -> closure(buffer set) -> C-ABI status, at 8,192 rows."""
+def make_launchers(h: Harness, shared: dict, code: int = 0):
+    """name -> closure(buffer set) -> C-ABI status, at 8,192 rows; `code` is the activations' dtype (0 bf16, 1 f32)."""
     lib, p, stream = h.lib, h.p, h.stream
     rows_padded = (ROWS + 127) // 128 * 128
-    w_norm, w_gated, cos, sin, cpos, table = (shared[k] for k in ("w_norm", "w_gated", "cos", "sin", "cpos", "table"))
+    w_norm, w_gated, cos, sin, cpos = (shared[k] for k in ("w_norm", "w_gated", "cos", "sin", "cpos"))
+    table = shared["table_f32"] if code else shared["table"]
     w_conv, seq_start, cache_map, w_head, w_head256 = (shared[k] for k in ("w_conv", "seq_start", "cache_map", "w_head", "w_head256"))
     op_bytes = 32 * ((ROWS + 63) // 64) * 2 * 64 * 128
 
@@ -429,58 +458,58 @@ def make_launchers(h: Harness, shared: dict):
 
     return {
         "rms_norm_quantise_nvfp4": lambda d: lib.clef_rms_norm_quantise_nvfp4(
-            stream(), p(d["x"]), p(w_norm), p(d["pk_h"]), p(d["sc_h"]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, 0),
+            stream(), p(d["x"]), p(w_norm), p(d["pk_h"]), p(d["sc_h"]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, code),
         "swiglu_quantise_nvfp4": lambda d: lib.clef_swiglu_quantise_nvfp4(
-            stream(), p(d["gate"]), p(d["up"]), p(d["pk_i"]), p(d["sc_i"]), ROWS, INTER, GS_SWIGLU, 128, 512, 0),
+            stream(), p(d["gate"]), p(d["up"]), p(d["pk_i"]), p(d["sc_i"]), ROWS, INTER, GS_SWIGLU, 128, 512, code),
         "rope_q": lambda d: lib.clef_rope(stream(), p(d["q_out"]), p(d["q"]), p(cos), p(sin), ROWS, Q_HEADS, HEAD_DIM,
-                                          ROTARY, None, None, p(cpos), 0),
+                                          ROTARY, None, None, p(cpos), code),
         "rope_qk": lambda d: lib.clef_rope_qk(stream(), p(d["q_out"]), p(d["q"]), Q_HEADS, p(d["k_out"]), p(d["k"]), KV_HEADS,
-                                              p(cos), p(sin), ROWS, HEAD_DIM, ROTARY, None, None, p(cpos), 0),
+                                              p(cos), p(sin), ROWS, HEAD_DIM, ROTARY, None, None, p(cpos), code),
         "rope_k": lambda d: lib.clef_rope(stream(), p(d["k_out"]), p(d["k"]), p(cos), p(sin), ROWS, KV_HEADS, HEAD_DIM,
-                                          ROTARY, None, None, p(cpos), 0),
-        "embed_gather": lambda d: lib.clef_embed_gather(stream(), p(table), p(d["ids"]), p(d["h"]), ROWS, HIDDEN, 0),
+                                          ROTARY, None, None, p(cpos), code),
+        "embed_gather": lambda d: lib.clef_embed_gather(stream(), p(table), p(d["ids"]), p(d["h"]), ROWS, HIDDEN, code),
         "embed_rms_norm_quantise_nvfp4": lambda d: lib.clef_embed_rms_norm_quantise_nvfp4(
-            stream(), p(table), p(d["ids"]), p(d["h"]), p(w_norm), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, 0),
+            stream(), p(table), p(d["ids"]), p(d["h"]), p(w_norm), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, code),
         "rms_norm_gated_quantise_nvfp4": lambda d: lib.clef_rms_norm_gated_quantise_nvfp4(
             stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["pk_g"]), p(d["sc_g"]), rows_padded * VH, HEAD_DIM, EPS,
-            GS_GATED, 128, 512, VH, ROWS * VH, 0),
+            GS_GATED, 128, 512, VH, ROWS * VH, code),
         "quantise_nvfp4": lambda d: lib.clef_quantise_nvfp4(stream(), p(d["x"]), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN,
-                                                            GS_NORM, 128, 512, 0),
-        "rms_norm": lambda d: lib.clef_rms_norm(stream(), p(d["x"]), p(w_norm), p(d["h"]), ROWS, HIDDEN, EPS, 0),
-        "swiglu": lambda d: lib.clef_swiglu(stream(), p(d["gate"]), p(d["up"]), p(d["act_i"]), ROWS * INTER, 0),
+                                                            GS_NORM, 128, 512, code),
+        "rms_norm": lambda d: lib.clef_rms_norm(stream(), p(d["x"]), p(w_norm), p(d["h"]), ROWS, HIDDEN, EPS, code),
+        "swiglu": lambda d: lib.clef_swiglu(stream(), p(d["gate"]), p(d["up"]), p(d["act_i"]), ROWS * INTER, code),
         "rms_norm_gated": lambda d: lib.clef_rms_norm_gated(stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["g_out"]),
-                                                            ROWS * VH, HEAD_DIM, EPS, 0),
+                                                            ROWS * VH, HEAD_DIM, EPS, code),
         "qk_norm_rope_q": lambda d: lib.clef_qk_norm_rope(stream(), p(d["q"]), p(w_head), p(cos), p(sin), p(d["h"]),
                                                           None, ROWS * Q_HEADS, Q_HEADS, HEAD_DIM, ROTARY, EPS, None,
-                                                          None, p(cpos), 0),
+                                                          None, p(cpos), code),
         "qk_norm_rope_q_hd256_gate": lambda d: lib.clef_qk_norm_rope(
             stream(), p(d["qg256"]), p(w_head256), p(cos), p(sin), p(d["q256"]), p(d["gate256"]), ROWS * Q_HEADS, Q_HEADS, 256,
-            ROTARY, EPS, None, None, p(cpos), 0),
+            ROTARY, EPS, None, None, p(cpos), code),
         "rope_kv_write": lambda d: lib.clef_rope_kv_write(
             stream(), p(d["cache_k"]), p(d["cache_v"]), p(d["k"]), p(d["v"]), p(cos), p(sin), ROWS, KV_HEADS, HEAD_DIM,
-            ROTARY, None, None, p(cpos), p(cache_map), None, 0),
+            ROTARY, None, None, p(cpos), p(cache_map), None, code),
         "qk_norm_rope_kv_write": lambda d: lib.clef_qk_norm_rope_kv_write(
             stream(), p(d["cache_k"]), p(d["cache_v"]), p(d["k"]), p(d["v"]), p(w_head), p(cos), p(sin), ROWS, KV_HEADS,
-            HEAD_DIM, ROTARY, EPS, None, None, p(cpos), p(cache_map), None, 0),
+            HEAD_DIM, ROTARY, EPS, None, None, p(cpos), p(cache_map), None, code),
         # attention output (q-shaped) gated by a same-shaped gate, as the operand of o_proj
         "sigmoid_mul_quantise_nvfp4": lambda d: lib.clef_sigmoid_mul_quantise_nvfp4(
-            stream(), p(d["q"]), p(d["res"]), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, GS_NORM, 128, 512, 0),
-        "sigmoid_mul": lambda d: lib.clef_sigmoid_mul(stream(), p(d["sum"]), p(d["q"]), p(d["res"]), ROWS * HIDDEN, 0),
-        "add": lambda d: lib.clef_add(stream(), p(d["sum"]), p(d["x"]), p(d["res"]), ROWS * HIDDEN, 0),
+            stream(), p(d["q"]), p(d["res"]), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, GS_NORM, 128, 512, code),
+        "sigmoid_mul": lambda d: lib.clef_sigmoid_mul(stream(), p(d["sum"]), p(d["q"]), p(d["res"]), ROWS * HIDDEN, code),
+        "add": lambda d: lib.clef_add(stream(), p(d["sum"]), p(d["x"]), p(d["res"]), ROWS * HIDDEN, code),
         "add_rms_norm_quantise_nvfp4": lambda d: lib.clef_add_rms_norm_quantise_nvfp4(
             stream(), p(d["sum"]), p(d["x"]), p(d["res"]), p(w_norm), p(d["pk_g"]), p(d["sc_g"]), ROWS, HIDDEN, EPS,
-            GS_NORM, 128, 512, 0),
-        "quantise_fp8": lambda d: lib.clef_quantise_fp8(stream(), p(d["x"]), p(d["q8_h"]), p(d["s8"]), ROWS, HIDDEN, 0),
+            GS_NORM, 128, 512, code),
+        "quantise_fp8": lambda d: lib.clef_quantise_fp8(stream(), p(d["x"]), p(d["q8_h"]), p(d["s8"]), ROWS, HIDDEN, code),
         "rms_norm_fp8_bf16": lambda d: lib.clef_rms_norm_fp8_bf16(stream(), p(d["x"]), p(w_norm), p(d["q8_h"]), p(d["s8"]),
-                                                                  p(d["sum"]), ROWS, HIDDEN, EPS, 0),
+                                                                  p(d["sum"]), ROWS, HIDDEN, EPS, code),
         "swiglu_quantise_fp8": lambda d: lib.clef_swiglu_quantise_fp8(stream(), p(d["gate"]), p(d["up"]), p(d["q8_i"]),
-                                                                      p(d["s8"]), ROWS, INTER, 0),
+                                                                      p(d["s8"]), ROWS, INTER, code),
         "rms_norm_gated_quantise_fp8": lambda d: lib.clef_rms_norm_gated_quantise_fp8(
-            stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["q8_h"]), p(d["s8"]), ROWS * VH, HEAD_DIM, EPS, VH, ROWS * VH, 0),
+            stream(), p(d["o"]), p(d["z"]), p(w_gated), p(d["q8_h"]), p(d["s8"]), ROWS * VH, HEAD_DIM, EPS, VH, ROWS * VH, code),
         "gdn_prep": lambda d: lib.clef_gdn_prep(stream(), p(d["mixed"]), p(d["gdn_v"]), ops(d, 0), ops(d, 1), ops(d, 2),
-                                                ops(d, 3), p(d["gdn_kn"]), ROWS, 32, 16, 128, CONV_DIM, 128 ** -0.5, 0),
+                                                ops(d, 3), p(d["gdn_kn"]), ROWS, 32, 16, 128, CONV_DIM, 128 ** -0.5, code),
         "causal_conv_silu": lambda d: lib.clef_causal_conv_silu(stream(), p(d["conv_out"]), p(d["mixed"]), p(w_conv), ROWS,
-                                                                CONV_DIM, CONV_K, p(seq_start), None, None, 0),
+                                                                CONV_DIM, CONV_K, p(seq_start), None, None, code),
     }
 
 
@@ -501,16 +530,19 @@ def make_shared(h: Harness):
     }
 
 
-def time_each_kernel(h: Harness, launchers, proto, steps: int):
+def time_each_kernel(h: Harness, launchers, proto, steps: int, bytes_per_row=None):
     """ms per launch of every entry point alone: a graph of launches that rotates over `sets` private copies of the
     tensors the entry point touches (at least ROTATE_BYTES of them, so neither reads nor writes are served by L2)."""
     torch = h.torch
     out, sets_used = {}, {}
+    bytes_per_row = bytes_per_row or BYTES_PER_ROW
     for name, fn in launchers.items():
+        if name not in bytes_per_row:
+            continue
         rec = Recorder(proto)
         h.ok(fn(rec))
         torch.cuda.synchronize()
-        per_set = BYTES_PER_ROW[name] * ROWS
+        per_set = bytes_per_row[name] * ROWS
         nsets = int(min(160, max(4, math.ceil(ROTATE_BYTES / per_set))))
         sets = [proto]
         for i in range(1, nsets):
@@ -939,6 +971,14 @@ def other_configurations(h: Harness, shared, launchers, sets):
         sweep[rung] = {"us_per_pass": float(np.median(times)) * 1e3, "requests": nreq, "slices": len(per_pass)}
         del per_pass, launches
     out["rung_sweep"] = sweep
+
+    # -- f32 activations (the reference engine's residual-stream type): the same entry points, each alone as above
+    shared32 = dict(shared)
+    shared32["table_f32"] = shared["table"].float()
+    proto32 = make_f32_set(h, sets[0])
+    ms32, sets32 = time_each_kernel(h, make_launchers(h, shared32, code=1), proto32, 24, F32_BYTES_PER_ROW)
+    out["f32_activations"] = {"ms": ms32, "sets": sets32}
+    del proto32, shared32
     return out
 
 
@@ -953,7 +993,13 @@ def summarise_extras(extras, peak):
         gb = step_bytes * rung / (v["us_per_pass"] * 1e-6) / 1e9
         sweep[str(rung)] = {"us_per_pass": round(v["us_per_pass"], 2), "rows_per_s": rung / (v["us_per_pass"] * 1e-6), "GBs": round(gb, 1),
                             "frac_of_measured_peak": round(gb / peak, 4), "requests": v["requests"]}
+    f32 = {}
+    for name, ms in extras["f32_activations"]["ms"].items():
+        gb = F32_BYTES_PER_ROW[name] * ROWS / (ms * 1e-3) / 1e9
+        f32[name] = {"us": round(ms * 1e3, 2), "GBs": round(gb, 1), "frac_of_measured_peak": round(gb / peak, 4),
+                     "bytes_per_row": F32_BYTES_PER_ROW[name], "sets": extras["f32_activations"]["sets"][name]}
     return {
+        "f32_activation_kernels_8192_rows": f32,
         "gated_chain_32768_rows_in_four_chunks": {
             "us_per_8192_row_chunk": round(g["ms_per_chunk"] * 1e3, 2), "ms_per_32768_rows": round(4 * g["ms_per_chunk"], 4),
             "rows_per_s": ROWS / (g["ms_per_chunk"] * 1e-3), "GBs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4)},

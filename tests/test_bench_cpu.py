@@ -18,6 +18,12 @@ def test_algorithmic_bytes_per_row():
     assert b["embed_gather"] == 8196 and b["rms_norm_gated_quantise_nvfp4"] == 9344 and b["embed_rms_norm_quantise_nvfp4"] == 9348
     assert sum(b[k] for k in bench.FULL_KERNELS) == 60296
     assert set(bench.STEP_KERNELS) == {"rms_norm_quantise_nvfp4", "swiglu_quantise_nvfp4", "rope_qk"}
+    # f32 activations: 4-byte activations, the same quantised outputs
+    f = bench.F32_BYTES_PER_ROW
+    assert f["rms_norm_quantise_nvfp4"] == 4 * 2048 + 1024 + 128 and f["swiglu_quantise_nvfp4"] == 8 * 6144 + 3072 + 384
+    assert f["rope_qk"] == 2 * 18 * 128 * 4 + 4 + 256 and set(f) <= set(b)
+    for name in f:   # an f32 entry never moves fewer bytes than its bf16 form, and at most twice as many
+        assert b[name] <= f[name] <= 2 * b[name]
 
 
 def test_recorded_traffic_of_the_dominant_kernel():
