@@ -152,9 +152,6 @@ inline int check_scale_layout(const char* what, int rows, int cols, int blk_mn, 
 
 inline bool use_hot() { return kernel_choice() != 1; }
 
-// Fused kernels that save an intermediate buffer but no time are reached only when the caller asks for them.
-inline bool use_memory_saving_fusions() { return kernel_choice() == 2; }
-
 // The tuned quantising kernels cover the global scales real checkpoints carry; see kHotGlobalScaleMin.
 inline bool hot_scale_ok(float global_scale) {
     return global_scale >= kHotGlobalScaleMin && global_scale <= kHotGlobalScaleMax;

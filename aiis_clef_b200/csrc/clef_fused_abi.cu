@@ -54,7 +54,7 @@ const char* clef_last_error(void) { return g_error; }
 int clef_version(void) { return 100; }
 
 void clef_set_kernel_choice(int choice) {
-    g_kernel_choice.store((choice == 1 || choice == 2) ? choice : 0, std::memory_order_relaxed);
+    g_kernel_choice.store(choice == 1 ? 1 : 0, std::memory_order_relaxed);
 }
 
 int clef_set_scale_layout(int layout) {

@@ -20,7 +20,8 @@ void launch_conv(cudaStream_t s, const DeviceInfo& dev, void* out, const void* x
                  int k, const int32_t* seq_start, const void* history, const int32_t* slot_map) {
     if (k == 4 && channels % 8 == 0 && use_hot() && T::kBytes == 2) {   // bf16: 4 channels per thread, three CTAs per SM (measured)
         static std::atomic<int> occ{0};
-        auto kernel = causal_conv_silu_c4_kernel<4, 8, 3>;
+        // 8,192 channels (16 + 16 heads of q and k and 32 of v, 128 wide) is the engine's mixed row: its stride is compiled in
+        auto kernel = channels == 8192 ? causal_conv_silu_c4_kernel<4, 8, 3, 8192> : causal_conv_silu_c4_kernel<4, 8, 3>;
         const int per_sm = ctas_per_sm(kernel, 0, occ);
         const size_t items = (size_t)((rows + 7) / 8) * (channels / 4);
         launch_hot(kernel, clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0, s, (uint16_t*)out,
@@ -176,16 +177,20 @@ int clef_gdn_prep(clef_stream_t stream, const void* mixed, float* v_out, void* q
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     const int nchunks = (seq_len + kGdnChunk - 1) / kGdnChunk;
-    const size_t warps = (size_t)nchunks * kGdnChunk * kh + (size_t)seq_len * heads;
+    const size_t warps = (size_t)nchunks * kGdnChunk * kh;
+    if (warps >= 0x7fffffffull || (size_t)seq_len * heads * (kGdnKd / 8) >= 0x7fffffffull) {
+        return fail(CLEF_ERR_TOO_LARGE, "%s: seq_len %d x heads %d exceeds the 32-bit item range", what, seq_len, heads);
+    }
     const unsigned grid = clamp_grid((warps + kCtaThreads / 32 - 1) / (kCtaThreads / 32), (size_t)dev.sms * 8);
+    const FastDiv kh_div = make_fast_div((uint32_t)kh), vvec_div = make_fast_div((uint32_t)heads * (kGdnKd / 8));
     if (dtype == CLEF_BF16) {
         gdn_prep_kernel<Bf16><<<grid, kCtaThreads, 0, as_stream(stream)>>>(
             (const uint16_t*)mixed, v_out, (uint8_t*)q_hi, (uint8_t*)q_lo, (uint8_t*)k_hi, (uint8_t*)k_lo, kn, seq_len, heads, kh,
-            nchunks, conv_dim, q_scale);
+            nchunks, conv_dim, q_scale, kh_div, vvec_div);
     } else {
         gdn_prep_kernel<F32><<<grid, kCtaThreads, 0, as_stream(stream)>>>(
             (const float*)mixed, v_out, (uint8_t*)q_hi, (uint8_t*)q_lo, (uint8_t*)k_hi, (uint8_t*)k_lo, kn, seq_len, heads, kh,
-            nchunks, conv_dim, q_scale);
+            nchunks, conv_dim, q_scale, kh_div, vvec_div);
     }
     return check_launch(what);
 }
@@ -207,10 +212,9 @@ int clef_gdn_conv_prep(clef_stream_t stream, const void* x, const float* w, floa
         !aligned(k_hi, 16) || !aligned(k_lo, 16) || !aligned(kn, 16) || (history && !aligned(history, 16))) {
         return fail(CLEF_ERR_INVALID, "%s: pointers must be 16-byte aligned", what);
     }
-    // The fused kernel is no faster than clef_causal_conv_silu + clef_gdn_prep (220 against 72 + 142 us at 8,192 tokens x
-    // 8,192 channels: it is held at two CTAs per SM); what it saves is the intermediate buffer. So it declines, and
-    // the caller runs the faster pair, unless the process asked for memory-saving fusions (clef_set_kernel_choice(2)).
-    if (k != 4 || !use_memory_saving_fusions()) return CLEF_DECLINED;
+    // One launch for 4 taps and 1, 2 or 4 value heads per key head (the repeat count is compiled in); other shapes, and
+    // the shape-general kernel choice, decline: the caller then runs clef_causal_conv_silu + clef_gdn_prep.
+    if (k != 4 || !use_hot() || (heads != kh && heads != 2 * kh && heads != 4 * kh)) return CLEF_DECLINED;
     if (rows == 0) return CLEF_OK;
     if ((size_t)rows * channels >= ((size_t)1 << 34)) return fail(CLEF_ERR_TOO_LARGE, "%s: %d x %d values", what, rows, channels);
     DeviceInfo dev;
@@ -224,12 +228,19 @@ int clef_gdn_conv_prep(clef_stream_t stream, const void* x, const float* w, floa
                    as_stream(stream), xp, w, v_out, (uint8_t*)q_hi, (uint8_t*)q_lo, (uint8_t*)k_hi, (uint8_t*)k_lo, kn, rows,
                    channels, (const int*)seq_start, hp, (const int*)slot_map, heads, kh, nchunks, q_scale, groups_div);
     };
-    static std::atomic<int> occ[2];
-    if (dtype == CLEF_BF16) {
-        launch(gdn_conv_prep_kernel<Bf16, 4, 8, 2>, occ[0], (const uint16_t*)x, (const uint16_t*)history);
+    static std::atomic<int> occ[6];
+    const int ratio = heads / kh;
+#define CLEF_GDN_FUSED(RATIO, SLOT)                                                                                          \
+    if (dtype == CLEF_BF16) launch(gdn_conv_prep_kernel<Bf16, 4, 8, 3, RATIO>, occ[SLOT], (const uint16_t*)x, (const uint16_t*)history); \
+    else launch(gdn_conv_prep_kernel<F32, 4, 8, 3, RATIO>, occ[SLOT + 1], (const float*)x, (const float*)history);
+    if (ratio == 1) {
+        CLEF_GDN_FUSED(1, 0)
+    } else if (ratio == 2) {
+        CLEF_GDN_FUSED(2, 2)
     } else {
-        launch(gdn_conv_prep_kernel<F32, 4, 8, 2>, occ[1], (const float*)x, (const float*)history);
+        CLEF_GDN_FUSED(4, 4)
     }
+#undef CLEF_GDN_FUSED
     return check_launch(what);
 }
 

@@ -273,20 +273,23 @@ causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T:
 // other strip (the first, a ragged last one, one holding a sequence start) takes the literal path. The arithmetic
 // is scalar on purpose: packed multiply-adds cost more register-pair moves here than they save (measured: 105
 // against 99 instructions per row of 4 values).
-template <int K, int R, int MIN_CTAS>
+// CH: the channel count when it is known at compile time (0: the `channels` argument). With a constant row stride the
+// 19 row addresses of a strip are immediate offsets from one base register instead of a multiply-add each.
+template <int K, int R, int MIN_CTAS, int CH = 0>
 __global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
 causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, const float* __restrict__ w, int rows,
-                           int channels, const int* __restrict__ seq_start, const uint16_t* __restrict__ history,
+                           int channels_arg, const int* __restrict__ seq_start, const uint16_t* __restrict__ history,
                            const int* __restrict__ slot_map, FastDiv cvecs_div) {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
-    const uint32_t cvecs = cvecs_div.d;   // channels / 4
+    const int channels = CH ? CH : channels_arg;
+    const uint32_t cvecs = CH ? (uint32_t)(CH / 4) : cvecs_div.d;   // channels / 4
     const uint32_t strips = ((uint32_t)rows + R - 1) / R;
     const uint32_t total = strips * cvecs;
     const uint32_t step = gridDim.x * kCtaThreads;
     const bool starts_vector = R == 8 && (reinterpret_cast<uintptr_t>(seq_start) & 15) == 0;
     for (uint32_t idx = blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
-        const uint32_t strip = fast_div(idx, cvecs_div);
+        const uint32_t strip = CH ? idx / (uint32_t)(CH / 4) : fast_div(idx, cvecs_div);
         const int c0 = (int)(idx - strip * cvecs) * 4;
         const int t0 = (int)strip * R;
         bool plain = t0 >= K - 1 && t0 + R <= rows;   // every row of the strip and of its halo exists
@@ -296,6 +299,17 @@ causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
             const uint16_t* base = x + (size_t)(t0 - (K - 1)) * channels + c0;
 #pragma unroll
             for (int i = 0; i < R + K - 1; ++i) raw[i] = ldg_stream_v2(base + (size_t)i * channels);
+#ifdef CLEF_CONV_L2_AHEAD
+            {   // the strip this thread handles next, named to L2 (16 threads share a 128-byte line)
+                const uint32_t nidx = idx + step;
+                if (nidx < total && (threadIdx.x & 15) == 0) {
+                    const uint32_t nstrip = CH ? nidx / (uint32_t)(CH / 4) : fast_div(nidx, cvecs_div);
+                    const uint16_t* nb = x + (size_t)(nstrip * R) * channels + (nidx - nstrip * cvecs) * 4;
+#pragma unroll
+                    for (int i = 0; i < R; ++i) prefetch_l2(nb + (size_t)i * channels);
+                }
+            }
+#endif
             if (K == 4) {   // a channel's four taps are one 16-byte load
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -437,45 +451,30 @@ __device__ __forceinline__ void load4_as_f32<F32>(const float* p, float* v) {
     v[0] = __uint_as_float(raw.x), v[1] = __uint_as_float(raw.y), v[2] = __uint_as_float(raw.z), v[3] = __uint_as_float(raw.w);
 }
 
+// All index arithmetic is 32-bit with multiply-high divisions (the launcher refuses sizes beyond 2^31 items): a
+// 64-bit division by a run-time value per item cost more instructions than the item's own work.
 template <typename T>
 __global__ void __launch_bounds__(kCtaThreads)
 gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict__ v_out, uint8_t* __restrict__ q_hi,
                 uint8_t* __restrict__ q_lo, uint8_t* __restrict__ k_hi, uint8_t* __restrict__ k_lo, float* __restrict__ kn,
-                int seq_len, int heads, int kh, int nchunks, int conv_dim, float q_scale) {
+                int seq_len, int heads, int kh, int nchunks, int conv_dim, float q_scale, FastDiv kh_div, FastDiv vvec_div) {
     const int lane = threadIdx.x & 31;
-    const size_t warp0 = ((size_t)blockIdx.x * kCtaThreads + threadIdx.x) >> 5;
-    const size_t warps = (size_t)gridDim.x * (kCtaThreads / 32);
+    const uint32_t warp0 = (blockIdx.x * kCtaThreads + threadIdx.x) >> 5;
+    const uint32_t warps = gridDim.x * (kCtaThreads / 32);
     const int ratio = heads / kh;
-    const size_t head_items = (size_t)nchunks * kGdnChunk * kh;   // pad rows of the last chunk included
-    const size_t v_items = (size_t)seq_len * heads;               // 128 values each
-    for (size_t item = warp0; item < head_items + v_items; item += warps) {
-        if (item >= head_items) {   // a 128-value piece of v: 4 values per lane, f32 out
-            const size_t j = item - head_items;
-            const size_t t = j / heads;
-            const int hh = (int)(j - t * heads);
-            const typename T::storage* src = mixed + t * conv_dim + (size_t)2 * kh * kGdnKd + (size_t)hh * kGdnKd + lane * 4;
-            float4 v;
-            if (T::kBytes == 2) {
-                const uint2 raw = ldg_stream_v2(src);
-                v = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
-            } else {
-                const uint4 raw = ldg_stream_v4(src);
-                v = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
-            }
-            *reinterpret_cast<float4*>(v_out + (t * heads + hh) * kGdnKd + lane * 4) = v;
-            continue;
-        }
-        const size_t t = item / kh;
-        const int h = (int)(item - t * kh);
-        const bool live = t < (size_t)seq_len;
+    const uint32_t head_items = (uint32_t)nchunks * kGdnChunk * (uint32_t)kh;   // pad rows of the last chunk included
+    for (uint32_t item = warp0; item < head_items; item += warps) {
+        const uint32_t t = fast_div(item, kh_div);
+        const int h = (int)(item - t * (uint32_t)kh);
+        const bool live = t < (uint32_t)seq_len;
         // Each lane reads its head rows twice: strided (p = lane + 32 i) for the sum in the reference's order, and
         // its 4 adjacent values (p = 4 lane ..) for the outputs, so that every store is 8 or 16 bytes wide. The
         // second read hits L1.
         float q[4] = {0.f, 0.f, 0.f, 0.f}, k[4] = {0.f, 0.f, 0.f, 0.f};
         float qa[4] = {0.f, 0.f, 0.f, 0.f}, ka[4] = {0.f, 0.f, 0.f, 0.f};
         if (live) {
-            const typename T::storage* qr = mixed + t * conv_dim + (size_t)h * kGdnKd;
-            const typename T::storage* kr = qr + (size_t)kh * kGdnKd;
+            const typename T::storage* qr = mixed + (size_t)t * conv_dim + h * kGdnKd;
+            const typename T::storage* kr = qr + kh * kGdnKd;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 q[i] = load_scalar<T>(qr + lane + 32 * i);
@@ -510,18 +509,37 @@ gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict
             kw[j] = pack_bf16x2(ka[2 * j], ka[2 * j + 1]);
             kw[2 + j] = pack_bf16x2(__fsub_rn(ka[2 * j], bf16_lo(kw[j])), __fsub_rn(ka[2 * j + 1], bf16_hi(kw[j])));
         }
-        const size_t chunk = t / kGdnChunk;
+        const uint32_t chunk = t / kGdnChunk;
         const int r = (int)(t - chunk * kGdnChunk);
+        // within an operand tile: row r, the lane's 8 bytes (p = 4 lane .. 4 lane + 3) in their xor-ed 16-byte segment
+        const uint32_t in_tile = (uint32_t)r * kGdnRowBytes + (uint32_t)(((((lane & 15) >> 1) ^ (r & 7)) << 4) + (lane & 1) * 8);
         for (int rep = 0; rep < ratio; ++rep) {
-            const int he = h * ratio + rep;
-            const size_t off = gdn_operand_offset((size_t)he * nchunks + chunk, r, lane * 4);
+            const uint32_t he = (uint32_t)(h * ratio + rep);
+            const size_t off = (((size_t)he * nchunks + chunk) * (kGdnKd / kGdnTileCols) + (lane >> 4)) * (size_t)(kGdnChunk * kGdnRowBytes) + in_tile;
             stg_v2(q_hi + off, make_uint2(qw[0], qw[1]));
             stg_v2(q_lo + off, make_uint2(qw[2], qw[3]));
             stg_v2(k_hi + off, make_uint2(kw[0], kw[1]));
             stg_v2(k_lo + off, make_uint2(kw[2], kw[3]));
             if (live) {
-                *reinterpret_cast<float4*>(kn + (t * heads + he) * kGdnKd + lane * 4) = make_float4(ka[0], ka[1], ka[2], ka[3]);
+                *reinterpret_cast<float4*>(kn + ((size_t)t * heads + he) * kGdnKd + lane * 4) = make_float4(ka[0], ka[1], ka[2], ka[3]);
             }
+        }
+    }
+    // v as f32: a flat conversion of each token's heads x 128 values, 8 per thread
+    const uint32_t vvec = vvec_div.d;   // heads * 16 vectors of 8 per token
+    const uint32_t v_total = (uint32_t)seq_len * vvec;
+    const typename T::storage* vsrc = mixed + 2 * kh * kGdnKd;
+    for (uint32_t idx = blockIdx.x * kCtaThreads + threadIdx.x; idx < v_total; idx += gridDim.x * kCtaThreads) {
+        const uint32_t t = fast_div(idx, vvec_div);
+        const typename T::storage* src = vsrc + (size_t)t * conv_dim + (idx - t * vvec) * 8;
+        float* dst = v_out + (size_t)idx * 8;
+        if (T::kBytes == 2) {
+            const uint4 raw = ldg_stream_v4(src);
+            stg_v4(dst, make_uint4(raw.x << 16, raw.x & 0xffff0000u, raw.y << 16, raw.y & 0xffff0000u));
+            stg_v4(dst + 4, make_uint4(raw.z << 16, raw.z & 0xffff0000u, raw.w << 16, raw.w & 0xffff0000u));
+        } else {
+            stg_v4(dst, ldg_stream_v4(src));
+            stg_v4(dst + 4, ldg_stream_v4(src + 4));
         }
     }
 }
@@ -539,7 +557,32 @@ gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict
 // per SM at 8 cycles per issued instruction leave both the issue slots and the memory system half idle. What the
 // fusion saves is the intermediate buffer and a launch, not time.
 // ---------------------------------------------------------------------------------------------
-template <typename T, int K, int R, int MIN_CTAS>
+// A strip that is not plain (it holds a sequence start, the first rows, or pad tokens of the last chunk), out of line:
+// every tap tested, the literal silu; a q or k row goes to the stage, a v row straight out.
+template <typename T, int K, int R>
+static __device__ __noinline__ void gdn_strip_literal(const typename T::storage* __restrict__ x, const float* __restrict__ w,
+                                                      float* st, float* v_row0, size_t v_row_stride, int t0, int rows, int c0,
+                                                      int channels, const int* __restrict__ seq_start,
+                                                      const typename T::storage* __restrict__ history,
+                                                      const int* __restrict__ slot_map, int lane) {
+#pragma unroll 1
+    for (int r = 0; r < R; ++r) {
+        const int t = t0 + r;
+        float o4[4] = {0.f, 0.f, 0.f, 0.f};   // a pad token of the last chunk: zero operands
+        if (t < rows) {
+#pragma unroll 1
+            for (int j = 0; j < 4; ++j) o4[j] = causal_conv_silu_element<T>(x, w, t, c0 + j, channels, K, seq_start, history, slot_map);
+        }
+        if (v_row0) {
+            if (t < rows) *reinterpret_cast<float4*>(v_row0 + (size_t)r * v_row_stride) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+        } else {
+            *reinterpret_cast<float4*>(st + r * kGdnKd + lane * 4) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+        }
+    }
+}
+
+// RATIO = heads / kh (value heads per key head), compiled in so that the repeated stores are straight-line code.
+template <typename T, int K, int R, int MIN_CTAS, int RATIO>
 __global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
 gdn_conv_prep_kernel(const typename T::storage* __restrict__ x, const float* __restrict__ w, float* __restrict__ v_out,
                      uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo, uint8_t* __restrict__ k_hi,
@@ -547,16 +590,23 @@ gdn_conv_prep_kernel(const typename T::storage* __restrict__ x, const float* __r
                      const int* __restrict__ seq_start, const typename T::storage* __restrict__ history,
                      const int* __restrict__ slot_map, int heads, int kh, int nchunks, float q_scale, FastDiv groups_div) {
     static_assert(kGdnChunk % R == 0, "a strip must not straddle two chunks");
+    static_assert(R == 8, "the reduce-scatter below is written for 8 rows");
     __shared__ float stage[kCtaThreads / 32][R * kGdnKd];
     pdl_launch_dependents();
     pdl_wait_prior_grids();
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    float* st = &stage[warp][0];
     const uint32_t groups = groups_div.d;                              // channels / 128
     const uint32_t strips = (uint32_t)nchunks * (kGdnChunk / R);       // pad tokens of the last chunk included
     const uint32_t total = strips * groups;
-    const int ratio = heads / kh;
-    const bool starts_vector = R == 8 && (reinterpret_cast<uintptr_t>(seq_start) & 15) == 0;
+    const bool starts_vector = (reinterpret_cast<uintptr_t>(seq_start) & 15) == 0;
+    const size_t v_row_stride = (size_t)heads * kGdnKd;
+    // within an operand tile: the lane's 8 bytes of row r sit in 16-byte segment ((lane & 15) >> 1) ^ (r & 7); a strip
+    // starts at a multiple of 8 rows of its chunk, so r & 7 is the row's index in the strip
+    const uint32_t seg16 = (uint32_t)((lane & 15) >> 1) << 4, in_seg = (uint32_t)(lane & 1) * 8;
+    const size_t tile_bytes = (size_t)kGdnChunk * kGdnRowBytes;
+    const size_t head_stride = (size_t)nchunks * (kGdnKd / kGdnTileCols) * tile_bytes;   // between expanded heads
     for (uint32_t item = blockIdx.x * (kCtaThreads / 32) + warp; item < total; item += gridDim.x * (kCtaThreads / 32)) {
         const uint32_t strip = fast_div(item, groups_div);
         const int g = (int)(item - strip * groups);
@@ -566,10 +616,27 @@ gdn_conv_prep_kernel(const typename T::storage* __restrict__ x, const float* __r
         if (t0 >= rows && is_v) {
             continue;
         }
+        float* v_row0 = is_v ? v_out + (size_t)t0 * v_row_stride + (size_t)(g - 2 * kh) * kGdnKd + lane * 4 : nullptr;
         bool plain = t0 >= K - 1 && t0 + R <= rows;   // every row of the strip and of its halo exists
-        float xs[R + K - 1][4];
-        float wt[4][K];
-        if (plain) {
+        if (plain && seq_start) {
+            const int lim = t0 - (K - 1);
+            if (starts_vector) {   // the 8 sequence starts as two 16-byte loads
+                const int4 a = __ldg(reinterpret_cast<const int4*>(seq_start + t0));
+                const int4 b = __ldg(reinterpret_cast<const int4*>(seq_start + t0) + 1);
+                plain = a.x <= lim && a.y <= lim + 1 && a.z <= lim + 2 && a.w <= lim + 3 && b.x <= lim + 4 && b.y <= lim + 5 &&
+                        b.z <= lim + 6 && b.w <= lim + 7;
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) plain &= __ldg(seq_start + t0 + r) <= lim + r;
+            }
+        }
+        if (!plain) {
+            gdn_strip_literal<T, K, R>(x, w, st, v_row0, v_row_stride, t0, rows, c0, channels, seq_start, history, slot_map, lane);
+        } else {
+            // Phase 1: convolution + silu of the strip, row by row: a v row goes straight out as f32, a q or k row is
+            // parked in the warp's stage (not carried in registers between the phases).
+            float xs[R + K - 1][4];
+            float wt[4][K];
             const typename T::storage* base = x + (size_t)(t0 - (K - 1)) * channels + c0;
 #pragma unroll
             for (int i = 0; i < R + K - 1; ++i) load4_as_f32<T>(base + (size_t)i * channels, xs[i]);
@@ -586,28 +653,9 @@ gdn_conv_prep_kernel(const typename T::storage* __restrict__ x, const float* __r
                     for (int tap = 0; tap < K; ++tap) wt[j][tap] = __ldg(w + (size_t)(c0 + j) * K + tap);
                 }
             }
-            if (seq_start) {
-                const int lim = t0 - (K - 1);
-                if (starts_vector) {
-                    const int4 a = __ldg(reinterpret_cast<const int4*>(seq_start + t0));
-                    const int4 b = __ldg(reinterpret_cast<const int4*>(seq_start + t0) + 1);
-                    plain = a.x <= lim && a.y <= lim + 1 && a.z <= lim + 2 && a.w <= lim + 3 && b.x <= lim + 4 &&
-                            b.y <= lim + 5 && b.z <= lim + 6 && b.w <= lim + 7;
-                } else {
 #pragma unroll
-                    for (int r = 0; r < R; ++r) plain &= __ldg(seq_start + t0 + r) <= lim + r;
-                }
-            }
-        }
-        // Phase 1: the convolved, activated values of the strip, o[r][j] for row t0 + r and channel c0 + j.
-        float o[R][4];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int t = t0 + r;
-            if (t >= rows) {   // a pad token of the last chunk: zero operands
-                o[r][0] = o[r][1] = o[r][2] = o[r][3] = 0.0f;
-            } else if (plain) {
-                float a4[4];
+            for (int r = 0; r < R; ++r) {
+                float a4[4], o4[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     a4[j] = 0.0f;
@@ -615,39 +663,26 @@ gdn_conv_prep_kernel(const typename T::storage* __restrict__ x, const float* __r
                     for (int tap = 0; tap < K; ++tap) a4[j] = __fmaf_rn(wt[j][tap], xs[r + tap][j], a4[j]);
                 }
                 const float m = fmaxf_nan(max3_abs_nan(fabsf(a4[0]), a4[1], a4[2]), fabsf(a4[3]));
-                if (m <= kSiluFastMaxAbs) {
+                if (m <= kSiluFastMaxAbs) {   // false for a NaN too
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) o[r][j] = silu_ieee_refined_f32(a4[j]);
+                    for (int j = 0; j < 4; ++j) o4[j] = silu_ieee_refined_f32(a4[j]);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) o[r][j] = silu_ieee_div(a4[j]);
+                    for (int j = 0; j < 4; ++j) o4[j] = silu_ieee_div(a4[j]);
                 }
-            } else {
-#pragma unroll 1
-                for (int j = 0; j < 4; ++j) {
-                    o[r][j] = causal_conv_silu_element<T>(x, w, t, c0 + j, channels, K, seq_start, history, slot_map);
+                if (is_v) {
+                    *reinterpret_cast<float4*>(v_row0 + (size_t)r * v_row_stride) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+                } else {
+                    *reinterpret_cast<float4*>(st + r * kGdnKd + lane * 4) = make_float4(o4[0], o4[1], o4[2], o4[3]);
                 }
             }
         }
         if (is_v) {
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (t0 + r < rows) {
-                    *reinterpret_cast<float4*>(v_out + (size_t)(t0 + r) * heads * kGdnKd + (size_t)(g - 2 * kh) * kGdnKd + lane * 4) =
-                        make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
-                }
-            }
             continue;
         }
-        // Phase 2: the R sums of squares. Every row goes through shared memory once so that lane l adds p = l,
-        // l + 32, l + 64, l + 96 in order; the R xor trees run as one reduce-scatter (same pairs, same order: the
-        // sums are bit-identical to R butterflies), after which lanes 4 r .. 4 r + 3 hold the total of row r.
-        static_assert(R == 8, "the reduce-scatter below is written for 8 rows");
-        float* st = &stage[warp][0];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            *reinterpret_cast<float4*>(st + r * kGdnKd + lane * 4) = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
-        }
+        // Phase 2: the R sums of squares. Lane l adds p = l, l + 32, l + 64, l + 96 of a row in order; the R xor trees
+        // run as one reduce-scatter (same pairs, same order: the sums are bit-identical to R butterflies), after which
+        // lanes 4 r .. 4 r + 3 hold the total of row r.
         __syncwarp();
         float s8[R];
 #pragma unroll
@@ -670,58 +705,40 @@ gdn_conv_prep_kernel(const typename T::storage* __restrict__ x, const float* __r
         for (int j = 0; j < 2; ++j) {
             s2[j] = __fadd_rn(b3 ? s4[2 + j] : s4[j], __shfl_xor_sync(kFullMask, b3 ? s4[j] : s4[2 + j], 8));
         }
-        float total = __fadd_rn(b2 ? s2[1] : s2[0], __shfl_xor_sync(kFullMask, b2 ? s2[0] : s2[1], 4));
-        total = __fadd_rn(total, __shfl_xor_sync(kFullMask, total, 2));
-        total = __fadd_rn(total, __shfl_xor_sync(kFullMask, total, 1));
+        float total_sq = __fadd_rn(b2 ? s2[1] : s2[0], __shfl_xor_sync(kFullMask, b2 ? s2[0] : s2[1], 4));
+        total_sq = __fadd_rn(total_sq, __shfl_xor_sync(kFullMask, total_sq, 2));
+        total_sq = __fadd_rn(total_sq, __shfl_xor_sync(kFullMask, total_sq, 1));
         const bool is_q = g < kh;
-        float my_scale = rsqrtf(__fadd_rn(total, 1e-6f));   // of row (lane >> 2)
+        float my_scale = rsqrtf(__fadd_rn(total_sq, 1e-6f));   // of row (lane >> 2)
         if (is_q) my_scale = __fmul_rn(my_scale, q_scale);
-        // Phase 3: scale in place, store kn, split into hi + lo in place, store. A strip starts at a multiple of 8
-        // rows of its chunk, so the swizzle term of row r is the constant r and every store address is a per-head
-        // base pointer plus a small offset.
+        // Phase 3: each lane scales its own 4 adjacent values of a row, stores kn, splits into hi + lo and stores
+        // 8 bytes into each operand tile, once per repeated head.
         const int h = is_q ? g : g - kh;
-        uint8_t* hi = is_q ? q_hi : k_hi;
-        uint8_t* lo = is_q ? q_lo : k_lo;
-        const size_t chunk = (size_t)(t0 / kGdnChunk);
-        const int rr0 = t0 - (int)chunk * kGdnChunk;
+        const uint32_t chunk = (uint32_t)t0 / kGdnChunk;
+        const uint32_t rr0 = (uint32_t)t0 - chunk * kGdnChunk;
+        const size_t base = ((((size_t)(h * RATIO) * nchunks + chunk) * (kGdnKd / kGdnTileCols) + (size_t)(lane >> 4)) * kGdnChunk + rr0) *
+                                kGdnRowBytes + in_seg;
+        uint8_t* hp = (is_q ? q_hi : k_hi) + base;
+        uint8_t* lp = (is_q ? q_lo : k_lo) + base;
+        float* kp = kn + ((size_t)t0 * heads + (size_t)(h * RATIO)) * kGdnKd + lane * 4;
+        const int live_rows = is_q ? 0 : min(R, rows - t0);   // rows whose normalised k also goes out as f32
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const float scale = __shfl_sync(kFullMask, my_scale, 4 * r);
+            const float4 raw4 = *reinterpret_cast<const float4*>(st + r * kGdnKd + lane * 4);   // this lane's own values
+            const float o0 = __fmul_rn(raw4.x, scale), o1 = __fmul_rn(raw4.y, scale), o2 = __fmul_rn(raw4.z, scale),
+                        o3 = __fmul_rn(raw4.w, scale);
+            const uint32_t hi0 = pack_bf16x2(o0, o1), hi1 = pack_bf16x2(o2, o3);
+            const uint32_t lo0 = pack_bf16x2(__fsub_rn(o0, bf16_lo(hi0)), __fsub_rn(o1, bf16_hi(hi0)));
+            const uint32_t lo1 = pack_bf16x2(__fsub_rn(o2, bf16_lo(hi1)), __fsub_rn(o3, bf16_hi(hi1)));
+            const uint32_t off = (uint32_t)r * kGdnRowBytes + (seg16 ^ ((uint32_t)r << 4));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[r][j] = __fmul_rn(o[r][j], scale);
-        }
-        if (!is_q) {
-            for (int rep = 0; rep < ratio; ++rep) {
-                float* kp = kn + ((size_t)t0 * heads + (size_t)(h * ratio + rep)) * kGdnKd + lane * 4;
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    if (t0 + r < rows) {
-                        *reinterpret_cast<float4*>(kp + (size_t)r * heads * kGdnKd) = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
-                    }
+            for (int rep = 0; rep < RATIO; ++rep) {
+                if (r < live_rows) {
+                    *reinterpret_cast<float4*>(kp + (size_t)r * v_row_stride + rep * kGdnKd) = make_float4(o0, o1, o2, o3);
                 }
-            }
-        }
-        uint32_t pk[R][4];   // hi words 0, 1 and lo words 0, 1 of the lane's 4 values
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                pk[r][j] = pack_bf16x2(o[r][2 * j], o[r][2 * j + 1]);
-                pk[r][2 + j] = pack_bf16x2(__fsub_rn(o[r][2 * j], bf16_lo(pk[r][j])), __fsub_rn(o[r][2 * j + 1], bf16_hi(pk[r][j])));
-            }
-        }
-        const uint32_t seg16 = (uint32_t)((lane & 15) >> 1) << 4;   // 16-byte segment of the lane's values, in bytes
-        const uint32_t in_seg = (uint32_t)(lane & 1) * 8;
-        for (int rep = 0; rep < ratio; ++rep) {
-            const size_t base = ((((size_t)(h * ratio + rep) * nchunks + chunk) * (kGdnKd / kGdnTileCols) + (size_t)(lane >> 4)) *
-                                     kGdnChunk + (size_t)rr0) * kGdnRowBytes;
-            uint8_t* hp = hi + base;
-            uint8_t* lp = lo + base;
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const uint32_t off = (uint32_t)r * kGdnRowBytes + ((seg16 ^ ((uint32_t)r << 4)) + in_seg);
-                stg_v2(hp + off, make_uint2(pk[r][0], pk[r][1]));
-                stg_v2(lp + off, make_uint2(pk[r][2], pk[r][3]));
+                stg_v2(hp + rep * head_stride + off, make_uint2(hi0, hi1));
+                stg_v2(lp + rep * head_stride + off, make_uint2(lo0, lo1));
             }
         }
     }

@@ -163,8 +163,7 @@ def nvfp4_m_tile_for(m: int) -> int:
 
 
 def set_kernel_choice(choice: int) -> None:
-    """0: tuned kernel when the shape has one (default); 1: always the shape-general kernel; 2: as 0, plus the fused
-    kernels that save an intermediate buffer but no time (clef_gdn_conv_prep)."""
+    """0: tuned kernel when the shape has one (default); 1: always the shape-general kernel."""
     load().clef_set_kernel_choice(int(choice))
 
 
@@ -539,7 +538,7 @@ class Device:
                                                         _ptr(out["q_lo"]), _ptr(out["k_hi"]), _ptr(out["k_lo"]), _ptr(out["kn"]),
                                                         seq_len, conv_dim, k, _ptr(seq_start), _ptr(history), _ptr(slot_map),
                                                         heads, kh, kd, q_scale, _dtype_code(x)), "clef_gdn_conv_prep")
-        if status == CLEF_DECLINED:   # the default (the pair is the faster form), or a tap count other than 4: the two calls
+        if status == CLEF_DECLINED:   # a tap count other than 4, heads / kh other than 1, 2, 4, or the general kernel choice: the two calls
             mixed = self.causal_conv_silu_dev(x, w, seq_len, conv_dim, k, seq_start, history, slot_map)
             return self.gdn_prep_dev(mixed, seq_len, kh, kd, heads, conv_dim)
         return out

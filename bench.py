@@ -88,6 +88,8 @@ BYTES_PER_ROW = {
     # the scan's operands from the convolved row (16 q/k heads, 32 v heads of 128): bf16 row in; q and k as bf16
     # hi + lo pairs for 32 expanded heads, normalised k and v as f32 out
     "gdn_prep": 2 * CONV_DIM + 4 * 32 * 128 * 2 + 2 * 32 * 128 * 4,                           # 81,920
+    # the two above in one launch (the convolved row never goes through memory): mixed row in, the scan's operands out
+    "gdn_conv_prep": 2 * CONV_DIM + 4 * 32 * 128 * 2 + 2 * 32 * 128 * 4 + 4,                  # 81,924
 }
 # The same entry points on f32 activations (the reference engine's own residual-stream type: the bit-exact drop-in),
 # reported under "other_configurations": 4-byte activations in and out, the quantised outputs unchanged.
@@ -456,6 +458,11 @@ def make_launchers(h: Harness, shared: dict, code: int = 0):
     def ops(d, i):
         return h.ctypes.c_void_p(d["gdn_ops"].data_ptr() + i * op_bytes)
 
+    def gdn_conv_prep(d):
+        """The convolution and the scan's operands in one launch."""
+        return lib.clef_gdn_conv_prep(stream(), p(d["mixed"]), p(w_conv), p(d["gdn_v"]), ops(d, 0), ops(d, 1), ops(d, 2), ops(d, 3),
+                                      p(d["gdn_kn"]), ROWS, CONV_DIM, CONV_K, p(seq_start), None, None, 32, 16, 128, 128 ** -0.5, code)
+
     return {
         "rms_norm_quantise_nvfp4": lambda d: lib.clef_rms_norm_quantise_nvfp4(
             stream(), p(d["x"]), p(w_norm), p(d["pk_h"]), p(d["sc_h"]), ROWS, HIDDEN, EPS, GS_NORM, 128, 512, code),
@@ -510,6 +517,7 @@ def make_launchers(h: Harness, shared: dict, code: int = 0):
                                                 ops(d, 3), p(d["gdn_kn"]), ROWS, 32, 16, 128, CONV_DIM, 128 ** -0.5, code),
         "causal_conv_silu": lambda d: lib.clef_causal_conv_silu(stream(), p(d["conv_out"]), p(d["mixed"]), p(w_conv), ROWS,
                                                                 CONV_DIM, CONV_K, p(seq_start), None, None, code),
+        "gdn_conv_prep": gdn_conv_prep,
     }
 
 

@@ -298,8 +298,7 @@ int clef_gdn_prep(clef_stream_t stream, const void* mixed, float* v_out, void* q
  * clef_causal_conv_silu followed by clef_gdn_prep in one launch, the convolved rows staying in f32 in between (as
  * in the reference). x [rows, channels] with channels = 2 kh kd + heads kd, w [channels, k] f32; the maps as for
  * clef_causal_conv_silu; outputs as for clef_gdn_prep. Returns CLEF_DECLINED (run the two calls) for a tap count
- * other than 4, and by default for every shape: on B200 the one-launch form is no faster than the two calls (it
- * saves the intermediate [rows, channels] buffer, not time), so it runs only after clef_set_kernel_choice(2). */
+ * other than 4, for heads / kh other than 1, 2 or 4, and under clef_set_kernel_choice(1). */
 int clef_gdn_conv_prep(clef_stream_t stream, const void* x, const float* w, float* v_out, void* q_hi, void* q_lo, void* k_hi,
                        void* k_lo, float* kn, int rows, int channels, int k, const int32_t* seq_start, const void* history,
                        const int32_t* slot_map, int heads, int kh, int kd, float q_scale, int dtype);
@@ -363,8 +362,7 @@ int clef_embed_rms_norm_quantise_nvfp4_ex(clef_stream_t stream, const void* tabl
                                           float eps, float global_scale, int blk_mn, int chunk, int dtype, int sf_layout);
 
 /* Kernel selection: 0 = automatic (tuned kernel when the shape has one; default), 1 = always the shape-general
- * kernel (tests, measurements), 2 = automatic, and fused kernels that save an intermediate buffer but no time are
- * used as well (today: clef_gdn_conv_prep). Process-wide; not part of the reference interface. */
+ * kernel (tests, measurements). Process-wide; not part of the reference interface. */
 void clef_set_kernel_choice(int choice);
 
 #ifdef __cplusplus

@@ -244,7 +244,7 @@ def test_gdn_prep_argument_errors():
 
 
 @pytest.mark.parametrize("mode", ["plain", "sequences", "history"])
-@pytest.mark.parametrize("seq_len,kh,heads", [(1, 4, 4), (64, 4, 8), (203, 4, 8), (778, 16, 32), (2048, 16, 32)])
+@pytest.mark.parametrize("seq_len,kh,heads", [(1, 4, 4), (64, 4, 8), (203, 4, 8), (778, 16, 32), (2048, 16, 32), (130, 4, 16)])
 def test_gdn_conv_prep_equals_the_reference_chain(seq_len, kh, heads, mode):
     """clef_gdn_conv_prep (one launch) against the reference kernels causal_conv_silu_kernel -> gdn_prep_kernel on the
     same GPU, the convolved rows in f32 in between: all six outputs byte for byte, from f32 and from bf16 rows."""
@@ -266,16 +266,19 @@ def test_gdn_conv_prep_equals_the_reference_chain(seq_len, kh, heads, mode):
                                     None if hist is None else dev_f32_from_bits(hist), d_sm)
     ref = ref_gpu.gdn_prep(conv.contiguous().view(-1), seq_len, kh, kd, heads, conv_dim)
     dev = clef.Device(0)
-    # by default the entry point declines (the two calls are the faster form) ...
+    # under the shape-general kernel choice the entry point declines (the caller runs the two calls) ...
     lib = clef.load()
     dx, dh = dev_bf16(xb), (None if hist is None else dev_bf16(hist))
     bufs = [torch.empty(heads * ((seq_len + 63) // 64) * 2 * 64 * 128, dtype=torch.uint8, device="cuda") for _ in range(4)]
     kn_, v_ = torch.empty(seq_len, heads, kd, device="cuda"), torch.empty(seq_len, heads * kd, device="cuda")
+    clef.set_kernel_choice(1)
     assert lib.clef_gdn_conv_prep(stream(), ptr(dx), ptr(dw), ptr(v_), ptr(bufs[0]), ptr(bufs[1]), ptr(bufs[2]), ptr(bufs[3]), ptr(kn_),
                                   seq_len, conv_dim, k, ptr(d_ss), ptr(dh), ptr(d_sm), heads, kh, kd,
                                   float(np.float32(1.0) / np.sqrt(np.float32(kd))), 0) == 1
-    # ... and runs as one launch once memory-saving fusions are asked for
-    clef.set_kernel_choice(2)
+    # ... and by default it is one launch (1, 2 or 4 value heads per key head; other ratios decline)
+    clef.set_kernel_choice(0)
+    assert lib.clef_gdn_conv_prep(stream(), ptr(dx), ptr(dw), ptr(v_), ptr(bufs[0]), ptr(bufs[1]), ptr(bufs[2]), ptr(bufs[3]), ptr(kn_),
+                                  seq_len, 2 * kh * kd + 3 * kh * kd, k, ptr(d_ss), ptr(dh), ptr(d_sm), 3 * kh, kh, kd, 0.1, 0) == 1
     for x_in, h_in in ((dev_f32_from_bits(xb), None if hist is None else dev_f32_from_bits(hist)),
                        (dev_bf16(xb), None if hist is None else dev_bf16(hist))):
         got = dev.gdn_conv_prep_dev(x_in, dw, seq_len, kh, kd, heads, conv_dim, k, d_ss, h_in, d_sm)
