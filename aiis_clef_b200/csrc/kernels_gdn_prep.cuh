@@ -299,8 +299,7 @@ causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
             const uint16_t* base = x + (size_t)(t0 - (K - 1)) * channels + c0;
 #pragma unroll
             for (int i = 0; i < R + K - 1; ++i) raw[i] = ldg_stream_v2(base + (size_t)i * channels);
-#ifdef CLEF_CONV_L2_AHEAD
-            {   // the strip this thread handles next, named to L2 (16 threads share a 128-byte line)
+            {   // the strip this thread handles next, named to L2 (16 threads share a 128-byte line): 70.5 -> 68.9 us
                 const uint32_t nidx = idx + step;
                 if (nidx < total && (threadIdx.x & 15) == 0) {
                     const uint32_t nstrip = CH ? nidx / (uint32_t)(CH / 4) : fast_div(nidx, cvecs_div);
@@ -309,7 +308,6 @@ causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
                     for (int i = 0; i < R; ++i) prefetch_l2(nb + (size_t)i * channels);
                 }
             }
-#endif
             if (K == 4) {   // a channel's four taps are one 16-byte load
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
