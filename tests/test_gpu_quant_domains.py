@@ -116,6 +116,28 @@ def test_rms_norm_quantise_outside_the_fast_domain(cols, global_scale):
     assert_bytes_equal(f_p, ref_p.cpu().numpy(), "f32 activations: packed vs reference chain")
 
 
+@pytest.mark.parametrize("rows,cols", [(2568, 2048), (1484, 4096), (3700, 2048), (2368, 2048), (8192, 2048), (1185, 4096)])
+def test_rms_norm_quantise_tail_round_shared_by_warp_pairs(rows, cols):
+    """Row counts that leave the tuned kernel a last round for at most half of its warps (the grid has 148 x 16 warps
+    at 2,048 columns, 148 x 8 at 4,096): that round's rows are split between two warps each. With full rounds in front
+    (2,568 = 2,368 + 200 rows; 1,484 = 1,184 + 300), pad rows inside the tail (rows not a multiple of 128), exactly
+    full rounds (2,368: no tail), and a tail too long for pairs (3,700); blocks outside the quantiser's short path and
+    zero rows land in the tail too. Bytes against the reference chain."""
+    rng = np.random.default_rng(rows + cols)
+    x = _with_zero_rows(normal_bf16(rng, (rows, cols), outlier_channels=8), rng)
+    x[-3] = adversarial_bf16_matrix(rng, 1, cols)[0]          # non-finite, denormal and tie blocks in the last rows
+    x[-40] = adversarial_bf16_matrix(rng, 1, cols)[0]
+    w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
+    dx, dw = dev_bf16(x), torch.from_numpy(w).cuda()
+    for gs in (80.0, 0.02):                                    # 0.02: subnormal scale codes, the literal path
+        got_p, got_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(dx), ptr(dw)], [rows, cols, 1e-6, gs, 128, 512, BF16])
+        normed = ref_gpu.rms_norm(dev_f32_from_bits(x), dw, rows, cols, 1e-6)
+        ref_p, ref_s = ref_gpu.quantise_nvfp4(normed, rows, cols, gs)
+        torch.cuda.synchronize()
+        assert_bytes_equal(got_s, ref_s.cpu().numpy(), f"scales vs reference chain (global scale {gs})")
+        assert_bytes_equal(got_p, ref_p.cpu().numpy(), f"packed vs reference chain (global scale {gs})")
+
+
 def test_rms_norm_quantise_f32_on_arbitrary_f32_rows():
     """f32 rows that are not bf16 values (the engine's residual stream), 4096 columns: the reference's own fused kernel
     serves this shape, and the chain must agree with it too; 8,192 rows cover the tuned kernel's tail."""
