@@ -516,9 +516,17 @@ rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restri
     // (the token ids are an activation of the pass: they are read after the wait)
     auto source_row = [&](int r) { return x + (size_t)(EMBED ? __ldg(ids + r) : r) * COLS; };
     if (EMBED && row < rows) name_row_to_l2(source_row(row));
+    // Tail balance as in the bf16 kernel: a last round for at most half of the grid's warps is shared by warp pairs.
+    constexpr bool PAIR = !ADD && !EMBED;
+    const int grid_warps = gridDim.x * 8;
+    const int tail_base = (rows_total / grid_warps) * grid_warps;
+    const bool pair_mode = PAIR && rows_total > tail_base && 2 * (rows_total - tail_base) <= grid_warps;
+    const int main_end = pair_mode ? tail_base : rows_total;
+    const int tail_row = tail_base + ((blockIdx.x * 8 + warp) >> 1);
+    const int half_id = warp & 1;
     __syncthreads();
 
-    for (; row < rows_total; row += gridDim.x * 8) {
+    for (; row < main_end; row += gridDim.x * 8) {
         uint8_t* prow = packed + (size_t)row * (COLS / 2);
         const uint32_t m_rest = fast_div((uint32_t)row, atom_div);
         const uint32_t m_atom = sf_row_slot((uint32_t)row - m_rest * (uint32_t)blk_mn, sf);
@@ -540,9 +548,15 @@ rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restri
             d[j][1] = ldg_stream_v8(xrow + (size_t)(lane + 32 * j) * 16 + 8);
         }
         const int next = row + gridDim.x * 8;
-        if (next < rows) {
+        if (next < min(rows, main_end)) {
             name_row_to_l2(source_row(next));
             if (ADD) name_row_to_l2(addend + (size_t)next * COLS);
+        } else if (PAIR && pair_mode && next >= main_end && tail_row < rows) {
+            // this warp's half of its tail row: NB / 2 blocks of 64 bytes per lane = NB * 8 lines, NB / 4 per lane
+#pragma unroll
+            for (int h = 0; h < NB / 4; ++h) {
+                prefetch_l2(x + (size_t)tail_row * COLS + (size_t)half_id * (COLS / 2) + (size_t)(lane + 32 * h) * 32);
+            }
         }
         if (ADD) {   // the addend arrives block by block, one block ahead of the sum
             const float* arow = addend + (size_t)row * COLS;
@@ -621,6 +635,92 @@ rms_norm_quant_f32_hot_kernel(const float* __restrict__ x, const float* __restri
                     // ADD: this lane stored the block's sum above, so it reads its own values back.
                     rms_block_cold_f32((ADD ? (const float*)sum_out + (size_t)row * COLS : xrow) + b * 16, weight + b * 16, inv, global_scale,
                                        reinterpret_cast<uint2*>(prow + b * 8), srow + (size_t)(b >> 2) * chunk + (b & 3));
+                }
+            }
+        }
+    }
+    if (PAIR && pair_mode && tail_row < rows_total) {
+        // The tail round, as in the bf16 kernel: two warps per row, the quads' sums of squares cross through shared
+        // memory and are added in the one-warp order.
+        constexpr int HB = NB / 2;
+        __shared__ float s_quads[4][2][HB * 4][32];
+        uint8_t* prow = packed + (size_t)tail_row * (COLS / 2);
+        const uint32_t m_rest = fast_div((uint32_t)tail_row, atom_div);
+        const uint32_t m_atom = sf_row_slot((uint32_t)tail_row - m_rest * (uint32_t)blk_mn, sf);
+        uint8_t* srow = scales + (size_t)m_rest * (BLOCKS / 4) * (size_t)chunk + (size_t)m_atom * 4;
+        if (tail_row >= rows) {   // a pad row: both warps zero their halves
+#pragma unroll
+            for (int i = 0; i < HB; ++i) {
+                const int b = lane + 32 * (half_id * HB + i);
+                *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(0u, 0u);
+                srow[(size_t)(b >> 2) * chunk + (b & 3)] = 0;
+            }
+        } else {
+            const float* xrow = x + (size_t)tail_row * COLS;
+            U8x32 d[HB][2];
+#pragma unroll
+            for (int i = 0; i < HB; ++i) {
+                d[i][0] = ldg_stream_v8(xrow + (size_t)(lane + 32 * (half_id * HB + i)) * 16);
+                d[i][1] = ldg_stream_v8(xrow + (size_t)(lane + 32 * (half_id * HB + i)) * 16 + 8);
+            }
+            f32x2 v[HB][8];
+            float quad[HB][4];
+#pragma unroll
+            for (int i = 0; i < HB; ++i) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const U8x32& hw = d[i][q >> 1];
+                    const int o = (q & 1) * 4;
+                    const float vx = __uint_as_float(hw.w[o]), vy = __uint_as_float(hw.w[o + 1]);
+                    const float vz = __uint_as_float(hw.w[o + 2]), vw = __uint_as_float(hw.w[o + 3]);
+                    v[i][2 * q] = f2_pack(vx, vy);
+                    v[i][2 * q + 1] = f2_pack(vz, vw);
+                    quad[i][q] = __fadd_rn(__fmaf_rn(vx, vx, __fmul_rn(vy, vy)), __fmaf_rn(vz, vz, __fmul_rn(vw, vw)));
+                    s_quads[warp >> 1][half_id][i * 4 + q][lane] = quad[i][q];
+                }
+            }
+            switch (warp >> 1) {   // the two warps of the pair meet at a barrier of their own (a constant id each)
+                case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+                case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+                case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+                default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+            }
+            float p[2][4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) p[a][k] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int i = j % HB;
+                const bool mine = (j / HB) == half_id;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float other = s_quads[warp >> 1][half_id ^ 1][i * 4 + k][lane];
+                    p[j & 1][k] = __fadd_rn(p[j & 1][k], mine ? quad[i][k] : other);
+                }
+            }
+            const float inv = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
+                                                       : inv_rms(row_tree_256(p, lane), COLS, eps);
+            const f32x2 inv2 = f2_splat(inv);
+#pragma unroll
+            for (int i = 0; i < HB; ++i) {
+                const int j = half_id * HB + i;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 w = s_w[(4 * j + q) * 32 + lane];
+                    v[i][2 * q] = f2_mul(f2_mul(v[i][2 * q], inv2), make_float2(w.x, w.y));
+                    v[i][2 * q + 1] = f2_mul(f2_mul(v[i][2 * q + 1], inv2), make_float2(w.z, w.w));
+                }
+                uint32_t stored, lo, hi;
+                const bool ok = quantise16_qp<false, true>(v[i], global_scale, s_inv, stored, lo, hi);
+                const int b = lane + 32 * j;
+                *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(lo, hi);
+                srow[(size_t)(b >> 2) * chunk + (b & 3)] = (uint8_t)stored;
+                if (!ok) {   // rare: the literal path overwrites what the fast path stored
+                    rms_block_cold_f32(xrow + b * 16, weight + b * 16, inv, global_scale, reinterpret_cast<uint2*>(prow + b * 8),
+                                       srow + (size_t)(b >> 2) * chunk + (b & 3));
                 }
             }
         }

@@ -128,7 +128,7 @@ def test_rms_norm_quantise_tail_round_shared_by_warp_pairs(rows, cols):
     x[-3] = adversarial_bf16_matrix(rng, 1, cols)[0]          # non-finite, denormal and tie blocks in the last rows
     x[-40] = adversarial_bf16_matrix(rng, 1, cols)[0]
     w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
-    dx, dw = dev_bf16(x), torch.from_numpy(w).cuda()
+    dx, dw, xf32 = dev_bf16(x), torch.from_numpy(w).cuda(), dev_f32_from_bits(x)
     for gs in (80.0, 0.02):                                    # 0.02: subnormal scale codes, the literal path
         got_p, got_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(dx), ptr(dw)], [rows, cols, 1e-6, gs, 128, 512, BF16])
         normed = ref_gpu.rms_norm(dev_f32_from_bits(x), dw, rows, cols, 1e-6)
@@ -136,6 +136,10 @@ def test_rms_norm_quantise_tail_round_shared_by_warp_pairs(rows, cols):
         torch.cuda.synchronize()
         assert_bytes_equal(got_s, ref_s.cpu().numpy(), f"scales vs reference chain (global scale {gs})")
         assert_bytes_equal(got_p, ref_p.cpu().numpy(), f"packed vs reference chain (global scale {gs})")
+        # the tuned f32 kernel has the same tail round
+        f_p, f_s = run_quant("clef_rms_norm_quantise_nvfp4", rows, cols, [ptr(xf32), ptr(dw)], [rows, cols, 1e-6, gs, 128, 512, 1])
+        assert_bytes_equal(f_s, ref_s.cpu().numpy(), f"f32 activations: scales vs reference chain (global scale {gs})")
+        assert_bytes_equal(f_p, ref_p.cpu().numpy(), f"f32 activations: packed vs reference chain (global scale {gs})")
 
 
 def test_rms_norm_quantise_f32_on_arbitrary_f32_rows():
