@@ -104,6 +104,15 @@ inline unsigned clamp_grid(size_t wanted, size_t cap) {
     return (unsigned)(g < 1 ? 1 : g);
 }
 
+// A grid for `wanted` CTA-sized pieces on `cap` resident CTAs in which every CTA runs the same number of rounds:
+// ceil(wanted / rounds) CTAs with rounds = ceil(wanted / cap), instead of `cap` CTAs whose last round is part empty.
+// For kernels with many resident CTAs per SM (an SM then holds one CTA fewer at most).
+inline unsigned balanced_grid(size_t wanted, size_t cap) {
+    if (wanted <= cap || cap == 0) return clamp_grid(wanted, cap);
+    const size_t rounds = (wanted + cap - 1) / cap;
+    return (unsigned)((wanted + rounds - 1) / rounds);
+}
+
 inline int check_launch(const char* what) {
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

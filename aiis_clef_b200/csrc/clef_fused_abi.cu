@@ -718,7 +718,7 @@ int clef_rope(clef_stream_t stream, void* out, const void* x, const float* cos_t
         const int per_sm = ctas_per_sm(rope_hot_kernel<false, false>, 0, occ);
         const size_t ctas = (hot_items + kCtaThreads - 1) / kCtaThreads, cap = (size_t)dev.sms * per_sm;
         auto kernel = rope_launch_is_short(ctas, cap) ? rope_hot_kernel<false, true> : rope_hot_kernel<false, false>;
-        launch_hot(kernel, clamp_grid(ctas, cap), 0, s, (uint16_t*)out, (const uint16_t*)x, cos_table, sin_table,
+        launch_hot(kernel, balanced_grid(ctas, cap), 0, s, (uint16_t*)out, (const uint16_t*)x, cos_table, sin_table,
                    (uint32_t)hot_items, heads, head_dim, rotary_dim, (const int*)seq_start, (const int*)pos_base,
                    (const int*)pos_map, make_fast_div((uint32_t)(head_dim / 32)), make_fast_div((uint32_t)heads), KvCacheDest{});
         return check_launch(what);

@@ -174,7 +174,7 @@ static int rope_qkv_impl(const char* what, clef_stream_t stream, void* q_out, co
                    rope_launch_is_short(ctas, (size_t)dev.sms * 6)) {   // the engine's case: a pass of at most 8,192 rows, positions from its map
             static std::atomic<int> occ{0};
             const int per_sm = ctas_per_sm(rope_qk_map_hot_kernel, 0, occ);
-            launch_hot(rope_qk_map_hot_kernel, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, as_stream(stream), segs, cos_table,
+            launch_hot(rope_qk_map_hot_kernel, balanced_grid(ctas, (size_t)dev.sms * per_sm), 0, as_stream(stream), segs, cos_table,
                        sin_table, head_dim, rotary_dim, (const int*)pos_map, make_fast_div((uint32_t)per_row));
         } else {
             static std::atomic<int> occ{0};
