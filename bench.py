@@ -117,7 +117,7 @@ DOMINANT = "swiglu_quantise_nvfp4"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel at 8,192 rows: read from a small
 # text file under profiles/ that also records a hash of the kernel sources it was measured on.
 TRAFFIC_FILE = ROOT / "profiles" / "swiglu_quantise_nvfp4_8192rows_dram_traffic.txt"
-KERNEL_SOURCES = ["kernels_hot.cuh", "nvfp4_codec.cuh", "common.cuh", "f32x2.cuh"]
+KERNEL_SOURCES = ["kernels_hot.cuh", "nvfp4_codec.cuh", "common.cuh", "f32x2.cuh", "silu_forms.cuh"]
 
 
 def measured_peak_gbs():
