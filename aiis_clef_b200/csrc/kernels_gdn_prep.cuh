@@ -546,14 +546,14 @@ gdn_prep_kernel(const typename T::storage* __restrict__ mixed, float* __restrict
 // gdn_conv_prep (kernels/gdn_chunk.cu:1008-1172): the causal convolution + silu and gdn_prep above in one launch, the
 // convolved row staying in f32 (as in the reference, whose stage is shared memory) instead of going through memory.
 // One warp owns a strip of R tokens x one 128-channel group: a q head, a k head or a 128-value piece of v. A lane
-// convolves 4 adjacent channels exactly as causal_conv_silu_c4_kernel does; for a q or k head the row then goes
-// through 512 bytes of shared memory once so that lane l can add the squares of p = l, l + 32, l + 64, l + 96 in
-// the reference's order, and each lane scales, splits and stores its own 4 adjacent values (8-byte stores into the
-// operand tiles). Tokens of the last chunk past `rows` are written as zeros.
-// Measured at 8,192 tokens x 8,192 channels: 214 us, the same as the two separate launches (72 + 141 us): the 32
-// values a lane carries between the phases hold the kernel at two CTAs per SM (126 registers), and 13 resident warps
-// per SM at 8 cycles per issued instruction leave both the issue slots and the memory system half idle. What the
-// fusion saves is the intermediate buffer and a launch, not time.
+// convolves 4 adjacent channels exactly as causal_conv_silu_c4_kernel does; a q or k head row is then parked in the
+// warp's 4 KiB stage of shared memory so that lane l can add the squares of p = l, l + 32, l + 64, l + 96 in the
+// reference's order, and each lane reads its own 4 adjacent values back to scale, split and store them (8-byte
+// stores into the operand tiles). Tokens of the last chunk past `rows` are written as zeros.
+// The strip's values are NOT carried in registers between the phases (a first version did: 126 registers, two CTAs
+// per SM, and with the literal path inlined into the unrolled row loop 100 M warp instructions and 214 us at 8,192
+// tokens x 8,192 channels, no faster than the two separate launches). In this form: 80 registers, three CTAs per SM,
+// 63 M instructions, 143.5 us against 69.0 + 134.5 us for the two launches.
 // ---------------------------------------------------------------------------------------------
 // A strip that is not plain (it holds a sequence start, the first rows, or pad tokens of the last chunk), out of line:
 // every tap tested, the literal silu; a q or k row goes to the stage, a v row straight out.

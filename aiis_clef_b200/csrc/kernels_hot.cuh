@@ -257,7 +257,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
     auto source_row = [&](int r) { return x + (size_t)(EMBED ? __ldg(ids + r) : r) * COLS; };
     // Tail balance (plain form): when the last round of rows would occupy at most half of the grid's warps, its rows
     // are handled by PAIRS of warps, half a row each (see the tail block below), so the round takes about half as long.
-    // At 8,192 rows the grid's 2,368 warps run three full rounds and 1,088 rows are left: 9.45 -> 8.9 us.
+    // At 8,192 rows the grid's 2,368 warps run three full rounds and 1,088 rows are left: 9.45 -> 8.74 us.
     constexpr bool PAIR = !ADD && !EMBED;
     const int grid_warps = gridDim.x * 8;
     const int tail_base = (rows_total / grid_warps) * grid_warps;
