@@ -44,41 +44,47 @@ def check(p0, s0, p1, s1, rows, cols, tile_m):
 
 @pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("tile_m", [128, 192])
+@pytest.mark.parametrize("f32", [False, True], ids=["bf16", "f32"])
 @pytest.mark.parametrize("rows,cols", [(7, 2048), (778, 2048), (300, 4096), (129, 512), (65, 1088)])
-def test_rms_norm_and_plain_quantiser(rows, cols, tile_m, choice):
+def test_rms_norm_and_plain_quantiser(rows, cols, tile_m, choice, f32):
     clef.set_kernel_choice(choice)
     dev = clef.Device(0)
     rng = np.random.default_rng(rows + cols + tile_m)
-    x = dev_bf16(normal_bf16(rng, (rows, cols), outlier_channels=3))
+    as_dev = (lambda bits: dev_bf16(bits).float()) if f32 else dev_bf16
+    x = as_dev(normal_bf16(rng, (rows, cols), outlier_channels=3))
     w = torch.from_numpy((rng.standard_normal(cols) * 0.1).astype(np.float32)).cuda()
     check(*both_layouts(lambda: dev.rms_norm_quantise_nvfp4_dev(x, w, rows, cols, 1e-6, 64.0, tile_m)), rows, cols, tile_m)
     check(*both_layouts(lambda: dev.quantise_nvfp4_dev(x, rows, cols, 3.0, tile_m)), rows, cols, tile_m)
-    b = dev_bf16(normal_bf16(rng, (rows, cols)))
+    b = as_dev(normal_bf16(rng, (rows, cols)))
     check(*both_layouts(lambda: dev.add_rms_norm_quantise_nvfp4_dev(x, b, w, rows, cols, 1e-6, 64.0, tile_m)[1:]), rows, cols, tile_m)
 
 
 @pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("tile_m", [128, 192])
+@pytest.mark.parametrize("f32", [False, True], ids=["bf16", "f32"])
 @pytest.mark.parametrize("rows,cols", [(5, 6144), (778, 1024), (130, 576)])
-def test_swiglu_and_sigmoid_mul(rows, cols, tile_m, choice):
+def test_swiglu_and_sigmoid_mul(rows, cols, tile_m, choice, f32):
     clef.set_kernel_choice(choice)
     dev = clef.Device(0)
     rng = np.random.default_rng(rows * cols + tile_m)
-    g = dev_bf16(to_bf16_bits((rng.standard_normal((rows, cols)) * 2).astype(np.float32)))
-    u = dev_bf16(normal_bf16(rng, (rows, cols)))
+    as_dev = (lambda bits: dev_bf16(bits).float()) if f32 else dev_bf16
+    g = as_dev(to_bf16_bits((rng.standard_normal((rows, cols)) * 2).astype(np.float32)))
+    u = as_dev(normal_bf16(rng, (rows, cols)))
     check(*both_layouts(lambda: dev.swiglu_quantise_nvfp4_dev(g, u, rows, cols, 48.0, tile_m)), rows, cols, tile_m)
     check(*both_layouts(lambda: dev.sigmoid_mul_quantise_nvfp4_dev(u, g, rows, cols, 48.0, tile_m)), rows, cols, tile_m)
 
 
 @pytest.mark.parametrize("choice", [0, 1], ids=["tuned", "general"])
 @pytest.mark.parametrize("tile_m", [128, 192])
+@pytest.mark.parametrize("f32", [False, True], ids=["bf16", "f32"])
 @pytest.mark.parametrize("tokens,vh", [(7, 16), (300, 16), (129, 32)])
-def test_gated_norm(tokens, vh, tile_m, choice):
+def test_gated_norm(tokens, vh, tile_m, choice, f32):
     clef.set_kernel_choice(choice)
     dev = clef.Device(0)
     rng = np.random.default_rng(tokens * vh + tile_m)
-    o = dev_bf16(normal_bf16(rng, (tokens * vh, 128)))
-    z = dev_bf16(normal_bf16(rng, (tokens * vh, 128)))
+    as_dev = (lambda bits: dev_bf16(bits).float()) if f32 else dev_bf16
+    o = as_dev(normal_bf16(rng, (tokens * vh, 128)))
+    z = as_dev(normal_bf16(rng, (tokens * vh, 128)))
     w = torch.from_numpy((1.0 + rng.standard_normal(128) * 0.1).astype(np.float32)).cuda()
     p0, s0, p1, s1 = both_layouts(lambda: dev.rms_norm_gated_quantise_nvfp4_dev(o, z, w, tokens * vh, 128, vh, 1e-6, 96.0, tile_m))
     check(p0, s0, p1, s1, tokens, vh * 128, tile_m)
