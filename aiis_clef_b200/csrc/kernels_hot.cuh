@@ -258,7 +258,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
     // Tail balance (plain form): when the last round of rows would occupy at most half of the grid's warps, its rows
     // are handled by PAIRS of warps, half a row each (see the tail block below), so the round takes about half as long.
     // At 8,192 rows the grid's 2,368 warps run three full rounds and 1,088 rows are left: 9.45 -> 8.74 us.
-    constexpr bool PAIR = !ADD && !EMBED;
+    constexpr bool PAIR = true;   // every form: the plain one prefetches its half row, the fused producers load it in the tail block
     const int grid_warps = gridDim.x * 8;
     const int tail_base = (rows_total / grid_warps) * grid_warps;
     const bool pair_mode = PAIR && rows_total > tail_base && 2 * (rows_total - tail_base) <= grid_warps;
@@ -281,7 +281,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
         for (int j = 0; j < NB; ++j) {
             d[j] = ldg_stream_v8(src + (size_t)(lane + 32 * j) * 16);
         }
-    } else if (PAIR && pair_mode && row >= main_end) {
+    } else if (!ADD && !EMBED && pair_mode && row >= main_end) {
         fetch_tail_half();
     }
     __syncthreads();
@@ -347,7 +347,7 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
             for (int j = 0; j < NB; ++j) {
                 d[j] = ldg_stream_v8(next_src + (size_t)(lane + 32 * j) * 16);
             }
-        } else if (PAIR && pair_mode && next >= main_end) {
+        } else if (!ADD && !EMBED && pair_mode && next >= main_end) {
             fetch_tail_half();
         }
         const float inv = (COLS & (COLS - 1)) == 0 ? inv_rms_pow2<COLS>(row_tree_256(p, lane), eps)
@@ -402,9 +402,25 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
         } else {
             f32x2 v[HB][8];
             float quad[HB][4];
+            if (ADD || EMBED) {   // no row-ahead prefetch in these forms: this warp's half row is loaded here
+                const uint16_t* src = source_row(tail_row);
+#pragma unroll
+                for (int i = 0; i < HB; ++i) d[i] = ldg_stream_v8(src + (size_t)(lane + 32 * (half * HB + i)) * 16);
+            }
 #pragma unroll
             for (int i = 0; i < HB; ++i) {
+                const size_t off = (size_t)tail_row * COLS + (size_t)(lane + 32 * (half * HB + i)) * 16;
+                if (EMBED) stg_v8(sum_out + off, d[i]);   // the gathered row
                 unpack16_quadpairs(d[i], v[i]);
+                if (ADD) {   // the stored (rounded) sum is what the norm sees, as in the main loop
+                    f32x2 t[8];
+                    unpack16_quadpairs(ldg_stream_v8(addend + off), t);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[i][e] = f2_add(v[i][e], t[e]);
+                    const U8x32 sum = pack16_bf16(v[i]);
+                    stg_v8(sum_out + off, sum);
+                    unpack16_quadpairs(sum, v[i]);
+                }
                 quad_squares(v[i], quad[i]);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) s_quads[warp >> 1][half][i * 4 + k][lane] = quad[i][k];
@@ -449,8 +465,9 @@ rms_norm_quant_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
                 *reinterpret_cast<uint2*>(prow + b * 8) = make_uint2(lo, hi);
                 srow[(size_t)(b >> 2) * chunk + (b & 3)] = (uint8_t)stored;
                 if (!ok) {   // rare: the literal path overwrites what the fast path stored
-                    rms_block_cold(x + (size_t)tail_row * COLS + b * 16, weight + b * 16, inv, global_scale,
-                                   reinterpret_cast<uint2*>(prow + b * 8), srow + (size_t)(b >> 2) * chunk + (b & 3));
+                    // ADD, EMBED: this lane stored the block's row above, so it reads its own bytes back.
+                    rms_block_cold(((ADD || EMBED) ? (const uint16_t*)sum_out : x) + (size_t)tail_row * COLS + b * 16, weight + b * 16,
+                                   inv, global_scale, reinterpret_cast<uint2*>(prow + b * 8), srow + (size_t)(b >> 2) * chunk + (b & 3));
                 }
             }
         }
