@@ -986,7 +986,12 @@ def other_configurations(h: Harness, shared, launchers, sets):
     proto32 = make_f32_set(h, sets[0])
     ms32, sets32 = time_each_kernel(h, make_launchers(h, shared32, code=1), proto32, 24, F32_BYTES_PER_ROW)
     out["f32_activations"] = {"ms": ms32, "sets": sets32}
-    del proto32, shared32
+    # the step itself on f32 activations: the three kernels in layer order, one graph per rotating buffer set
+    launch32 = make_launchers(h, shared32, code=1)
+    sets_f32 = [proto32] + [make_f32_set(h, sets[i]) for i in (1, 2)]
+    graphs = [h.capture([lambda d=d, n=n: launch32[n](d) for n in STEP_KERNELS]) for d in sets_f32]
+    out["f32_step_ms"] = float(np.median(h.time_graphs(graphs, 60))) / 60
+    del graphs, sets_f32, proto32, shared32
     return out
 
 
@@ -1006,8 +1011,15 @@ def summarise_extras(extras, peak):
         gb = F32_BYTES_PER_ROW[name] * ROWS / (ms * 1e-3) / 1e9
         f32[name] = {"us": round(ms * 1e3, 2), "GBs": round(gb, 1), "frac_of_measured_peak": round(gb / peak, 4),
                      "bytes_per_row": F32_BYTES_PER_ROW[name], "sets": extras["f32_activations"]["sets"][name]}
+    f32_step_bytes = sum(F32_BYTES_PER_ROW[k] for k in STEP_KERNELS) * ROWS
+    f32_step_gbs = f32_step_bytes / (extras["f32_step_ms"] * 1e-3) / 1e9
     return {
         "f32_activation_kernels_8192_rows": f32,
+        "f32_activation_step_8192_rows": {
+            "us_per_step": round(extras["f32_step_ms"] * 1e3, 2), "rows_per_s": ROWS / (extras["f32_step_ms"] * 1e-3),
+            "GBs": round(f32_step_gbs, 1), "frac_of_measured_peak": round(f32_step_gbs / peak, 4), "bytes_per_step": f32_step_bytes,
+            "note": "the headline step's three launches on f32 activations (the reference engine's own type), one graph per "
+                    "rotating buffer set, median of 5 batches of 60 replays"},
         "gated_chain_32768_rows_in_four_chunks": {
             "us_per_8192_row_chunk": round(g["ms_per_chunk"] * 1e3, 2), "ms_per_32768_rows": round(4 * g["ms_per_chunk"], 4),
             "rows_per_s": ROWS / (g["ms_per_chunk"] * 1e-3), "GBs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4)},
