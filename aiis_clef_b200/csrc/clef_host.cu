@@ -520,6 +520,117 @@ int clef_host_rms_norm_gated_quantise_nvfp4(clef_device* dev, const void* x, con
                      });
 }
 
+// ---- the reference's plain host-slice wrappers (src/cuda/mod.rs:853-973) ---------------------------------
+
+int clef_host_rms_norm(clef_device* dev, const void* x, const float* weight, void* out, int rows, int cols, float eps,
+                       int dtype) {
+    const char* what = "clef_host_rms_norm";
+    if (int rc = check_handle(dev, what)) return rc;
+    if (dtype != CLEF_BF16 && dtype != CLEF_F32) return fail(CLEF_ERR_INVALID, "%s: dtype %d", what, dtype);
+    if (rows < 0 || cols <= 0 || cols % 4 != 0) return fail(CLEF_ERR_INVALID, "%s: rows %d, cols %d (cols must be a multiple of 4)", what, rows, cols);
+    if (!x || !out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (rows == 0) return CLEF_OK;
+    std::lock_guard<std::mutex> guard(dev->lock);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_rms_norm");
+    std::vector<void*> consts;
+    if (int rc = upload_consts(dev, {{weight, (size_t)cols * sizeof(float)}}, consts)) return rc;
+    const size_t row = (size_t)cols * elem_bytes(dtype);
+    std::vector<RowStream> in{{x, nullptr, row, 0}};
+    std::vector<RowStream> outs{{nullptr, out, row, 0}};
+    const int tile = pick_tile_rows(rows, 128, 2 * row);
+    return run_tiled(dev, rows, 1, tile, in, outs, false, [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
+        return clef_rms_norm(st, base + in[0].offset, (const float*)consts[0], base + outs[0].offset, n_live, cols, eps, dtype);
+    });
+}
+
+int clef_host_rms_norm_gated(clef_device* dev, const void* x, const void* gate, const float* weight, void* out, int rows,
+                             int cols, float eps, int dtype) {
+    const char* what = "clef_host_rms_norm_gated";
+    if (int rc = check_handle(dev, what)) return rc;
+    if (dtype != CLEF_BF16 && dtype != CLEF_F32) return fail(CLEF_ERR_INVALID, "%s: dtype %d", what, dtype);
+    if (rows < 0 || cols <= 0 || cols % 4 != 0) return fail(CLEF_ERR_INVALID, "%s: rows %d, cols %d (cols must be a multiple of 4)", what, rows, cols);
+    if (!x || !out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (rows == 0) return CLEF_OK;
+    std::lock_guard<std::mutex> guard(dev->lock);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_rms_norm_gated");
+    std::vector<void*> consts;
+    if (int rc = upload_consts(dev, {{weight, (size_t)cols * sizeof(float)}}, consts)) return rc;
+    const size_t row = (size_t)cols * elem_bytes(dtype);
+    std::vector<RowStream> in{{x, nullptr, row, 0}};
+    if (gate) in.push_back({gate, nullptr, row, 0});
+    std::vector<RowStream> outs{{nullptr, out, row, 0}};
+    const int tile = pick_tile_rows(rows, 128, (gate ? 3 : 2) * row);
+    return run_tiled(dev, rows, 1, tile, in, outs, false, [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
+        return clef_rms_norm_gated(st, base + in[0].offset, gate ? base + in[1].offset : nullptr, (const float*)consts[0],
+                                   base + outs[0].offset, n_live, cols, eps, dtype);
+    });
+}
+
+int clef_host_swiglu(clef_device* dev, const void* gate, const void* up, void* out, size_t total, int dtype) {
+    const char* what = "clef_host_swiglu";
+    if (int rc = check_handle(dev, what)) return rc;
+    if (dtype != CLEF_BF16 && dtype != CLEF_F32) return fail(CLEF_ERR_INVALID, "%s: dtype %d", what, dtype);
+    if (total % 4 != 0) return fail(CLEF_ERR_INVALID, "%s: total %zu must be a multiple of 4", what, total);
+    if (!gate || !up || !out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (total == 0) return CLEF_OK;
+    // the flat arrays are cut into "rows" of the largest power of two up to 4,096 values that divides their length
+    size_t width = 4;
+    while (width < 4096 && total % (2 * width) == 0) width *= 2;
+    if (total / width > 0x7fffffffull) return fail(CLEF_ERR_TOO_LARGE, "%s: %zu values", what, total);
+    const int rows = (int)(total / width);
+    std::lock_guard<std::mutex> guard(dev->lock);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_swiglu");
+    const size_t row = width * elem_bytes(dtype);
+    std::vector<RowStream> in{{gate, nullptr, row, 0}, {up, nullptr, row, 0}};
+    std::vector<RowStream> outs{{nullptr, out, row, 0}};
+    const int tile = pick_tile_rows(rows, 128, 3 * row);
+    return run_tiled(dev, rows, 1, tile, in, outs, false, [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
+        return clef_swiglu(st, base + in[0].offset, base + in[1].offset, base + outs[0].offset, (size_t)n_live * width, dtype);
+    });
+}
+
+int clef_host_causal_conv_silu(clef_device* dev, const void* x, const float* w, void* out, int rows, int channels, int k,
+                               int dtype) {
+    const char* what = "clef_host_causal_conv_silu";
+    if (int rc = check_handle(dev, what)) return rc;
+    if (dtype != CLEF_BF16 && dtype != CLEF_F32) return fail(CLEF_ERR_INVALID, "%s: dtype %d", what, dtype);
+    if (rows < 0 || channels <= 0 || k <= 0) return fail(CLEF_ERR_INVALID, "%s: rows %d channels %d k %d", what, rows, channels, k);
+    if (!x || !w || !out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (rows == 0) return CLEF_OK;
+    std::lock_guard<std::mutex> guard(dev->lock);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_causal_conv_silu");
+    std::vector<void*> consts;
+    if (int rc = upload_consts(dev, {{w, (size_t)channels * k * sizeof(float)}}, consts)) return rc;
+    // a row's taps reach k - 1 rows back, so the sequence goes through as ONE tile (a single sequence without history,
+    // as Device::causal_conv_silu runs it)
+    const size_t row = (size_t)channels * elem_bytes(dtype);
+    std::vector<RowStream> in{{x, nullptr, row, 0}};
+    std::vector<RowStream> outs{{nullptr, out, row, 0}};
+    return run_tiled(dev, rows, 1, rows, in, outs, false, [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
+        return clef_causal_conv_silu(st, base + outs[0].offset, base + in[0].offset, (const float*)consts[0], n_live, channels, k,
+                                     nullptr, nullptr, nullptr, dtype);
+    });
+}
+
+int clef_host_rope_tables(clef_device* dev, const int32_t* positions, float* cos_out, float* sin_out, int count,
+                          int rotary_dim, float theta) {
+    const char* what = "clef_host_rope_tables";
+    if (int rc = check_handle(dev, what)) return rc;
+    if (count < 0 || rotary_dim <= 0 || rotary_dim % 2 != 0) return fail(CLEF_ERR_INVALID, "%s: count %d rotary_dim %d", what, count, rotary_dim);
+    if (!positions || !cos_out || !sin_out) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (count == 0) return CLEF_OK;
+    std::lock_guard<std::mutex> guard(dev->lock);
+    CLEF_DEVICE_SCOPE(dev, "clef_host_rope_tables");
+    const size_t row = (size_t)rotary_dim * sizeof(float);
+    std::vector<RowStream> in{{positions, nullptr, sizeof(int32_t), 0}};
+    std::vector<RowStream> outs{{nullptr, cos_out, row, 0}, {nullptr, sin_out, row, 0}};
+    const int tile = pick_tile_rows(count, 128, 2 * row + 4);
+    return run_tiled(dev, count, 1, tile, in, outs, false, [&](cudaStream_t st, char* base, int, int n_live, int) -> int {
+        return clef_rope_tables(st, (const int32_t*)(base + in[0].offset), (float*)(base + outs[0].offset),
+                                (float*)(base + outs[1].offset), n_live, rotary_dim, theta);
+    });
+}
+
 int clef_host_rope(clef_device* dev, void* out, const void* x, const float* cos_table, const float* sin_table,
                    int table_rows, int rows, int heads, int head_dim, int rotary_dim, const int32_t* pos_map,
                    int dtype) {

@@ -617,6 +617,11 @@ HOST_SYMBOLS = {
     "clef_host_swiglu_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I]),
     "clef_host_rms_norm_gated_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _I, _I]),
     "clef_host_rope": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I]),
+    "clef_host_rms_norm": (_I, [_P, _P, _P, _P, _I, _I, _F, _I]),
+    "clef_host_rms_norm_gated": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I]),
+    "clef_host_swiglu": (_I, [_P, _P, _P, _P, _SZ, _I]),
+    "clef_host_causal_conv_silu": (_I, [_P, _P, _P, _P, _I, _I, _I, _I]),
+    "clef_host_rope_tables": (_I, [_P, _P, _P, _P, _I, _I, _F]),
     "clef_pass_maps_build": (_I, [ctypes.POINTER(_ChunkSpec), _SZ, _SZ, _I, _SZ, _SZ, ctypes.POINTER(_PassMaps)]),
     "clef_pass_geometries": (_I, [_SZ, _SZ, ctypes.POINTER(_SZ), _SZ]),
     "clef_rungs_decompose": (_I, [_SZ, _SZ, _SZ, ctypes.POINTER(_SZ), ctypes.POINTER(_SZ), _SZ]),
@@ -808,6 +813,27 @@ class HostDevice:
                                                                 rows, cols, vh, eps, global_scale, tile_m,
                                                                 self._code(x)),
                "clef_host_rms_norm_gated_quantise_nvfp4")
+
+    # -- the reference's plain host-slice wrappers, src/cuda/mod.rs:853-973 ------------------------------------
+    def rms_norm(self, x, weight, out, rows, cols, eps):
+        _check(self.lib.clef_host_rms_norm(self.handle, self._hp(x), self._hp(weight), self._hp(out), rows, cols, eps,
+                                           self._code(x)), "clef_host_rms_norm")
+
+    def rms_norm_gated(self, x, gate, weight, out, rows, cols, eps):
+        _check(self.lib.clef_host_rms_norm_gated(self.handle, self._hp(x), self._hp(gate), self._hp(weight), self._hp(out), rows,
+                                                 cols, eps, self._code(x)), "clef_host_rms_norm_gated")
+
+    def swiglu(self, gate, up, out, total):
+        _check(self.lib.clef_host_swiglu(self.handle, self._hp(gate), self._hp(up), self._hp(out), total, self._code(gate)),
+               "clef_host_swiglu")
+
+    def causal_conv_silu(self, x, w, out, rows, channels, k):
+        _check(self.lib.clef_host_causal_conv_silu(self.handle, self._hp(x), self._hp(w), self._hp(out), rows, channels, k,
+                                                   self._code(x)), "clef_host_causal_conv_silu")
+
+    def rope_tables(self, positions, cos_out, sin_out, count, rotary_dim, theta):
+        _check(self.lib.clef_host_rope_tables(self.handle, self._hp(positions), self._hp(cos_out), self._hp(sin_out), count,
+                                              rotary_dim, theta), "clef_host_rope_tables")
 
     def rope(self, out, x, cos, sin, table_rows, rows, heads, head_dim, rotary_dim, pos_map=None):
         _check(self.lib.clef_host_rope(self.handle, self._hp(out), self._hp(x), self._hp(cos), self._hp(sin),

@@ -74,6 +74,21 @@ int clef_host_swiglu_quantise_nvfp4(clef_device* dev, const void* gate, const vo
 int clef_host_rms_norm_gated_quantise_nvfp4(clef_device* dev, const void* x, const void* gate, const float* weight,
                                             uint8_t* packed, uint8_t* scales, int rows, int cols, int vh, float eps,
                                             float global_scale, int tile_m, int dtype);
+/* Device::rms_norm (src/cuda/mod.rs:853-879): out = x * inv_rms * (1 + weight); weight may be NULL (no weight). */
+int clef_host_rms_norm(clef_device* dev, const void* x, const float* weight, void* out, int rows, int cols, float eps,
+                       int dtype);
+/* Device::rms_norm_gated (src/cuda/mod.rs:881-909): out = x * inv_rms * weight * silu(gate); gate and weight may be
+ * NULL as in the kernel. */
+int clef_host_rms_norm_gated(clef_device* dev, const void* x, const void* gate, const float* weight, void* out, int rows,
+                             int cols, float eps, int dtype);
+/* Device::swiglu (src/cuda/mod.rs:911-933): out = silu(gate) * up over flat arrays of `total` values (a multiple of 4). */
+int clef_host_swiglu(clef_device* dev, const void* gate, const void* up, void* out, size_t total, int dtype);
+/* Device::causal_conv_silu (src/cuda/mod.rs:935-945): one sequence of `rows` tokens without history, w [channels, k]. */
+int clef_host_causal_conv_silu(clef_device* dev, const void* x, const float* w, void* out, int rows, int channels, int k,
+                               int dtype);
+/* Device::rope_tables (src/cuda/mod.rs:947-973): cos_out, sin_out [count, rotary_dim] for the given positions. */
+int clef_host_rope_tables(clef_device* dev, const int32_t* positions, float* cos_out, float* sin_out, int count,
+                          int rotary_dim, float theta);
 /* pos_map may be NULL (position = row index), as in Device::rope_apply. cos/sin: [table_rows, rotary_dim]. */
 int clef_host_rope(clef_device* dev, void* out, const void* x, const float* cos_table, const float* sin_table,
                    int table_rows, int rows, int heads, int head_dim, int rotary_dim, const int32_t* pos_map,

@@ -179,3 +179,57 @@ def test_table_uploaded_through_the_handle_then_gathered_over_several_tiles(host
             assert_bytes_equal(back.numpy(), want.reshape(-1), "download of the uploaded table")
         finally:
             host_dev.set_pipelined(False)
+
+
+@pytest.mark.parametrize("f32", [True, False], ids=["f32", "bf16"])
+def test_plain_host_wrappers_equal_the_device_entry_points(host_dev, f32):
+    """Device::{rms_norm, rms_norm_gated, swiglu, causal_conv_silu, rope_tables} as host-slice calls
+    (src/cuda/mod.rs:853-973): host arrays in, host arrays out, byte for byte what the device-resident entry points
+    give on the same values (those are compared with the reference kernels in test_gpu_parity_elem.py and
+    test_gpu_gdn_prep.py); several row tiles on both streams, optional operands absent."""
+    dev = clef.Device(0)
+    rng = np.random.default_rng(5 + int(f32))
+    as_host = (lambda bits: orc.bits_to_torch_bf16(bits).float().numpy()) if f32 else (lambda bits: bits)
+    as_dev = (lambda bits: dev_bf16(bits).float()) if f32 else dev_bf16
+    out_like = lambda a: np.empty_like(a)
+    same = lambda got, want, what: assert_bytes_equal(got.view(np.uint8).reshape(-1), want.contiguous().cpu().view(torch.uint8).numpy().reshape(-1), what)
+    # rms_norm: 20,000 x 2048 is several tiles
+    rows, cols = 20000, 2048
+    xb = normal_bf16(rng, (rows, cols), outlier_channels=4)
+    w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
+    x, out = as_host(xb), out_like(as_host(xb))
+    host_dev.rms_norm(x, w, out, rows, cols, 1e-6)
+    same(out, dev.rms_norm_dev(as_dev(xb), torch.from_numpy(w).cuda(), rows, cols, 1e-6), "host rms_norm")
+    host_dev.rms_norm(x, None, out, rows, cols, 1e-6)
+    same(out, dev.rms_norm_dev(as_dev(xb), None, rows, cols, 1e-6), "host rms_norm without weight")
+    # rms_norm_gated over head rows
+    rows, cols = 1300 * 16, 128
+    xb, gb = normal_bf16(rng, (rows, cols)), normal_bf16(rng, (rows, cols))
+    wg = (1.0 + rng.standard_normal(cols) * 0.1).astype(np.float32)
+    x, g, out = as_host(xb), as_host(gb), out_like(as_host(xb))
+    host_dev.rms_norm_gated(x, g, wg, out, rows, cols, 1e-6)
+    same(out, dev.rms_norm_gated_dev(as_dev(xb), as_dev(gb), torch.from_numpy(wg).cuda(), rows, cols, 1e-6), "host rms_norm_gated")
+    host_dev.rms_norm_gated(x, None, wg, out, rows, cols, 1e-6)
+    same(out, dev.rms_norm_gated_dev(as_dev(xb), None, torch.from_numpy(wg).cuda(), rows, cols, 1e-6), "host rms_norm_gated without gate")
+    # swiglu on flat arrays whose length is not a multiple of a large power of two
+    total = 4 * 1234567
+    gb, ub = normal_bf16(rng, (total,)), normal_bf16(rng, (total,))
+    g, u, out = as_host(gb), as_host(ub), out_like(as_host(gb))
+    host_dev.swiglu(g, u, out, total)
+    same(out, dev.swiglu_dev(as_dev(gb), as_dev(ub), total), "host swiglu")
+    # causal convolution + silu of one sequence
+    rows, channels, k = 777, 1024, 4
+    xb = normal_bf16(rng, (rows, channels))
+    wc = (rng.standard_normal((channels, k)) * 0.5).astype(np.float32)
+    x, out = as_host(xb), out_like(as_host(xb))
+    host_dev.causal_conv_silu(x, wc, out, rows, channels, k)
+    same(out, dev.causal_conv_silu_dev(as_dev(xb), torch.from_numpy(wc).cuda(), rows, channels, k), "host causal_conv_silu")
+    # rope tables
+    if f32:
+        count, rot = 70000, 64
+        pos = rng.integers(0, 1 << 20, count).astype(np.int32)
+        cos, sin = np.empty((count, rot), np.float32), np.empty((count, rot), np.float32)
+        host_dev.rope_tables(pos, cos, sin, count, rot, 1e7)
+        want_c, want_s = dev.rope_tables_dev(torch.from_numpy(pos).cuda(), count, rot, 1e7)
+        same(cos, want_c, "host rope_tables cos")
+        same(sin, want_s, "host rope_tables sin")
