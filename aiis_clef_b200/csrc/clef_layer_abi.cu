@@ -394,6 +394,23 @@ int clef_sigmoid_mul_quantise_nvfp4_ex(clef_stream_t stream, const void* x, cons
     return clef_sigmoid_mul_quantise_nvfp4_impl(stream, x, gate, packed, scales, rows, cols, global_scale, blk_mn, chunk, dtype, sf_layout);
 }
 
+int clef_copy_bytes(clef_stream_t stream, void* dst, size_t dst_offset, const void* src, size_t src_offset, size_t bytes) {
+    const char* what = "clef_copy_bytes";
+    if (!dst || !src) return fail(CLEF_ERR_INVALID, "%s: null pointer", what);
+    if (bytes == 0) return CLEF_OK;
+    uint8_t* d = static_cast<uint8_t*>(dst) + dst_offset;
+    const uint8_t* s8 = static_cast<const uint8_t*>(src) + src_offset;
+    if (d < s8 + bytes && s8 < d + bytes) return fail(CLEF_ERR_INVALID, "%s: the ranges overlap", what);
+    DeviceInfo dev;
+    if (int r = device_info(dev)) return r;
+    static std::atomic<int> occ{0};
+    const int per_sm = ctas_per_sm(copy_bytes_kernel, 0, occ);
+    const size_t threads = (reinterpret_cast<uintptr_t>(d) ^ reinterpret_cast<uintptr_t>(s8)) & 31 ? bytes : bytes / 32 + 64;
+    launch_hot(copy_bytes_kernel, clamp_grid((threads + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0,
+               as_stream(stream), d, s8, bytes);
+    return check_launch(what);
+}
+
 int clef_add(clef_stream_t stream, void* out, const void* a, const void* b, size_t total, int dtype) {
     const char* what = "clef_add";
     if (int r = check_dtype(dtype, what)) return r;

@@ -198,4 +198,25 @@ add_hot_kernel(uint16_t* out, const uint16_t* a, const uint16_t* b, uint32_t blo
     }
 }
 
+// copy_kernel, copy_u8_kernel, copy_range_u8_kernel (kernels/elementwise.cu:317-342): device-to-device copies inside a
+// captured pass. One kernel for the three: 32 bytes per thread where both addresses allow, single bytes for a ragged
+// head and tail or for addresses that are not congruent modulo 32.
+static __global__ void __launch_bounds__(kCtaThreads)
+copy_bytes_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, size_t bytes) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const size_t tid = (size_t)blockIdx.x * kCtaThreads + threadIdx.x, step = (size_t)gridDim.x * kCtaThreads;
+    const uintptr_t da = reinterpret_cast<uintptr_t>(dst), sa = reinterpret_cast<uintptr_t>(src);
+    if (((da ^ sa) & 31) != 0) {   // not congruent: bytes
+        for (size_t i = tid; i < bytes; i += step) dst[i] = src[i];
+        return;
+    }
+    size_t head = (32 - (da & 31)) & 31;
+    if (head > bytes) head = bytes;
+    const size_t chunks = (bytes - head) / 32, tail = head + chunks * 32;
+    if (tid < head) dst[tid] = src[tid];
+    for (size_t c = tid; c < chunks; c += step) stg_v8(dst + head + c * 32, ldg_stream_v8(src + head + c * 32));
+    if (tail + tid < bytes) dst[tail + tid] = src[tail + tid];   // fewer than 32 bytes
+}
+
 }  // namespace clef

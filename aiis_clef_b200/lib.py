@@ -55,6 +55,7 @@ SYMBOLS = {
     "clef_qk_norm_rope_kv_write": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _I]),
     "clef_sigmoid_mul": (_I, [_P, _P, _P, _P, _SZ, _I]),
     "clef_sigmoid_mul_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I]),
+    "clef_copy_bytes": (_I, [_P, _P, _SZ, _P, _SZ, _SZ]),
     "clef_add": (_I, [_P, _P, _P, _P, _SZ, _I]),
     "clef_add_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
     "clef_embed_rms_norm_quantise_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _I, _I]),
@@ -416,6 +417,12 @@ class Device:
         with torch.cuda.device(self.device):
             _check(self.lib.clef_add(_stream(), _ptr(out), _ptr(a), _ptr(b), total, _dtype_code(a)), "clef_add")
         return out
+
+    # -- src/cuda/mod.rs:4642-4720 (copy_into, copy_bytes_at, copy_bytes) ------------------------------------
+    def copy_bytes_dev(self, dst, dst_offset: int, src, src_offset: int, nbytes: int):
+        _dev_tensor(dst, "dst"), _dev_tensor(src, "src")
+        with torch.cuda.device(self.device):
+            _check(self.lib.clef_copy_bytes(_stream(), _ptr(dst), dst_offset, _ptr(src), src_offset, nbytes), "clef_copy_bytes")
 
     def add_rms_norm_quantise_nvfp4_dev(self, a, b, weight, rows: int, cols: int, eps: float, global_scale: float,
                                         tile_m: int, sum_out=None):

@@ -211,6 +211,12 @@ int clef_sigmoid_mul_quantise_nvfp4(clef_stream_t stream, const void* x, const v
                                     uint8_t* scales, int rows, int cols, float global_scale, int blk_mn, int chunk,
                                     int dtype);
 
+/* copy_kernel, copy_u8_kernel, copy_range_u8_kernel (kernels/elementwise.cu:317-342), Device::copy_into,
+ * Device::copy_bytes, Device::copy_bytes_at (src/cuda/mod.rs:4642-4720): `bytes` bytes from src + src_offset to
+ * dst + dst_offset, device to device, inside the pass's graph. Any alignment; the ranges must not overlap
+ * (copy_into of `values` f32 values is bytes = 4 * values). */
+int clef_copy_bytes(clef_stream_t stream, void* dst, size_t dst_offset, const void* src, size_t src_offset, size_t bytes);
+
 /* add_kernel (kernels/head.cu:117-129), Device::add_dev (src/cuda/mod.rs:1686-1704): out = a + b.
  * out may be a or b. */
 int clef_add(clef_stream_t stream, void* out, const void* a, const void* b, size_t total, int dtype);

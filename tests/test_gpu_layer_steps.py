@@ -451,3 +451,24 @@ def test_embed_rms_norm_quantise_equals_the_two_calls(tokens, hidden, vocab, dty
     pk.check_guards("packed")
     sc.check_guards("scales")
     assert np.array_equal(pk.bytes(), pk2.bytes()) and np.array_equal(sc.bytes(), sc2.bytes()) and torch.equal(h2, want_h)
+
+
+# ---- device-to-device copies inside a pass (copy_kernel, copy_u8_kernel, copy_range_u8_kernel) -------------------------
+@pytest.mark.parametrize("nbytes", [0, 1, 31, 32, 33, 4096, 100003, 8192 * 2048 * 2])
+@pytest.mark.parametrize("dst_off,src_off", [(0, 0), (32, 64), (5, 37), (7, 8), (1, 0), (16, 48)])
+def test_copy_bytes(nbytes, dst_off, src_off):
+    """clef_copy_bytes against a plain slice copy, for offsets that are congruent modulo 32 (the 32-byte path with a
+    ragged head and tail) and that are not (the byte path); the bytes either side of the destination range stay."""
+    gen = torch.Generator(device="cuda").manual_seed(nbytes + dst_off * 64 + src_off)
+    src = torch.randint(0, 256, (nbytes + src_off + 64,), device="cuda", generator=gen, dtype=torch.uint8)
+    dst = torch.full((nbytes + dst_off + 64,), 0xA5, device="cuda", dtype=torch.uint8)
+    clef.Device(0).copy_bytes_dev(dst, dst_off, src, src_off, nbytes)
+    torch.cuda.synchronize()
+    assert torch.equal(dst[dst_off:dst_off + nbytes], src[src_off:src_off + nbytes])
+    assert (dst[:dst_off] == 0xA5).all() and (dst[dst_off + nbytes:] == 0xA5).all()
+
+
+def test_copy_bytes_refuses_overlap():
+    buf = torch.zeros(1024, device="cuda", dtype=torch.uint8)
+    assert clef.load().clef_copy_bytes(stream(), ptr(buf), 0, ptr(buf), 16, 64) == -1
+    assert clef.load().clef_copy_bytes(stream(), ptr(buf), 0, ptr(buf), 64, 64) == 0
