@@ -56,33 +56,42 @@ int fp8_rows_impl(const char* what, int mode, clef_stream_t stream, const void* 
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
-    if (dtype == CLEF_BF16 && use_hot() && mode == kFp8RmsNorm && (cols == 2048 || cols == 4096) && aligned(a, 32) &&
+    if (use_hot() && mode == kFp8RmsNorm && (cols == 2048 || cols == 4096) && aligned(a, 32) &&
         aligned(out, 16) && (!bf_out || aligned(bf_out, 32))) {
         const size_t groups = ((size_t)rows + 7) / 8;
         const size_t smem = (size_t)cols * sizeof(float);
-#define CLEF_FP8_HOT(NB, MODE)                                                                                      \
+#define CLEF_FP8_HOT(NB, MODE, T)                                                                                   \
     {                                                                                                               \
         static std::atomic<int> occ{0};                                                                             \
-        const int per_sm = ctas_per_sm(fp8_rows_hot_kernel<NB, MODE>, smem, occ);                                   \
-        launch_hot(fp8_rows_hot_kernel<NB, MODE>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,            \
-                   (const uint16_t*)a, weight, out, scales, bf_out, rows, eps);                                     \
+        const int per_sm = ctas_per_sm(fp8_rows_hot_kernel<NB, MODE, T>, smem, occ);                                \
+        launch_hot(fp8_rows_hot_kernel<NB, MODE, T>, clamp_grid(groups, (size_t)dev.sms * per_sm), smem, s,         \
+                   (const Storage<T>*)a, weight, out, scales, bf_out, rows, eps);                                   \
     }
-        if (cols == 2048) CLEF_FP8_HOT(4, kFp8RmsNorm) else CLEF_FP8_HOT(8, kFp8RmsNorm)
+        if (dtype == CLEF_BF16) {
+            if (cols == 2048) CLEF_FP8_HOT(4, kFp8RmsNorm, Bf16) else CLEF_FP8_HOT(8, kFp8RmsNorm, Bf16)
+        } else {
+            if (cols == 2048) CLEF_FP8_HOT(4, kFp8RmsNorm, F32) else CLEF_FP8_HOT(8, kFp8RmsNorm, F32)
+        }
 #undef CLEF_FP8_HOT
         return check_launch(what);
     }
-    if (dtype == CLEF_BF16 && use_hot() && mode != kFp8RmsNorm && aligned(a, 32) && (!b || aligned(b, 32)) && aligned(out, 16)) {
+    if (use_hot() && mode != kFp8RmsNorm && aligned(a, 32) && (!b || aligned(b, 32)) && aligned(out, 16)) {
         // cols = 512 * WPR * BPL with BPL 3 or 4 blocks per lane and WPR 1, 2, 4 or 8 warps per row
         const int bpl = (cols % 1536 == 0) ? 3 : ((cols % 2048 == 0) ? 4 : 0);
         const int wpr = bpl ? cols / (512 * bpl) : 0;
         if (wpr == 1 || wpr == 2 || wpr == 4 || wpr == 8) {
-#define CLEF_FP8_TEAM(MODE, BPL, WPR)                                                                               \
+#define CLEF_FP8_TEAM_T(MODE, BPL, WPR, T)                                                                          \
     {                                                                                                               \
         static std::atomic<int> occ{0};                                                                             \
-        const int per_sm = ctas_per_sm(fp8_team_hot_kernel<MODE, BPL, WPR>, 0, occ);                                \
+        const int per_sm = ctas_per_sm(fp8_team_hot_kernel<MODE, BPL, WPR, T>, 0, occ);                             \
         const size_t ctas = ((size_t)rows + (8 / WPR) - 1) / (8 / WPR);                                             \
-        launch_hot(fp8_team_hot_kernel<MODE, BPL, WPR>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,           \
-                   (const uint16_t*)a, (const uint16_t*)b, out, scales, rows);                                      \
+        launch_hot(fp8_team_hot_kernel<MODE, BPL, WPR, T>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,        \
+                   (const Storage<T>*)a, (const Storage<T>*)b, out, scales, rows);                                  \
+    }
+#define CLEF_FP8_TEAM(MODE, BPL, WPR)                                                \
+    {                                                                                \
+        if (dtype == CLEF_BF16) CLEF_FP8_TEAM_T(MODE, BPL, WPR, Bf16)                \
+        else CLEF_FP8_TEAM_T(MODE, BPL, WPR, F32)                                    \
     }
 #define CLEF_FP8_TEAM_W(MODE, BPL)                                      \
     if (wpr == 1) CLEF_FP8_TEAM(MODE, BPL, 1)                           \
@@ -96,6 +105,7 @@ int fp8_rows_impl(const char* what, int mode, clef_stream_t stream, const void* 
             }
 #undef CLEF_FP8_TEAM_W
 #undef CLEF_FP8_TEAM
+#undef CLEF_FP8_TEAM_T
             return check_launch(what);
         }
     }
@@ -165,15 +175,20 @@ int clef_rms_norm_gated_quantise_fp8(clef_stream_t stream, const void* x, const 
     DeviceInfo dev;
     if (int r = device_info(dev)) return r;
     cudaStream_t s = as_stream(stream);
-    if (dtype == CLEF_BF16 && use_hot() && cols == 128 && rows_live == rows && (vh == 8 || vh == 16 || vh == 32 || vh == 64) &&
+    if (use_hot() && cols == 128 && rows_live == rows && (vh == 8 || vh == 16 || vh == 32 || vh == 64) &&
         aligned(x, 32) && aligned(gate, 32) && aligned(out, 16)) {
-#define CLEF_FP8_GATED_HOT(STEPS, WPT)                                                                            \
+#define CLEF_FP8_GATED_HOT_T(STEPS, WPT, T)                                                                       \
     {                                                                                                             \
         static std::atomic<int> occ{0};                                                                           \
-        const int per_sm = ctas_per_sm(fp8_gated_hot_kernel<STEPS, WPT>, 0, occ);                                 \
+        const int per_sm = ctas_per_sm(fp8_gated_hot_kernel<STEPS, WPT, T>, 0, occ);                              \
         const size_t ctas = ((size_t)tokens + (8 / WPT) - 1) / (8 / WPT);                                         \
-        launch_hot(fp8_gated_hot_kernel<STEPS, WPT>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,            \
-                   (const uint16_t*)x, (const uint16_t*)gate, weight, out, scales, tokens, eps);                  \
+        launch_hot(fp8_gated_hot_kernel<STEPS, WPT, T>, clamp_grid(ctas, (size_t)dev.sms * per_sm), 0, s,         \
+                   (const Storage<T>*)x, (const Storage<T>*)gate, weight, out, scales, tokens, eps);              \
+    }
+#define CLEF_FP8_GATED_HOT(STEPS, WPT)                                            \
+    {                                                                             \
+        if (dtype == CLEF_BF16) CLEF_FP8_GATED_HOT_T(STEPS, WPT, Bf16)            \
+        else CLEF_FP8_GATED_HOT_T(STEPS, WPT, F32)                                \
     }
         // one step per warp, vh / 8 warps per token: measured ahead of two steps per warp (which spills at 128 registers)
         if (vh == 8) CLEF_FP8_GATED_HOT(1, 1)
@@ -181,6 +196,7 @@ int clef_rms_norm_gated_quantise_fp8(clef_stream_t stream, const void* x, const 
         else if (vh == 32) CLEF_FP8_GATED_HOT(1, 4)
         else CLEF_FP8_GATED_HOT(1, 8)
 #undef CLEF_FP8_GATED_HOT
+#undef CLEF_FP8_GATED_HOT_T
         return check_launch(what);
     }
     const int hmax = (vh + 7) / 8;

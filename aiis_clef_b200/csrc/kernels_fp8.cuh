@@ -253,20 +253,76 @@ __device__ __forceinline__ uint32_t e4m3_mag_fast(float p) {
 constexpr float kFp8FastMinAmax = 7.888609052e-31f;   // 2^-100
 constexpr float kFp8FastMaxAmax = 3.0e38f;
 
-// 16 values of a row in the quad-pair layout -> 16 code bytes in natural order. `inv2` = splat(1 / scale).
-// Signs come from t + 0.0f, which turns -0.0 into +0.0 (the reference's (t < 0) is false for it) and changes
-// nothing else; NaN rows never get here.
+// The tuned kernels serve bf16 and f32 activations. A lane's 16-value block is one 32-byte load of bf16 (widened into
+// the quad-pair layout) or two of f32 (pairs of consecutive values: nothing to widen). With bf16 the next row's raw
+// registers are fetched while the current row is processed; with f32 the loaded registers are the row, so it is
+// loaded at the top of its iteration and the next one is only named to L2.
+template <typename T>
+struct RawBlock16 {
+    U8x32 r[T::kBytes / 2];
+};
+template <typename T>
+__device__ __forceinline__ RawBlock16<T> ldg_block16(const typename T::storage* p) {
+    RawBlock16<T> b;
+#pragma unroll
+    for (int i = 0; i < T::kBytes / 2; ++i) b.r[i] = ldg_stream_v8(reinterpret_cast<const uint8_t*>(p) + 32 * i);
+    return b;
+}
+template <typename T>
+__device__ __forceinline__ void unpack_block16(const RawBlock16<T>& b, f32x2* v) {
+    if (T::kBytes == 2) {
+        unpack16_quadpairs(b.r[0], v);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[i] = f2_pack(__uint_as_float(b.r[0].w[2 * i]), __uint_as_float(b.r[0].w[2 * i + 1]));
+            v[4 + i] = f2_pack(__uint_as_float(b.r[T::kBytes / 2 - 1].w[2 * i]), __uint_as_float(b.r[T::kBytes / 2 - 1].w[2 * i + 1]));
+        }
+    }
+}
+// (x*x + y*y) + (z*z + w*w) per quad with the reference build's contraction, for either pair order.
+template <bool NAT>
+__device__ __forceinline__ void quad_squares_of(const f32x2* v, float* quad) {
+    if (!NAT) {
+        quad_squares(v, quad);
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            quad[q] = __fadd_rn(__fmaf_rn(v[2 * q].x, v[2 * q].x, __fmul_rn(v[2 * q].y, v[2 * q].y)),
+                                __fmaf_rn(v[2 * q + 1].x, v[2 * q + 1].x, __fmul_rn(v[2 * q + 1].y, v[2 * q + 1].y)));
+        }
+    }
+}
+// One quad (of weights) in the order the pairs of `NAT` want it: (x, z, y, w) for quad pairs, natural otherwise.
+template <bool NAT>
+__device__ __forceinline__ float4 quad_order(float4 w) {
+    return NAT ? w : make_float4(w.x, w.z, w.y, w.w);
+}
+template <bool NAT>
+__device__ __forceinline__ U8x32 pack16_bf16_of(const f32x2* v) {
+    if (!NAT) return pack16_bf16(v);
+    U8x32 o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.w[i] = pack_bf16x2(v[i].x, v[i].y);
+    return o;
+}
+
+// 16 values of a row (quad pairs, or consecutive pairs with NAT) -> 16 code bytes in natural order. `inv2` =
+// splat(1 / scale). Signs come from t + 0.0f, which turns -0.0 into +0.0 (the reference's (t < 0) is false for it)
+// and changes nothing else; NaN rows never get here.
+template <bool NAT = false>
 __device__ __forceinline__ uint4 fp8_encode16_qp(const f32x2* v, f32x2 inv2) {
     uint32_t word[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-        const f32x2 a = f2_add(v[2 * q], f2_splat(0.0f)), b = f2_add(v[2 * q + 1], f2_splat(0.0f));   // (x, z), (y, w)
-        const uint32_t cx = e4m3_mag_fast(__fmul_rn(fabsf(a.x), inv2.x)), cy = e4m3_mag_fast(__fmul_rn(fabsf(b.x), inv2.x));
-        const uint32_t cz = e4m3_mag_fast(__fmul_rn(fabsf(a.y), inv2.x)), cw = e4m3_mag_fast(__fmul_rn(fabsf(b.y), inv2.x));
+        const f32x2 a = f2_add(v[2 * q], f2_splat(0.0f)), b = f2_add(v[2 * q + 1], f2_splat(0.0f));   // (x, z), (y, w); NAT: (x, y), (z, w)
+        const float x = a.x, y = NAT ? a.y : b.x, z = NAT ? b.x : a.y, w = b.y;
+        const uint32_t cx = e4m3_mag_fast(__fmul_rn(fabsf(x), inv2.x)), cy = e4m3_mag_fast(__fmul_rn(fabsf(y), inv2.x));
+        const uint32_t cz = e4m3_mag_fast(__fmul_rn(fabsf(z), inv2.x)), cw = e4m3_mag_fast(__fmul_rn(fabsf(w), inv2.x));
         const uint32_t mags = cx | (cy << 8) | (cz << 16) | (cw << 24);
         // top bytes of x, y, z, w -> bytes 0..3
-        const uint32_t xy = __byte_perm(__float_as_uint(a.x), __float_as_uint(b.x), 0x0073);
-        const uint32_t zw = __byte_perm(__float_as_uint(a.y), __float_as_uint(b.y), 0x0073);
+        const uint32_t xy = __byte_perm(__float_as_uint(x), __float_as_uint(y), 0x0073);
+        const uint32_t zw = __byte_perm(__float_as_uint(z), __float_as_uint(w), 0x0073);
         const uint32_t tops = __byte_perm(xy, zw, 0x5410);
         word[q] = mags | (tops & 0x80808080u);
     }
@@ -275,15 +331,15 @@ __device__ __forceinline__ uint4 fp8_encode16_qp(const f32x2* v, f32x2 inv2) {
 
 // Literal encoder for one block of a row that left the short encoder's domain: values recomputed from global
 // memory in natural order. MODE as in fp8_rows_kernel; inv_norm is the row's 1 / rms (RMSNorm only).
-template <int MODE>
-static __device__ __noinline__ void fp8_block_cold(const uint16_t* ablk, const uint16_t* bblk, const float* wblk,
-                                                   float inv_norm, float inv_scale, uint4* dst) {
+template <int MODE, typename T>
+static __device__ __noinline__ void fp8_block_cold(const typename T::storage* ablk, const typename T::storage* bblk,
+                                                   const float* wblk, float inv_norm, float inv_scale, uint4* dst) {
     uint32_t word[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        float t = __uint_as_float((uint32_t)ablk[i] << 16);
+        float t = load_scalar<T>(ablk + i);
         if (MODE == kFp8SwiGLU) {
-            t = silu_ieee_div(t) * __uint_as_float((uint32_t)bblk[i] << 16);
+            t = silu_ieee_div(t) * load_scalar<T>(bblk + i);
         } else if (MODE == kFp8RmsNorm) {
             t = t * inv_norm * (1.0f + wblk[i]);
         }
@@ -305,12 +361,14 @@ __device__ __forceinline__ float block_abs_max_ignoring_nan(const f32x2* v) {
 // quantise_fp8 (MODE plain) and rms_norm_fp8_bf16 (MODE RmsNorm, bf_out optional) for cols = NB * 512, one warp
 // per row: the row structure, prefetch and summation tree of rms_norm_quant_hot_kernel; the row maximum is a
 // 5-step butterfly, the row scale is computed by every lane, each lane encodes its NB blocks (16 bytes each).
-template <int NB, int MODE>
+template <int NB, int MODE, typename T = Bf16>
 __global__ void __launch_bounds__(kCtaThreads, (NB <= 4 ? 2 : 1))
-fp8_rows_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight, uint8_t* __restrict__ out,
+fp8_rows_hot_kernel(const typename T::storage* __restrict__ x, const float* __restrict__ weight, uint8_t* __restrict__ out,
                     uint16_t* __restrict__ scales, uint16_t* __restrict__ bf_out, int rows, float eps) {
     constexpr int COLS = NB * 512;
-    extern __shared__ float4 s_w[];   // (1 + w), quad-pair layout, as in rms_norm_quant_hot_kernel
+    constexpr bool NAT = T::kBytes == 4, REGPF = T::kBytes == 2;
+    constexpr int LINE = 128 / T::kBytes;   // values per 128-byte line
+    extern __shared__ float4 s_w[];   // (1 + w) in the pairs' order, as in rms_norm_quant_hot_kernel
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     pdl_launch_dependents();
@@ -318,34 +376,41 @@ fp8_rows_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
         for (int idx = threadIdx.x; idx < COLS / 4; idx += kCtaThreads) {
             const int l = idx & 31, q = (idx >> 5) & 3, j = idx >> 7;
             const float4 w = *reinterpret_cast<const float4*>(weight + (l + 32 * j) * 16 + 4 * q);
-            s_w[idx] = make_float4(1.0f + w.x, 1.0f + w.z, 1.0f + w.y, 1.0f + w.w);
+            s_w[idx] = quad_order<NAT>(make_float4(1.0f + w.x, 1.0f + w.y, 1.0f + w.z, 1.0f + w.w));
         }
     }
     int row = blockIdx.x * 8 + warp;
-    if (row < rows) {   // this warp's first row towards L2 (a lane covers 128 bytes); see prefetch_l2
+    auto name_row_to_l2 = [&](int r) {   // a row is NB * 1 KiB (bf16) or NB * 2 KiB (f32): a lane covers 128 bytes per step
 #pragma unroll
-        for (int h = 0; h < NB / 4; ++h) {
-            prefetch_l2(x + (size_t)row * COLS + (size_t)(lane + 32 * h) * 64);
+        for (int h = 0; h < NB * T::kBytes / 8; ++h) {
+            prefetch_l2(x + (size_t)r * COLS + (size_t)(lane + 32 * h) * LINE);
         }
-    }
+    };
+    if (row < rows) name_row_to_l2(row);   // this warp's first row towards L2; see prefetch_l2
     pdl_wait_prior_grids();
-    U8x32 d[NB];
-    if (row < rows) {
+    RawBlock16<T> d[NB];
+    if (REGPF && row < rows) {
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            d[j] = ldg_stream_v8(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
+            d[j] = ldg_block16<T>(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
         }
     }
     __syncthreads();
     for (; row < rows; row += gridDim.x * 8) {
+        if (!REGPF) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                d[j] = ldg_block16<T>(x + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16);
+            }
+        }
         f32x2 v[NB][8];
         float p[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            unpack16_quadpairs(d[j], v[j]);
+            unpack_block16<T>(d[j], v[j]);
             if (MODE == kFp8RmsNorm) {
                 float quad[4];
-                quad_squares(v[j], quad);
+                quad_squares_of<NAT>(v[j], quad);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     p[j & 1][k] = __fadd_rn(p[j & 1][k], quad[k]);
@@ -354,9 +419,13 @@ fp8_rows_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
         }
         const int next = row + gridDim.x * 8;
         if (next < rows) {
+            if (REGPF) {
 #pragma unroll
-            for (int j = 0; j < NB; ++j) {
-                d[j] = ldg_stream_v8(x + (size_t)next * COLS + (size_t)(lane + 32 * j) * 16);
+                for (int j = 0; j < NB; ++j) {
+                    d[j] = ldg_block16<T>(x + (size_t)next * COLS + (size_t)(lane + 32 * j) * 16);
+                }
+            } else {
+                name_row_to_l2(next);
             }
         }
         float inv_norm = 0.0f;
@@ -393,7 +462,7 @@ fp8_rows_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
             const f32x2 inv2 = f2_splat((scale > 0.0f) ? __frcp_rn(scale) : 0.0f);
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
-                *reinterpret_cast<uint4*>(orow + (size_t)(lane + 32 * j) * 16) = fp8_encode16_qp(v[j], inv2);
+                *reinterpret_cast<uint4*>(orow + (size_t)(lane + 32 * j) * 16) = fp8_encode16_qp<NAT>(v[j], inv2);
             }
         } else {
             // A NaN, an infinity or a tiny maximum in the row: the recipe's own maximum (NaN ignored), literal codes.
@@ -413,14 +482,14 @@ fp8_rows_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ we
             const float inv_scale = (scale > 0.0f) ? __fdiv_rn(1.0f, scale) : 0.0f;
             for (int j = 0; j < NB; ++j) {
                 const int b = lane + 32 * j;
-                fp8_block_cold<MODE>(x + (size_t)row * COLS + b * 16, nullptr, weight + b * 16, inv_norm, inv_scale,
-                                     reinterpret_cast<uint4*>(orow + (size_t)b * 16));
+                fp8_block_cold<MODE, T>(x + (size_t)row * COLS + b * 16, nullptr, weight + b * 16, inv_norm, inv_scale,
+                                        reinterpret_cast<uint4*>(orow + (size_t)b * 16));
             }
         }
         if (MODE == kFp8RmsNorm && bf_out) {
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
-                stg_v8(bf_out + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16, pack16_bf16(v[j]));
+                stg_v8(bf_out + (size_t)row * COLS + (size_t)(lane + 32 * j) * 16, pack16_bf16_of<NAT>(v[j]));
             }
         }
     }
@@ -439,12 +508,16 @@ __device__ __forceinline__ void team_barrier(int team) {
 // (8 / WPR rows per CTA at a time), lane l of team warp w holds the 16-value blocks (32 w + l) + 32 WPR j, j < BPL,
 // keeps their f32 values in registers, and the team's row maximum goes through shared memory: one named barrier
 // per row, the slots double-buffered by row parity so a fast warp's next row cannot overwrite a slow warp's read.
-template <int MODE, int BPL, int WPR>
+// f32 activations: the gate's silu is silu_ieee_refined_f32_x2 (the IEEE quotient for every f32 |g| <= 44).
+template <int MODE, int BPL, int WPR, typename T = Bf16>
 __global__ void __launch_bounds__(kCtaThreads, 2)
-fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, uint8_t* __restrict__ out,
-                    uint16_t* __restrict__ scales, int rows) {
+fp8_team_hot_kernel(const typename T::storage* __restrict__ a, const typename T::storage* __restrict__ b,
+                    uint8_t* __restrict__ out, uint16_t* __restrict__ scales, int rows) {
     constexpr int COLS = 512 * WPR * BPL;
     constexpr int TEAMS = (kCtaThreads / 32) / WPR;
+    constexpr bool NAT = T::kBytes == 4, REGPF = T::kBytes == 2;
+    constexpr int LPB = 4 * T::kBytes;      // 128-byte lines in the 32 blocks a warp loads at once
+    constexpr int LINE = 128 / T::kBytes;   // values per line
     __shared__ float s_max[2][2][kCtaThreads / 32];   // [fast | literal][row parity][warp]
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -452,32 +525,63 @@ fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__
     const int first_block = wt * 32 + lane;
     pdl_launch_dependents();
     int row = blockIdx.x * TEAMS + team;
-    if (row < rows && lane < 8 * BPL) {   // this warp's share of the team's first row towards L2; see prefetch_l2
-        const size_t off = (size_t)row * COLS + (size_t)(wt * 32 + 32 * WPR * (lane >> 3)) * 16 + (size_t)(lane & 7) * 64;
-        prefetch_l2(a + off);
-        if (MODE == kFp8SwiGLU) prefetch_l2(b + off);
-    }
+    auto name_row_to_l2 = [&](int r) {   // this warp's share of the team's row r: LPB lines per group of 32 blocks
+#pragma unroll
+        for (int h = 0; h < (BPL * LPB + 31) / 32; ++h) {
+            const int idx = lane + 32 * h;
+            if (idx < BPL * LPB) {
+                const size_t off = (size_t)r * COLS + (size_t)(wt * 32 + 32 * WPR * (idx / LPB)) * 16 + (size_t)(idx % LPB) * LINE;
+                prefetch_l2(a + off);
+                if (MODE == kFp8SwiGLU) prefetch_l2(b + off);
+            }
+        }
+    };
+    if (row < rows) name_row_to_l2(row);   // see prefetch_l2
     pdl_wait_prior_grids();
-    U8x32 da[BPL], db[MODE == kFp8SwiGLU ? BPL : 1];
-    if (row < rows) {
+    RawBlock16<T> da[REGPF ? BPL : 1], db[REGPF && MODE == kFp8SwiGLU ? BPL : 1];
+    if (REGPF && row < rows) {
 #pragma unroll
         for (int j = 0; j < BPL; ++j) {
             const size_t off = (size_t)row * COLS + (size_t)(first_block + 32 * WPR * j) * 16;
-            da[j] = ldg_stream_v8(a + off);
-            if (MODE == kFp8SwiGLU) db[j] = ldg_stream_v8(b + off);
+            da[j] = ldg_block16<T>(a + off);
+            if (MODE == kFp8SwiGLU) db[j] = ldg_block16<T>(b + off);
         }
     }
     int parity = 0;
     for (; row < rows; row += gridDim.x * TEAMS, parity ^= 1) {
         f32x2 v[BPL][8];
         float amax = 0.0f;
+        RawBlock16<T> ub;   // f32: the `b` block of the current j, fetched one block ahead
+        if (!REGPF) {
+            // all of this lane's `a` blocks at once (they are the values: no raw copies), `b` one block ahead
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) {
+                unpack_block16<T>(ldg_block16<T>(a + (size_t)row * COLS + (size_t)(first_block + 32 * WPR * j) * 16), v[j]);
+            }
+            if (MODE == kFp8SwiGLU) ub = ldg_block16<T>(b + (size_t)row * COLS + (size_t)first_block * 16);
+            const int next = row + gridDim.x * TEAMS;
+            if (next < rows) name_row_to_l2(next);
+        }
 #pragma unroll
         for (int j = 0; j < BPL; ++j) {
-            unpack16_quadpairs(da[j], v[j]);
+            if (REGPF) unpack_block16<T>(da[j], v[j]);
             if (MODE == kFp8SwiGLU) {
                 f32x2 u[8];
-                unpack16_quadpairs(db[j], u);
-                if (gated_fast_domain<kActSwiGLU, false>(v[j], u, nullptr)) {
+                unpack_block16<T>(REGPF ? db[j] : ub, u);
+                if (!REGPF && j + 1 < BPL) {
+                    ub = ldg_block16<T>(b + (size_t)row * COLS + (size_t)(first_block + 32 * WPR * (j + 1)) * 16);
+                }
+                if (NAT) {
+                    if (block_abs_max(v[j]) <= kSiluFastMaxAbs) {   // false for a NaN
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[j][i] = f2_mul(silu_ieee_refined_f32_x2(v[j][i]), u[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            v[j][i] = make_float2(gated_literal<kActSwiGLU>(v[j][i].x, u[i].x), gated_literal<kActSwiGLU>(v[j][i].y, u[i].y));
+                        }
+                    }
+                } else if (gated_fast_domain<kActSwiGLU, false>(v[j], u, nullptr)) {
                     gated_fast<kActSwiGLU>(v[j], u);
                 } else {
 #pragma unroll
@@ -489,12 +593,12 @@ fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__
             amax = fmaxf_nan(amax, block_abs_max(v[j]));
         }
         const int next = row + gridDim.x * TEAMS;
-        if (next < rows) {
+        if (REGPF && next < rows) {
 #pragma unroll
             for (int j = 0; j < BPL; ++j) {
                 const size_t off = (size_t)next * COLS + (size_t)(first_block + 32 * WPR * j) * 16;
-                da[j] = ldg_stream_v8(a + off);
-                if (MODE == kFp8SwiGLU) db[j] = ldg_stream_v8(b + off);
+                da[j] = ldg_block16<T>(a + off);
+                if (MODE == kFp8SwiGLU) db[j] = ldg_block16<T>(b + off);
             }
         }
 #pragma unroll
@@ -520,7 +624,7 @@ fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__
             const f32x2 inv2 = f2_splat((scale > 0.0f) ? __frcp_rn(scale) : 0.0f);
 #pragma unroll
             for (int j = 0; j < BPL; ++j) {
-                *reinterpret_cast<uint4*>(orow + (size_t)(first_block + 32 * WPR * j) * 16) = fp8_encode16_qp(v[j], inv2);
+                *reinterpret_cast<uint4*>(orow + (size_t)(first_block + 32 * WPR * j) * 16) = fp8_encode16_qp<NAT>(v[j], inv2);
             }
         } else {
             float m = 0.0f;
@@ -548,8 +652,8 @@ fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__
             const float inv_scale = (scale > 0.0f) ? __fdiv_rn(1.0f, scale) : 0.0f;
             for (int j = 0; j < BPL; ++j) {
                 const size_t off = (size_t)row * COLS + (size_t)(first_block + 32 * WPR * j) * 16;
-                fp8_block_cold<MODE>(a + off, MODE == kFp8SwiGLU ? b + off : nullptr, nullptr, 0.0f, inv_scale,
-                                     reinterpret_cast<uint4*>(out + off));
+                fp8_block_cold<MODE, T>(a + off, MODE == kFp8SwiGLU ? b + off : nullptr, nullptr, 0.0f, inv_scale,
+                                        reinterpret_cast<uint4*>(out + off));
             }
         }
     }
@@ -557,13 +661,13 @@ fp8_team_hot_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__
 
 
 // Literal values and codes of one 16-value block of the gated norm (kernels/quantise.cu:149-157, 185-190).
-static __device__ __noinline__ void fp8_gated_block_cold(const uint16_t* xblk, const uint16_t* gblk, const float* wblk,
-                                                         float inv_norm, float inv_scale, uint4* dst) {
+template <typename T>
+static __device__ __noinline__ void fp8_gated_block_cold(const typename T::storage* xblk, const typename T::storage* gblk,
+                                                         const float* wblk, float inv_norm, float inv_scale, uint4* dst) {
     uint32_t word[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        const float t = __uint_as_float((uint32_t)xblk[i] << 16) * inv_norm * wblk[i] *
-                        silu_fast_div(__uint_as_float((uint32_t)gblk[i] << 16));
+        const float t = load_scalar<T>(xblk + i) * inv_norm * wblk[i] * silu_fast_div(load_scalar<T>(gblk + i));
         word[i >> 2] |= fp8_code(t, inv_scale) << (8 * (i & 3));
     }
     *dst = make_uint4(word[0], word[1], word[2], word[3]);
@@ -573,15 +677,18 @@ static __device__ __noinline__ void fp8_gated_block_cold(const uint16_t* xblk, c
 // WPT warps own a token; in each of its STEPS steps a warp normalises 8 head rows with the lane layout and the
 // summation tree of gated_norm_quant_hot_kernel (4 lanes per head row); the values stay in registers until the
 // token's maximum is known (butterfly, then the team exchange of fp8_team_hot_kernel).
-template <int STEPS, int WPT>
+template <int STEPS, int WPT, typename T = Bf16>
 __global__ void __launch_bounds__(kCtaThreads, 2)
-fp8_gated_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, const float* __restrict__ weight,
-                     uint8_t* __restrict__ out, uint16_t* __restrict__ scales, int tokens, float eps) {
+fp8_gated_hot_kernel(const typename T::storage* __restrict__ x, const typename T::storage* __restrict__ gate,
+                     const float* __restrict__ weight, uint8_t* __restrict__ out, uint16_t* __restrict__ scales,
+                     int tokens, float eps) {
     constexpr int COLS = 128;
     constexpr int VH = 8 * STEPS * WPT;
     constexpr int TEAMS = (kCtaThreads / 32) / WPT;
+    constexpr bool NAT = T::kBytes == 4, REGPF = T::kBytes == 2;
+    constexpr int LINE = 128 / T::kBytes;   // values per 128-byte line
     __shared__ float s_max[2][2][kCtaThreads / 32];
-    __shared__ float4 s_w[32];   // plain weight, quad-pair layout: s_w[(h * 4 + q) * 4 + m]
+    __shared__ float4 s_w[32];   // plain weight in the pairs' order: s_w[(h * 4 + q) * 4 + m]
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int m = lane & 3;
@@ -590,23 +697,30 @@ fp8_gated_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
     if (threadIdx.x < 32) {
         const int mm = threadIdx.x & 3, q = (threadIdx.x >> 2) & 3, h = threadIdx.x >> 4;
         const float4 t = *reinterpret_cast<const float4*>(weight + (mm + 4 * h) * 16 + 4 * q);
-        s_w[threadIdx.x] = make_float4(t.x, t.z, t.y, t.w);
+        s_w[threadIdx.x] = quad_order<NAT>(t);
     }
     // Head row of this lane group in step s of token t: t * VH + (wt * STEPS + s) * 8 + (lane >> 2).
     auto head_row = [&](int token, int step) { return (size_t)token * VH + (size_t)(wt * STEPS + step) * 8 + (lane >> 2); };
     int token = blockIdx.x * TEAMS + team;
-    if (token < tokens) {   // the warp's first 8 head rows towards L2: 16 lines of x, 16 of gate; see prefetch_l2
-        const size_t first = ((size_t)token * VH + (size_t)(wt * STEPS) * 8) * COLS;
-        prefetch_l2((lane < 16 ? x : gate) + first + (size_t)(lane & 15) * 64);
-    }
+    // the 8 head rows of a step are 16 lines (bf16) or 32 (f32) of x and as many of the gate
+    auto name_step_to_l2 = [&](int t, int step) {
+        const size_t first = ((size_t)t * VH + (size_t)(wt * STEPS + step) * 8) * COLS;
+        if (REGPF) {
+            prefetch_l2((lane < 16 ? x : gate) + first + (size_t)(lane & 15) * LINE);
+        } else {
+            prefetch_l2(x + first + (size_t)lane * LINE);
+            prefetch_l2(gate + first + (size_t)lane * LINE);
+        }
+    };
+    if (token < tokens) name_step_to_l2(token, 0);   // see prefetch_l2
     pdl_wait_prior_grids();
     __syncthreads();
-    U8x32 dx[2], dg[2];
-    if (token < tokens) {
+    RawBlock16<T> dx[2], dg[2];
+    if (REGPF && token < tokens) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            dx[h] = ldg_stream_v8(x + head_row(token, 0) * COLS + (m + 4 * h) * 16);
-            dg[h] = ldg_stream_v8(gate + head_row(token, 0) * COLS + (m + 4 * h) * 16);
+            dx[h] = ldg_block16<T>(x + head_row(token, 0) * COLS + (m + 4 * h) * 16);
+            dg[h] = ldg_block16<T>(gate + head_row(token, 0) * COLS + (m + 4 * h) * 16);
         }
     }
     int parity = 0;
@@ -618,20 +732,31 @@ fp8_gated_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
         for (int step = 0; step < STEPS; ++step) {
             f32x2 gv[2][8];
             float quad[2][4];
+            if (!REGPF) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    dx[h] = ldg_block16<T>(x + head_row(token, step) * COLS + (m + 4 * h) * 16);
+                    dg[h] = ldg_block16<T>(gate + head_row(token, step) * COLS + (m + 4 * h) * 16);
+                }
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                unpack16_quadpairs(dx[h], v[step][h]);
-                unpack16_quadpairs(dg[h], gv[h]);
-                quad_squares(v[step][h], quad[h]);
+                unpack_block16<T>(dx[h], v[step][h]);
+                unpack_block16<T>(dg[h], gv[h]);
+                quad_squares_of<NAT>(v[step][h], quad[h]);
             }
-            // fetch the next step (of this token, or the first of this team's next token)
+            // fetch (bf16) or name to L2 (f32) the next step (of this token, or the first of this team's next token)
             const int ntoken = (step + 1 < STEPS) ? token : token + gridDim.x * TEAMS;
             const int nstep = (step + 1 < STEPS) ? step + 1 : 0;
             if (ntoken < tokens) {
+                if (REGPF) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    dx[h] = ldg_stream_v8(x + head_row(ntoken, nstep) * COLS + (m + 4 * h) * 16);
-                    dg[h] = ldg_stream_v8(gate + head_row(ntoken, nstep) * COLS + (m + 4 * h) * 16);
+                    for (int h = 0; h < 2; ++h) {
+                        dx[h] = ldg_block16<T>(x + head_row(ntoken, nstep) * COLS + (m + 4 * h) * 16);
+                        dg[h] = ldg_block16<T>(gate + head_row(ntoken, nstep) * COLS + (m + 4 * h) * 16);
+                    }
+                } else {
+                    name_step_to_l2(ntoken, nstep);
                 }
             }
             inv_norm[step] = inv_rms_pow2<COLS>(head_tree_32(quad[0], quad[1], lane), eps);
@@ -687,7 +812,7 @@ fp8_gated_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     *reinterpret_cast<uint4*>(out + head_row(token, step) * COLS + (m + 4 * h) * 16) =
-                        fp8_encode16_qp(v[step][h], inv2);
+                        fp8_encode16_qp<NAT>(v[step][h], inv2);
                 }
             }
         } else {
@@ -718,7 +843,7 @@ fp8_gated_hot_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
             for (int step = 0; step < STEPS; ++step) {
                 for (int h = 0; h < 2; ++h) {
                     const size_t off = head_row(token, step) * COLS + (m + 4 * h) * 16;
-                    fp8_gated_block_cold(x + off, gate + off, weight + (m + 4 * h) * 16, inv_norm[step], inv_scale,
+                    fp8_gated_block_cold<T>(x + off, gate + off, weight + (m + 4 * h) * 16, inv_norm[step], inv_scale,
                                          reinterpret_cast<uint4*>(out + off));
                 }
             }

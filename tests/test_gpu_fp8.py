@@ -226,6 +226,106 @@ def test_rms_norm_gated_quantise_fp8_ragged_tail_and_errors():
     assert lib.clef_quantise_fp8(stream(), ptr(dx), out.ptr, scales.ptr, 4, 32768, BF16) == -3
 
 
+def test_fp8_quantisers_on_arbitrary_f32_values():
+    """f32 activations that are not bf16 values (GEMM accumulators), at the widths the tuned f32 kernels serve and
+    8,192 rows (grid-stride loops, ragged last CTA): codes, scales and the bf16 twin against the reference's own
+    kernels, bit for bit. Gates beyond +-44, infinities, NaN, zero rows and tiny rows take the literal paths."""
+    dev = clef.Device(0)
+
+    def general(fn, *args):
+        """The same entry point on the shape-general kernels (each compared with the reference kernels elsewhere)."""
+        clef.set_kernel_choice(1)
+        try:
+            got = fn(*args)
+            torch.cuda.synchronize()
+        finally:
+            clef.set_kernel_choice(0)
+        return got
+
+    def spoil(t):
+        t[2] = 0.0
+        t[3, 5] = 3.0e38
+        t[4] = 1e-39
+        t[5, 9] = float("inf")
+        t[6, 11] = float("nan")
+        t[7] = 1e-30
+        t[9] = -0.0
+
+    for rows in (8192, 333):
+        gen = torch.Generator(device="cuda").manual_seed(rows + 17)
+        # plain and SwiGLU: one width per blocks-per-lane / warps-per-row shape
+        for cols in (512, 1536, 2048, 4096, 6144, 12288):
+            if rows == 8192 and cols not in (2048, 6144):
+                continue
+            gate = torch.randn(rows, cols, device="cuda", generator=gen) * 3.0
+            up = torch.randn(rows, cols, device="cuda", generator=gen) * 2.0
+            gate[:, 7] *= 25.0                      # |g| beyond the short form's range in every row
+            spoil(gate)
+            up[8, 100] = float("inf")
+            up[10, 120] = float("nan")
+            up[11] = 0.0
+            q, s = dev.quantise_fp8_dev(gate, rows, cols)
+            # the reference's launch is one row per CTA above 1792 columns only
+            rq, rs = ref_gpu.quantise_fp8(gate, rows, cols) if cols > 1792 else general(dev.quantise_fp8_dev, gate, rows, cols)
+            assert torch.equal(s, rs) and torch.equal(q, rq), f"plain, {rows} x {cols}"
+            q, s = dev.swiglu_quantise_fp8_dev(gate, up, rows, cols)
+            rq, rs = ref_gpu.swiglu_quantise_fp8(gate, up, rows, cols)
+            assert torch.equal(s, rs) and torch.equal(q, rq), f"SwiGLU, {rows} x {cols}"
+        # RMSNorm with the bf16 twin: the reference kernel at 4096, the chain of the general kernels at 2048
+        for cols in (2048, 4096):
+            x = torch.randn(rows, cols, device="cuda", generator=gen) * 1.5
+            x[:, 3] *= 40.0
+            spoil(x)
+            w = torch.randn(cols, device="cuda", generator=gen) * 0.3
+            q, s, bf = Guarded(rows * cols), Guarded(rows * 2), Guarded(rows * cols * 2)
+            assert call("clef_rms_norm_fp8_bf16", stream(), ptr(x), ptr(w), q.ptr, s.ptr, bf.ptr, rows, cols, 1e-6, F32) == 0
+            torch.cuda.synchronize()
+            for g, name in ((q, "codes"), (s, "scales"), (bf, "bf16")):
+                g.check_guards(name)
+            finite = np.ones(rows, bool)
+            finite[[5, 6]] = False
+            if cols == 4096:
+                rq, rs, rbf = ref_gpu.rms_norm_fp8_bf16(x, w, rows, cols, 1e-6)
+                want_q, want_s, want_bf = rq.cpu().numpy().reshape(-1), as_u16(rs), as_u16(rbf).reshape(rows, cols)
+            else:
+                g_q, g_s, g_bf = Guarded(rows * cols), Guarded(rows * 2), Guarded(rows * cols * 2)
+                assert general(call, "clef_rms_norm_fp8_bf16", stream(), ptr(x), ptr(w), g_q.ptr, g_s.ptr, g_bf.ptr, rows,
+                               cols, 1e-6, F32) == 0
+                want_q, want_s, want_bf = g_q.bytes(), g_s.bytes().view(np.uint16), g_bf.bytes().view(np.uint16).reshape(rows, cols)
+            assert_bytes_equal(s.bytes().view(np.uint16), want_s, f"norm scales, {rows} x {cols}")
+            assert_bytes_equal(q.bytes(), want_q, f"norm codes, {rows} x {cols}")
+            assert_bytes_equal(bf.bytes().view(np.uint16).reshape(rows, cols)[finite], want_bf[finite], f"bf16 twin, {rows} x {cols}")
+        # gated norm: 128-wide heads, every team shape
+        for vh in (8, 16, 32, 64):
+            tokens = rows if vh <= 32 else rows // 4
+            hr = tokens * vh
+            x = torch.randn(hr, 128, device="cuda", generator=gen) * 1.5
+            g = torch.randn(hr, 128, device="cuda", generator=gen) * 3.0
+            g[:, 7] *= 25.0
+            spoil(x)
+            g[vh * 3 + 1, 40] = float("inf")
+            g[vh * 4 + 1, 41] = float("nan")
+            x[vh * 5: vh * 6] = 0.0               # a token of zeros
+            w = 1.0 + torch.randn(128, device="cuda", generator=gen) * 0.1
+            out, scales = Guarded(hr * 128), Guarded(tokens * 2)
+            assert call("clef_rms_norm_gated_quantise_fp8", stream(), ptr(x), ptr(g), ptr(w), out.ptr, scales.ptr, hr, 128,
+                        1e-6, vh, hr, F32) == 0
+            torch.cuda.synchronize()
+            out.check_guards("codes")
+            scales.check_guards("scales")
+            if vh <= 32:
+                rq, rs = ref_gpu.rms_norm_gated_quantise_fp8(x, g, w, hr, 128, vh, 1e-6)
+                want_q, want_s = rq.cpu().numpy().reshape(-1), as_u16(rs)
+            else:                                  # beyond the reference's launch: the general kernel
+                g_out, g_scales = Guarded(hr * 128), Guarded(tokens * 2)
+                assert general(call, "clef_rms_norm_gated_quantise_fp8", stream(), ptr(x), ptr(g), ptr(w), g_out.ptr,
+                               g_scales.ptr, hr, 128, 1e-6, vh, hr, F32) == 0
+                want_q, want_s = g_out.bytes(), g_scales.bytes().view(np.uint16)
+            assert_bytes_equal(scales.bytes().view(np.uint16), want_s, f"gated scales, {tokens} tokens x {vh}")
+            assert_bytes_equal(out.bytes(), want_q, f"gated codes, {tokens} tokens x {vh}")
+            del x, g, out, scales
+
+
 def test_fp8_full_size():
     """130,712 rows: codes and scales of the plain and the SwiGLU quantiser against the reference kernels."""
     rows = 130712
