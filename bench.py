@@ -105,6 +105,10 @@ F32_BYTES_PER_ROW = {
     "qk_norm_rope_q_hd256_gate": 2 * Q_HEADS * 512 * 4 + 4 + 2 * (ROTARY // 2) * 4,
     "sigmoid_mul_quantise_nvfp4": 2 * 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
     "add_rms_norm_quantise_nvfp4": 3 * 4 * HIDDEN + HIDDEN // 2 + HIDDEN // 16,
+    "quantise_fp8": 4 * HIDDEN + HIDDEN + 2,
+    "rms_norm_fp8_bf16": 4 * HIDDEN + HIDDEN + 2 + 2 * HIDDEN,
+    "swiglu_quantise_fp8": 2 * 4 * INTER + INTER + 2,
+    "rms_norm_gated_quantise_fp8": 2 * 4 * HIDDEN + HIDDEN + 2,
 }
 # The step, in the order a layer runs its kernels: the partial RoPE of the q and the k heads (attention block; they
 # share their positions and go out as one launch, clef_rope_qk), RMSNorm+NVFP4 (the MLP block's input norm) and
