@@ -18,26 +18,15 @@ namespace {
 template <typename T>
 void launch_conv(cudaStream_t s, const DeviceInfo& dev, void* out, const void* x, const float* w, int rows, int channels,
                  int k, const int32_t* seq_start, const void* history, const int32_t* slot_map) {
-    if (k == 4 && channels % 8 == 0 && use_hot() && T::kBytes == 2) {   // bf16: 4 channels per thread, three CTAs per SM (measured)
+    if (k == 4 && channels % 8 == 0 && use_hot()) {   // 4 channels per thread, three CTAs per SM (measured)
         static std::atomic<int> occ{0};
         // 8,192 channels (16 + 16 heads of q and k and 32 of v, 128 wide) is the engine's mixed row: its stride is compiled in
-        auto kernel = channels == 8192 ? causal_conv_silu_c4_kernel<4, 8, 3, 8192> : causal_conv_silu_c4_kernel<4, 8, 3>;
+        auto kernel = channels == 8192 ? causal_conv_silu_c4_kernel<4, 8, 3, 8192, T> : causal_conv_silu_c4_kernel<4, 8, 3, 0, T>;
         const int per_sm = ctas_per_sm(kernel, 0, occ);
         const size_t items = (size_t)((rows + 7) / 8) * (channels / 4);
-        launch_hot(kernel, clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0, s, (uint16_t*)out,
-                   (const uint16_t*)x, w, rows, channels, (const int*)seq_start, (const uint16_t*)history,
-                   (const int*)slot_map, make_fast_div((uint32_t)(channels / 4)));
-        return;
-    }
-    if (k == 4 && channels % 8 == 0 && use_hot()) {
-        constexpr int kRows = T::kBytes == 2 ? 8 : 4;   // rows per thread: 11 (bf16) or 7 (f32) 16/32-byte loads in flight
-        static std::atomic<int> occ{0};
-        auto kernel = causal_conv_silu_kernel<T, 4, kRows>;
-        const int per_sm = ctas_per_sm(kernel, 0, occ);
-        const size_t items = (size_t)((rows + kRows - 1) / kRows) * (channels / 8);
         launch_hot(kernel, clamp_grid((items + kCtaThreads - 1) / kCtaThreads, (size_t)dev.sms * per_sm), 0, s,
                    (Storage<T>*)out, (const Storage<T>*)x, w, rows, channels, (const int*)seq_start,
-                   (const Storage<T>*)history, (const int*)slot_map, make_fast_div((uint32_t)(channels / 8)));
+                   (const Storage<T>*)history, (const int*)slot_map, make_fast_div((uint32_t)(channels / 4)));
         return;
     }
     static std::atomic<int> occ{0};

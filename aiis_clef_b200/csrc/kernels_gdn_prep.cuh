@@ -65,21 +65,9 @@ __device__ __forceinline__ void unpack8<F32>(const Raw8<F32>& r, float* v) {
 // whose source row lies before the token's sequence start (seq_start[t]) taken from the convolution history of
 // the token's slot (history[slot_map[t]], K - 1 rows per slot) when there is one and skipped otherwise;
 // silu(a) = a / (1 + __expf(-a)) with the IEEE quotient.
-// A thread owns 8 channels and R consecutive rows and slides a K-row window over them, so every x value is
-// loaded once. channels % 8 == 0.
+// A thread owns 4 channels and R consecutive rows (plus the K - 1 rows above them), so every x value is loaded
+// once per strip. channels % 8 == 0.
 // ---------------------------------------------------------------------------------------------
-struct Float8 {
-    float v[8];
-};
-// The literal silu of 8 accumulators, out of line: taken when one of them is outside the short form's domain.
-static __device__ __noinline__ Float8 silu8_literal(float a0, float a1, float a2, float a3, float a4, float a5, float a6,
-                                                    float a7) {
-    Float8 r;
-    r.v[0] = silu_ieee_div(a0), r.v[1] = silu_ieee_div(a1), r.v[2] = silu_ieee_div(a2), r.v[3] = silu_ieee_div(a3);
-    r.v[4] = silu_ieee_div(a4), r.v[5] = silu_ieee_div(a5), r.v[6] = silu_ieee_div(a6), r.v[7] = silu_ieee_div(a7);
-    return r;
-}
-
 // One output value by the literal expression, reading its taps from global memory: the general kernel's element and
 // the tuned kernel's path for strips that touch a sequence start.
 template <typename T>
@@ -150,136 +138,47 @@ static __device__ __noinline__ void causal_conv_silu_strip_literal(typename T::s
     }
 }
 
+// 4 channels of a row as loaded (8 bytes of bf16, 16 of f32), widened, and stored.
 template <typename T>
-__device__ __forceinline__ void unpack8_pairs(const Raw8<T>& r, f32x2* v);
+struct Raw4;
 template <>
-__device__ __forceinline__ void unpack8_pairs<Bf16>(const Raw8<Bf16>& r, f32x2* v) {
-    v[0] = f2_pack(bf16_lo(r.a.x), bf16_hi(r.a.x)), v[1] = f2_pack(bf16_lo(r.a.y), bf16_hi(r.a.y));
-    v[2] = f2_pack(bf16_lo(r.a.z), bf16_hi(r.a.z)), v[3] = f2_pack(bf16_lo(r.a.w), bf16_hi(r.a.w));
+struct Raw4<Bf16> {
+    uint2 d;
+};
+template <>
+struct Raw4<F32> {
+    uint4 d;
+};
+__device__ __forceinline__ Raw4<Bf16> load4_raw(const uint16_t* p) { return Raw4<Bf16>{ldg_stream_v2(p)}; }
+__device__ __forceinline__ Raw4<F32> load4_raw(const float* p) { return Raw4<F32>{ldg_stream_v4(p)}; }
+__device__ __forceinline__ void unpack4(const Raw4<Bf16>& r, float* v) {
+    v[0] = bf16_lo(r.d.x), v[1] = bf16_hi(r.d.x), v[2] = bf16_lo(r.d.y), v[3] = bf16_hi(r.d.y);
 }
-template <>
-__device__ __forceinline__ void unpack8_pairs<F32>(const Raw8<F32>& r, f32x2* v) {
-    v[0] = f2_pack(__uint_as_float(r.a.x), __uint_as_float(r.a.y)), v[1] = f2_pack(__uint_as_float(r.a.z), __uint_as_float(r.a.w));
-    v[2] = f2_pack(__uint_as_float(r.b.x), __uint_as_float(r.b.y)), v[3] = f2_pack(__uint_as_float(r.b.z), __uint_as_float(r.b.w));
+__device__ __forceinline__ void unpack4(const Raw4<F32>& r, float* v) {
+    v[0] = __uint_as_float(r.d.x), v[1] = __uint_as_float(r.d.y), v[2] = __uint_as_float(r.d.z), v[3] = __uint_as_float(r.d.w);
+}
+__device__ __forceinline__ void store4(uint16_t* p, const float* v) {
+    stg_v2(p, make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
+}
+__device__ __forceinline__ void store4(float* p, const float* v) {
+    stg_v4(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
 }
 
-// A strip none of whose rows has a tap before its sequence start (all but the strips that hold a sequence start or
-// the first K - 1 rows) runs without per-tap tests, two channels per packed multiply-add, the silu in its short
-// exact form (silu_ieee_refined_f32_x2); the other strips take the literal path. Used for f32 storage; bf16 storage takes
-// the 4-channel kernel below.
-// Two CTAs per SM (128 registers) measured best: one CTA (145 registers) or three and four (spills) are 20 to 60 %
-// slower, and so was keeping the next strip's loads in flight during the arithmetic (159 registers).
-template <typename T, int K, int R>
-__global__ void __launch_bounds__(kCtaThreads, 2)
-causal_conv_silu_kernel(typename T::storage* __restrict__ out, const typename T::storage* __restrict__ x,
-                        const float* __restrict__ w, int rows, int channels, const int* __restrict__ seq_start,
-                        const typename T::storage* __restrict__ history, const int* __restrict__ slot_map,
-                        FastDiv cvecs_div) {
-    pdl_launch_dependents();
-    pdl_wait_prior_grids();
-    const uint32_t cvecs = cvecs_div.d;
-    const uint32_t strips = ((uint32_t)rows + R - 1) / R;
-    const uint32_t total = strips * cvecs;
-    const uint32_t step = gridDim.x * kCtaThreads;
-    for (uint32_t idx = blockIdx.x * kCtaThreads + threadIdx.x; idx < total; idx += step) {
-        const uint32_t strip = fast_div(idx, cvecs_div);
-        const int c0 = (int)(idx - strip * cvecs) * 8;
-        const int t0 = (int)strip * R;
-        const int t1 = min(t0 + R, rows);
-        // All R + K - 1 rows of the strip are requested before any is used, so a thread has that many loads in flight.
-        Raw8<T> raw[R + K - 1];
-#pragma unroll
-        for (int i = 0; i < R + K - 1; ++i) {
-            const int src = t0 - (K - 1) + i;
-            if (src >= 0 && src < rows) {
-                raw[i] = load8_raw<T>(x + (size_t)src * channels + c0);
-            } else {
-                raw[i] = Raw8<T>{};
-            }
-        }
-        bool plain = t0 >= K - 1;
-        if (seq_start) {
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (t0 + r < rows) plain &= __ldg(seq_start + t0 + r) <= t0 + r - (K - 1);
-            }
-        }
-        f32x2 wt[4][K];   // wt[p][tap] = the tap weights of channels c0 + 2p and c0 + 2p + 1
-        if (K == 4) {     // a channel's four taps are one 16-byte load
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                const float4 ta = __ldg(reinterpret_cast<const float4*>(w) + (c0 + 2 * p));
-                const float4 tb = __ldg(reinterpret_cast<const float4*>(w) + (c0 + 2 * p + 1));
-                wt[p][0] = f2_pack(ta.x, tb.x), wt[p][1] = f2_pack(ta.y, tb.y);
-                wt[p][2 % K] = f2_pack(ta.z, tb.z), wt[p][3 % K] = f2_pack(ta.w, tb.w);
-            }
-        } else {
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-#pragma unroll
-                for (int tap = 0; tap < K; ++tap) {
-                    wt[p][tap] = f2_pack(__ldg(w + (size_t)(c0 + 2 * p) * K + tap), __ldg(w + (size_t)(c0 + 2 * p + 1) * K + tap));
-                }
-            }
-        }
-        if (!plain) {
-            causal_conv_silu_strip_literal<T, K>(out, x, w, t0, t1, c0, channels, seq_start, history, slot_map);
-            continue;
-        }
-        f32x2 win[K][4];   // win[i] = x[t - (K-1) + i] for the current row t; win[K-1] is the row itself
-#pragma unroll
-        for (int i = 0; i < K - 1; ++i) {
-            unpack8_pairs<T>(raw[i], win[i + 1]);
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int t = t0 + r;
-            if (t >= rows) {
-                break;
-            }
-#pragma unroll
-            for (int i = 0; i < K - 1; ++i) {
-#pragma unroll
-                for (int p = 0; p < 4; ++p) win[i][p] = win[i + 1][p];
-            }
-            unpack8_pairs<T>(raw[r + K - 1], win[K - 1]);
-            f32x2 acc[4];
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                acc[p] = f2_fma(wt[p][0], win[0][p], f2_splat(0.0f));
-#pragma unroll
-                for (int tap = 1; tap < K; ++tap) acc[p] = f2_fma(wt[p][tap], win[tap][p], acc[p]);
-            }
-            float o[8];
-            if (silu_f32_magnitude_domain_x2<4>(acc)) {
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    const f32x2 q = silu_ieee_refined_f32_x2(acc[p]);
-                    o[2 * p] = q.x, o[2 * p + 1] = q.y;
-                }
-            } else {
-                const Float8 lit = silu8_literal(acc[0].x, acc[0].y, acc[1].x, acc[1].y, acc[2].x, acc[2].y, acc[3].x, acc[3].y);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = lit.v[j];
-            }
-            store8<T>(out + (size_t)t * channels + c0, o);
-        }
-    }
-}
-
-// bf16 storage, 4 channels per thread (8-byte loads and stores): half the registers of the 8-channel form, so more
-// warps are resident to overlap one thread's load phase with another's arithmetic. A strip that lies inside the
+// 4 channels per thread (8-byte loads and stores of bf16, 16-byte ones of f32): half the registers of an 8-channel
+// form, so more warps are resident to overlap one thread's load phase with another's arithmetic. A strip that lies inside the
 // matrix with its halo and has no tap before a sequence start runs without any per-row or per-tap test; every
 // other strip (the first, a ragged last one, one holding a sequence start) takes the literal path. The arithmetic
 // is scalar on purpose: packed multiply-adds cost more register-pair moves here than they save (measured: 105
 // against 99 instructions per row of 4 values).
 // CH: the channel count when it is known at compile time (0: the `channels` argument). With a constant row stride the
 // 19 row addresses of a strip are immediate offsets from one base register instead of a multiply-add each.
-template <int K, int R, int MIN_CTAS, int CH = 0>
+template <int K, int R, int MIN_CTAS, int CH = 0, typename T = Bf16>
 __global__ void __launch_bounds__(kCtaThreads, MIN_CTAS)
-causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ x, const float* __restrict__ w, int rows,
-                           int channels_arg, const int* __restrict__ seq_start, const uint16_t* __restrict__ history,
-                           const int* __restrict__ slot_map, FastDiv cvecs_div) {
+causal_conv_silu_c4_kernel(typename T::storage* __restrict__ out, const typename T::storage* __restrict__ x,
+                           const float* __restrict__ w, int rows, int channels_arg, const int* __restrict__ seq_start,
+                           const typename T::storage* __restrict__ history, const int* __restrict__ slot_map,
+                           FastDiv cvecs_div) {
+    constexpr int kLineThreads = 32 / T::kBytes;   // threads whose 4 channels share a 128-byte line
     pdl_launch_dependents();
     pdl_wait_prior_grids();
     const int channels = CH ? CH : channels_arg;
@@ -293,17 +192,17 @@ causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
         const int c0 = (int)(idx - strip * cvecs) * 4;
         const int t0 = (int)strip * R;
         bool plain = t0 >= K - 1 && t0 + R <= rows;   // every row of the strip and of its halo exists
-        uint2 raw[R + K - 1];
+        Raw4<T> raw[R + K - 1];
         float wt[4][K];
         if (plain) {
-            const uint16_t* base = x + (size_t)(t0 - (K - 1)) * channels + c0;
+            const typename T::storage* base = x + (size_t)(t0 - (K - 1)) * channels + c0;
 #pragma unroll
-            for (int i = 0; i < R + K - 1; ++i) raw[i] = ldg_stream_v2(base + (size_t)i * channels);
-            {   // the strip this thread handles next, named to L2 (16 threads share a 128-byte line): 70.5 -> 68.9 us
+            for (int i = 0; i < R + K - 1; ++i) raw[i] = load4_raw(base + (size_t)i * channels);
+            {   // the strip this thread handles next, named to L2 (one thread per 128-byte line): 70.5 -> 68.9 us with bf16
                 const uint32_t nidx = idx + step;
-                if (nidx < total && (threadIdx.x & 15) == 0) {
+                if (nidx < total && (threadIdx.x & (kLineThreads - 1)) == 0) {
                     const uint32_t nstrip = CH ? nidx / (uint32_t)(CH / 4) : fast_div(nidx, cvecs_div);
-                    const uint16_t* nb = x + (size_t)(nstrip * R) * channels + (nidx - nstrip * cvecs) * 4;
+                    const typename T::storage* nb = x + (size_t)(nstrip * R) * channels + (nidx - nstrip * cvecs) * 4;
 #pragma unroll
                     for (int i = 0; i < R; ++i) prefetch_l2(nb + (size_t)i * channels);
                 }
@@ -336,16 +235,14 @@ causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
         }
         if (!plain) {
             if ((c0 & 4) == 0) {   // the literal path works on 8 channels: the even thread of a pair does both halves
-                causal_conv_silu_strip_literal<Bf16, K>(out, x, w, t0, min(t0 + R, rows), c0, channels, seq_start, history, slot_map);
+                causal_conv_silu_strip_literal<T, K>(out, x, w, t0, min(t0 + R, rows), c0, channels, seq_start, history, slot_map);
             }
             continue;
         }
         float xs[R + K - 1][4];   // every row of the strip widened once; row r reads xs[r .. r + K - 1]
 #pragma unroll
-        for (int i = 0; i < R + K - 1; ++i) {
-            xs[i][0] = bf16_lo(raw[i].x), xs[i][1] = bf16_hi(raw[i].x), xs[i][2] = bf16_lo(raw[i].y), xs[i][3] = bf16_hi(raw[i].y);
-        }
-        uint16_t* orow = out + (size_t)t0 * channels + c0;
+        for (int i = 0; i < R + K - 1; ++i) unpack4(raw[i], xs[i]);
+        typename T::storage* orow = out + (size_t)t0 * channels + c0;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             float a4[4];
@@ -364,7 +261,7 @@ causal_conv_silu_c4_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
 #pragma unroll
                 for (int j = 0; j < 4; ++j) o4[j] = silu_ieee_div(a4[j]);
             }
-            stg_v2(orow + (size_t)r * channels, make_uint2(pack_bf16x2(o4[0], o4[1]), pack_bf16x2(o4[2], o4[3])));
+            store4(orow + (size_t)r * channels, o4);
         }
     }
 }
