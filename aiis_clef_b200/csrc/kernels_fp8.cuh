@@ -307,14 +307,44 @@ __device__ __forceinline__ U8x32 pack16_bf16_of(const f32x2* v) {
     return o;
 }
 
+// Four scaled values p = t * inv with 2^-6 <= |p| < 464 (signs kept) -> their four code bytes, x in the lowest,
+// by the hardware converter cvt.rn.satfinite.e4m3x2.f32. From the smallest normal E4M3 value up the reference encoder
+// is round-half-up on the 3-bit mantissa (carrying into the exponent) with saturation at 448 = 0x7E, which is also
+// the converter's finite maximum. The converter rounds ties to even: an exact tie has zero low mantissa bits, so
+// setting the lowest one lifts it just above the tie, and no other value changes its rounding (a value below a tie
+// stays below it, a code point stays nearest to itself). Below 2^-6 the reference's subnormal codes are not the
+// converter's (7.5/512 <= p < 8/512 gives 7 where the converter gives 8, and the f32 just below 2^-10 gives 1), so
+// those quads keep the integer form. Compared with the reference encoder for every f32 pattern of the domain, both
+// signs, every byte position (oracle/ref_probe.cu).
+constexpr float kFp8HwMinP = 0.015625f;   // 2^-6
+__device__ __forceinline__ uint32_t e4m3x4_hw(float x, float y, float z, float w) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"   // the first source operand lands in the high byte
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r)
+        : "f"(__uint_as_float(__float_as_uint(x) | 1u)), "f"(__uint_as_float(__float_as_uint(y) | 1u)),
+          "f"(__uint_as_float(__float_as_uint(z) | 1u)), "f"(__uint_as_float(__float_as_uint(w) | 1u)));
+    return r;
+}
+
 // 16 values of a row (quad pairs, or consecutive pairs with NAT) -> 16 code bytes in natural order. `inv2` =
-// splat(1 / scale). Signs come from t + 0.0f, which turns -0.0 into +0.0 (the reference's (t < 0) is false for it)
-// and changes nothing else; NaN rows never get here.
+// splat(1 / scale). A quad whose four scaled magnitudes are all at least 2^-6 goes through the hardware converter
+// (scaling is monotonic, so the smallest magnitude decides); the others take the integer form, where signs come
+// from t + 0.0f, which turns -0.0 into +0.0 (the reference's (t < 0) is false for it) and changes nothing else.
+// NaN rows never get here.
 template <bool NAT = false>
 __device__ __forceinline__ uint4 fp8_encode16_qp(const f32x2* v, f32x2 inv2) {
     uint32_t word[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
+        const float smallest = min3_abs(fabsf(v[2 * q].x), v[2 * q].y, fminf(fabsf(v[2 * q + 1].x), fabsf(v[2 * q + 1].y)));
+        if (__fmul_rn(smallest, inv2.x) >= kFp8HwMinP) {
+            const f32x2 pa = f2_mul(v[2 * q], inv2), pb = f2_mul(v[2 * q + 1], inv2);   // (x, z), (y, w); NAT: (x, y), (z, w)
+            word[q] = e4m3x4_hw(pa.x, NAT ? pa.y : pb.x, NAT ? pb.x : pa.y, pb.y);
+            continue;
+        }
         const f32x2 a = f2_add(v[2 * q], f2_splat(0.0f)), b = f2_add(v[2 * q + 1], f2_splat(0.0f));   // (x, z), (y, w); NAT: (x, y), (z, w)
         const float x = a.x, y = NAT ? a.y : b.x, z = NAT ? b.x : a.y, w = b.y;
         const uint32_t cx = e4m3_mag_fast(__fmul_rn(fabsf(x), inv2.x)), cy = e4m3_mag_fast(__fmul_rn(fabsf(y), inv2.x));

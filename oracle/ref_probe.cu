@@ -80,7 +80,7 @@ extern "C" __global__ void probe_e2m1(unsigned long long base, unsigned long lon
 // (clef::quantise16_rare handles it the same way), everything else through e4m3_encode_finite.
 extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long long count, ProbeResult* result) {
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-    unsigned long long checked = 0, checked_fast = 0;
+    unsigned long long checked = 0, checked_fast = 0, checked_hw = 0;
     for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         const uint32_t bits = (uint32_t)(base + i);
         const float v = __uint_as_float(bits);
@@ -99,10 +99,21 @@ extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long lon
                 report(&result[2], bits);
             }
         }
+        if (bits >= 0x3C800000u && bits < 0x43E80000u) {   // the hardware-converter form on its domain, 2^-6 <= v < 464:
+            ++checked_hw;                                  // v in every byte position, both signs, beside a partner of the domain
+            const float q = __uint_as_float(0x3C800000u + mix(bits) % (0x43E80000u - 0x3C800000u));
+            const uint32_t want_q = to_e4m3(q);
+            const uint32_t w0 = clef::e4m3x4_hw(v, -q, q, -v), w1 = clef::e4m3x4_hw(-q, v, -v, q);
+            if (w0 != (want | ((want_q | 0x80u) << 8) | (want_q << 16) | ((want | 0x80u) << 24)) ||
+                w1 != ((want_q | 0x80u) | (want << 8) | ((want | 0x80u) << 16) | (want_q << 24))) {
+                report(&result[3], bits);
+            }
+        }
     }
     atomicAdd(&result[0].checked, checked);
     atomicAdd(&result[1].checked, checked);
     atomicAdd(&result[2].checked, checked_fast);
+    atomicAdd(&result[3].checked, checked_hw);
 }
 
 // result[0]: decoder on all 256 bytes (bit-exact f32); result[1]: inv_scale for `global_scale`.

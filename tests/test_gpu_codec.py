@@ -24,10 +24,12 @@ def test_e2m1_all_patterns():
 
 
 def test_e4m3_encoder_all_patterns():
-    """Both encoders (the block-scale one and the FP8 quantisers' element one) against the reference's to_e4m3."""
+    """The encoders (the block-scale one, the FP8 quantisers' element one in its general, short and hardware-converter
+    forms) against the reference's to_e4m3."""
     res = ref_gpu.probe_e4m3(0, 1 << 32)
     assert res[0]["checked"] == 1 << 32 and res[1]["checked"] == 1 << 32
     assert res[2]["checked"] == 0x43E80000            # every pattern of [+0, 464)
+    assert res[3]["checked"] == 0x43E80000 - 0x3C800000   # the hardware-converter form: every pattern of [2^-6, 464)
     assert all(r["mismatches"] == 0 for r in res), _fmt(res)
 
 
