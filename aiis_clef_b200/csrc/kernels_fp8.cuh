@@ -307,16 +307,17 @@ __device__ __forceinline__ U8x32 pack16_bf16_of(const f32x2* v) {
     return o;
 }
 
-// Four scaled values p = t * inv with 2^-6 <= |p| < 464 (signs kept) -> their four code bytes, x in the lowest,
-// by the hardware converter cvt.rn.satfinite.e4m3x2.f32. From the smallest normal E4M3 value up the reference encoder
-// is round-half-up on the 3-bit mantissa (carrying into the exponent) with saturation at 448 = 0x7E, which is also
-// the converter's finite maximum. The converter rounds ties to even: an exact tie has zero low mantissa bits, so
-// setting the lowest one lifts it just above the tie, and no other value changes its rounding (a value below a tie
-// stays below it, a code point stays nearest to itself). Below 2^-6 the reference's subnormal codes are not the
-// converter's (7.5/512 <= p < 8/512 gives 7 where the converter gives 8, and the f32 just below 2^-10 gives 1), so
-// those quads keep the integer form. Compared with the reference encoder for every f32 pattern of the domain, both
-// signs, every byte position (oracle/ref_probe.cu).
-constexpr float kFp8HwMinP = 0.015625f;   // 2^-6
+// Four scaled values p = t * inv with |p| < 464 (signs kept) -> their four code bytes, x in the lowest, by the hardware
+// converter cvt.rn.satfinite.e4m3x2.f32. From the smallest normal E4M3 value up the reference encoder is round-half-up
+// on the 3-bit mantissa (carrying into the exponent) with saturation at 448 = 0x7E, which is also the converter's
+// finite maximum. The converter rounds ties to even: an exact tie has zero low mantissa bits, so setting the lowest
+// one lifts it just above the tie, and no other value changes its rounding (a value below a tie stays below it, a
+// code point stays nearest to itself). The same holds for the subnormal codes 1 to 7. The converter's bytes differ
+// from the reference's only where it answers 0 or 8 in the low seven bits: 7.5/512 <= p < 8/512 gives 7 in the
+// reference (its subnormal branch clamps) and 8 here, the f32 just below 2^-10 gives 1 there (its p * 512 + 0.5
+// rounds up to 1) and 0 here, and -0.0 keeps its sign here. e4m3x4_suspect flags exactly the words that hold such a
+// byte; the caller recomputes them with the integer form. Compared with the reference encoder for every f32 pattern
+// of [0, 464), both signs, every byte position: each byte is either flagged or equal (oracle/ref_probe.cu).
 __device__ __forceinline__ uint32_t e4m3x4_hw(float x, float y, float z, float w) {
     uint32_t r;
     asm("{\n\t.reg .b16 lo, hi;\n\t"
@@ -328,33 +329,47 @@ __device__ __forceinline__ uint32_t e4m3x4_hw(float x, float y, float z, float w
           "f"(__uint_as_float(__float_as_uint(z) | 1u)), "f"(__uint_as_float(__float_as_uint(w) | 1u)));
     return r;
 }
+// Non-zero iff one of the four bytes is 0x00, 0x08, 0x80 or 0x88 (a zero byte after the mask, by the borrow test).
+__device__ __forceinline__ uint32_t e4m3x4_suspect(uint32_t word) {
+    const uint32_t m = word & 0x77777777u;
+    return (m - 0x01010101u) & ~m & 0x80808080u;
+}
+
+// The four codes of one quad by the integer form, for any magnitudes below 464: signs from t + 0.0f, which turns
+// -0.0 into +0.0 (the reference's (t < 0) is false for it) and changes nothing else. Out of line: it runs for the
+// few quads the converter form flags.
+static __device__ __noinline__ uint32_t fp8_encode4_int(float x, float y, float z, float w, float inv) {
+    x = __fadd_rn(x, 0.0f), y = __fadd_rn(y, 0.0f), z = __fadd_rn(z, 0.0f), w = __fadd_rn(w, 0.0f);
+    const uint32_t cx = e4m3_mag_fast(__fmul_rn(fabsf(x), inv)), cy = e4m3_mag_fast(__fmul_rn(fabsf(y), inv));
+    const uint32_t cz = e4m3_mag_fast(__fmul_rn(fabsf(z), inv)), cw = e4m3_mag_fast(__fmul_rn(fabsf(w), inv));
+    const uint32_t mags = cx | (cy << 8) | (cz << 16) | (cw << 24);
+    // top bytes of x, y, z, w -> bytes 0..3
+    const uint32_t xy = __byte_perm(__float_as_uint(x), __float_as_uint(y), 0x0073);
+    const uint32_t zw = __byte_perm(__float_as_uint(z), __float_as_uint(w), 0x0073);
+    return mags | (__byte_perm(xy, zw, 0x5410) & 0x80808080u);
+}
 
 // 16 values of a row (quad pairs, or consecutive pairs with NAT) -> 16 code bytes in natural order. `inv2` =
-// splat(1 / scale). A quad whose four scaled magnitudes are all at least 2^-6 goes through the hardware converter
-// (scaling is monotonic, so the smallest magnitude decides); the others take the integer form, where signs come
-// from t + 0.0f, which turns -0.0 into +0.0 (the reference's (t < 0) is false for it) and changes nothing else.
+// splat(1 / scale). Every quad goes through the hardware converter; one test per block sends the flagged quads
+// (a zero, a value that rounds to zero, one at the top of the subnormal codes) through the integer form.
 // NaN rows never get here.
 template <bool NAT = false>
 __device__ __forceinline__ uint4 fp8_encode16_qp(const f32x2* v, f32x2 inv2) {
-    uint32_t word[4];
+    uint32_t word[4], suspect[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-        const float smallest = min3_abs(fabsf(v[2 * q].x), v[2 * q].y, fminf(fabsf(v[2 * q + 1].x), fabsf(v[2 * q + 1].y)));
-        if (__fmul_rn(smallest, inv2.x) >= kFp8HwMinP) {
-            const f32x2 pa = f2_mul(v[2 * q], inv2), pb = f2_mul(v[2 * q + 1], inv2);   // (x, z), (y, w); NAT: (x, y), (z, w)
-            word[q] = e4m3x4_hw(pa.x, NAT ? pa.y : pb.x, NAT ? pb.x : pa.y, pb.y);
-            continue;
+        const f32x2 pa = f2_mul(v[2 * q], inv2), pb = f2_mul(v[2 * q + 1], inv2);   // (x, z), (y, w); NAT: (x, y), (z, w)
+        word[q] = e4m3x4_hw(pa.x, NAT ? pa.y : pb.x, NAT ? pb.x : pa.y, pb.y);
+        suspect[q] = e4m3x4_suspect(word[q]);
+    }
+    if ((suspect[0] | suspect[1]) | (suspect[2] | suspect[3])) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (suspect[q]) {
+                const f32x2 a = v[2 * q], b = v[2 * q + 1];
+                word[q] = fp8_encode4_int(a.x, NAT ? a.y : b.x, NAT ? b.x : a.y, b.y, inv2.x);
+            }
         }
-        const f32x2 a = f2_add(v[2 * q], f2_splat(0.0f)), b = f2_add(v[2 * q + 1], f2_splat(0.0f));   // (x, z), (y, w); NAT: (x, y), (z, w)
-        const float x = a.x, y = NAT ? a.y : b.x, z = NAT ? b.x : a.y, w = b.y;
-        const uint32_t cx = e4m3_mag_fast(__fmul_rn(fabsf(x), inv2.x)), cy = e4m3_mag_fast(__fmul_rn(fabsf(y), inv2.x));
-        const uint32_t cz = e4m3_mag_fast(__fmul_rn(fabsf(z), inv2.x)), cw = e4m3_mag_fast(__fmul_rn(fabsf(w), inv2.x));
-        const uint32_t mags = cx | (cy << 8) | (cz << 16) | (cw << 24);
-        // top bytes of x, y, z, w -> bytes 0..3
-        const uint32_t xy = __byte_perm(__float_as_uint(x), __float_as_uint(y), 0x0073);
-        const uint32_t zw = __byte_perm(__float_as_uint(z), __float_as_uint(w), 0x0073);
-        const uint32_t tops = __byte_perm(xy, zw, 0x5410);
-        word[q] = mags | (tops & 0x80808080u);
     }
     return make_uint4(word[0], word[1], word[2], word[3]);
 }

@@ -384,7 +384,8 @@ def probe_e2m1(base: int, count: int):
 
 def probe_e4m3(base: int, count: int):
     """[scale encoder e4m3_encode_finite (+inf literal), element encoder e4m3_encode_any, short element encoder
-    e4m3_mag_fast on 0 <= v < 464, hardware-converter form e4m3x4_hw on 2^-6 <= v < 464] against to_e4m3."""
+    e4m3_mag_fast on 0 <= v < 464, hardware-converter form e4m3x4_hw with its flagged bytes on the same patterns]
+    against to_e4m3."""
     buf = _result_buffer(4)
     launch("ref_probe", "probe_e4m3", (148 * 8,), (256,),
            [(base, ctypes.c_ulonglong), (count, ctypes.c_ulonglong), buf])

@@ -99,15 +99,33 @@ extern "C" __global__ void probe_e4m3(unsigned long long base, unsigned long lon
                 report(&result[2], bits);
             }
         }
-        if (bits >= 0x3C800000u && bits < 0x43E80000u) {   // the hardware-converter form on its domain, 2^-6 <= v < 464:
-            ++checked_hw;                                  // v in every byte position, both signs, beside a partner of the domain
-            const float q = __uint_as_float(0x3C800000u + mix(bits) % (0x43E80000u - 0x3C800000u));
+        if (bits < 0x43E80000u) {   // the hardware-converter form on +0 <= v < 464: v in every byte position, both signs,
+            ++checked_hw;           // beside a partner of the domain; a byte is either flagged (0 or 8 in its low seven
+                                    // bits) or the reference's, and the word test fires exactly when a byte is flagged
+            const float q = __uint_as_float(mix(bits) % 0x43E80000u);
             const uint32_t want_q = to_e4m3(q);
-            const uint32_t w0 = clef::e4m3x4_hw(v, -q, q, -v), w1 = clef::e4m3x4_hw(-q, v, -v, q);
-            if (w0 != (want | ((want_q | 0x80u) << 8) | (want_q << 16) | ((want | 0x80u) << 24)) ||
-                w1 != ((want_q | 0x80u) | (want << 8) | ((want | 0x80u) << 16) | (want_q << 24))) {
-                report(&result[3], bits);
+            const uint32_t got_w[2] = {clef::e4m3x4_hw(v, -q, q, -v), clef::e4m3x4_hw(-q, v, -v, q)};
+            const uint32_t neg_v = want | (bits ? 0x80u : 0u), neg_q = want_q | (q > 0.0f ? 0x80u : 0u);   // (t < 0) is false for -0.0
+            const uint32_t want_w[2] = {want | (neg_q << 8) | (want_q << 16) | (neg_v << 24),
+                                        neg_q | (want << 8) | (neg_v << 16) | (want_q << 24)};
+            bool bad = false;
+            for (int k = 0; k < 2; ++k) {
+                bool flagged = false;
+                for (int byte = 0; byte < 4; ++byte) {
+                    const uint32_t g = (got_w[k] >> (8 * byte)) & 0xFFu, w = (want_w[k] >> (8 * byte)) & 0xFFu;
+                    if ((g & 0x77u) == 0u) {
+                        flagged = true;
+                    } else if (g != w) {
+                        bad = true;
+                    }
+                }
+                if ((clef::e4m3x4_suspect(got_w[k]) != 0u) != flagged) bad = true;
+                // what the kernels do with a flagged word
+                if (flagged && clef::fp8_encode4_int(k == 0 ? v : -q, k == 0 ? -q : v, k == 0 ? q : -v, k == 0 ? -v : q, 1.0f) != want_w[k]) {
+                    bad = true;
+                }
             }
+            if (bad) report(&result[3], bits);
         }
     }
     atomicAdd(&result[0].checked, checked);
