@@ -778,7 +778,7 @@ int clef_qk_norm_rope(clef_stream_t stream, const void* x, const float* weight, 
         const FastDiv heads_div = make_fast_div((uint32_t)heads);
         auto launch = [&](auto kernel, std::atomic<int>& occ) {
             const int per_sm = ctas_per_sm(kernel, 0, occ);
-            launch_hot(kernel, clamp_grid(hot_groups, (size_t)dev.sms * per_sm), 0, as_stream(stream), (const uint16_t*)x,
+            launch_hot(kernel, balanced_grid(hot_groups, (size_t)dev.sms * per_sm), 0, as_stream(stream), (const uint16_t*)x,
                        weight, cos_table, sin_table, (uint16_t*)out, (uint16_t*)gate_out, (uint32_t)rows, eps,
                        (const int*)seq_start, (const int*)pos_base, (const int*)pos_map, heads_div, KvCacheDest{});
         };

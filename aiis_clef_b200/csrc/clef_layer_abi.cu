@@ -256,7 +256,7 @@ int clef_qk_norm_rope_kv_write(clef_stream_t stream, void* cache_k, void* cache_
         const size_t groups = (2 * rows + 63) / 64;
         auto launch = [&](auto kernel, std::atomic<int>& occ) {
             const int per_sm = ctas_per_sm(kernel, 0, occ);
-            launch_hot(kernel, clamp_grid(groups, (size_t)dev.sms * per_sm), 0, s, (const uint16_t*)k_raw, weight, cos_table,
+            launch_hot(kernel, balanced_grid(groups, (size_t)dev.sms * per_sm), 0, s, (const uint16_t*)k_raw, weight, cos_table,
                        sin_table, (uint16_t*)cache_k, (uint16_t*)nullptr, (uint32_t)rows, eps, (const int*)seq_start,
                        (const int*)pos_base, (const int*)pos_map, make_fast_div((uint32_t)kv_heads),
                        KvCacheDest{(const int*)cache_map, (const int*)cache_len, (const uint16_t*)v, (uint16_t*)cache_v});

@@ -2135,17 +2135,28 @@ rope_f32_hot_kernel(RopeSegmentsF32 segs, const float* __restrict__ cos_t, const
 
 // ---------------------------------------------------------------------------------------------
 // Per-head RMSNorm + partial RoPE (kernels/elementwise.cu:70-142) for head_dim 128, rotary_dim 64.
-// Four lanes own one head row: lane m holds chunk m (dims 16m .. 16m+15, inside the rotary span)
-// and chunk m + 4 (pass-through dims), a warp 8 head rows. The norm tree is the gated kernel's
-// (head_tree_32). The rotation pairs dims j and j + 32, i.e. chunk m of lanes m and m ^ 2: the
-// partner's RAW bf16 words cross by shuffle and both lanes normalise both halves. With `gate_out`
-// the input row is [q | gate] and the gate half is copied.
+// Four lanes own one head row, a warp 8 head rows. Lane m holds the four 8-value pieces at dims 8m, 32 + 8m,
+// 64 + 8m and 96 + 8m (16-byte loads), i.e. quads i, i + 8, i + 16 and i + 24 for i = 2m and 2m + 1. That
+// puts both members of every rotation pair (dims j and j + 32) and the first two levels of the norm tree in one
+// lane: the reference association (lane l of a warp holds quad l; tree 16, 8, 4, 2, 1 over l) adds quads
+// (i, i + 16), then (i, i + 8) in-lane, levels 4 and 2 cross lane bits 1 and 0 (two shuffles each, the pair of
+// partial sums a lane keeps), and the last level adds the lane's two sums. 4 shuffles per 8 head rows, no value
+// crosses lanes for the rotation. With `gate_out` the input row is [q | gate] and the gate half is copied.
 // ---------------------------------------------------------------------------------------------
 // With KV (GATE must be false, rows % 8 == 0): `out` is the key cache, the head rows of token t are written at
 // cache row kv_cache_row(t), and the value rows ride along as head rows [rows, 2 rows) that are copied to the
 // value cache at the same cache row, so one launch fills both caches.
+__device__ __forceinline__ void unpack8_quadpairs(const uint4& d, f32x2* v) {
+    v[0] = f2_pack(bf16_lo(d.x), bf16_lo(d.y)), v[1] = f2_pack(bf16_hi(d.x), bf16_hi(d.y));   // (x, z), (y, w)
+    v[2] = f2_pack(bf16_lo(d.z), bf16_lo(d.w)), v[3] = f2_pack(bf16_hi(d.z), bf16_hi(d.w));
+}
+__device__ __forceinline__ uint4 pack8_bf16(const f32x2* v) {
+    return make_uint4(pack_bf16x2(v[0].x, v[1].x), pack_bf16x2(v[0].y, v[1].y), pack_bf16x2(v[2].x, v[3].x),
+                      pack_bf16x2(v[2].y, v[3].y));
+}
+
 template <bool GATE, bool KV>
-__global__ void __launch_bounds__(kCtaThreads, 2)
+__global__ void __launch_bounds__(kCtaThreads, ((GATE || KV) ? 2 : 3))
 qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict__ weight,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint16_t* __restrict__ out,
                         uint16_t* __restrict__ gate_out, uint32_t rows, float eps, const int* __restrict__ seq_start,
@@ -2155,7 +2166,7 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
     constexpr int HD = 128, ROT = 64, STRIDE = GATE ? 2 * HD : HD;
     const uint32_t key_rows = rows;
     if (KV) rows *= 2;
-    __shared__ float4 s_w[32];   // (1 + w), quad-pair layout: s_w[c * 4 + q] for chunk c, quad q
+    __shared__ float4 s_w[32];   // (1 + w) of quad i in the quad-pair order (x, z, y, w)
     const int lane = threadIdx.x & 31;
     const int m = lane & 3;
     const uint32_t groups_in_grid = gridDim.x * (kCtaThreads / 4);
@@ -2176,14 +2187,18 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
     auto row_ptr = [&](uint32_t r) {
         return (KV && r >= key_rows) ? kv.v + (size_t)(r - key_rows) * HD : x + (size_t)r * STRIDE;
     };
-    U8x32 d[2], dgate[2];
-    if (hrow < rows) {
+    uint4 d[4];   // piece h: dims 32 h + 8 m .. + 7
+    U8x32 dgate[2];
+    auto fetch = [&](uint32_t r) {
+        const uint16_t* src = row_ptr(r) + 8 * m;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            d[h] = ldg_stream_v8(row_ptr(hrow) + (m + 4 * h) * 16);
-            if (GATE) dgate[h] = ldg_stream_v8(x + (size_t)hrow * STRIDE + HD + (m + 4 * h) * 16);
+        for (int h = 0; h < 4; ++h) d[h] = ldg_stream_v4(src + 32 * h);
+        if (GATE) {
+            dgate[0] = ldg_stream_v8(x + (size_t)r * STRIDE + HD + m * 16);
+            dgate[1] = ldg_stream_v8(x + (size_t)r * STRIDE + HD + (m + 4) * 16);
         }
-    }
+    };
+    if (hrow < rows) fetch(hrow);
     __syncthreads();
     for (uint32_t base = hrow - (uint32_t)(lane >> 2); base < rows; base += groups_in_grid, hrow += groups_in_grid) {
         const bool live = hrow < rows;
@@ -2192,83 +2207,77 @@ qk_norm_rope_hot_kernel(const uint16_t* __restrict__ x, const float* __restrict_
                 const uint32_t vrow = hrow - key_rows;
                 const int token = (int)fast_div(vrow, heads_div);
                 const size_t dst = (kv_cache_row(token, kv.cache_map, kv.cache_len) * heads_div.d + (vrow - (uint32_t)token * heads_div.d)) * HD;
-                stg_v8(kv.cache_v + dst + m * 16, d[0]);
-                stg_v8(kv.cache_v + dst + (m + 4) * 16, d[1]);
+#pragma unroll
+                for (int h = 0; h < 4; ++h) stg_v4(kv.cache_v + dst + 32 * h + 8 * m, d[h]);
             }
             const uint32_t next_v = hrow + groups_in_grid;
-            if (next_v < rows) {
-                d[0] = ldg_stream_v8(row_ptr(next_v) + m * 16);
-                d[1] = ldg_stream_v8(row_ptr(next_v) + (m + 4) * 16);
-            }
+            if (next_v < rows) fetch(next_v);
             continue;
         }
-        f32x2 v[2][8], pv[8];
-        float quad[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        U8x32 praw;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {   // partner's raw rotary chunk (lane m ^ 2)
-            praw.w[i] = __shfl_xor_sync(kFullMask, d[0].w[i], 2);
-        }
+        f32x2 v[4][4];
+        float quad[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
         if (live) {
-            unpack16_quadpairs(d[0], v[0]);
-            unpack16_quadpairs(d[1], v[1]);
-            unpack16_quadpairs(praw, pv);
-            quad_squares(v[0], quad[0]);
-            quad_squares(v[1], quad[1]);
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                unpack8_quadpairs(d[h], v[h]);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {   // quad = fma(x,x,y*y) + fma(z,z,w*w), the reference build's contraction
+                    const f32x2 t = f2_mul(v[h][2 * e + 1], v[h][2 * e + 1]);
+                    const f32x2 sq = f2_fma(v[h][2 * e], v[h][2 * e], t);
+                    quad[h][e] = __fadd_rn(sq.x, sq.y);
+                }
+            }
             if (GATE) {
                 stg_v8(gate_out + (size_t)hrow * HD + m * 16, dgate[0]);
                 stg_v8(gate_out + (size_t)hrow * HD + (m + 4) * 16, dgate[1]);
             }
         }
         const uint32_t next = hrow + groups_in_grid;
-        if (next < rows) {
+        if (next < rows) fetch(next);
+        float s[2];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                d[h] = ldg_stream_v8(row_ptr(next) + (m + 4 * h) * 16);
-                if (GATE) dgate[h] = ldg_stream_v8(x + (size_t)next * STRIDE + HD + (m + 4 * h) * 16);
-            }
+        for (int e = 0; e < 2; ++e) {
+            // quads (i, i + 16) and (i + 8, i + 24), then the two sums: reference lanes l, l + 16 and l, l + 8
+            s[e] = __fadd_rn(__fadd_rn(quad[0][e], quad[2][e]), __fadd_rn(quad[1][e], quad[3][e]));
+            s[e] = __fadd_rn(s[e], __shfl_xor_sync(kFullMask, s[e], 2));   // l, l + 4
+            s[e] = __fadd_rn(s[e], __shfl_xor_sync(kFullMask, s[e], 1));   // l, l + 2
         }
-        const float total = head_tree_32(quad[0], quad[1], lane);
+        const float total = __fadd_rn(s[0], s[1]);                         // l, l + 1
         if (!live) {
             continue;
         }
         const f32x2 inv2 = f2_splat(inv_rms_pow2<HD>(total, eps));
-        const int pm = m ^ 2;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float4 wa = s_w[m * 4 + q], wb = s_w[(m + 4) * 4 + q], wp = s_w[pm * 4 + q];
-            v[0][2 * q] = f2_mul(f2_mul(v[0][2 * q], inv2), make_float2(wa.x, wa.y));
-            v[0][2 * q + 1] = f2_mul(f2_mul(v[0][2 * q + 1], inv2), make_float2(wa.z, wa.w));
-            v[1][2 * q] = f2_mul(f2_mul(v[1][2 * q], inv2), make_float2(wb.x, wb.y));
-            v[1][2 * q + 1] = f2_mul(f2_mul(v[1][2 * q + 1], inv2), make_float2(wb.z, wb.w));
-            pv[2 * q] = f2_mul(f2_mul(pv[2 * q], inv2), make_float2(wp.x, wp.y));
-            pv[2 * q + 1] = f2_mul(f2_mul(pv[2 * q + 1], inv2), make_float2(wp.z, wp.w));
+        for (int h = 0; h < 4; ++h) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float4 w = s_w[8 * h + 2 * m + e];
+                v[h][2 * e] = f2_mul(f2_mul(v[h][2 * e], inv2), make_float2(w.x, w.y));
+                v[h][2 * e + 1] = f2_mul(f2_mul(v[h][2 * e + 1], inv2), make_float2(w.z, w.w));
+            }
         }
         const int token = (int)fast_div(hrow, heads_div);
         const int pos = rope_position(token, seq_start, pos_base, pos_map);
-        const float* cp = cos_t + (size_t)pos * ROT + (m & 1) * 16;
-        const float* sp = sin_t + (size_t)pos * ROT + (m & 1) * 16;
-        const bool holds_lo = m < 2;
+        const float* cp = cos_t + (size_t)pos * ROT + m * 8;
+        const float* sp = sin_t + (size_t)pos * ROT + m * 8;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float4 c = __ldg(reinterpret_cast<const float4*>(cp) + q);
-            const float4 sn = __ldg(reinterpret_cast<const float4*>(sp) + q);
+        for (int e = 0; e < 2; ++e) {
+            const float4 c = __ldg(reinterpret_cast<const float4*>(cp) + e);
+            const float4 sn = __ldg(reinterpret_cast<const float4*>(sp) + e);
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int i = 2 * q + e;
-                const f32x2 c2 = e == 0 ? make_float2(c.x, c.z) : make_float2(c.y, c.w);
-                const f32x2 s2 = e == 0 ? make_float2(sn.x, sn.z) : make_float2(sn.y, sn.w);
+            for (int i = 0; i < 2; ++i) {
+                const f32x2 c2 = i == 0 ? make_float2(c.x, c.z) : make_float2(c.y, c.w);
+                const f32x2 s2 = i == 0 ? make_float2(sn.x, sn.z) : make_float2(sn.y, sn.w);
                 // lo' = fma(lo, c, -(hi * s));  hi' = fma(lo, s, hi * c)   (the reference build's contraction)
-                const f32x2 lo = holds_lo ? v[0][i] : pv[i];
-                const f32x2 hi = holds_lo ? pv[i] : v[0][i];
-                const f32x2 t = f2_mul(hi, holds_lo ? make_float2(-s2.x, -s2.y) : c2);
-                v[0][i] = f2_fma(lo, holds_lo ? c2 : s2, t);
+                const f32x2 lo = v[0][2 * e + i], hi = v[1][2 * e + i];
+                v[0][2 * e + i] = f2_fma(lo, c2, f2_mul(hi, make_float2(-s2.x, -s2.y)));
+                v[1][2 * e + i] = f2_fma(lo, s2, f2_mul(hi, c2));
             }
         }
         const size_t orow = KV ? (kv_cache_row(token, kv.cache_map, kv.cache_len) * heads_div.d + (hrow - (uint32_t)token * heads_div.d)) * HD
                                : (size_t)hrow * HD;
-        stg_v8(out + orow + m * 16, pack16_bf16(v[0]));
-        stg_v8(out + orow + (m + 4) * 16, pack16_bf16(v[1]));
+#pragma unroll
+        for (int h = 0; h < 4; ++h) stg_v4(out + orow + 32 * h + 8 * m, pack8_bf16(v[h]));
     }
 }
 
