@@ -897,6 +897,9 @@ swiglu_quant_hot_kernel(const uint16_t* __restrict__ gate, const uint16_t* __res
 
     pdl_launch_dependents();
     fill_inv_scale_table(s_inv, global_scale);
+    if (unit0 < live_units && lane < 16) {   // this warp's first unit towards L2 (8 lines of gate, 8 of up); see prefetch_l2
+        prefetch_l2((lane < 8 ? gate : up) + (size_t)unit0 * 512 + (size_t)(lane & 7) * 64);
+    }
     pdl_wait_prior_grids();
     U8x32 g[UNITS], u[UNITS];
 #pragma unroll
@@ -1267,6 +1270,9 @@ quantise_hot_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ packed
     const int k1_count = cols >> 6;
     pdl_launch_dependents();
     fill_inv_scale_table(s_inv, global_scale);
+    if (unit0 < live_units && lane < 8) {   // this warp's first unit towards L2 (8 lines); see prefetch_l2
+        prefetch_l2(x + (size_t)unit0 * 512 + (size_t)lane * 64);
+    }
     pdl_wait_prior_grids();
     U8x32 d[UNITS];
 #pragma unroll
